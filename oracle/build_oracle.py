@@ -1,0 +1,106 @@
+"""Build recipe for the CPU checkers (TEST INFRASTRUCTURE ONLY).
+
+Two artefacts, neither of which the product library links, loads or calls:
+
+* ``oracle/liboracle.so``            -- the C restatement in ``preproc_oracle.c`` (gcc, no dependencies).
+* ``oracle/_ref/libref_golden.so``   -- the reference project's own CPU golden functions, compiled from the
+  reference tree where it lies (only when that tree is present). The two golden function templates sit inside
+  gtest translation units, so they are cut out by signature into a scratch directory, compiled together with
+  ``ref_golden_wrap.cpp`` and the reference's header-only host helpers, and the scratch copy is removed again.
+  The reference's own build system is not run.
+
+Usage: ``python oracle/build_oracle.py [--ref-root DIR] [--force]``
+"""
+from __future__ import annotations
+
+import argparse
+import os
+import shutil
+import subprocess
+import sys
+import tempfile
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ORACLE_SRC = os.path.join(HERE, "preproc_oracle.c")
+ORACLE_SO = os.path.join(HERE, "liboracle.so")
+REF_DIR = os.path.join(HERE, "_ref")
+REF_SO = os.path.join(REF_DIR, "libref_golden.so")
+REF_WRAP = os.path.join(HERE, "ref_golden_wrap.cpp")
+DEFAULT_REF_ROOT = os.environ.get("CVCUDA_REFERENCE_ROOT", "/root/reference")
+
+# -ffp-contract=off: the goldens are defined by un-fused float32 arithmetic in source order.
+CFLAGS = ["-O2", "-fPIC", "-shared", "-ffp-contract=off", "-fno-fast-math", "-pthread"]
+
+
+def _stale(target: str, *sources: str) -> bool:
+    if not os.path.exists(target):
+        return True
+    t = os.path.getmtime(target)
+    return any(os.path.getmtime(s) > t for s in sources if os.path.exists(s))
+
+
+def build_oracle(force: bool = False) -> str:
+    if force or _stale(ORACLE_SO, ORACLE_SRC, os.path.join(HERE, "preproc_oracle.h")):
+        cmd = ["gcc", "-std=c11", *CFLAGS, "-o", ORACLE_SO, ORACLE_SRC, "-lm"]
+        subprocess.check_call(cmd)
+    return ORACLE_SO
+
+
+def _cut_function(path: str, marker: str) -> str:
+    """Return the text of the top-level function template whose signature contains `marker`:
+    from the `template<...>` line above it to the first line that is exactly '}'."""
+    with open(path, "r", encoding="utf-8") as f:
+        lines = f.read().split("\n")
+    hit = next(i for i, ln in enumerate(lines) if marker in ln)
+    start = hit
+    while not lines[start].lstrip().startswith("template<"):
+        start -= 1
+    end = next(i for i in range(hit, len(lines)) if lines[i] == "}")
+    return "\n".join(lines[start : end + 1]) + "\n"
+
+
+def build_ref(ref_root: str = DEFAULT_REF_ROOT, force: bool = False) -> str | None:
+    """Compile the reference's golden functions into oracle/_ref/. Returns None when the tree is absent."""
+    rccr_tu = os.path.join(ref_root, "tests/cvcuda/system/TestOpResizeCropConvertReformat.cpp")
+    cfnr_tu = os.path.join(ref_root, "tests/cvcuda/system/TestOpCropFlipNormalizeReformat.cpp")
+    if not (os.path.exists(rccr_tu) and os.path.exists(cfnr_tu)):
+        return REF_SO if os.path.exists(REF_SO) else None
+    if not (force or _stale(REF_SO, REF_WRAP, rccr_tu, cfnr_tu)):
+        return REF_SO
+    os.makedirs(REF_DIR, exist_ok=True)
+    scratch = tempfile.mkdtemp(prefix="refgold_")
+    try:
+        with open(os.path.join(scratch, "rccr.inc"), "w") as f:
+            f.write(_cut_function(rccr_tu, "void ResizeCropConvert(      DstT *dst,"))
+        with open(os.path.join(scratch, "cfnr.inc"), "w") as f:
+            f.write(_cut_function(cfnr_tu, "static void CropFlipNormalizeReformat("))
+        inc = [
+            "-I" + os.path.join(ref_root, "tests"),
+            "-I" + os.path.join(ref_root, "src/cvcuda/include"),
+            "-I" + os.path.join(ref_root, "src/nvcv/src/include"),
+            "-I/usr/local/cuda/include",
+            "-I" + scratch,
+        ]
+        cmd = [
+            "g++", "-std=c++17", *CFLAGS, "-w",
+            '-DREF_GOLDEN_RCCR_INC="rccr.inc"', '-DREF_GOLDEN_CFNR_INC="cfnr.inc"',
+            *inc, "-o", REF_SO, REF_WRAP,
+        ]
+        subprocess.check_call(cmd)
+    finally:
+        shutil.rmtree(scratch, ignore_errors=True)
+    return REF_SO
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--ref-root", default=DEFAULT_REF_ROOT)
+    ap.add_argument("--force", action="store_true")
+    a = ap.parse_args()
+    print("oracle:", build_oracle(a.force))
+    print("reference golden:", build_ref(a.ref_root, a.force) or "reference tree absent, not built")
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,270 @@
+"""ctypes front-end of the CPU checkers (TEST INFRASTRUCTURE ONLY).
+
+Only tests/, __graft_entry__.smoke() and bench.py's CPU-baseline legs may import this module; the product
+package never does. It wraps
+
+* ``liboracle.so``        -- the C restatement (preproc_oracle.c), always available after build_oracle.py ran;
+* ``_ref/libref_golden.so`` -- the reference project's own golden functions, when they were compiled.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from dataclasses import dataclass, field
+from typing import Optional, Sequence
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+
+U8, S8, U16, S16, U32, S32, F32, F16 = range(8)
+NP_DTYPES = {U8: np.uint8, S8: np.int8, U16: np.uint16, S16: np.int16, U32: np.uint32, S32: np.int32,
+             F32: np.float32, F16: np.float16}
+DTYPE_CODE = {np.dtype(v): k for k, v in NP_DTYPES.items()}
+
+NEAREST, LINEAR = 0, 1
+BORDER_CONSTANT, BORDER_REPLICATE, BORDER_REFLECT, BORDER_WRAP, BORDER_REFLECT101 = range(5)
+
+
+class _Image(C.Structure):
+    _fields_ = [("base", C.c_void_p), ("width", C.c_int32), ("height", C.c_int32),
+                ("rowStride", C.c_int64), ("planeStride", C.c_int64)]
+
+
+class _Dst(C.Structure):
+    _fields_ = [("base", C.c_void_p), ("dtype", C.c_int32), ("width", C.c_int32), ("height", C.c_int32),
+                ("sampleStride", C.c_int64), ("rowStride", C.c_int64), ("pixStride", C.c_int64),
+                ("chanStride", C.c_int64)]
+
+
+class _ResizeParams(C.Structure):
+    _fields_ = [("resizeW", C.c_int32), ("resizeH", C.c_int32), ("cropX", C.c_int32), ("cropY", C.c_int32),
+                ("interp", C.c_int32), ("srcCast", C.c_int32), ("manip", C.c_int32), ("epilogue", C.c_int32),
+                ("scale", C.c_float), ("offset", C.c_float), ("base", C.c_float * 4), ("mul", C.c_float * 4),
+                ("gscale", C.c_float), ("shift", C.c_float),
+                ("dstX", C.c_int32), ("dstY", C.c_int32), ("regionW", C.c_int32), ("regionH", C.c_int32),
+                ("padValue", C.c_float)]
+
+
+class _SliceParams(C.Structure):
+    _fields_ = [("srcType", C.c_int32), ("srcPlanar", C.c_int32), ("channels", C.c_int32), ("border", C.c_int32),
+                ("borderValue", C.c_float), ("base", C.POINTER(C.c_float)), ("baseCh", C.c_int32),
+                ("scale", C.POINTER(C.c_float)), ("scaleCh", C.c_int32),
+                ("gscale", C.c_float), ("shift", C.c_float), ("epsilon", C.c_float), ("flags", C.c_uint32)]
+
+
+_lib = None
+_ref = None
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        path = os.path.join(_HERE, "liboracle.so")
+        if not os.path.exists(path):
+            from . import build_oracle  # noqa: WPS433
+            build_oracle.build_oracle()
+        L = C.CDLL(path)
+        L.oracle_resize_crop.restype = C.c_int
+        L.oracle_resize_crop.argtypes = [C.POINTER(_Image), C.c_int32, C.c_void_p, C.c_void_p,
+                                         C.POINTER(_ResizeParams), C.POINTER(_Dst), C.c_int32]
+        L.oracle_crop_flip_normalize.restype = C.c_int
+        L.oracle_crop_flip_normalize.argtypes = [C.POINTER(_Image), C.c_int32, C.c_void_p, C.c_void_p,
+                                                 C.POINTER(_SliceParams), C.POINTER(_Dst), C.c_int32]
+        L.oracle_resize_source_bytes.restype = C.c_int64
+        L.oracle_resize_source_bytes.argtypes = [C.c_int32, C.c_int32, C.c_int64, C.c_void_p,
+                                                 C.POINTER(_ResizeParams)]
+        L.oracle_sat_u8.restype = C.c_uint8
+        L.oracle_sat_u8.argtypes = [C.c_float]
+        L.oracle_sat_s16.restype = C.c_int16
+        L.oracle_sat_s16.argtypes = [C.c_float]
+        L.oracle_sat_s32.restype = C.c_int32
+        L.oracle_sat_s32.argtypes = [C.c_float]
+        L.oracle_f32_to_f16_bits.restype = C.c_uint16
+        L.oracle_f32_to_f16_bits.argtypes = [C.c_float]
+        _lib = L
+    return _lib
+
+
+def ref() -> Optional[C.CDLL]:
+    """The reference's own golden functions, or None when they were not compiled."""
+    global _ref
+    if _ref is None:
+        path = os.path.join(_HERE, "_ref", "libref_golden.so")
+        if not os.path.exists(path):
+            return None
+        R = C.CDLL(path)
+        R.ref_rccr.restype = C.c_int
+        R.ref_rccr.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int,
+                               C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_float, C.c_float, C.c_int]
+        R.ref_cfnr.restype = C.c_int
+        R.ref_cfnr.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int,
+                               C.c_int, C.c_int, C.c_int, C.c_float, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
+                               C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_float, C.c_float, C.c_float, C.c_uint32]
+        for name, rt in (("ref_sat_u8_f32", C.c_uint8), ("ref_sat_s32_f32", C.c_int32), ("ref_sat_s16_f32", C.c_int16)):
+            f = getattr(R, name)
+            f.restype = rt
+            f.argtypes = [C.c_float]
+        _ref = R
+    return _ref
+
+
+# ------------------------------------------------------------------------------------------------ helpers
+
+@dataclass
+class ResizeSpec:
+    """Parameters of the resize/crop/convert/reformat path (see preproc_oracle.h: OracleResizeParams)."""
+    resize: tuple  # (w, h)
+    crop: tuple = (0, 0)  # (x, y)
+    out_size: tuple = (0, 0)  # region (w, h) = output size when there is no canvas
+    interp: int = LINEAR
+    src_cast: bool = True
+    manip: int = 0
+    scale: float = 1.0
+    offset: float = 0.0
+    base: Optional[Sequence[float]] = None  # per-channel normalisation: (v-base)*mul*gscale+shift
+    mul: Optional[Sequence[float]] = None
+    gscale: float = 1.0
+    shift: float = 0.0
+    canvas: Optional[tuple] = None  # (w, h) of the output when the region is placed inside a larger canvas
+    dst_pos: tuple = (0, 0)
+    pad_value: float = 0.0
+    extra: dict = field(default_factory=dict)
+
+    def to_c(self) -> _ResizeParams:
+        p = _ResizeParams()
+        p.resizeW, p.resizeH = self.resize
+        p.cropX, p.cropY = self.crop
+        p.interp, p.srcCast, p.manip = int(self.interp), int(bool(self.src_cast)), int(self.manip)
+        p.epilogue = 0 if self.base is None else 1
+        p.scale, p.offset = np.float32(self.scale), np.float32(self.offset)
+        for i in range(4):
+            p.base[i] = np.float32(self.base[i]) if self.base is not None and i < len(self.base) else 0.0
+            p.mul[i] = np.float32(self.mul[i]) if self.mul is not None and i < len(self.mul) else 1.0
+        p.gscale, p.shift = np.float32(self.gscale), np.float32(self.shift)
+        p.dstX, p.dstY = self.dst_pos
+        p.regionW, p.regionH = self.out_size
+        p.padValue = np.float32(self.pad_value)
+        return p
+
+    @property
+    def canvas_size(self) -> tuple:
+        return self.canvas if self.canvas is not None else self.out_size
+
+
+def _images_c(images: Sequence[np.ndarray], planar: bool = False):
+    arr = (_Image * len(images))()
+    for i, im in enumerate(images):
+        if planar:  # C,H,W
+            c, h, w = im.shape
+            assert im.strides[2] == im.itemsize
+            arr[i] = _Image(im.ctypes.data, w, h, im.strides[1], im.strides[0])
+        else:  # H,W,C
+            h, w, c = im.shape
+            assert im.strides[2] == im.itemsize and im.strides[1] == im.itemsize * c
+            arr[i] = _Image(im.ctypes.data, w, h, im.strides[0], 0)
+    return arr
+
+
+def _dst_c(out: np.ndarray, planar: bool) -> _Dst:
+    """out is [N,C,H,W] when planar else [N,H,W,C]."""
+    if planar:
+        n, c, h, w = out.shape
+        ss, cs, rs, ps = out.strides
+    else:
+        n, h, w, c = out.shape
+        ss, rs, ps, cs = out.strides
+    return _Dst(out.ctypes.data, DTYPE_CODE[out.dtype], w, h, ss, rs, ps, cs)
+
+
+def resize_crop(images: Sequence[np.ndarray], spec: ResizeSpec, out_dtype=np.float32, planar: bool = True,
+                roi: Optional[np.ndarray] = None, flip: Optional[np.ndarray] = None, nthreads: int = 1) -> np.ndarray:
+    """Run the restated golden on a list of HxWx3 uint8 arrays (rows may be padded). Returns NCHW or NHWC."""
+    n = len(images)
+    cw, ch = spec.canvas_size
+    out = np.empty((n, 3, ch, cw) if planar else (n, ch, cw, 3), dtype=out_dtype)
+    imgs = _images_c(images)
+    roi_p = flip_p = None
+    if roi is not None:
+        roi = np.ascontiguousarray(roi, dtype=np.int32)
+        roi_p = roi.ctypes.data
+    if flip is not None:
+        flip = np.ascontiguousarray(flip, dtype=np.int32)
+        flip_p = flip.ctypes.data
+    p, d = spec.to_c(), _dst_c(out, planar)
+    rc = lib().oracle_resize_crop(imgs, n, roi_p, flip_p, C.byref(p), C.byref(d), nthreads)
+    if rc != 0:
+        raise ValueError("oracle_resize_crop rejected its arguments")
+    return out
+
+
+def crop_flip_normalize(images: Sequence[np.ndarray], src_planar: bool, crop_rect: np.ndarray, flip: np.ndarray,
+                        out_size: tuple, out_dtype, out_planar: bool, border: int, border_value: float,
+                        base: np.ndarray, scale: np.ndarray, gscale: float = 1.0, shift: float = 0.0,
+                        epsilon: float = 0.0, flags: int = 0, nthreads: int = 1) -> np.ndarray:
+    """Restated CropFlipNormalizeReformat golden. images: HxWxC (interleaved) or CxHxW (planar) arrays."""
+    n = len(images)
+    ch = images[0].shape[0] if src_planar else images[0].shape[2]
+    w, h = out_size
+    out = np.empty((n, ch, h, w) if out_planar else (n, h, w, ch), dtype=out_dtype)
+    imgs = _images_c(images, planar=src_planar)
+    crop_rect = np.ascontiguousarray(crop_rect, dtype=np.int32)
+    flip = np.ascontiguousarray(flip, dtype=np.int32)
+    base = np.ascontiguousarray(base, dtype=np.float32)
+    scale = np.ascontiguousarray(scale, dtype=np.float32)
+    p = _SliceParams(DTYPE_CODE[images[0].dtype], int(src_planar), ch, border, border_value,
+                     base.ctypes.data_as(C.POINTER(C.c_float)), base.size,
+                     scale.ctypes.data_as(C.POINTER(C.c_float)), scale.size, gscale, shift, epsilon, flags)
+    d = _dst_c(out, out_planar)
+    rc = lib().oracle_crop_flip_normalize(imgs, n, crop_rect.ctypes.data, flip.ctypes.data, C.byref(p), C.byref(d),
+                                          nthreads)
+    if rc != 0:
+        raise ValueError("oracle_crop_flip_normalize rejected its arguments")
+    return out
+
+
+def resize_source_bytes(src_w: int, src_h: int, row_stride: int, spec: ResizeSpec, roi=None) -> int:
+    p = spec.to_c()
+    roi_p = None
+    if roi is not None:
+        roi = np.ascontiguousarray(roi, dtype=np.int32)
+        roi_p = roi.ctypes.data
+    return int(lib().oracle_resize_source_bytes(src_w, src_h, row_stride, roi_p, C.byref(p)))
+
+
+# ------------------------------------------------------------------------------------------------ reference golden
+
+def ref_rccr(src: np.ndarray, resize, crop, out_size, interp, manip, scale, offset, src_cast, out_dtype,
+             planar: bool) -> np.ndarray:
+    """The reference's ResizeCropConvert on a packed [N,H,W,3] uint8 batch."""
+    R = ref()
+    assert R is not None
+    src = np.ascontiguousarray(src, dtype=np.uint8)
+    n, h, w, _ = src.shape
+    ow, oh = out_size
+    out = np.empty((n, 3, oh, ow) if planar else (n, oh, ow, 3), dtype=out_dtype)
+    R.ref_rccr(out.ctypes.data, ow, oh, int(planar), int(np.dtype(out_dtype) == np.float32), src.ctypes.data, w, h, n,
+               resize[0], resize[1], crop[0], crop[1], interp, manip, float(scale), float(offset), int(src_cast))
+    return out
+
+
+def ref_cfnr(image: np.ndarray, src_planar: bool, rect, flip: int, out_size, out_dtype, out_planar: bool, border: int,
+             border_value: float, base, scale, gscale, shift, epsilon, flags) -> np.ndarray:
+    """The reference's CropFlipNormalizeReformat golden on one packed image."""
+    R = ref()
+    assert R is not None
+    image = np.ascontiguousarray(image)
+    if src_planar:
+        ch, h, w = image.shape
+    else:
+        h, w, ch = image.shape
+    ow, oh = out_size
+    out = np.empty((ch, oh, ow) if out_planar else (oh, ow, ch), dtype=out_dtype)
+    base = np.ascontiguousarray(base, dtype=np.float32)
+    scale = np.ascontiguousarray(scale, dtype=np.float32)
+    rc = R.ref_cfnr(out.ctypes.data, DTYPE_CODE[out.dtype], int(out_planar), ow, oh, image.ctypes.data,
+                    DTYPE_CODE[image.dtype], int(src_planar), w, h, ch, border, border_value, flip,
+                    int(rect[0]), int(rect[1]), int(rect[2]), int(rect[3]), base.ctypes.data, base.size,
+                    scale.ctypes.data, scale.size, gscale, shift, epsilon, flags)
+    assert rc == 0
+    return out

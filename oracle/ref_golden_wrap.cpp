@@ -1,0 +1,246 @@
+// TEST INFRASTRUCTURE ONLY -- never linked into, loaded by, or called from the product library.
+//
+// C-callable wrapper around the reference project's own CPU golden functions, so that the C
+// restatement in preproc_oracle.c can be pinned against the real thing.
+//
+// The golden functions live inside gtest translation units that cannot be compiled as they are
+// (googletest is absent), so build_oracle.py cuts the two function templates out of the reference tree
+// at build time into a scratch directory (REF_GOLDEN_RCCR_INC / REF_GOLDEN_CFNR_INC), compiles this
+// file against them plus the reference's header-only host helpers, and deletes the scratch files.
+// Nothing from the reference is stored in this repository.
+//
+//   tests/cvcuda/system/TestOpResizeCropConvertReformat.cpp:76-172   ResizeCropConvert<DstT,SrcT>
+//   tests/cvcuda/system/TestOpCropFlipNormalizeReformat.cpp:43-149   CropFlipNormalizeReformat<T_Src,T_Dst,B>
+//   tests/common/InterpUtils.hpp:38-89                               test::ValueAt
+//   tests/common/BorderUtils.cpp:24-137                              test::IsInside + border index rules
+//   cvcuda/cuda_tools/SaturateCast.hpp                               cuda::SaturateCast (host path)
+
+#include <cuda_runtime.h> // int2, long4 (vector types only; no runtime call is made)
+
+#include <algorithm>
+#include <cmath>
+#include <cstdint>
+#include <cstring>
+#include <vector>
+
+// Stand-ins for the two object-model classes the golden code queries. The real ones call into
+// libnvcv_types, which is not built here; the golden functions only ask for these two counts.
+namespace nvcv {
+struct ImageFormat
+{
+    int channels, planes;
+
+    int numChannels() const
+    {
+        return channels;
+    }
+
+    int numPlanes() const
+    {
+        return planes;
+    }
+};
+
+struct Size2D
+{
+    int w, h;
+};
+} // namespace nvcv
+
+#include <common/InterpUtils.hpp>
+#include <cvcuda/OpNormalize.h> // CVCUDA_NORMALIZE_SCALE_IS_STDDEV
+#include <cvcuda/Types.h>
+#include <cvcuda/cuda_tools/SaturateCast.hpp>
+#include <nvcv/Rect.h>
+#include <nvcv/Size.h>
+
+// tests/common/BorderUtils.cpp is a plain source file with no main(): compile it in place.
+#include <common/BorderUtils.cpp>
+
+namespace test = nvcv::test;
+namespace cuda = nvcv::cuda;
+
+#include REF_GOLDEN_RCCR_INC
+#include REF_GOLDEN_CFNR_INC
+
+namespace {
+
+template<typename S, typename D>
+int cfnr_border(int border, std::vector<uint8_t> &hDst, long4 outStrides, std::vector<uint8_t> &hSrc, long4 inStrides,
+                nvcv::Size2D srcSize, nvcv::Size2D dstSize, nvcv::ImageFormat fmt, nvcv::ImageFormat dstFmt,
+                float borderValue, int flip, NVCVRectI rect, const std::vector<float> &base, nvcv::ImageFormat baseFmt,
+                const std::vector<float> &scale, nvcv::ImageFormat scaleFmt, float gScale, float gShift, float eps,
+                uint32_t flags)
+{
+#define CALL(B)                                                                                                      \
+    CropFlipNormalizeReformat<S, D, B>(hDst, 0, outStrides, hSrc, 0, inStrides, srcSize, dstSize, fmt, dstFmt,       \
+                                       borderValue, flip, rect, base, 0, {1, 1}, baseFmt, scale, 0, {1, 1}, scaleFmt, \
+                                       gScale, gShift, eps, flags);                                                  \
+    return 0
+    switch (border)
+    {
+    case NVCV_BORDER_CONSTANT:
+        CALL(NVCV_BORDER_CONSTANT);
+    case NVCV_BORDER_REPLICATE:
+        CALL(NVCV_BORDER_REPLICATE);
+    case NVCV_BORDER_REFLECT:
+        CALL(NVCV_BORDER_REFLECT);
+    case NVCV_BORDER_WRAP:
+        CALL(NVCV_BORDER_WRAP);
+    case NVCV_BORDER_REFLECT101:
+        CALL(NVCV_BORDER_REFLECT101);
+    }
+#undef CALL
+    return -1;
+}
+
+template<typename S, typename... A>
+int cfnr_dst(int dstType, A &&...a)
+{
+    switch (dstType)
+    {
+    case 0:
+        return cfnr_border<S, uint8_t>(a...);
+    case 1:
+        return cfnr_border<S, int8_t>(a...);
+    case 2:
+        return cfnr_border<S, uint16_t>(a...);
+    case 3:
+        return cfnr_border<S, int16_t>(a...);
+    case 4:
+        return cfnr_border<S, uint32_t>(a...);
+    case 5:
+        return cfnr_border<S, int32_t>(a...);
+    case 6:
+        return cfnr_border<S, float>(a...);
+    }
+    return -1;
+}
+
+const int kTypeSize[7] = {1, 1, 2, 2, 4, 4, 4};
+
+} // namespace
+
+extern "C"
+{
+// Dense batch of packed (unpadded) interleaved 3-channel uint8 images -> packed output.
+// dstIsFloat: 0 = uint8 output, 1 = float32 output.  dstPlanar: 0 = NHWC, 1 = NCHW.
+int ref_rccr(void *dst, int dstW, int dstH, int dstPlanar, int dstIsFloat, const uint8_t *src, int srcW, int srcH,
+             int numImages, int newW, int newH, int cropX, int cropY, int interp, int manip, float scale,
+             float offset, int srcCast)
+{
+    nvcv::ImageFormat srcFmt{3, 1}, dstFmt{3, dstPlanar ? 3 : 1};
+    NVCVSize2D        dstSize{dstW, dstH}, srcSize{srcW, srcH}, newSize{newW, newH};
+    int2              crop{cropX, cropY};
+    if (dstIsFloat)
+        ResizeCropConvert((float *)dst, dstSize, dstFmt, src, srcSize, srcFmt, numImages, newSize, crop,
+                          (NVCVInterpolationType)interp, (NVCVChannelManip)manip, scale, offset, srcCast != 0);
+    else
+        ResizeCropConvert((uint8_t *)dst, dstSize, dstFmt, src, srcSize, srcFmt, numImages, newSize, crop,
+                          (NVCVInterpolationType)interp, (NVCVChannelManip)manip, scale, offset, srcCast != 0);
+    return 0;
+}
+
+// One image. Type codes: 0 u8, 1 s8, 2 u16, 3 s16, 4 u32, 5 s32, 6 f32. Source and destination are
+// packed (no row padding); planar flags select CHW vs HWC. base/scale hold baseCh / scaleCh floats.
+int ref_cfnr(void *dst, int dstType, int dstPlanar, int dstW, int dstH, const void *src, int srcType, int srcPlanar,
+             int srcW, int srcH, int channels, int border, float borderValue, int flip, int cropX, int cropY,
+             int cropW, int cropH, const float *base, int baseCh, const float *scale, int scaleCh, float gScale,
+             float gShift, float eps, uint32_t flags)
+{
+    if (dstType < 0 || dstType > 6 || srcType < 0 || srcType > 6)
+        return -1;
+    const long ss = kTypeSize[srcType], ds = kTypeSize[dstType];
+    // A one-channel image has a single plane: the golden code derives planarity from numPlanes() > 1.
+    if (channels == 1)
+        srcPlanar = dstPlanar = 0;
+
+    std::vector<uint8_t> hSrc((size_t)srcW * srcH * channels * ss), hDst((size_t)dstW * dstH * channels * ds);
+    std::memcpy(hSrc.data(), src, hSrc.size());
+
+    // Stride vectors exactly as the reference test driver builds them
+    // (TestOpCropFlipNormalizeReformat.cpp:354-388).
+    long4 in, out;
+    in.x = (long)srcW * srcH * channels * ss;
+    if (srcPlanar)
+    {
+        in.y = (long)srcW * srcH * ss;
+        in.z = (long)srcW * ss;
+        in.w = ss;
+    }
+    else
+    {
+        in.y = (long)srcW * channels * ss;
+        in.z = (long)channels * ss;
+        in.w = ss;
+    }
+    out.x = (long)dstW * dstH * channels * ds;
+    if (dstPlanar)
+    {
+        out.y = (long)dstW * dstH * ds;
+        out.z = (long)dstW * ds;
+        out.w = ds;
+    }
+    else
+    {
+        out.y = (long)dstW * channels * ds;
+        out.z = (long)channels * ds;
+        out.w = ds;
+    }
+
+    nvcv::ImageFormat  fmt{channels, srcPlanar ? channels : 1}, dfmt{channels, dstPlanar ? channels : 1};
+    nvcv::ImageFormat  bfmt{baseCh, 1}, sfmt{scaleCh, 1};
+    std::vector<float> vb(base, base + baseCh), vs(scale, scale + scaleCh);
+    NVCVRectI          rect{cropX, cropY, cropW, cropH};
+    nvcv::Size2D       ssz{srcW, srcH}, dsz{dstW, dstH};
+
+    int rc = -1;
+#define SRC(T)                                                                                                   \
+    rc = cfnr_dst<T>(dstType, border, hDst, out, hSrc, in, ssz, dsz, fmt, dfmt, borderValue, flip, rect, vb, bfmt, \
+                     vs, sfmt, gScale, gShift, eps, flags)
+    switch (srcType)
+    {
+    case 0:
+        SRC(uint8_t);
+        break;
+    case 1:
+        SRC(int8_t);
+        break;
+    case 2:
+        SRC(uint16_t);
+        break;
+    case 3:
+        SRC(int16_t);
+        break;
+    case 4:
+        SRC(uint32_t);
+        break;
+    case 5:
+        SRC(int32_t);
+        break;
+    case 6:
+        SRC(float);
+        break;
+    }
+#undef SRC
+    if (rc == 0)
+        std::memcpy(dst, hDst.data(), hDst.size());
+    return rc;
+}
+
+// cuda::SaturateCast host path, exposed so the restated rounding can be compared value by value.
+uint8_t ref_sat_u8_f32(float v)
+{
+    return cuda::SaturateCast<uint8_t>(v);
+}
+
+int32_t ref_sat_s32_f32(float v)
+{
+    return cuda::SaturateCast<int32_t>(v);
+}
+
+int16_t ref_sat_s16_f32(float v)
+{
+    return cuda::SaturateCast<int16_t>(v);
+}
+}
