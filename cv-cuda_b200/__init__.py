@@ -1,0 +1,30 @@
+"""B200-native fused image pre-processing (ResizeCropConvertReformat, CropFlipNormalizeReformat).
+
+The package directory name contains a hyphen, so load it with ``__graft_entry__.load_package()`` (or
+``importlib``) under the module name ``cvcuda_b200``.
+
+Everything computes in ``libcvcuda_b200.so`` (hand-written sm_100a kernels); there is no CPU or PyTorch fallback:
+importing the operator functions fails loudly when the library has not been built.
+"""
+from . import ops as _ops
+from .ops import (  # noqa: F401
+    Border,
+    ChannelManip,
+    ImageBatchVarShape,
+    Interp,
+    NORMALIZE_SCALE_IS_STDDEV,
+    RectI,
+    crop_flip_normalize_reformat,
+    crop_flip_normalize_reformat_into,
+    fused_preprocess_into,
+    last_error,
+    launch_count,
+    lib,
+    lib_path,
+    read_device_error,
+    resize_crop_convert_reformat,
+    resize_crop_convert_reformat_into,
+    set_kernel_path,
+)
+
+__all__ = [n for n in dir(_ops) if not n.startswith("_")]

@@ -1,0 +1,438 @@
+// Host side of the plain-C launch layer: argument validation, kernel selection and launch.
+// The single translation unit that contains all device code of the library.
+#include "resize_kernels.cuh"
+#include "slice_kernels.cuh"
+
+#include <algorithm>
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <map>
+#include <mutex>
+#include <tuple>
+
+namespace b200pp {
+
+// ------------------------------------------------------------------------------------------------ error state
+
+static thread_local char t_lastError[512] = "";
+
+int fail(int status, const char *fmt, ...)
+{
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(t_lastError, sizeof(t_lastError), fmt, ap);
+    va_end(ap);
+    return status;
+}
+
+static std::atomic<int>      g_kernelPath{0};
+static std::atomic<uint64_t> g_launchCount{0};
+
+static int check_launch(const char *what)
+{
+    cudaError_t e = cudaPeekAtLastError();
+    if (e != cudaSuccess)
+    {
+        cudaGetLastError();
+        return fail(B200PP_ERROR_INTERNAL, "%s: kernel launch failed: %s", what, cudaGetErrorString(e));
+    }
+    g_launchCount.fetch_add(1, std::memory_order_relaxed);
+    return B200PP_SUCCESS;
+}
+
+static int elem_size(int dtype)
+{
+    switch (dtype)
+    {
+    case B200PP_U8:
+    case B200PP_S8:
+        return 1;
+    case B200PP_U16:
+    case B200PP_S16:
+    case B200PP_F16:
+        return 2;
+    case B200PP_U32:
+    case B200PP_S32:
+    case B200PP_F32:
+        return 4;
+    }
+    return 0;
+}
+
+// ------------------------------------------------------------------------------------------------ device facts
+
+struct DeviceFacts
+{
+    int smCount      = 0;
+    int maxSmemOptin = 0;
+};
+
+static const DeviceFacts &device_facts(int dev)
+{
+    static std::mutex                 mu;
+    static std::map<int, DeviceFacts> cache;
+    std::lock_guard<std::mutex>       lock(mu);
+    auto                              it = cache.find(dev);
+    if (it == cache.end())
+    {
+        DeviceFacts f;
+        cudaDeviceGetAttribute(&f.smCount, cudaDevAttrMultiProcessorCount, dev);
+        cudaDeviceGetAttribute(&f.maxSmemOptin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+        it = cache.emplace(dev, f).first;
+    }
+    return it->second;
+}
+
+// Resident CTAs per SM of one staged-kernel instantiation for a block size and dynamic shared-memory size; also raises
+// the kernel's dynamic shared-memory limit the first time a size is seen on a device.
+template<typename K>
+static int staged_occupancy(K kernel, int dev, int kernelId, int block, int smemBytes)
+{
+    static std::mutex                                     mu;
+    static std::map<std::tuple<int, int, int, int>, int> cache;
+    std::lock_guard<std::mutex>                           lock(mu);
+    auto key = std::make_tuple(dev, kernelId, block, smemBytes);
+    auto it  = cache.find(key);
+    if (it == cache.end())
+    {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smemBytes) != cudaSuccess)
+        {
+            cudaGetLastError();
+            it = cache.emplace(key, 0).first;
+        }
+        else
+        {
+            int n = 0;
+            if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, block, smemBytes) != cudaSuccess)
+            {
+                cudaGetLastError();
+                n = 0;
+            }
+            it = cache.emplace(key, n).first;
+        }
+    }
+    return it->second;
+}
+
+// ------------------------------------------------------------------------------------------------ resize dispatch
+
+template<int INTERP, int DK>
+static int launch_resize_gather(const ResizeKParams &kp, cudaStream_t stream)
+{
+    dim3 block(32, 8);
+    dim3 grid((kp.dstW + 31) / 32, (kp.dstH + 7) / 8, std::min(kp.numSamples, 32768));
+    resize_gather_kernel<INTERP, DK><<<grid, block, 0, stream>>>(kp);
+    return check_launch("ResizeCropConvertReformat (gather)");
+}
+
+// Returns 1 when the staged kernel was launched, 0 when it does not apply (caller falls back), <0 never.
+template<int INTERP, int DK>
+static int launch_resize_staged(const ResizeKParams &kp, int srcWBound, cudaStream_t stream, int *status)
+{
+    int dev = 0;
+    cudaGetDevice(&dev);
+    const DeviceFacts &facts = device_facts(dev);
+
+    StagedCfg cfg{};
+    cfg.rowsPerStage = INTERP == B200PP_INTERP_LINEAR ? 2 : 1;
+
+    // Shared-memory bytes one staged source row may need for `cols` destination columns: the tapped span is at most
+    // cols*srcW/resizeW + 2 pixels, plus alignment slack on both ends.
+    auto seg_for = [&](int cols) {
+        long long span = (static_cast<long long>(cols) * srcWBound + kp.resizeW - 1) / kp.resizeW + 3;
+        span           = std::min<long long>(span, srcWBound);
+        long long b    = span * 3 + 32;
+        return static_cast<int>((b + 127) / 128 * 128);
+    };
+    const int kMaxSeg = 32 * 1024;
+    cfg.chunkCols     = kp.dstW;
+    while (cfg.chunkCols > 32 && seg_for(cfg.chunkCols) > kMaxSeg) cfg.chunkCols = (cfg.chunkCols + 1) / 2;
+    cfg.segBytes     = std::min(seg_for(cfg.chunkCols), kMaxSeg);
+    cfg.chunksPerRow = (kp.dstW + cfg.chunkCols - 1) / cfg.chunkCols;
+    cfg.totalUnits   = static_cast<long long>(kp.numSamples) * kp.dstH * cfg.chunksPerRow;
+
+    const int stageBytes = cfg.segBytes * cfg.rowsPerStage;
+    cfg.stages           = std::max(2, std::min(8, (48 * 1024) / stageBytes));
+    const int smemBytes  = cfg.stages * stageBytes + cfg.stages * (int)sizeof(UnitInfo) + cfg.stages * 16 + 128;
+    if (smemBytes > facts.maxSmemOptin)
+        return 0;
+
+    const int colsPerThread = (cfg.chunkCols + 255) / 256;
+    int       consumers     = ((cfg.chunkCols + colsPerThread - 1) / colsPerThread + 31) / 32 * 32;
+    consumers               = std::max(32, std::min(consumers, 480));
+    const int block         = kProducerThreads + consumers;
+
+    auto      kernel = resize_staged_kernel<INTERP, DK>;
+    const int occ    = staged_occupancy(kernel, dev, INTERP * 4 + DK, block, smemBytes);
+    if (occ <= 0)
+        return 0;
+    const long long grid = std::min<long long>(cfg.totalUnits, static_cast<long long>(facts.smCount) * occ);
+    kernel<<<static_cast<unsigned>(grid), block, smemBytes, stream>>>(kp, cfg);
+    *status = check_launch("ResizeCropConvertReformat (staged)");
+    return 1;
+}
+
+template<int INTERP, int DK>
+static int run_resize(const ResizeKParams &kp, int srcWBound, cudaStream_t stream)
+{
+    const int path = g_kernelPath.load(std::memory_order_relaxed);
+    // The staged kernel writes one destination row per unit with warp-contiguous stores; tiny outputs gain nothing.
+    const bool wantStaged = path == 2 || (path == 0 && kp.dstW >= 32);
+    if (wantStaged)
+    {
+        int status = B200PP_SUCCESS;
+        if (launch_resize_staged<INTERP, DK>(kp, srcWBound, stream, &status))
+            return status;
+    }
+    return launch_resize_gather<INTERP, DK>(kp, stream);
+}
+
+template<int INTERP>
+static int run_resize_dk(int dk, const ResizeKParams &kp, int srcWBound, cudaStream_t stream)
+{
+    switch (dk)
+    {
+    case DST_U8:
+        return run_resize<INTERP, DST_U8>(kp, srcWBound, stream);
+    case DST_F32:
+        return run_resize<INTERP, DST_F32>(kp, srcWBound, stream);
+    default:
+        return run_resize<INTERP, DST_F16>(kp, srcWBound, stream);
+    }
+}
+
+} // namespace b200pp
+
+using namespace b200pp;
+
+// ================================================================================================ C entry points
+
+extern "C" int b200ppResizeCropConvertReformat(const B200ppSource *src, const B200ppDest *dst, const B200ppResizeOp *op,
+                                               cudaStream_t stream)
+{
+    if (!src || !dst || !op)
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "Null argument");
+    if (src->numSamples != 0 && (!dst->base || (!src->base && !src->imageList)))
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "Input and output must be cuda-accessible, pitch-linear memory");
+
+    // Same checks, order and status codes as the reference operator
+    // (src/cvcuda/priv/OpResizeCropConvertReformat.cu:446-539 and :591-668).
+    if (src->channels != dst->channels)
+        return fail(B200PP_ERROR_NOT_COMPATIBLE,
+                    "Input and output must have same number of channels: Provided %d input and %d output channels",
+                    src->channels, dst->channels);
+    if (src->channels != 3)
+        return fail(B200PP_ERROR_NOT_COMPATIBLE,
+                    "Only three-channel input is currently supported: Provided %d input channels", src->channels);
+    if (src->dtype != B200PP_U8)
+        return fail(B200PP_ERROR_NOT_COMPATIBLE, "Input must be of data type uchar.");
+    if (dst->dtype != B200PP_U8 && dst->dtype != B200PP_F32 && dst->dtype != B200PP_F16)
+        return fail(B200PP_ERROR_NOT_COMPATIBLE, "Output must be of data type uchar, float or half.");
+    if (src->planar)
+        return fail(B200PP_ERROR_NOT_COMPATIBLE, "Input must be non-planar (i.e., interleaved).");
+    if (op->resizeW <= 1 || op->resizeH <= 1)
+        return fail(B200PP_ERROR_INVALID_ARGUMENT,
+                    "Invalid resize dimensions: width x hight = %d x %d dimensions must be larger than 1.", op->resizeW,
+                    op->resizeH);
+
+    const bool wholeDst = (op->regionW == 0 && op->regionH == 0);
+    const int  regionW = wholeDst ? dst->width : op->regionW, regionH = wholeDst ? dst->height : op->regionH;
+    const int  dstX = wholeDst ? 0 : op->dstX, dstY = wholeDst ? 0 : op->dstY;
+    if (dst->width < 1 || dst->height < 1 || regionW < 1 || regionH < 1 || dstX < 0 || dstY < 0
+        || static_cast<long long>(dstX) + regionW > dst->width || static_cast<long long>(dstY) + regionH > dst->height)
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "Invalid placement: region (%d, %d, %d, %d) does not fit the %d x %d output",
+                    dstX, dstY, regionW, regionH, dst->width, dst->height);
+    if (op->cropX < 0 || op->cropY < 0 || static_cast<long long>(op->cropX) + regionW > op->resizeW
+        || static_cast<long long>(op->cropY) + regionH > op->resizeH)
+        return fail(B200PP_ERROR_INVALID_ARGUMENT,
+                    "Invalid crop region: crop region(x, y, w, h) = (%d, %d, %d, %d) extends beyond bounds of resized tensor",
+                    op->cropX, op->cropY, regionW, regionH);
+    if (op->interp != B200PP_INTERP_NEAREST && op->interp != B200PP_INTERP_LINEAR)
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, op->interp == 2   ? "Interpolation not implemented: NVCV_INTERP_CUBIC"
+                                                   : op->interp == 3 ? "Interpolation not implemented: NVCV_INTERP_AREA"
+                                                                     : "Invalid interpolation");
+    if (op->manip != B200PP_CHANNEL_NO_OP && op->manip != B200PP_CHANNEL_REVERSE)
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "Invalid channel manipulation");
+    if (src->numSamples < 0)
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "Negative batch size");
+    if (!src->imageList && (src->width < 1 || src->height < 1))
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "Invalid input size");
+    if (src->numSamples == 0)
+        return B200PP_SUCCESS;
+
+    ResizeKParams kp{};
+    kp.srcBase         = static_cast<const uint8_t *>(src->base);
+    kp.srcSampleStride = src->sampleStride;
+    kp.srcRowStride    = src->rowStride;
+    kp.srcW            = src->width;
+    kp.srcH            = src->height;
+    kp.list            = src->imageList;
+    kp.roi             = op->roi;
+    kp.roiStride       = op->roiStride ? op->roiStride : 16;
+    kp.flip            = op->flipCode;
+    kp.numSamples      = src->numSamples;
+    kp.resizeW         = op->resizeW;
+    kp.resizeH         = op->resizeH;
+    kp.cropX           = op->cropX;
+    kp.cropY           = op->cropY;
+    kp.srcCast         = op->srcCast != 0;
+    kp.dstX            = dstX;
+    kp.dstY            = dstY;
+    kp.regionW         = regionW;
+    kp.regionH         = regionH;
+    kp.padValue        = op->padValue;
+    kp.perChannel      = op->perChannel != 0;
+    kp.scale           = op->scale;
+    kp.offset          = op->offset;
+    for (int c = 0; c < 3; ++c)
+    {
+        kp.base[c] = op->base[c];
+        kp.mul[c]  = op->mul[c];
+        kp.mapC[c] = op->manip == B200PP_CHANNEL_REVERSE ? 2 - c : c;
+    }
+    kp.gscale  = op->gscale;
+    kp.shift   = op->shift;
+    kp.dst     = static_cast<uint8_t *>(dst->base);
+    kp.dSample = dst->sampleStride;
+    kp.dRow    = dst->rowStride;
+    kp.dPix    = dst->pixStride;
+    kp.dChan   = dst->chanStride;
+    kp.dstW    = dst->width;
+    kp.dstH    = dst->height;
+
+    const int dk        = dst->dtype == B200PP_U8 ? DST_U8 : (dst->dtype == B200PP_F32 ? DST_F32 : DST_F16);
+    const int srcWBound = src->imageList ? (src->maxWidth > 0 ? src->maxWidth : 3840) : src->width;
+    if (op->interp == B200PP_INTERP_NEAREST)
+        return run_resize_dk<B200PP_INTERP_NEAREST>(dk, kp, srcWBound, stream);
+    return run_resize_dk<B200PP_INTERP_LINEAR>(dk, kp, srcWBound, stream);
+}
+
+extern "C" int b200ppCropFlipNormalizeReformat(const B200ppSource *src, const B200ppDest *dst, const B200ppSliceOp *op,
+                                               cudaStream_t stream)
+{
+    if (!src || !dst || !op)
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "Null argument");
+    if (src->numSamples != 0 && (!dst->base || (!src->base && !src->imageList)))
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "Input and output must be cuda-accessible, pitch-linear memory");
+    if (!op->cropRect || !op->flipCode || !op->base || !op->scale)
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "cropRect, flipCode, base and scale must be cuda-accessible tensors");
+
+    // Checks of the reference operator (src/cvcuda/priv/OpCropFlipNormalizeReformat.cu:430-464, :304-317, :342-356).
+    const int channels = src->channels;
+    if (channels < 1 || channels > 4)
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "Input must have 1 to 4 channels");
+    if (!(op->baseChannels == 1 || op->baseChannels >= channels))
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "Channel of base tensor must be 1 or >= input/output tensor channels");
+    if (!(op->scaleChannels == 1 || op->scaleChannels >= channels))
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "Channel of scale tensor must be 1 or >= input/output tensor channels");
+    if (src->dtype < B200PP_U8 || src->dtype > B200PP_F32)
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "Unsupported input data type");
+    if (dst->dtype < B200PP_U8 || dst->dtype > B200PP_F16)
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "Unsupported output data type");
+    if (op->border < B200PP_BORDER_CONSTANT || op->border > B200PP_BORDER_REFLECT101)
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "Unsupported border mode");
+    if (dst->channels != channels)
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "Input and output must have the same number of channels");
+    if (src->numSamples < 0 || dst->width < 1 || dst->height < 1)
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "Invalid batch or output size");
+    if (src->numSamples == 0)
+        return B200PP_SUCCESS;
+
+    SliceKParams kp{};
+    kp.srcBase         = static_cast<const uint8_t *>(src->base);
+    kp.srcSampleStride = src->sampleStride;
+    kp.srcRowStride    = src->rowStride;
+    kp.srcPlaneStride  = src->planeStride;
+    kp.srcW            = src->width;
+    kp.srcH            = src->height;
+    kp.list            = src->imageList;
+    kp.srcPlanar       = src->planar != 0 && channels > 1;
+    kp.channels        = channels;
+    kp.numSamples      = src->numSamples;
+    kp.cropRect        = op->cropRect;
+    kp.cropRectStride  = op->cropRectStride ? op->cropRectStride : 16;
+    kp.flip            = op->flipCode;
+    kp.border          = op->border;
+    // static_cast<T_Src>(borderValue), then the promotion to float that the normalisation applies to every source value
+    switch (src->dtype)
+    {
+    case B200PP_U8:
+        kp.borderAsSrc = static_cast<float>(static_cast<uint8_t>(op->borderValue));
+        break;
+    case B200PP_S8:
+        kp.borderAsSrc = static_cast<float>(static_cast<int8_t>(op->borderValue));
+        break;
+    case B200PP_U16:
+        kp.borderAsSrc = static_cast<float>(static_cast<uint16_t>(op->borderValue));
+        break;
+    case B200PP_S16:
+        kp.borderAsSrc = static_cast<float>(static_cast<int16_t>(op->borderValue));
+        break;
+    case B200PP_U32:
+        kp.borderAsSrc = static_cast<float>(static_cast<uint32_t>(op->borderValue));
+        break;
+    case B200PP_S32:
+        kp.borderAsSrc = static_cast<float>(static_cast<int32_t>(op->borderValue));
+        break;
+    default:
+        kp.borderAsSrc = op->borderValue;
+        break;
+    }
+    kp.base            = op->base;
+    kp.baseChanStride  = op->baseChanStride ? op->baseChanStride : 4;
+    kp.baseCh          = op->baseChannels;
+    kp.scale           = op->scale;
+    kp.scaleChanStride = op->scaleChanStride ? op->scaleChanStride : 4;
+    kp.scaleCh         = op->scaleChannels;
+    kp.gscale          = op->gscale;
+    kp.shift           = op->shift;
+    kp.epsilon         = op->epsilon;
+    // The reference kernel receives the whole flags word as a bool
+    // (src/cvcuda/priv/OpCropFlipNormalizeReformat.cu:46,73): any set bit selects the standard-deviation formula.
+    kp.stddev  = op->flags != 0;
+    kp.dst     = static_cast<uint8_t *>(dst->base);
+    kp.dSample = dst->sampleStride;
+    kp.dRow    = dst->rowStride;
+    kp.dPix    = dst->pixStride;
+    kp.dChan   = dst->chanStride;
+    kp.dstW    = dst->width;
+    kp.dstH    = dst->height;
+
+    dim3 block(32, 8);
+    dim3 grid((kp.dstW + 31) / 32, (kp.dstH + 7) / 8, std::min(kp.numSamples, 32768));
+    slice_gather_kernel<4><<<grid, block, 0, stream>>>(kp, src->dtype, dst->dtype, elem_size(src->dtype),
+                                                       elem_size(dst->dtype));
+    return check_launch("CropFlipNormalizeReformat");
+}
+
+extern "C" const char *b200ppGetLastErrorMessage(void)
+{
+    return t_lastError;
+}
+
+extern "C" int b200ppSetKernelPath(int path)
+{
+    return g_kernelPath.exchange(path);
+}
+
+extern "C" uint64_t b200ppGetLaunchCount(void)
+{
+    return g_launchCount.load();
+}
+
+extern "C" int b200ppReadDeviceError(uint32_t *outError)
+{
+    if (!outError)
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "Null argument");
+    unsigned int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, g_deviceError, sizeof(v)) != cudaSuccess
+        || cudaMemcpyToSymbol(g_deviceError, &zero, sizeof(zero)) != cudaSuccess)
+    {
+        cudaGetLastError();
+        return fail(B200PP_ERROR_INTERNAL, "Could not read the device error word");
+    }
+    *outError = v;
+    return B200PP_SUCCESS;
+}

@@ -1,0 +1,491 @@
+"""Host-side mirror of the reference's Python operator interface for the fused pre-processing path.
+
+Function names, argument names and meaning follow the reference binding
+(python/mod_cvcuda/OpResizeCropConvertReformat.cpp:207-420, python/mod_cvcuda/OpCropFlipNormalizeReformat.cpp:86-165);
+tensors are ``torch`` CUDA tensors instead of ``nvcv.Tensor`` objects, and a variable-shape batch is an
+:class:`ImageBatchVarShape` of CUDA tensors. PyTorch only provides device memory and streams here: every value is
+computed by ``libcvcuda_b200.so`` through its plain-C entry points (``include/cvcuda_b200/preproc.h``).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import enum
+import os
+from typing import NamedTuple, Optional, Sequence, Tuple, Union
+
+import numpy as np
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB_NAME = "libcvcuda_b200.so"
+
+
+# ------------------------------------------------------------------------------------------------ enums / small types
+
+class Interp(enum.IntEnum):
+    """NVCVInterpolationType (src/cvcuda/include/cvcuda/Types.h:39-51)."""
+    NEAREST = 0
+    LINEAR = 1
+    CUBIC = 2
+    AREA = 3
+    LANCZOS = 4
+
+
+class ChannelManip(enum.IntEnum):
+    """NVCVChannelManip (Types.h:63-67)."""
+    NO_OP = 0
+    REVERSE = 1
+
+
+class Border(enum.IntEnum):
+    """NVCVBorderType (src/nvcv/src/include/nvcv/BorderType.h:36-43)."""
+    CONSTANT = 0
+    REPLICATE = 1
+    REFLECT = 2
+    WRAP = 3
+    REFLECT101 = 4
+
+
+NORMALIZE_SCALE_IS_STDDEV = 1
+
+
+class RectI(NamedTuple):
+    """nvcv.RectI: x, y, width, height."""
+    x: int
+    y: int
+    width: int
+    height: int
+
+
+class Status(enum.IntEnum):
+    SUCCESS = 0
+    ERROR_NOT_IMPLEMENTED = 1
+    ERROR_INVALID_ARGUMENT = 2
+    ERROR_INVALID_IMAGE_FORMAT = 3
+    ERROR_INTERNAL = 8
+    ERROR_NOT_COMPATIBLE = 9
+    ERROR_OVERFLOW = 10
+
+
+class Error(RuntimeError):
+    """A failed operator call; ``status`` holds the NVCVStatus code the C entry point returned."""
+
+    def __init__(self, status: int, message: str):
+        try:
+            name = Status(status).name
+        except ValueError:
+            name = str(status)
+        super().__init__(f"NVCV_{name}: {message}")
+        self.status = status
+        self.message = message
+
+
+# ------------------------------------------------------------------------------------------------ C structs
+
+class _ImagePlane(C.Structure):
+    _fields_ = [("width", C.c_int32), ("height", C.c_int32), ("rowStride", C.c_int32), ("basePtr", C.c_void_p)]
+
+
+class _ImageBuffer(C.Structure):
+    _fields_ = [("numPlanes", C.c_int32), ("planes", _ImagePlane * 6)]
+
+
+class _Source(C.Structure):
+    _fields_ = [("dtype", C.c_int32), ("channels", C.c_int32), ("planar", C.c_int32), ("numSamples", C.c_int32),
+                ("base", C.c_void_p), ("sampleStride", C.c_int64), ("rowStride", C.c_int64),
+                ("planeStride", C.c_int64), ("width", C.c_int32), ("height", C.c_int32),
+                ("imageList", C.c_void_p), ("maxWidth", C.c_int32), ("maxHeight", C.c_int32)]
+
+
+class _Dest(C.Structure):
+    _fields_ = [("base", C.c_void_p), ("dtype", C.c_int32), ("channels", C.c_int32), ("width", C.c_int32),
+                ("height", C.c_int32), ("sampleStride", C.c_int64), ("rowStride", C.c_int64),
+                ("pixStride", C.c_int64), ("chanStride", C.c_int64)]
+
+
+class _ResizeOp(C.Structure):
+    _fields_ = [("resizeW", C.c_int32), ("resizeH", C.c_int32), ("cropX", C.c_int32), ("cropY", C.c_int32),
+                ("interp", C.c_int32), ("srcCast", C.c_int32), ("manip", C.c_int32), ("perChannel", C.c_int32),
+                ("scale", C.c_float), ("offset", C.c_float), ("base", C.c_float * 4), ("mul", C.c_float * 4),
+                ("gscale", C.c_float), ("shift", C.c_float),
+                ("dstX", C.c_int32), ("dstY", C.c_int32), ("regionW", C.c_int32), ("regionH", C.c_int32),
+                ("padValue", C.c_float),
+                ("roi", C.c_void_p), ("roiStride", C.c_int64), ("flipCode", C.c_void_p)]
+
+
+class _SliceOp(C.Structure):
+    _fields_ = [("cropRect", C.c_void_p), ("cropRectStride", C.c_int64), ("flipCode", C.c_void_p),
+                ("border", C.c_int32), ("borderValue", C.c_float),
+                ("base", C.c_void_p), ("baseChannels", C.c_int32), ("baseChanStride", C.c_int64),
+                ("scale", C.c_void_p), ("scaleChannels", C.c_int32), ("scaleChanStride", C.c_int64),
+                ("gscale", C.c_float), ("shift", C.c_float), ("epsilon", C.c_float), ("flags", C.c_uint32)]
+
+
+assert C.sizeof(_ImagePlane) == 24 and C.sizeof(_ImageBuffer) == 152  # NVCVImageBufferStrided layout
+
+_DTYPE_CODE = {torch.uint8: 0, torch.int8: 1, torch.int16: 3, torch.int32: 5, torch.float32: 6, torch.float16: 7}
+for _name, _code in (("uint16", 2), ("uint32", 4)):
+    if hasattr(torch, _name):
+        _DTYPE_CODE[getattr(torch, _name)] = _code
+
+
+# ------------------------------------------------------------------------------------------------ library
+
+_lib: Optional[C.CDLL] = None
+
+
+def lib_path() -> str:
+    return os.path.join(_HERE, _LIB_NAME)
+
+
+def lib() -> C.CDLL:
+    """The CUDA library. Raises if it has not been built: there is no other implementation to fall back to."""
+    global _lib
+    if _lib is None:
+        path = lib_path()
+        if not os.path.exists(path):
+            raise RuntimeError(f"{path} is missing: run `python cv-cuda_b200/build.py` (or __graft_entry__.build()). "
+                               "This package has no CPU or PyTorch fallback.")
+        L = C.CDLL(path)
+        L.b200ppResizeCropConvertReformat.restype = C.c_int
+        L.b200ppResizeCropConvertReformat.argtypes = [C.POINTER(_Source), C.POINTER(_Dest), C.POINTER(_ResizeOp),
+                                                      C.c_void_p]
+        L.b200ppCropFlipNormalizeReformat.restype = C.c_int
+        L.b200ppCropFlipNormalizeReformat.argtypes = [C.POINTER(_Source), C.POINTER(_Dest), C.POINTER(_SliceOp),
+                                                      C.c_void_p]
+        L.b200ppGetLastErrorMessage.restype = C.c_char_p
+        L.b200ppSetKernelPath.restype = C.c_int
+        L.b200ppSetKernelPath.argtypes = [C.c_int]
+        L.b200ppGetLaunchCount.restype = C.c_uint64
+        L.b200ppReadDeviceError.restype = C.c_int
+        L.b200ppReadDeviceError.argtypes = [C.POINTER(C.c_uint32)]
+        _lib = L
+    return _lib
+
+
+def last_error() -> str:
+    return lib().b200ppGetLastErrorMessage().decode()
+
+
+def set_kernel_path(path: int) -> int:
+    """0 automatic, 1 per-pixel gather kernels, 2 staged kernels where they apply. Returns the previous setting."""
+    return lib().b200ppSetKernelPath(int(path))
+
+
+def launch_count() -> int:
+    return int(lib().b200ppGetLaunchCount())
+
+
+def read_device_error() -> int:
+    v = C.c_uint32(0)
+    _check(lib().b200ppReadDeviceError(C.byref(v)))
+    return int(v.value)
+
+
+def _check(status: int) -> None:
+    if status != 0:
+        raise Error(status, last_error())
+
+
+def _stream_handle(stream) -> int:
+    if stream is None:
+        return torch.cuda.current_stream().cuda_stream
+    if isinstance(stream, int):
+        return stream
+    return stream.cuda_stream
+
+
+# ------------------------------------------------------------------------------------------------ tensor views
+
+class ImageBatchVarShape:
+    """A batch of images of different sizes, the counterpart of nvcv.ImageBatchVarShape.
+
+    Images are CUDA tensors: ``[H, W, C]`` (interleaved) or ``[C, H, W]`` (planar, ``planar=True``), innermost dimension
+    contiguous, rows possibly padded. The device-side descriptor table has the memory layout of
+    ``NVCVImageBufferStrided[]`` (src/nvcv/src/include/nvcv/ImageData.h:52-66) and is uploaded when first needed after
+    a change, like ``ImageBatchVarShape::exportData`` does (src/nvcv/src/priv/ImageBatchVarShape.cpp:215-254).
+    """
+
+    def __init__(self, images: Sequence[torch.Tensor] = (), planar: bool = False):
+        self.planar = planar
+        self._images = []
+        self._table = None
+        self.pushback(images)
+
+    def pushback(self, images: Union[torch.Tensor, Sequence[torch.Tensor]]) -> None:
+        if isinstance(images, torch.Tensor):
+            images = [images]
+        for im in images:
+            if im.dim() != 3 or not im.is_cuda:
+                raise Error(Status.ERROR_INVALID_ARGUMENT, "Images must be 3-D CUDA tensors")
+            if im.stride(2) != 1 or (not self.planar and im.stride(1) != im.shape[2]):
+                raise Error(Status.ERROR_INVALID_ARGUMENT, "Image pixels must be contiguous within a row")
+            if self._images and (im.dtype != self._images[0].dtype or self._channels(im) != self.channels):
+                raise Error(Status.ERROR_INVALID_ARGUMENT,
+                            "All input images in a batch must have the same format (including number of channels)")
+            self._images.append(im)
+        self._table = None
+
+    def _channels(self, im: torch.Tensor) -> int:
+        return im.shape[0] if self.planar else im.shape[2]
+
+    def __len__(self) -> int:
+        return len(self._images)
+
+    def __getitem__(self, i: int) -> torch.Tensor:
+        return self._images[i]
+
+    @property
+    def channels(self) -> int:
+        return self._channels(self._images[0])
+
+    @property
+    def dtype(self) -> torch.dtype:
+        return self._images[0].dtype
+
+    @property
+    def device(self) -> torch.device:
+        return self._images[0].device
+
+    def size(self, i: int) -> Tuple[int, int]:
+        im = self._images[i]
+        return (im.shape[2], im.shape[1]) if self.planar else (im.shape[1], im.shape[0])
+
+    @property
+    def max_size(self) -> Tuple[int, int]:
+        sizes = [self.size(i) for i in range(len(self))]
+        return max(s[0] for s in sizes), max(s[1] for s in sizes)
+
+    def descriptor_table(self) -> torch.Tensor:
+        """uint8 CUDA tensor holding ``NVCVImageBufferStrided[len(self)]``."""
+        if self._table is None:
+            arr = (_ImageBuffer * len(self._images))()
+            for i, im in enumerate(self._images):
+                es = im.element_size()
+                if self.planar:
+                    c, h, w = im.shape
+                    arr[i].numPlanes = c
+                    for k in range(c):
+                        arr[i].planes[k] = _ImagePlane(w, h, im.stride(1) * es, im.data_ptr() + k * im.stride(0) * es)
+                else:
+                    h, w, c = im.shape
+                    arr[i].numPlanes = 1
+                    arr[i].planes[0] = _ImagePlane(w, h, im.stride(0) * es, im.data_ptr())
+            host = torch.frombuffer(bytearray(bytes(arr)), dtype=torch.uint8).pin_memory()
+            self._table = host.to(self.device, non_blocking=True)
+        return self._table
+
+
+def _source_of(src: Union[torch.Tensor, ImageBatchVarShape]):
+    """Returns (struct, keepalive)."""
+    s = _Source()
+    if isinstance(src, ImageBatchVarShape):
+        if len(src) == 0:
+            raise Error(Status.ERROR_INVALID_ARGUMENT, "Input image batch is empty")
+        table = src.descriptor_table()
+        s.dtype = _DTYPE_CODE[src.dtype]
+        s.channels, s.planar, s.numSamples = src.channels, int(src.planar), len(src)
+        s.imageList = table.data_ptr()
+        s.maxWidth, s.maxHeight = src.max_size
+        return s, table
+    if not src.is_cuda:
+        raise Error(Status.ERROR_INVALID_ARGUMENT, "Input must be a cuda-accessible, pitch-linear tensor")
+    t = src if src.dim() == 4 else src.unsqueeze(0)
+    if t.dim() != 4:
+        raise Error(Status.ERROR_NOT_COMPATIBLE, "Input tensor must have 'NHWC' or 'HWC' layout")
+    n, h, w, c = t.shape
+    es = t.element_size()
+    if t.stride(3) != 1 or t.stride(2) != c:
+        raise Error(Status.ERROR_INVALID_ARGUMENT, "Input pixels must be contiguous within a row")
+    s.dtype = _DTYPE_CODE[t.dtype]
+    s.channels, s.planar, s.numSamples = c, 0, n
+    s.base = t.data_ptr()
+    s.sampleStride, s.rowStride, s.planeStride = t.stride(0) * es, t.stride(1) * es, 0
+    s.width, s.height = w, h
+    return s, t
+
+
+def _dest_of(dst: torch.Tensor, layout: str):
+    """layout: 'NHWC', 'HWC', 'NCHW' or 'CHW'. Returns (struct, samples)."""
+    if not dst.is_cuda:
+        raise Error(Status.ERROR_INVALID_ARGUMENT, "Output must be a cuda-accessible, pitch-linear tensor")
+    if layout not in ("NHWC", "HWC", "NCHW", "CHW"):
+        raise Error(Status.ERROR_NOT_COMPATIBLE,
+                    f"Output tensor must have 'NHWC', 'NCHW', 'HWC', or 'CHW' layout: Layout provided {layout}")
+    if dst.dim() != len(layout):
+        raise Error(Status.ERROR_INVALID_ARGUMENT, "Output tensor rank does not match its layout")
+    t = dst if dst.dim() == 4 else dst.unsqueeze(0)
+    es = t.element_size()
+    d = _Dest()
+    d.base, d.dtype = t.data_ptr(), _DTYPE_CODE[t.dtype]
+    if layout.endswith("HWC"):
+        n, h, w, c = t.shape
+        d.sampleStride, d.rowStride, d.pixStride, d.chanStride = (t.stride(i) * es for i in range(4))
+    else:
+        n, c, h, w = t.shape
+        d.sampleStride, d.chanStride, d.rowStride, d.pixStride = (t.stride(i) * es for i in range(4))
+    d.channels, d.width, d.height = c, w, h
+    return d, n
+
+
+def _default_layout(t: torch.Tensor, layout: str) -> str:
+    if layout:
+        return layout
+    return "NHWC" if t.dim() == 4 else "HWC"
+
+
+# ------------------------------------------------------------------------------------------------ operators
+
+def fused_preprocess_into(dst: torch.Tensor, src: Union[torch.Tensor, ImageBatchVarShape], *, resize_dim, interp,
+                          crop_pos=(0, 0), layout: str = "", manip=ChannelManip.NO_OP, scale: float = 1.0,
+                          offset: float = 0.0, base: Optional[Sequence[float]] = None,
+                          mul: Optional[Sequence[float]] = None, gscale: float = 1.0, shift: float = 0.0,
+                          srcCast: bool = True, roi: Optional[torch.Tensor] = None,
+                          flip_code: Optional[torch.Tensor] = None, dst_pos=(0, 0), region_size=None,
+                          pad_value: float = 0.0, stream=None) -> torch.Tensor:
+    """The whole fused pass in one call: resize (of the optional per-sample ``roi``) -> crop -> optional flip ->
+    affine -> channel map -> cast -> layout, optionally placed inside a padded canvas.
+
+    A superset of :func:`resize_crop_convert_reformat_into`: ``base``/``mul`` select the per-channel form
+    ``(v - base[c]) * mul[c] * gscale + shift``; ``roi`` is an int32 CUDA tensor ``[N, 4]`` of ``(x, y, w, h)``;
+    ``flip_code`` an int32 CUDA tensor ``[N]``; ``dst_pos``/``region_size``/``pad_value`` describe a letterbox.
+    float16 destinations are accepted here.
+    """
+    layout = _default_layout(dst, layout)
+    s, keep_src = _source_of(src)
+    d, n_out = _dest_of(dst, layout)
+    if n_out != s.numSamples:
+        raise Error(Status.ERROR_INVALID_ARGUMENT,
+                    "Input and output must have the same batch size (i.e., same number of images): Provided "
+                    f"{s.numSamples} input and {n_out} output images / samples")
+    op = _ResizeOp()
+    op.resizeW, op.resizeH = int(resize_dim[0]), int(resize_dim[1])
+    op.cropX, op.cropY = int(crop_pos[0]), int(crop_pos[1])
+    op.interp, op.srcCast, op.manip = int(interp), int(bool(srcCast)), int(manip)
+    op.perChannel = int(base is not None or mul is not None)
+    op.scale, op.offset, op.gscale, op.shift = float(scale), float(offset), float(gscale), float(shift)
+    for i in range(4):
+        op.base[i] = float(base[i]) if base is not None and i < len(base) else 0.0
+        op.mul[i] = float(mul[i]) if mul is not None and i < len(mul) else 1.0
+    if region_size is not None:
+        op.dstX, op.dstY = int(dst_pos[0]), int(dst_pos[1])
+        op.regionW, op.regionH = int(region_size[0]), int(region_size[1])
+    op.padValue = float(pad_value)
+    if roi is not None:
+        if roi.dtype != torch.int32 or not roi.is_cuda or roi.shape[-1] != 4 or roi.stride(-1) != 1:
+            raise Error(Status.ERROR_INVALID_ARGUMENT, "roi must be an int32 CUDA tensor [N, 4]")
+        op.roi = roi.data_ptr()
+        op.roiStride = roi.stride(0) * 4 if roi.dim() > 1 else 16
+    if flip_code is not None:
+        if flip_code.dtype != torch.int32 or not flip_code.is_cuda or not flip_code.is_contiguous():
+            raise Error(Status.ERROR_INVALID_ARGUMENT, "flip_code must be a packed int32 CUDA tensor [N]")
+        op.flipCode = flip_code.data_ptr()
+    _check(lib().b200ppResizeCropConvertReformat(C.byref(s), C.byref(d), C.byref(op), _stream_handle(stream)))
+    return dst
+
+
+def resize_crop_convert_reformat_into(dst: torch.Tensor, src: Union[torch.Tensor, ImageBatchVarShape],
+                                      resize_dim: Tuple[int, int], interp: Interp, cropPos: Tuple[int, int], *,
+                                      layout: str = "", manip: ChannelManip = ChannelManip.NO_OP, scale: float = 1.0,
+                                      offset: float = 0.0, srcCast: bool = True, stream=None) -> torch.Tensor:
+    """cvcuda.resize_crop_convert_reformat_into (python/mod_cvcuda/OpResizeCropConvertReformat.cpp:263-316,374-420).
+
+    ``layout`` names the layout of ``dst`` (a torch tensor carries none); default NHWC / HWC by rank. The crop size
+    is the width and height of ``dst``. Like the reference operator, float16 output is refused here
+    (src/cvcuda/priv/OpResizeCropConvertReformat.cu:476-479); use :func:`fused_preprocess_into` for it.
+    """
+    if dst.dtype not in (torch.uint8, torch.float32):
+        raise Error(Status.ERROR_NOT_COMPATIBLE, "Output must be of data type uchar or float.")
+    return fused_preprocess_into(dst, src, resize_dim=resize_dim, interp=interp, crop_pos=cropPos, layout=layout,
+                                 manip=manip, scale=scale, offset=offset, srcCast=srcCast, stream=stream)
+
+
+def resize_crop_convert_reformat(src: Union[torch.Tensor, ImageBatchVarShape], resize_dim: Tuple[int, int],
+                                 interp: Interp, crop_rect: Union[RectI, Tuple[int, int, int, int]], *,
+                                 layout: str = "", data_type: Optional[torch.dtype] = None,
+                                 manip: ChannelManip = ChannelManip.NO_OP, scale: float = 1.0, offset: float = 0.0,
+                                 srcCast: bool = True, stream=None) -> torch.Tensor:
+    """cvcuda.resize_crop_convert_reformat (python/mod_cvcuda/OpResizeCropConvertReformat.cpp:58-104,145-196).
+
+    Allocates the output: shape from ``crop_rect`` (x, y, width, height), layout from ``layout`` (default: the
+    input's), element type from ``data_type`` (default: the input's).
+    """
+    rect = RectI(*crop_rect)
+    if isinstance(src, ImageBatchVarShape):
+        n, c, rank4, dev, in_dtype = len(src), src.channels, True, src.device, src.dtype
+        if c != 3:
+            raise Error(Status.ERROR_INVALID_ARGUMENT, "Input must have 3 channels.")
+        out_layout = layout or "NHWC"
+        if out_layout in ("HWC", "NHW", "HW"):
+            out_layout = "NHWC"
+        elif out_layout == "CHW":
+            out_layout = "NCHW"
+    else:
+        if src.dim() not in (3, 4):
+            raise Error(Status.ERROR_INVALID_IMAGE_FORMAT, "Input tensor must have layout 'HWC' or 'NHWC'.")
+        rank4 = src.dim() == 4
+        n = src.shape[0] if rank4 else 1
+        c, dev, in_dtype = src.shape[-1], src.device, src.dtype
+        out_layout = layout or ("NHWC" if rank4 else "HWC")
+        if len(out_layout) != src.dim():
+            raise Error(Status.ERROR_INVALID_IMAGE_FORMAT, "Output tensor rank must match input tensor rank.")
+    if out_layout not in ("HWC", "NHWC", "CHW", "NCHW"):
+        raise Error(Status.ERROR_INVALID_IMAGE_FORMAT, "Output tensor must have layout 'HWC', 'NHWC', 'CHW', or 'NCHW'.")
+    shape = (rect.height, rect.width, c) if out_layout.endswith("HWC") else (c, rect.height, rect.width)
+    if rank4:
+        shape = (n,) + shape
+    dst = torch.empty(shape, dtype=data_type or in_dtype, device=dev)
+    return resize_crop_convert_reformat_into(dst, src, resize_dim, interp, (rect.x, rect.y), layout=out_layout,
+                                             manip=manip, scale=scale, offset=offset, srcCast=srcCast, stream=stream)
+
+
+def _param_tensor(t: torch.Tensor, what: str):
+    if not t.is_cuda or t.dtype != torch.float32:
+        raise Error(Status.ERROR_INVALID_ARGUMENT, f"Input {what} must be cuda-accessible, pitch-linear tensor")
+    return t.data_ptr(), t.shape[-1], t.stride(-1) * 4
+
+
+def crop_flip_normalize_reformat_into(dst: torch.Tensor, src: ImageBatchVarShape, rect: torch.Tensor,
+                                      flip_code: torch.Tensor, base: torch.Tensor, scale: torch.Tensor,
+                                      globalscale: float = 1.0, globalshift: float = 0.0, epsilon: float = 0.0,
+                                      flags: Optional[int] = None, border: Border = Border.CONSTANT,
+                                      bvalue: float = 0.0, *, layout: str = "", stream=None) -> torch.Tensor:
+    """cvcuda.crop_flip_normalize_reformat_into (python/mod_cvcuda/OpCropFlipNormalizeReformat.cpp:37-63,128-165).
+
+    ``rect``: int32 CUDA tensor ``[N, 1, 1, 4]`` of (x, y, w, h); ``flip_code``: int32 ``[N]``; ``base``/``scale``:
+    float32 ``[1, 1, 1, C]`` (or one value). ``layout`` names the layout of ``dst`` ('NHWC' default, or 'NCHW').
+    """
+    layout = layout or "NHWC"
+    if layout not in ("NHWC", "NCHW"):
+        raise Error(Status.ERROR_INVALID_ARGUMENT, "Invalid tensor layout in output")
+    if not isinstance(src, ImageBatchVarShape):
+        raise Error(Status.ERROR_INVALID_ARGUMENT, "Input must be a var-shape image batch")
+    s, keep = _source_of(src)
+    d, n_out = _dest_of(dst, layout)
+    if n_out < s.numSamples:
+        raise Error(Status.ERROR_INVALID_ARGUMENT, "Output has fewer samples than the input batch")
+    if rect.dtype != torch.int32 or not rect.is_cuda or rect.shape[-1] != 4 or rect.stride(-1) != 1:
+        raise Error(Status.ERROR_INVALID_ARGUMENT, "Input cropRect must be cuda-accessible, pitch-linear tensor")
+    if flip_code.dtype != torch.int32 or not flip_code.is_cuda or not flip_code.is_contiguous():
+        raise Error(Status.ERROR_INVALID_ARGUMENT, "Input flipCode must be cuda-accessible, pitch-linear tensor")
+    op = _SliceOp()
+    op.cropRect, op.cropRectStride = rect.data_ptr(), rect.stride(0) * 4
+    op.flipCode = flip_code.data_ptr()
+    op.border, op.borderValue = int(border), float(bvalue)
+    op.base, op.baseChannels, op.baseChanStride = _param_tensor(base, "base")
+    op.scale, op.scaleChannels, op.scaleChanStride = _param_tensor(scale, "scale")
+    op.gscale, op.shift, op.epsilon = float(globalscale), float(globalshift), float(epsilon)
+    op.flags = int(flags or 0)
+    _check(lib().b200ppCropFlipNormalizeReformat(C.byref(s), C.byref(d), C.byref(op), _stream_handle(stream)))
+    return dst
+
+
+def crop_flip_normalize_reformat(src: ImageBatchVarShape, out_shape: Sequence[int], out_dtype: torch.dtype,
+                                 out_layout: str, rect: torch.Tensor, flip_code: torch.Tensor, base: torch.Tensor,
+                                 scale: torch.Tensor, globalscale: float = 1.0, globalshift: float = 0.0,
+                                 epsilon: float = 0.0, flags: Optional[int] = None, border: Border = Border.CONSTANT,
+                                 bvalue: float = 0.0, *, stream=None) -> torch.Tensor:
+    """cvcuda.crop_flip_normalize_reformat (python/mod_cvcuda/OpCropFlipNormalizeReformat.cpp:65-74,86-126)."""
+    dst = torch.empty(tuple(out_shape), dtype=out_dtype, device=src.device)
+    return crop_flip_normalize_reformat_into(dst, src, rect, flip_code, base, scale, globalscale, globalshift, epsilon,
+                                             flags, border, bvalue, layout=out_layout, stream=stream)

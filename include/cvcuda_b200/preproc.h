@@ -1,0 +1,211 @@
+/*
+ * Fused image pre-processing for NVIDIA B200 (sm_100a): plain-C launch layer.
+ *
+ * These entry points take only pointers, sizes and byte strides. The handle-based operator API of
+ * cvcuda_ops.h (the drop-in for the reference's C operators) translates its tensor / image-batch handles
+ * into these structs and calls the same functions, and so can any foreign-function binding.
+ *
+ * All pointers are device-accessible memory unless stated otherwise. All strides are in bytes.
+ * Every function is asynchronous with respect to `stream`, allocates nothing and returns an NVCVStatus
+ * value (0 = success); the message of the last failure on the calling thread is kept for
+ * b200ppGetLastErrorMessage().
+ */
+#ifndef CVCUDA_B200_PREPROC_H
+#define CVCUDA_B200_PREPROC_H
+
+#include <stdint.h>
+
+#if defined(__cplusplus)
+extern "C"
+{
+#endif
+
+#if !defined(__DRIVER_TYPES_H__) && !defined(__CUDA_RUNTIME_H__)
+typedef struct CUstream_st *cudaStream_t;
+#endif
+
+#define B200PP_PUBLIC __attribute__((visibility("default")))
+
+/* Status codes: numerically identical to NVCVStatus (reference: src/nvcv/src/include/nvcv/Status.h:48-62). */
+enum
+{
+    B200PP_SUCCESS                = 0,
+    B200PP_ERROR_NOT_IMPLEMENTED  = 1,
+    B200PP_ERROR_INVALID_ARGUMENT = 2,
+    B200PP_ERROR_INTERNAL         = 8,
+    B200PP_ERROR_NOT_COMPATIBLE   = 9,
+    B200PP_ERROR_OVERFLOW         = 10
+};
+
+/* Element types. 0..6 are the types the reference's CropFlipNormalizeReformat dispatches on
+ * (src/cvcuda/priv/OpCropFlipNormalizeReformat.cu:335-341,453-458); F16 is an addition, output only. */
+enum
+{
+    B200PP_U8  = 0,
+    B200PP_S8  = 1,
+    B200PP_U16 = 2,
+    B200PP_S16 = 3,
+    B200PP_U32 = 4,
+    B200PP_S32 = 5,
+    B200PP_F32 = 6,
+    B200PP_F16 = 7
+};
+
+/* Interpolation: NVCVInterpolationType values (src/cvcuda/include/cvcuda/Types.h:39-51). */
+enum
+{
+    B200PP_INTERP_NEAREST = 0,
+    B200PP_INTERP_LINEAR  = 1
+};
+
+/* Channel manipulation: NVCVChannelManip (Types.h:63-67). */
+enum
+{
+    B200PP_CHANNEL_NO_OP   = 0,
+    B200PP_CHANNEL_REVERSE = 1
+};
+
+/* Border modes: NVCVBorderType (src/nvcv/src/include/nvcv/BorderType.h:36-43). */
+enum
+{
+    B200PP_BORDER_CONSTANT   = 0,
+    B200PP_BORDER_REPLICATE  = 1,
+    B200PP_BORDER_REFLECT    = 2,
+    B200PP_BORDER_WRAP       = 3,
+    B200PP_BORDER_REFLECT101 = 4
+};
+
+/* Bit 0 of B200ppSliceOp::flags: `scale` holds standard deviations (CVCUDA_NORMALIZE_SCALE_IS_STDDEV,
+ * src/cvcuda/include/cvcuda/OpNormalize.h:43). */
+#define B200PP_NORMALIZE_SCALE_IS_STDDEV 1u
+
+/* One plane of one image; same memory layout as NVCVImagePlaneStrided
+ * (src/nvcv/src/include/nvcv/ImageData.h:27-50). */
+typedef struct B200ppImagePlane
+{
+    int32_t  width, height;
+    int32_t  rowStride;
+    uint8_t *basePtr;
+} B200ppImagePlane;
+
+/* One image of a variable-shape batch; same memory layout as NVCVImageBufferStrided (ImageData.h:52-66), so the
+ * device array an exported NVCVImageBatchVarShape points to can be passed as B200ppSource::imageList unchanged. */
+typedef struct B200ppImageBuffer
+{
+    int32_t          numPlanes;
+    B200ppImagePlane planes[6];
+} B200ppImageBuffer;
+
+/* Source batch: either one dense tensor (imageList == NULL) or a device array of per-image descriptors. */
+typedef struct B200ppSource
+{
+    int32_t dtype;    /* element type */
+    int32_t channels; /* 1..4 */
+    int32_t planar;   /* 0: channels interleaved per pixel; 1: one plane per channel */
+    int32_t numSamples;
+
+    /* dense tensor */
+    const void *base;
+    int64_t     sampleStride, rowStride, planeStride;
+    int32_t     width, height;
+
+    /* variable-shape batch: device array of numSamples descriptors */
+    const B200ppImageBuffer *imageList;
+    int32_t maxWidth, maxHeight; /* upper bounds of the image sizes if known, else 0 (a tuning hint only) */
+} B200ppSource;
+
+/* Destination tensor: element (n, y, x, c) lives at base + n*sampleStride + y*rowStride + x*pixStride + c*chanStride,
+ * which covers NHWC (pixStride = C*elem, chanStride = elem) and NCHW (pixStride = elem, chanStride = plane). */
+typedef struct B200ppDest
+{
+    void   *base;
+    int32_t dtype;
+    int32_t channels;
+    int32_t width, height;
+    int64_t sampleStride, rowStride, pixStride, chanStride;
+} B200ppDest;
+
+/* Resize -> crop -> (flip) -> affine -> channel map -> cast -> layout, in one pass.
+ *
+ * With roi = flipCode = NULL, perChannel = 0 and the region equal to the destination this is exactly the reference's
+ * ResizeCropConvertReformat (kernels src/cvcuda/priv/OpResizeCropConvertReformat.cu:137-278, golden arithmetic
+ * tests/cvcuda/system/TestOpResizeCropConvertReformat.cpp:95-171). The other fields are additions the reference's
+ * operator cannot express in one call. */
+typedef struct B200ppResizeOp
+{
+    int32_t resizeW, resizeH; /* size each source image (or its roi) is resized to */
+    int32_t cropX, cropY;     /* top-left of the crop inside the resized image */
+    int32_t interp;           /* B200PP_INTERP_NEAREST or _LINEAR */
+    int32_t srcCast;          /* round the interpolated value to uint8 before the affine step */
+    int32_t manip;            /* B200PP_CHANNEL_* ; output channel (C-1-c) receives source channel c when reversed */
+
+    int32_t perChannel;       /* 0: out = scale*v + offset          (the reference operator's formula)
+                                 1: out = (v - base[c])*mul[c]*gscale + shift, c = source channel */
+    float   scale, offset;
+    float   base[4], mul[4];
+    float   gscale, shift;
+
+    /* Placement of the cropped region inside the destination (letterbox). regionW/H = 0 means "the whole destination".
+     * Destination pixels outside the region receive padValue pushed through the same affine step. */
+    int32_t dstX, dstY, regionW, regionH;
+    float   padValue;
+
+    /* Optional per-sample device arrays. roi: int32 (x, y, w, h) per sample, roiStride bytes apart (0 = packed): the
+     * sample's source is that sub-view of its image. flipCode: packed int32 per sample, applied to region coordinates
+     * after the resize with the reference's codes (1 mirror x, 0 mirror y, -1 both, anything else none). */
+    const int32_t *roi;
+    int64_t        roiStride;
+    const int32_t *flipCode;
+} B200ppResizeOp;
+
+/* Crop (with border) -> flip -> per-channel normalise -> cast -> layout: the reference's CropFlipNormalizeReformat
+ * (kernel src/cvcuda/priv/OpCropFlipNormalizeReformat.cu:137-186 with :38-116, golden arithmetic
+ * tests/cvcuda/system/TestOpCropFlipNormalizeReformat.cpp:57-148). */
+typedef struct B200ppSliceOp
+{
+    const int32_t *cropRect;       /* device: int32 (x, y, w, h) per sample */
+    int64_t        cropRectStride; /* bytes between samples (0 = packed 16) */
+    const int32_t *flipCode;       /* device: packed int32 per sample */
+    int32_t        border;         /* B200PP_BORDER_* */
+    float          borderValue;
+    const float   *base;  /* device */
+    int32_t        baseChannels;  /* 1, or >= source channels */
+    int64_t        baseChanStride; /* bytes between channel values (0 = packed 4) */
+    const float   *scale; /* device */
+    int32_t        scaleChannels;
+    int64_t        scaleChanStride;
+    float          gscale, shift, epsilon;
+    uint32_t       flags;
+} B200ppSliceOp;
+
+/* Replaces: cvcuda::priv::ResizeCropConvertReformat::operator() (tensor and var-shape),
+ * src/cvcuda/priv/OpResizeCropConvertReformat.cu:418-554 and :556-683, minus the handle unpacking.
+ * Sources must be interleaved 3-channel uint8; destination uint8, float32 or float16. */
+B200PP_PUBLIC int b200ppResizeCropConvertReformat(const B200ppSource *src, const B200ppDest *dst,
+                                                  const B200ppResizeOp *op, cudaStream_t stream);
+
+/* Replaces: cvcuda::priv::CropFlipNormalizeReformat::operator(),
+ * src/cvcuda/priv/OpCropFlipNormalizeReformat.cu:366-468, minus the handle unpacking. */
+B200PP_PUBLIC int b200ppCropFlipNormalizeReformat(const B200ppSource *src, const B200ppDest *dst,
+                                                  const B200ppSliceOp *op, cudaStream_t stream);
+
+/* Message of the last failed call on this thread ("" if none). Mirrors nvcvPeekAtLastStatusMessage
+ * (src/nvcv/src/include/nvcv/Status.h). */
+B200PP_PUBLIC const char *b200ppGetLastErrorMessage(void);
+
+/* Kernel selection for tests and profiling: 0 automatic (default), 1 force the per-pixel gather kernels,
+ * 2 force the staged (bulk-copy pipelined) kernels where they apply. Process-wide. Returns the previous value. */
+B200PP_PUBLIC int b200ppSetKernelPath(int path);
+
+/* Number of kernels this library has launched in this process (all threads). */
+B200PP_PUBLIC uint64_t b200ppGetLaunchCount(void);
+
+/* Reads and clears the device-side error word of the current device (blocking). Non-zero means a kernel gave up
+ * on a bounded wait; bit layout is documented next to the kernels. */
+B200PP_PUBLIC int b200ppReadDeviceError(uint32_t *outError);
+
+#if defined(__cplusplus)
+}
+#endif
+
+#endif /* CVCUDA_B200_PREPROC_H */

@@ -1,0 +1,73 @@
+"""Generates tests/golden/*.npz by running the REFERENCE's own golden functions (oracle/_ref/libref_golden.so,
+compiled from the reference tree by oracle/build_oracle.py) on seeded inputs.
+
+Run where the reference tree is available:  python tests/golden/make_golden.py
+The fixtures pin the C restatement (and through it the CUDA kernels) on machines without the reference tree.
+"""
+import os
+import sys
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.dirname(HERE))
+
+from oracle import build_oracle, oracle as O  # noqa: E402
+import ref_tables as T  # noqa: E402
+
+
+def rccr_cases():
+    """Small seeded cases covering both interpolations, both layouts, both dtypes, swap, rescale and source cast."""
+    rng = np.random.default_rng(1234)
+    specs = [
+        # (w, h, n), resize, interp, out, crop, scale, offset, manip, planar, dtype, cast
+        ((64, 48, 2), (32, 32), 1, (28, 28), (2, 2), 1.0 / 255.0, 0.0, 1, True, np.float32, False),
+        ((64, 48, 2), (32, 32), 1, (28, 28), (2, 2), 1.0, 0.0, 0, True, np.float32, True),
+        ((37, 29, 3), (50, 41), 1, (50, 41), (0, 0), 1 / 127.5, -1.0, 1, False, np.float32, False),
+        ((37, 29, 3), (50, 41), 1, (33, 20), (9, 11), 0.5, 3.0, 0, True, np.uint8, False),
+        ((64, 48, 2), (32, 32), 0, (28, 28), (2, 2), 2.0, -255.0, 1, True, np.float32, False),
+        ((37, 29, 3), (50, 41), 0, (33, 20), (9, 11), -1.0, 255.0, 1, False, np.uint8, True),
+        ((120, 90, 1), (16, 12), 1, (16, 12), (0, 0), 1.0, 0.0, 0, False, np.uint8, True),
+    ]
+    out = {}
+    for i, (s, rs, interp, osz, crop, sc, off, manip, planar, dt, cast) in enumerate(specs):
+        w, h, n = s
+        src = rng.integers(0, 256, (n, h, w, 3), dtype=np.uint8)
+        ref = O.ref_rccr(src, rs, crop, osz, interp, manip, sc, off, cast, dt, planar)
+        out[f"rccr{i}_src"] = src
+        out[f"rccr{i}_ref"] = ref
+        out[f"rccr{i}_par"] = np.array([rs[0], rs[1], interp, osz[0], osz[1], crop[0], crop[1], manip, int(planar),
+                                        int(cast)], np.int32)
+        out[f"rccr{i}_aff"] = np.array([sc, off], np.float32)
+    out["rccr_count"] = np.array(len(specs))
+    return out
+
+
+def cfnr_cases():
+    out = {}
+    k = 0
+    for ri, row in enumerate(T.CFNR_ROWS):
+        small = row._replace(images=2, width=min(row.width, 17), height=min(row.height, 19))
+        images, rects, flips, base, scale, osz = T.cfnr_case(small, seed=100 + ri)
+        for i, im in enumerate(images):
+            ref = O.ref_cfnr(im, small.src_planar, rects[i], int(flips[i]), osz, small.dst_dtype, small.dst_planar,
+                             small.border, 1.0, base, scale, small.gscale, small.gshift, small.eps, small.flags)
+            out[f"cfnr{k}_src"] = im
+            out[f"cfnr{k}_ref"] = ref
+            out[f"cfnr{k}_par"] = np.array([*rects[i], flips[i], osz[0], osz[1], int(small.src_planar),
+                                            int(small.dst_planar), small.border, small.flags], np.int32)
+            out[f"cfnr{k}_f"] = np.array([small.gscale, small.gshift, small.eps], np.float32)
+            out[f"cfnr{k}_base"] = base
+            out[f"cfnr{k}_scale"] = scale
+            k += 1
+    out["cfnr_count"] = np.array(k)
+    return out
+
+
+if __name__ == "__main__":
+    assert build_oracle.build_ref() is not None, "reference tree not available"
+    np.savez_compressed(os.path.join(HERE, "rccr_golden.npz"), **rccr_cases())
+    np.savez_compressed(os.path.join(HERE, "cfnr_golden.npz"), **cfnr_cases())
+    print("written", [f for f in os.listdir(HERE) if f.endswith(".npz")])

@@ -1,0 +1,286 @@
+"""GPU parity: ResizeCropConvertReformat (dense and var-shape) and its fused extensions, against the CPU oracle,
+through the library's C entry points, on both kernel paths (1 = per-pixel gather, 2 = staged bulk-copy pipeline)."""
+import numpy as np
+import pytest
+import torch
+
+import ref_tables as T
+from gpu_util import assert_parity, kernel_path, padded_images, to_dev
+
+pytestmark = pytest.mark.gpu
+
+PATHS = (1, 2)
+MEAN = (123.675, 116.28, 103.53)
+STD = (58.395, 57.12, 57.375)
+INV_STD = tuple(float(np.float32(1.0) / np.float32(s)) for s in STD)
+
+
+def _torch_dtype(dt):
+    return {np.uint8: torch.uint8, np.float32: torch.float32, np.float16: torch.float16}[dt]
+
+
+def _run_dense(pkg, src, r, path):
+    with kernel_path(pkg, path):
+        out = pkg.resize_crop_convert_reformat(
+            to_dev(src), r.resize, r.interp, (*r.crop, *r.out), layout="NCHW" if r.planar else "NHWC",
+            data_type=_torch_dtype(r.dtype), manip=r.manip, scale=r.scale, offset=r.offset, srcCast=r.src_cast)
+        torch.cuda.synchronize()
+    return out.cpu().numpy()
+
+
+@pytest.mark.parametrize("idx", range(len(T.RCCR_ROWS)))
+def test_reference_table_tensor(pkg, oracle, idx):
+    """The reference's 63 tensor test rows, on its ramp input and on seeded uniform bytes."""
+    r = T.RCCR_ROWS[idx]
+    w, h, n = r.src
+    n = min(n, 3)
+    rng = np.random.default_rng(1234 + idx)
+    spec = oracle.ResizeSpec(resize=r.resize, crop=r.crop, out_size=r.out, interp=r.interp, src_cast=r.src_cast,
+                             manip=r.manip, scale=r.scale, offset=r.offset)
+    for name, src in (("ramp", T.ramp_batch(n, h, w)), ("uniform", rng.integers(0, 256, (n, h, w, 3), dtype=np.uint8))):
+        want = oracle.resize_crop(list(src), spec, r.dtype, r.planar, nthreads=8)
+        for path in PATHS:
+            got = _run_dense(pkg, src, r, path)
+            assert_parity(got, want, exact=(r.interp == T.NEAREST), what=f"row {idx} {name} path {path}")
+    assert pkg.read_device_error() == 0
+
+
+@pytest.mark.parametrize("idx", range(0, len(T.RCCR_ROWS), 3))
+def test_reference_table_varshape(pkg, oracle, idx):
+    """Var-shape variant of the reference test: image sizes drawn in [0.8, 1.2] x nominal when interpolating."""
+    r = T.RCCR_ROWS[idx]
+    w, h, n = r.src
+    n = min(n, 4)
+    rng = np.random.default_rng(4321 + idx)
+    images = []
+    for _ in range(n):
+        iw = int(rng.integers(int(w * 0.8), int(w * 1.2) + 1)) if r.interp else w
+        ih = int(rng.integers(int(h * 0.8), int(h * 1.2) + 1)) if r.interp else h
+        images.append(rng.integers(0, 256, (max(ih, 1), max(iw, 1), 3), dtype=np.uint8))
+    spec = oracle.ResizeSpec(resize=r.resize, crop=r.crop, out_size=r.out, interp=r.interp, src_cast=r.src_cast,
+                             manip=r.manip, scale=r.scale, offset=r.offset)
+    want = oracle.resize_crop(images, spec, r.dtype, r.planar, nthreads=8)
+    batch = pkg.ImageBatchVarShape(padded_images(images))
+    for path in PATHS:
+        with kernel_path(pkg, path):
+            out = pkg.resize_crop_convert_reformat(batch, r.resize, r.interp, (*r.crop, *r.out),
+                                                   layout="NCHW" if r.planar else "NHWC",
+                                                   data_type=_torch_dtype(r.dtype), manip=r.manip, scale=r.scale,
+                                                   offset=r.offset, srcCast=r.src_cast)
+            torch.cuda.synchronize()
+        assert_parity(out.cpu().numpy(), want, exact=(r.interp == T.NEAREST), what=f"row {idx} path {path}")
+    assert pkg.read_device_error() == 0
+
+
+@pytest.mark.parametrize("src_cast", [False, True])
+def test_config1_small_dense_batch(pkg, oracle, src_cast):
+    """N=4, 480x640 RGB -> bilinear 256x256 -> centre 224x224 -> BGR -> float32 NCHW, value*(1/255)+0."""
+    rng = np.random.default_rng(1234)
+    src = rng.integers(0, 256, (4, 480, 640, 3), dtype=np.uint8)
+    spec = oracle.ResizeSpec(resize=(256, 256), crop=(16, 16), out_size=(224, 224), interp=1, src_cast=src_cast,
+                             manip=1, scale=1.0 / 255.0, offset=0.0)
+    want = oracle.resize_crop(list(src), spec, np.float32, True, nthreads=8)
+    for path in PATHS:
+        with kernel_path(pkg, path):
+            out = pkg.resize_crop_convert_reformat(to_dev(src), (256, 256), pkg.Interp.LINEAR, (16, 16, 224, 224),
+                                                   layout="NCHW", data_type=torch.float32,
+                                                   manip=pkg.ChannelManip.REVERSE, scale=1.0 / 255.0, srcCast=src_cast)
+            torch.cuda.synchronize()
+        got = out.cpu().numpy()
+        assert got.shape == (4, 3, 224, 224)
+        assert_parity(got, want, what=f"config 1 path {path}")
+        assert np.array_equal(got, want), "expected bit-equality with the golden arithmetic"
+
+
+def test_config2_classification_reduced_batch(pkg, oracle):
+    """1080p -> 256x256 -> 224x224, per-channel mean/std, float32 NCHW (4 images instead of 256)."""
+    rng = np.random.default_rng(1234)
+    src = rng.integers(0, 256, (4, 1080, 1920, 3), dtype=np.uint8)
+    spec = oracle.ResizeSpec(resize=(256, 256), crop=(16, 16), out_size=(224, 224), interp=1, src_cast=False,
+                             base=MEAN, mul=INV_STD)
+    want = oracle.resize_crop(list(src), spec, np.float32, True, nthreads=8)
+    tsrc = to_dev(src)
+    for path in PATHS:
+        out = torch.empty((4, 3, 224, 224), dtype=torch.float32, device="cuda")
+        with kernel_path(pkg, path):
+            pkg.fused_preprocess_into(out, tsrc, resize_dim=(256, 256), interp=1, crop_pos=(16, 16), layout="NCHW",
+                                      base=MEAN, mul=INV_STD, srcCast=False)
+            torch.cuda.synchronize()
+        assert_parity(out.cpu().numpy(), want, what=f"config 2 path {path}")
+
+
+def _random_resized_crop_rects(rng, sizes):
+    """One rectangle per image: 8-100 % of the area, aspect in [3/4, 4/3], ten tries then a centre fallback."""
+    rects = []
+    for w, h in sizes:
+        for _ in range(10):
+            area = rng.uniform(0.08, 1.0) * w * h
+            logr = rng.uniform(np.log(3 / 4), np.log(4 / 3))
+            ar = np.exp(logr)
+            cw, ch = int(round(np.sqrt(area * ar))), int(round(np.sqrt(area / ar)))
+            if 0 < cw <= w and 0 < ch <= h:
+                rects.append((int(rng.integers(0, w - cw + 1)), int(rng.integers(0, h - ch + 1)), cw, ch))
+                break
+        else:
+            s = min(w, h)
+            rects.append(((w - s) // 2, (h - s) // 2, s, s))
+    return np.array(rects, np.int32)
+
+
+def test_config3_varshape_crop_resize_flip_normalize_fp16(pkg, oracle):
+    """Random rectangle -> bilinear 224x224 -> horizontal flip p=0.5 -> mean/std -> float16 NCHW (8 images)."""
+    rng = np.random.default_rng(1234)
+    n = 8
+    sizes = [(int(rng.integers(480, 3841)), int(rng.integers(360, 2161))) for _ in range(n)]
+    images = [rng.integers(0, 256, (h, w, 3), dtype=np.uint8) for w, h in sizes]
+    rects = _random_resized_crop_rects(rng, sizes)
+    flips = np.where(rng.random(n) < 0.5, 1, 2).astype(np.int32)
+    flips[0], flips[1] = 1, 2
+    spec = oracle.ResizeSpec(resize=(224, 224), out_size=(224, 224), interp=1, src_cast=True, base=MEAN, mul=INV_STD)
+    want = oracle.resize_crop(images, spec, np.float16, True, roi=rects, flip=flips, nthreads=8)
+    batch = pkg.ImageBatchVarShape(padded_images(images))
+    for path in PATHS:
+        out = torch.empty((n, 3, 224, 224), dtype=torch.float16, device="cuda")
+        with kernel_path(pkg, path):
+            pkg.fused_preprocess_into(out, batch, resize_dim=(224, 224), interp=1, layout="NCHW", base=MEAN,
+                                      mul=INV_STD, srcCast=True, roi=to_dev(rects), flip_code=to_dev(flips))
+            torch.cuda.synchronize()
+        assert_parity(out.cpu().numpy(), want, what=f"config 3 path {path}")
+    assert pkg.read_device_error() == 0
+
+
+def test_config4_letterbox(pkg, oracle):
+    """1080p -> 640x360 placed at rows 140..499 of a 640x640 canvas padded with 114, BGR, x/255, float32 NCHW."""
+    rng = np.random.default_rng(1234)
+    src = rng.integers(0, 256, (2, 1080, 1920, 3), dtype=np.uint8)
+    spec = oracle.ResizeSpec(resize=(640, 360), out_size=(640, 360), interp=1, src_cast=True, manip=1,
+                             scale=1.0 / 255.0, canvas=(640, 640), dst_pos=(0, 140), pad_value=114.0)
+    want = oracle.resize_crop(list(src), spec, np.float32, True, nthreads=8)
+    tsrc = to_dev(src)
+    for path in PATHS:
+        out = torch.full((2, 3, 640, 640), -1.0, dtype=torch.float32, device="cuda")
+        with kernel_path(pkg, path):
+            pkg.fused_preprocess_into(out, tsrc, resize_dim=(640, 360), interp=1, layout="NCHW", manip=1,
+                                      scale=1.0 / 255.0, srcCast=True, dst_pos=(0, 140), region_size=(640, 360),
+                                      pad_value=114.0)
+            torch.cuda.synchronize()
+        got = out.cpu().numpy()
+        assert_parity(got, want, what=f"config 4 path {path}")
+        assert np.all(got[:, :, :140, :] == np.float32(114.0) * np.float32(1.0 / 255.0))
+
+
+@pytest.mark.parametrize("interp", [0, 1])
+def test_config5_4k_to_448_fp16(pkg, oracle, interp):
+    """4K -> 512x512 -> centre 448x448, mean/std, float16 NCHW, nearest and linear (2 images per GPU here)."""
+    rng = np.random.default_rng(1234)
+    src = rng.integers(0, 256, (2, 2160, 3840, 3), dtype=np.uint8)
+    spec = oracle.ResizeSpec(resize=(512, 512), crop=(32, 32), out_size=(448, 448), interp=interp, src_cast=False,
+                             base=MEAN, mul=INV_STD)
+    want = oracle.resize_crop(list(src), spec, np.float16, True, nthreads=8)
+    tsrc = to_dev(src)
+    for path in PATHS:
+        out = torch.empty((2, 3, 448, 448), dtype=torch.float16, device="cuda")
+        with kernel_path(pkg, path):
+            pkg.fused_preprocess_into(out, tsrc, resize_dim=(512, 512), interp=interp, crop_pos=(32, 32), layout="NCHW",
+                                      base=MEAN, mul=INV_STD, srcCast=False)
+            torch.cuda.synchronize()
+        assert_parity(out.cpu().numpy(), want, exact=(interp == 0), what=f"config 5 interp {interp} path {path}")
+
+
+@pytest.mark.parametrize("offset,pad", [(0, 32), (1, 32), (16, 16), (0, 1), (3, 1)])
+@pytest.mark.parametrize("interp", [0, 1])
+def test_alignment_and_pitch_variants(pkg, oracle, offset, pad, interp):
+    """Unaligned base pointers and unpadded odd pitches make the staged kernel read straight from global memory."""
+    rng = np.random.default_rng(99 + offset + pad)
+    images = [rng.integers(0, 256, (h, w, 3), dtype=np.uint8) for w, h in ((101, 77), (333, 45), (64, 64))]
+    spec = oracle.ResizeSpec(resize=(80, 60), crop=(3, 2), out_size=(70, 50), interp=interp, src_cast=False, manip=1,
+                             scale=0.25, offset=-3.0)
+    want = oracle.resize_crop(images, spec, np.float32, True)
+    batch = pkg.ImageBatchVarShape(padded_images(images, pad_to=pad, offset=offset))
+    for path in PATHS:
+        with kernel_path(pkg, path):
+            out = pkg.resize_crop_convert_reformat(batch, (80, 60), interp, (3, 2, 70, 50), layout="NCHW",
+                                                   data_type=torch.float32, manip=1, scale=0.25, offset=-3.0,
+                                                   srcCast=False)
+            torch.cuda.synchronize()
+        assert_parity(out.cpu().numpy(), want, exact=(interp == 0), what=f"offset {offset} pad {pad} path {path}")
+    assert pkg.read_device_error() == 0
+
+
+@pytest.mark.parametrize("case", [
+    # (src w, h), resize, crop, out
+    ((1, 1), (2, 2), (0, 0), (2, 2)),
+    ((2, 1), (5, 3), (1, 0), (4, 3)),
+    ((1, 7), (3, 9), (0, 2), (3, 5)),
+    ((500, 3), (40, 2), (0, 0), (40, 2)),
+    ((4000, 16), (33, 8), (0, 0), (33, 8)),   # 121x horizontal reduction: taps skip whole sectors
+    ((16, 4000), (8, 35), (1, 1), (7, 33)),
+    ((70, 50), (700, 500), (100, 100), (517, 311)),  # 10x enlargement: consecutive rows share source rows
+    ((9000, 8), (3000, 8), (0, 0), (3000, 8)),  # wide rows: the destination row is split into chunks
+])
+@pytest.mark.parametrize("interp", [0, 1])
+def test_shape_edge_cases(pkg, oracle, case, interp):
+    (w, h), rs, crop, osz = case
+    rng = np.random.default_rng(w * 31 + h)
+    src = rng.integers(0, 256, (2, h, w, 3), dtype=np.uint8)
+    for dt, planar in ((np.float32, True), (np.uint8, False), (np.uint8, True), (np.float32, False)):
+        spec = oracle.ResizeSpec(resize=rs, crop=crop, out_size=osz, interp=interp, src_cast=False, scale=0.5, offset=1.0)
+        want = oracle.resize_crop(list(src), spec, dt, planar)
+        for path in PATHS:
+            with kernel_path(pkg, path):
+                out = pkg.resize_crop_convert_reformat(to_dev(src), rs, interp, (*crop, *osz),
+                                                       layout="NCHW" if planar else "NHWC", data_type=_torch_dtype(dt),
+                                                       scale=0.5, offset=1.0, srcCast=False)
+                torch.cuda.synchronize()
+            assert_parity(out.cpu().numpy(), want, exact=(interp == 0), what=f"{case} {dt.__name__} path {path}")
+    assert pkg.read_device_error() == 0
+
+
+def test_hwc_rank3_tensors_and_strided_output(pkg, oracle):
+    """A single HWC image in, CHW out; and writing into a sub-view of a larger output tensor (true strides)."""
+    rng = np.random.default_rng(11)
+    src = rng.integers(0, 256, (1, 90, 120, 3), dtype=np.uint8)
+    spec = oracle.ResizeSpec(resize=(60, 45), crop=(5, 5), out_size=(48, 36), interp=1, src_cast=True, scale=2.0)
+    want = oracle.resize_crop(list(src), spec, np.float32, True)
+    out = pkg.resize_crop_convert_reformat(to_dev(src[0]), (60, 45), 1, (5, 5, 48, 36), layout="CHW",
+                                           data_type=torch.float32, scale=2.0)
+    assert out.shape == (3, 36, 48)
+    assert_parity(out.cpu().numpy()[None], want, what="rank-3")
+    big = torch.zeros((1, 3, 50, 64), dtype=torch.float32, device="cuda")
+    view = big[:, :, 7:43, 8:56]
+    pkg.resize_crop_convert_reformat_into(view, to_dev(src), (60, 45), 1, (5, 5), layout="NCHW", scale=2.0)
+    torch.cuda.synchronize()
+    assert_parity(view.cpu().numpy(), want, what="strided output")
+    assert float(big.sum()) == pytest.approx(float(view.sum()))  # nothing written outside the view
+
+
+def test_empty_batch_is_a_noop(pkg):
+    src = torch.empty((0, 32, 32, 3), dtype=torch.uint8, device="cuda")
+    before = pkg.launch_count()
+    out = pkg.resize_crop_convert_reformat(src, (16, 16), 1, (0, 0, 16, 16), layout="NCHW", data_type=torch.float32)
+    assert out.shape == (0, 3, 16, 16) and pkg.launch_count() == before
+
+
+@pytest.mark.parametrize("idx", range(len(T.RCCR_NEGATIVE_ROWS)))
+@pytest.mark.parametrize("varshape", [False, True])
+def test_negative_rows_return_the_reference_status(pkg, idx, varshape):
+    """The reference's negative tests: same NVCVStatus code for the same bad argument, and nothing is launched."""
+    r = T.RCCR_NEGATIVE_ROWS[idx]
+    tdt = {"u8": torch.uint8, "f32": torch.float32, "f16": torch.float16}
+    if varshape:
+        if r.src_planar:
+            src = pkg.ImageBatchVarShape([torch.zeros((r.src_channels, 32, 32), dtype=tdt[r.src_dtype], device="cuda")
+                                          for _ in range(r.n_in)], planar=True)
+        else:
+            src = pkg.ImageBatchVarShape([torch.zeros((32, 32, r.src_channels), dtype=tdt[r.src_dtype], device="cuda")
+                                          for _ in range(r.n_in)])
+    else:
+        if r.src_planar:
+            pytest.skip("a planar source tensor is expressed by its layout string, which torch tensors do not carry")
+        src = torch.zeros((r.n_in, 32, 32, r.src_channels), dtype=tdt[r.src_dtype], device="cuda")
+    dst = torch.zeros((r.n_out, r.out[1], r.out[0], r.dst_channels), dtype=tdt[r.dst_dtype], device="cuda")
+    before = pkg.launch_count()
+    with pytest.raises(pkg.ops.Error) as e:
+        pkg.resize_crop_convert_reformat_into(dst, src, r.resize, r.interp, r.crop, layout="NHWC")
+    assert pkg.ops.Status(e.value.status).name == r.status, e.value.message
+    assert pkg.launch_count() == before
