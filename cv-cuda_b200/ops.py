@@ -216,8 +216,8 @@ class ImageBatchVarShape:
         if isinstance(images, torch.Tensor):
             images = [images]
         for im in images:
-            if im.dim() != 3 or not im.is_cuda:
-                raise Error(Status.ERROR_INVALID_ARGUMENT, "Images must be 3-D CUDA tensors")
+            if im.dim() != 3 or not (im.is_cuda or im.is_pinned()):
+                raise Error(Status.ERROR_INVALID_ARGUMENT, "Images must be 3-D CUDA (or page-locked host) tensors")
             if im.stride(2) != 1 or (not self.planar and im.stride(1) != im.shape[2]):
                 raise Error(Status.ERROR_INVALID_ARGUMENT, "Image pixels must be contiguous within a row")
             if self._images and (im.dtype != self._images[0].dtype or self._channels(im) != self.channels):
@@ -245,7 +245,8 @@ class ImageBatchVarShape:
 
     @property
     def device(self) -> torch.device:
-        return self._images[0].device
+        d = self._images[0].device
+        return d if d.type == "cuda" else torch.device("cuda", torch.cuda.current_device())
 
     def size(self, i: int) -> Tuple[int, int]:
         im = self._images[i]
@@ -276,6 +277,11 @@ class ImageBatchVarShape:
         return self._table
 
 
+def _device_accessible(t: torch.Tensor) -> bool:
+    """CUDA memory, or page-locked host memory (which the GPU addresses directly under unified addressing)."""
+    return t.is_cuda or t.is_pinned()
+
+
 def _source_of(src: Union[torch.Tensor, ImageBatchVarShape]):
     """Returns (struct, keepalive)."""
     s = _Source()
@@ -288,7 +294,7 @@ def _source_of(src: Union[torch.Tensor, ImageBatchVarShape]):
         s.imageList = table.data_ptr()
         s.maxWidth, s.maxHeight = src.max_size
         return s, table
-    if not src.is_cuda:
+    if not _device_accessible(src):
         raise Error(Status.ERROR_INVALID_ARGUMENT, "Input must be a cuda-accessible, pitch-linear tensor")
     t = src if src.dim() == 4 else src.unsqueeze(0)
     if t.dim() != 4:
@@ -307,7 +313,7 @@ def _source_of(src: Union[torch.Tensor, ImageBatchVarShape]):
 
 def _dest_of(dst: torch.Tensor, layout: str):
     """layout: 'NHWC', 'HWC', 'NCHW' or 'CHW'. Returns (struct, samples)."""
-    if not dst.is_cuda:
+    if not _device_accessible(dst):
         raise Error(Status.ERROR_INVALID_ARGUMENT, "Output must be a cuda-accessible, pitch-linear tensor")
     if layout not in ("NHWC", "HWC", "NCHW", "CHW"):
         raise Error(Status.ERROR_NOT_COMPATIBLE,
@@ -425,7 +431,8 @@ def resize_crop_convert_reformat(src: Union[torch.Tensor, ImageBatchVarShape], r
             raise Error(Status.ERROR_INVALID_IMAGE_FORMAT, "Input tensor must have layout 'HWC' or 'NHWC'.")
         rank4 = src.dim() == 4
         n = src.shape[0] if rank4 else 1
-        c, dev, in_dtype = src.shape[-1], src.device, src.dtype
+        c, in_dtype = src.shape[-1], src.dtype
+        dev = src.device if src.is_cuda else torch.device("cuda", torch.cuda.current_device())
         out_layout = layout or ("NHWC" if rank4 else "HWC")
         if len(out_layout) != src.dim():
             raise Error(Status.ERROR_INVALID_IMAGE_FORMAT, "Output tensor rank must match input tensor rank.")

@@ -1,0 +1,65 @@
+"""A small, self-ending run of one kernel, sized for an `ncu` capture.
+
+    python cv-cuda_b200/profile_case.py [--case classify|4k|letterbox] [--images 32] [--path 0|1|2] [--launches 5]
+
+`classify` is the 1080p -> 256x256 -> 224x224 float32 NCHW case of bench.py at a reduced batch: 32 images are
+199 MB of source, larger than the 126 MB L2, so DRAM counters still mean something, while the whole run holds well
+under 1 GB on the device. Prints the device time per launch measured with CUDA events (never quote that figure from
+a run under a profiler).
+"""
+import argparse
+import os
+import sys
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+import __graft_entry__ as ge  # noqa: E402
+
+MEAN = (123.675, 116.28, 103.53)
+INV_STD = tuple(float(np.float32(1.0) / np.float32(s)) for s in (58.395, 57.12, 57.375))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--case", default="classify", choices=("classify", "4k", "4k-nearest", "letterbox"))
+    ap.add_argument("--images", type=int, default=32)
+    ap.add_argument("--path", type=int, default=0)
+    ap.add_argument("--launches", type=int, default=5)
+    a = ap.parse_args()
+    pkg = ge.load_package()
+    pkg.set_kernel_path(a.path)
+    g = torch.Generator(device="cuda")
+    g.manual_seed(1234)
+    n = a.images
+    if a.case == "classify":
+        src = torch.randint(0, 256, (n, 1080, 1920, 3), dtype=torch.uint8, device="cuda", generator=g)
+        out = torch.empty((n, 3, 224, 224), dtype=torch.float32, device="cuda")
+        kw = dict(resize_dim=(256, 256), interp=1, crop_pos=(16, 16), layout="NCHW", base=MEAN, mul=INV_STD, srcCast=False)
+    elif a.case in ("4k", "4k-nearest"):
+        src = torch.randint(0, 256, (n, 2160, 3840, 3), dtype=torch.uint8, device="cuda", generator=g)
+        out = torch.empty((n, 3, 448, 448), dtype=torch.float16, device="cuda")
+        kw = dict(resize_dim=(512, 512), interp=int(a.case == "4k"), crop_pos=(32, 32), layout="NCHW", base=MEAN,
+                  mul=INV_STD, srcCast=False)
+    else:
+        src = torch.randint(0, 256, (n, 1080, 1920, 3), dtype=torch.uint8, device="cuda", generator=g)
+        out = torch.empty((n, 3, 640, 640), dtype=torch.float32, device="cuda")
+        kw = dict(resize_dim=(640, 360), interp=1, layout="NCHW", manip=1, scale=1.0 / 255.0, srcCast=True,
+                  dst_pos=(0, 140), region_size=(640, 360), pad_value=114.0)
+    for _ in range(3):
+        pkg.fused_preprocess_into(out, src, **kw)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(a.launches):
+        pkg.fused_preprocess_into(out, src, **kw)
+    e1.record()
+    torch.cuda.synchronize()
+    print(f"case {a.case} images {n} path {a.path}: {e0.elapsed_time(e1) / a.launches * 1000:.1f} us per launch, "
+          f"device error {pkg.read_device_error()}")
+
+
+if __name__ == "__main__":
+    main()
