@@ -34,7 +34,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     cmd = [
         NVCC, "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
         # the goldens are defined by un-fused float arithmetic: never contract a*b+c into an FMA
-        "--fmad=false",
+        "--fmad=false", "--ftz=false", "--prec-div=true", "--prec-sqrt=true",
         "-Xcompiler", "-fPIC,-fvisibility=hidden,-Wall", "-shared",
         "-I" + os.path.join(ROOT, "include"), "-I" + CSRC,
         "-o", LIB, *srcs, "-ldl",

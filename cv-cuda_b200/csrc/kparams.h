@@ -56,6 +56,7 @@ struct StagedCfg
     int       chunkCols;    // destination columns per work unit
     int       chunksPerRow;
     long long totalUnits;   // numSamples * dstH * chunksPerRow
+    long long blockUnits;   // consecutive units dealt to a CTA at a time
 };
 
 // Arguments of the crop/flip/normalise kernel.

@@ -23,42 +23,94 @@ namespace b200pp {
 // for a free ring slot, 4 = the producer gave up draining its copies at exit.
 __device__ unsigned int g_deviceError;
 
-constexpr int kProducerThreads = 32;
-constexpr unsigned long long kWaitLimitNs = 2000000000ull; // 2 s
+constexpr int                kProducerThreads = 32;
+constexpr unsigned long long kWaitLimitNs     = 2000000000ull; // 2 s
 
 // ------------------------------------------------------------------------------------------------ pixel maths
+//
+// Integer <-> float conversion instructions run at a fraction of the FP32 rate and the straightforward kernel would
+// issue fifteen of them per pixel. None is needed:
+//
+//  * A source byte b is loaded zero-extended and its bit pattern is used AS a float: the denormal b * 2^-149. The
+//    vertical weights are pre-multiplied by 2^127 and the horizontal ones by 2^22 (exact, once per row / per column).
+//    (b*2^-149) * (wy*2^127) is the normal number (b*wy) * 2^-22 with exactly the mantissa rounding of the golden's
+//    b*wy, and multiplying by wx*2^22 gives exactly the golden's (b*wy)*wx. Denormal operands run at full rate.
+//  * Round-half-even + clamp to [0, 255] (the uint8 saturate cast) is clamp, then add and subtract 1.5 * 2^23.
 
-// One destination pixel of the linear path. r0/r1 point at byte 0 of the two tapped source rows in whatever
-// memory they are staged in; o0/o1 are the byte offsets of the left/right tap pixel.
-template<int DK>
-__device__ __forceinline__ void linear_pixel(const ResizeKParams &p, const uint8_t *r0, const uint8_t *r1, int o0,
-                                             int o1, float wx1, float wy1, uint8_t *dstPix)
+constexpr float kTwo127 = 1.7014118346046923e38f; // 2^127
+constexpr float kTwo22  = 4194304.0f;             // 2^22
+constexpr float kRound  = 12582912.0f;            // 1.5 * 2^23
+
+__device__ __forceinline__ float raw_byte(const uint8_t *p)
 {
-    const float wx0 = __fsub_rn(1.0f, wx1);
-    const float wy0 = __fsub_rn(1.0f, wy1);
+    return __uint_as_float(static_cast<unsigned>(*p));
+}
+
+// float(SaturateCast<uint8_t>(v)) for finite v
+__device__ __forceinline__ float round_sat_u8(float v)
+{
+    v = fminf(fmaxf(v, 0.0f), 255.0f);
+    return __fsub_rn(__fadd_rn(v, kRound), kRound);
+}
+
+// Byte offsets of the three destination channels of a pixel (channel map applied).
+struct ChanOff
+{
+    long long c[3];
+};
+
+__device__ __forceinline__ ChanOff chan_offsets(const ResizeKParams &p)
+{
+    ChanOff o;
+#pragma unroll
+    for (int c = 0; c < 3; ++c) o.c[c] = p.mapC[c] * p.dChan;
+    return o;
+}
+
+// Affine step + cast + store of source channel c.
+template<int DK>
+__device__ __forceinline__ void emit(const ResizeKParams &p, int c, float v, uint8_t *dst)
+{
+    v = affine(p, c, v);
+    if constexpr (DK == DST_U8)
+        *dst = static_cast<uint8_t>(__float_as_uint(__fadd_rn(fminf(fmaxf(v, 0.0f), 255.0f), kRound)));
+    else
+        store_elem<DK>(dst, v);
+}
+
+// One destination pixel of the linear path. r0/r1 point at byte 0 of the two tapped source rows in whatever memory
+// they live in; o0/o1 are the byte offsets of the left/right tap pixel. Weights are pre-scaled:
+// wy*s = wy * 2^127, wx*s = wx * 2^22.
+template<int DK>
+__device__ __forceinline__ void linear_pixel(const ResizeKParams &p, const ChanOff &co, const uint8_t *r0,
+                                             const uint8_t *r1, int o0, int o1, float wx0s, float wx1s, float wy0s,
+                                             float wy1s, uint8_t *dstPix)
+{
 #pragma unroll
     for (int c = 0; c < 3; ++c)
     {
-        float v = blend4(static_cast<float>(r0[o0 + c]), static_cast<float>(r0[o1 + c]),
-                         static_cast<float>(r1[o0 + c]), static_cast<float>(r1[o1 + c]), wx0, wx1, wy0, wy1);
+        float v = blend4(raw_byte(r0 + o0 + c), raw_byte(r0 + o1 + c), raw_byte(r1 + o0 + c), raw_byte(r1 + o1 + c), wx0s,
+                         wx1s, wy0s, wy1s);
         if (p.srcCast)
-            v = static_cast<float>(sat_u8(v));
-        store_elem<DK>(dstPix + p.mapC[c] * p.dChan, affine(p, c, v));
+            v = round_sat_u8(v);
+        emit<DK>(p, c, v, dstPix + co.c[c]);
     }
 }
 
 template<int DK>
-__device__ __forceinline__ void nearest_pixel(const ResizeKParams &p, const uint8_t *r0, int o0, uint8_t *dstPix)
+__device__ __forceinline__ void nearest_pixel(const ResizeKParams &p, const ChanOff &co, const uint8_t *r0, int o0,
+                                              uint8_t *dstPix)
 {
 #pragma unroll
-    for (int c = 0; c < 3; ++c) store_elem<DK>(dstPix + p.mapC[c] * p.dChan, affine(p, c, static_cast<float>(r0[o0 + c])));
+    for (int c = 0; c < 3; ++c)
+        emit<DK>(p, c, __fmul_rn(__fmul_rn(raw_byte(r0 + o0 + c), kTwo127), kTwo22), dstPix + co.c[c]);
 }
 
 template<int DK>
-__device__ __forceinline__ void pad_pixel(const ResizeKParams &p, uint8_t *dstPix)
+__device__ __forceinline__ void pad_pixel(const ResizeKParams &p, const ChanOff &co, uint8_t *dstPix)
 {
 #pragma unroll
-    for (int c = 0; c < 3; ++c) store_elem<DK>(dstPix + p.mapC[c] * p.dChan, affine(p, c, p.padValue));
+    for (int c = 0; c < 3; ++c) emit<DK>(p, c, p.padValue, dstPix + co.c[c]);
 }
 
 // ------------------------------------------------------------------------------------------------ gather kernel
@@ -70,14 +122,15 @@ __global__ void __launch_bounds__(256) resize_gather_kernel(const ResizeKParams 
     const int y = blockIdx.y * blockDim.y + threadIdx.y;
     if (x >= p.dstW || y >= p.dstH)
         return;
+    const ChanOff co = chan_offsets(p);
 
     for (int n = blockIdx.z; n < p.numSamples; n += gridDim.z)
     {
-        uint8_t *dstPix = p.dst + n * p.dSample + y * p.dRow + x * p.dPix;
+        uint8_t  *dstPix = p.dst + n * p.dSample + y * p.dRow + x * p.dPix;
         const int rx = x - p.dstX, ry = y - p.dstY;
         if (rx < 0 || ry < 0 || rx >= p.regionW || ry >= p.regionH)
         {
-            pad_pixel<DK>(p, dstPix);
+            pad_pixel<DK>(p, co, dstPix);
             continue;
         }
         const Geom g  = load_geom(p, n);
@@ -88,7 +141,7 @@ __global__ void __launch_bounds__(256) resize_gather_kernel(const ResizeKParams 
         {
             const int sx = nearest_tap(g.scaleW, dx, g.w);
             const int sy = nearest_tap(g.scaleH, dy, g.h);
-            nearest_pixel<DK>(p, g.base + sy * g.pitch, 3 * sx, dstPix);
+            nearest_pixel<DK>(p, co, g.base + sy * g.pitch, 3 * sx, dstPix);
         }
         else
         {
@@ -96,7 +149,9 @@ __global__ void __launch_bounds__(256) resize_gather_kernel(const ResizeKParams 
             float wx1, wy1;
             linear_tap(g.scaleW, dx, g.w, sx0, sx1, wx1);
             linear_tap(g.scaleH, dy, g.h, sy0, sy1, wy1);
-            linear_pixel<DK>(p, g.base + sy0 * g.pitch, g.base + sy1 * g.pitch, 3 * sx0, 3 * sx1, wx1, wy1, dstPix);
+            linear_pixel<DK>(p, co, g.base + sy0 * g.pitch, g.base + sy1 * g.pitch, 3 * sx0, 3 * sx1,
+                             __fmul_rn(__fsub_rn(1.0f, wx1), kTwo22), __fmul_rn(wx1, kTwo22),
+                             __fmul_rn(__fsub_rn(1.0f, wy1), kTwo127), __fmul_rn(wy1, kTwo127), dstPix);
         }
     }
 }
@@ -174,54 +229,137 @@ __device__ __forceinline__ void bulk_load(void *smemDst, const void *gmemSrc, un
 // What the producer tells the consumers about the unit staged in one ring slot.
 struct UnitInfo
 {
-    int            mode; // 0: nothing to sample (row outside the region); 1: rows staged in shared memory; 2: read global
-    int            y, x0, x1;
+    int            mode; // UNIT_*
+    int            x0, x1;
     int            flipX;
     int            srcW;
     int            segOrigin; // source-row byte offset that shared-memory offset 0 of the slot corresponds to
     int            sameRow;   // linear: both taps come from one source row
     float          scaleW;
-    float          wy1;
+    float          wy0s, wy1s; // vertical weights * 2^127
     long long      dstRowOff;
+    long long      tapKey; // units with equal keys have identical column taps (same sample geometry, chunk and flip)
     const uint8_t *g0, *g1; // tapped source rows in global memory (byte 0 of the row of the sub-view)
 };
 
 enum
 {
-    UNIT_PAD    = 0,
-    UNIT_STAGED = 1,
-    UNIT_DIRECT = 2
+    UNIT_PAD    = 0, // nothing to sample: the row lies outside the placed region
+    UNIT_STAGED = 1, // rows are in the shared-memory slot
+    UNIT_DIRECT = 2  // read the rows from global memory (unaligned image, or a segment larger than a slot)
 };
 
-// Columns [x0, x1) of one destination row, strided over the consumer threads so that a warp writes 32 adjacent pixels.
-template<int INTERP, int DK>
-__device__ __forceinline__ void consume_columns(const ResizeKParams &p, const UnitInfo &info, const uint8_t *r0,
-                                                const uint8_t *r1, int origin, uint8_t *dstRow, int ct,
-                                                int consumerThreads)
+// Horizontal taps of one destination column: byte offsets of the left/right source pixel within the source row
+// (o0 < 0 marks a column outside the placed region), the weights * 2^22 and the column's destination byte offset.
+struct ColTap
 {
-    for (int x = info.x0 + ct; x < info.x1; x += consumerThreads)
+    int       o0, o1;
+    float     wx0s, wx1s;
+    long long dstOff;
+};
+
+template<int INTERP>
+__device__ __forceinline__ ColTap make_tap(const ResizeKParams &p, const UnitInfo &info, int x)
+{
+    ColTap t;
+    t.dstOff     = x * p.dPix;
+    t.wx0s       = 0.f;
+    t.wx1s       = 0.f;
+    const int rx = x - p.dstX;
+    if (rx < 0 || rx >= p.regionW)
     {
-        uint8_t  *dstPix = dstRow + x * p.dPix;
-        const int rx     = x - p.dstX;
-        if (rx < 0 || rx >= p.regionW)
+        t.o0 = t.o1 = -1;
+        return t;
+    }
+    const int dx = (info.flipX ? p.regionW - 1 - rx : rx) + p.cropX;
+    if constexpr (INTERP == B200PP_INTERP_NEAREST)
+    {
+        t.o0 = t.o1 = 3 * nearest_tap(info.scaleW, dx, info.srcW);
+    }
+    else
+    {
+        int   s0, s1;
+        float wx1;
+        linear_tap(info.scaleW, dx, info.srcW, s0, s1, wx1);
+        t.o0   = 3 * s0;
+        t.o1   = 3 * s1;
+        t.wx0s = __fmul_rn(__fsub_rn(1.0f, wx1), kTwo22);
+        t.wx1s = __fmul_rn(wx1, kTwo22);
+    }
+    return t;
+}
+
+// One destination pixel from rows r0/r1 whose first byte is source-row byte `origin`.
+template<int INTERP, int DK>
+__device__ __forceinline__ void consume_pixel(const ResizeKParams &p, const ChanOff &co, const UnitInfo &info,
+                                              const ColTap &t, const uint8_t *r0, const uint8_t *r1, int origin,
+                                              uint8_t *dstRow)
+{
+    uint8_t *dstPix = dstRow + t.dstOff;
+    if (t.o0 < 0)
+        pad_pixel<DK>(p, co, dstPix);
+    else if constexpr (INTERP == B200PP_INTERP_NEAREST)
+        nearest_pixel<DK>(p, co, r0, t.o0 - origin, dstPix);
+    else
+        linear_pixel<DK>(p, co, r0, r1, t.o0 - origin, t.o1 - origin, t.wx0s, t.wx1s, info.wy0s, info.wy1s, dstPix);
+}
+
+constexpr int kCachedCols = 2;
+
+// Columns [x0, x1) of one destination row, strided over the consumer threads so that a warp writes 32 adjacent pixels.
+// The taps of a thread's first kCachedCols columns stay in registers while consecutive units share a tap key, which
+// for a dense batch is the whole launch.
+template<int INTERP, int DK>
+__device__ __forceinline__ void consume_columns(const ResizeKParams &p, const ChanOff &co, const UnitInfo &info,
+                                                const uint8_t *r0, const uint8_t *r1, int origin, uint8_t *dstRow,
+                                                int ct, int consumerThreads, ColTap (&cache)[kCachedCols], bool refresh)
+{
+#pragma unroll
+    for (int k = 0; k < kCachedCols; ++k)
+    {
+        const int x = info.x0 + ct + k * consumerThreads;
+        if (x < info.x1)
         {
-            pad_pixel<DK>(p, dstPix);
-            continue;
-        }
-        const int dx = (info.flipX ? p.regionW - 1 - rx : rx) + p.cropX;
-        if constexpr (INTERP == B200PP_INTERP_NEAREST)
-        {
-            nearest_pixel<DK>(p, r0, 3 * nearest_tap(info.scaleW, dx, info.srcW) - origin, dstPix);
-        }
-        else
-        {
-            int   sx0, sx1;
-            float wx1;
-            linear_tap(info.scaleW, dx, info.srcW, sx0, sx1, wx1);
-            linear_pixel<DK>(p, r0, r1, 3 * sx0 - origin, 3 * sx1 - origin, wx1, info.wy1, dstPix);
+            if (refresh)
+                cache[k] = make_tap<INTERP>(p, info, x);
+            consume_pixel<INTERP, DK>(p, co, info, cache[k], r0, r1, origin, dstRow);
         }
     }
+    for (int x = info.x0 + ct + kCachedCols * consumerThreads; x < info.x1; x += consumerThreads)
+    {
+        const ColTap t = make_tap<INTERP>(p, info, x);
+        consume_pixel<INTERP, DK>(p, co, info, t, r0, r1, origin, dstRow);
+    }
 }
+
+// Units are dealt to CTAs in blocks of cfg.blockUnits consecutive units, round-robin over the CTAs.
+// Block size 1 keeps all CTAs on neighbouring destination rows (dense batches); a large block keeps a CTA inside one
+// sample so that per-sample column taps stay cached (variable-shape batches).
+struct UnitWalk
+{
+    long long blockUnits, stride; // stride = gridDim.x * blockUnits
+    long long first;              // first unit of this CTA
+    long long count;              // units this CTA processes
+
+    __device__ __forceinline__ UnitWalk(const StagedCfg &cfg)
+    {
+        blockUnits = cfg.blockUnits;
+        stride     = static_cast<long long>(gridDim.x) * blockUnits;
+        first      = static_cast<long long>(blockIdx.x) * blockUnits;
+        const long long blocks = (cfg.totalUnits + blockUnits - 1) / blockUnits;
+        const long long mine   = blockIdx.x < blocks ? (blocks - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+        count                  = mine * blockUnits;
+        if (mine > 0 && (blocks - 1) % gridDim.x == blockIdx.x)
+            count -= blocks * blockUnits - cfg.totalUnits; // the last block of the launch may be short
+    }
+
+    // global index of this CTA's k-th unit
+    __device__ __forceinline__ long long unit(long long k) const
+    {
+        const long long j = k / blockUnits;
+        return first + j * stride + (k - j * blockUnits);
+    }
+};
 
 template<int INTERP, int DK>
 __global__ void __launch_bounds__(512) resize_staged_kernel(const ResizeKParams p, const StagedCfg cfg)
@@ -237,6 +375,7 @@ __global__ void __launch_bounds__(512) resize_staged_kernel(const ResizeKParams 
 
     const int consumerThreads = blockDim.x - kProducerThreads;
     const int consumerWarps   = consumerThreads / 32;
+    const int lane            = threadIdx.x & 31;
 
     if (threadIdx.x == 0)
     {
@@ -250,108 +389,145 @@ __global__ void __launch_bounds__(512) resize_staged_kernel(const ResizeKParams 
     }
     __syncthreads();
 
-    // contiguous range of units per CTA: a CTA mostly stays inside one sample
-    const long long uBegin = cfg.totalUnits * blockIdx.x / gridDim.x;
-    const long long uEnd   = cfg.totalUnits * (blockIdx.x + 1) / gridDim.x;
-    const long long unitsPerSample = static_cast<long long>(p.dstH) * cfg.chunksPerRow;
+    const UnitWalk walk(cfg);
 
     if (threadIdx.x < kProducerThreads)
     {
-        // ===================================================================== producer (one thread)
-        if (threadIdx.x != 0)
-            return;
-        int       cachedN = -1;
-        Geom      g{};
-        bool      aligned = false;
-        long long k       = 0;
-        bool      failed  = false;
-        for (long long u = uBegin; u < uEnd; ++u, ++k)
+        // ===================================================================== producer warp
+        // Geometry of 32 consecutive units is worked out by the 32 lanes side by side (sample descriptors, row taps,
+        // tapped span, copy addresses); the lanes then take turns, in unit order, to claim a ring slot, publish the
+        // unit and issue its bulk copies.
+        const bool perSampleTaps = p.list != nullptr || p.roi != nullptr;
+        const int  unitsPerSample = p.dstH * cfg.chunksPerRow;
+        int        s           = 0;
+        unsigned   emptyParity = 1; // phase the consumers complete when they release the slot's previous use
+        bool       failed      = false;
+        long long  issued      = 0;
+
+        for (long long kb = 0; kb < walk.count && !failed; kb += 32)
         {
-            const int s = static_cast<int>(k % S);
-            if (k >= S && !mbar_wait(&empty[s], static_cast<unsigned>((k / S - 1) & 1)))
+            const long long k     = kb + lane;
+            const bool      valid = k < walk.count;
+            UnitInfo           info{};
+            unsigned long long copySrc = 0;
+            long long          rowDelta = 0;
+            unsigned           nb = 0;
+            if (valid)
             {
-                atomicOr(&g_deviceError, 2u);
-                failed = true;
-                break;
-            }
-            const int n     = static_cast<int>(u / unitsPerSample);
-            const int rem   = static_cast<int>(u - n * unitsPerSample);
-            const int y     = rem / cfg.chunksPerRow;
-            const int chunk = rem - y * cfg.chunksPerRow;
-            if (n != cachedN)
-            {
-                g       = load_geom(p, n);
-                aligned = ((reinterpret_cast<unsigned long long>(g.image) | static_cast<unsigned long long>(g.pitch)) & 15ull) == 0;
-                cachedN = n;
-            }
-            UnitInfo &info = infos[s];
-            info.y         = y;
-            info.x0        = chunk * cfg.chunkCols;
-            info.x1        = min(info.x0 + cfg.chunkCols, p.dstW);
-            info.dstRowOff = n * p.dSample + y * p.dRow;
-            info.flipX     = (g.flip == 1 || g.flip == -1);
-            info.srcW      = g.w;
-            info.scaleW    = g.scaleW;
+                const long long u     = walk.unit(k);
+                const int       n     = static_cast<int>(u / unitsPerSample);
+                const int       rem   = static_cast<int>(u - static_cast<long long>(n) * unitsPerSample);
+                const int       y     = rem / cfg.chunksPerRow;
+                const int       chunk = rem - y * cfg.chunksPerRow;
+                const Geom      g     = load_geom(p, n);
+                const bool      aligned
+                    = ((reinterpret_cast<unsigned long long>(g.image) | static_cast<unsigned long long>(g.pitch)) & 15ull) == 0;
 
-            const int ry  = y - p.dstY;
-            const int rx0 = max(info.x0 - p.dstX, 0);
-            const int rx1 = min(info.x1 - p.dstX, p.regionW) - 1; // inclusive
-            if (ry < 0 || ry >= p.regionH || rx1 < rx0)
-            {
-                info.mode = UNIT_PAD;
-                mbar_arrive(&full[s]);
-                continue;
-            }
-            const int dy  = ((g.flip == 0 || g.flip == -1) ? p.regionH - 1 - ry : ry) + p.cropY;
-            const int dlo = (info.flipX ? p.regionW - 1 - rx1 : rx0) + p.cropX;
-            const int dhi = (info.flipX ? p.regionW - 1 - rx0 : rx1) + p.cropX;
+                info.x0        = chunk * cfg.chunkCols;
+                info.x1        = min(info.x0 + cfg.chunkCols, p.dstW);
+                info.dstRowOff = n * p.dSample + y * p.dRow;
+                info.flipX     = (g.flip == 1 || g.flip == -1);
+                info.tapKey    = ((perSampleTaps ? static_cast<long long>(n) + 1 : 0) * cfg.chunksPerRow + chunk) * 2 + info.flipX;
+                info.srcW      = g.w;
+                info.scaleW    = g.scaleW;
 
-            int sy0, sy1, sxmin, sxmax;
-            if constexpr (INTERP == B200PP_INTERP_NEAREST)
-            {
-                sy0 = sy1 = nearest_tap(g.scaleH, dy, g.h);
-                info.wy1  = 0.f;
-                sxmin     = nearest_tap(g.scaleW, dlo, g.w);
-                sxmax     = nearest_tap(g.scaleW, dhi, g.w);
-            }
-            else
-            {
-                float w;
-                int   t;
-                linear_tap(g.scaleH, dy, g.h, sy0, sy1, info.wy1);
-                linear_tap(g.scaleW, dlo, g.w, sxmin, t, w);
-                linear_tap(g.scaleW, dhi, g.w, t, sxmax, w);
-            }
-            info.g0      = g.base + sy0 * g.pitch;
-            info.g1      = g.base + sy1 * g.pitch;
-            info.sameRow = (sy0 == sy1);
+                const int ry  = y - p.dstY;
+                const int rx0 = max(info.x0 - p.dstX, 0);
+                const int rx1 = min(info.x1 - p.dstX, p.regionW) - 1; // inclusive
+                if (ry < 0 || ry >= p.regionH || rx1 < rx0)
+                {
+                    info.mode = UNIT_PAD;
+                }
+                else
+                {
+                    const int dy  = ((g.flip == 0 || g.flip == -1) ? p.regionH - 1 - ry : ry) + p.cropY;
+                    const int dlo = (info.flipX ? p.regionW - 1 - rx1 : rx0) + p.cropX;
+                    const int dhi = (info.flipX ? p.regionW - 1 - rx0 : rx1) + p.cropX;
+                    int       sy0, sy1, sxmin, sxmax;
+                    if constexpr (INTERP == B200PP_INTERP_NEAREST)
+                    {
+                        sy0 = sy1 = nearest_tap(g.scaleH, dy, g.h);
+                        sxmin     = nearest_tap(g.scaleW, dlo, g.w);
+                        sxmax     = nearest_tap(g.scaleW, dhi, g.w);
+                    }
+                    else
+                    {
+                        float w, wy1;
+                        int   t;
+                        linear_tap(g.scaleH, dy, g.h, sy0, sy1, wy1);
+                        info.wy0s = __fmul_rn(__fsub_rn(1.0f, wy1), kTwo127);
+                        info.wy1s = __fmul_rn(wy1, kTwo127);
+                        linear_tap(g.scaleW, dlo, g.w, sxmin, t, w);
+                        linear_tap(g.scaleW, dhi, g.w, t, sxmax, w);
+                    }
+                    info.g0      = g.base + sy0 * g.pitch;
+                    info.g1      = g.base + sy1 * g.pitch;
+                    info.sameRow = (sy0 == sy1);
+                    rowDelta     = (sy1 - sy0) * g.pitch;
 
-            const unsigned long long a0 = reinterpret_cast<unsigned long long>(info.g0) + 3ull * sxmin;
-            const unsigned long long a1 = reinterpret_cast<unsigned long long>(info.g0) + 3ull * (sxmax + 1);
-            const unsigned long long s0 = a0 & ~15ull;
-            const unsigned long long s1 = (a1 + 15ull) & ~15ull;
-            const unsigned           nb = static_cast<unsigned>(s1 - s0);
-            if (!aligned || nb > static_cast<unsigned>(cfg.segBytes))
-            {
-                info.mode = UNIT_DIRECT;
-                mbar_arrive(&full[s]);
-                continue;
+                    const unsigned long long a0 = reinterpret_cast<unsigned long long>(info.g0) + 3ull * sxmin;
+                    const unsigned long long a1 = reinterpret_cast<unsigned long long>(info.g0) + 3ull * (sxmax + 1);
+                    copySrc                     = a0 & ~15ull;
+                    nb                          = static_cast<unsigned>(((a1 + 15ull) & ~15ull) - copySrc);
+                    if (!aligned || nb > static_cast<unsigned>(cfg.segBytes))
+                    {
+                        info.mode = UNIT_DIRECT;
+                    }
+                    else
+                    {
+                        info.mode      = UNIT_STAGED;
+                        info.segOrigin = 3 * sxmin - static_cast<int>(a0 & 15ull);
+                    }
+                }
             }
-            info.mode      = UNIT_STAGED;
-            info.segOrigin = 3 * sxmin - static_cast<int>(a0 & 15ull);
 
-            unsigned char *slot   = ring + s * slotBytes;
-            const bool     twoRow = (INTERP == B200PP_INTERP_LINEAR) && !info.sameRow;
-            mbar_arrive_expect_tx(&full[s], twoRow ? 2u * nb : nb);
-            bulk_load(slot, reinterpret_cast<const void *>(s0), nb, &full[s]);
-            if (twoRow)
-                bulk_load(slot + cfg.segBytes, reinterpret_cast<const void *>(s0 + (sy1 - sy0) * g.pitch), nb, &full[s]);
+            const int batch = static_cast<int>(min(32ll, walk.count - kb));
+            for (int j = 0; j < batch; ++j)
+            {
+                bool bad = false;
+                if (lane == j)
+                {
+                    if (kb + j >= S && !mbar_wait(&empty[s], emptyParity))
+                    {
+                        atomicOr(&g_deviceError, 2u);
+                        bad = true;
+                    }
+                    else
+                    {
+                        infos[s] = info;
+                        if (info.mode == UNIT_STAGED)
+                        {
+                            unsigned char *slot   = ring + s * slotBytes;
+                            const bool     twoRow = (INTERP == B200PP_INTERP_LINEAR) && !info.sameRow;
+                            mbar_arrive_expect_tx(&full[s], twoRow ? 2u * nb : nb);
+                            bulk_load(slot, reinterpret_cast<const void *>(copySrc), nb, &full[s]);
+                            if (twoRow)
+                                bulk_load(slot + cfg.segBytes, reinterpret_cast<const void *>(copySrc + rowDelta), nb, &full[s]);
+                        }
+                        else
+                        {
+                            mbar_arrive(&full[s]);
+                        }
+                    }
+                }
+                if (__any_sync(0xffffffffu, bad))
+                {
+                    failed = true;
+                    break;
+                }
+                ++issued;
+                if (++s == S)
+                {
+                    s = 0;
+                    emptyParity ^= 1u;
+                }
+            }
         }
-        if (failed)
+        if (failed && lane == 0)
         {
             // Consumers have stopped releasing slots. Give the copies already issued a bounded time to land before
             // the CTA's shared memory goes away.
-            for (long long j = (k > S ? k - S : 0); j < k; ++j)
+            for (long long j = (issued > S ? issued - S : 0); j < issued; ++j)
                 if (!mbar_wait(&full[j % S], static_cast<unsigned>((j / S) & 1)))
                 {
                     atomicOr(&g_deviceError, 4u);
@@ -362,39 +538,52 @@ __global__ void __launch_bounds__(512) resize_staged_kernel(const ResizeKParams 
     }
 
     // ========================================================================= consumers
-    const int ct   = threadIdx.x - kProducerThreads;
-    const int lane = threadIdx.x & 31;
-    long long k    = 0;
-    for (long long u = uBegin; u < uEnd; ++u, ++k)
+    const int     ct         = threadIdx.x - kProducerThreads;
+    const ChanOff co         = chan_offsets(p);
+    long long     cachedKey  = -1;
+    int           s          = 0;
+    unsigned      fullParity = 0;
+    ColTap        cache[kCachedCols];
+    for (long long k = 0; k < walk.count; ++k)
     {
-        const int s = static_cast<int>(k % S);
-        if (!mbar_wait(&full[s], static_cast<unsigned>((k / S) & 1)))
+        if (!mbar_wait(&full[s], fullParity))
         {
             atomicOr(&g_deviceError, 1u);
             return;
         }
-        const UnitInfo info = infos[s];
+        const UnitInfo info   = infos[s];
         uint8_t       *dstRow = p.dst + info.dstRowOff;
 
         if (info.mode == UNIT_PAD)
         {
-            for (int x = info.x0 + ct; x < info.x1; x += consumerThreads) pad_pixel<DK>(p, dstRow + x * p.dPix);
-        }
-        else if (info.mode == UNIT_STAGED)
-        {
-            // Kept as its own call site so that the row pointers visibly derive from the shared-memory ring and the
-            // tap reads compile to shared-memory loads.
-            const uint8_t *r0 = ring + s * slotBytes;
-            consume_columns<INTERP, DK>(p, info, r0, info.sameRow ? r0 : r0 + cfg.segBytes, info.segOrigin, dstRow, ct,
-                                        consumerThreads);
+            for (int x = info.x0 + ct; x < info.x1; x += consumerThreads) pad_pixel<DK>(p, co, dstRow + x * p.dPix);
         }
         else
         {
-            consume_columns<INTERP, DK>(p, info, info.g0, info.g1, 0, dstRow, ct, consumerThreads);
+            const bool refresh = info.tapKey != cachedKey;
+            cachedKey          = info.tapKey;
+            if (info.mode == UNIT_STAGED)
+            {
+                // Its own call site: the row pointers visibly derive from the shared-memory ring, so the tap reads
+                // compile to shared-memory loads.
+                const uint8_t *r0 = ring + s * slotBytes;
+                consume_columns<INTERP, DK>(p, co, info, r0, info.sameRow ? r0 : r0 + cfg.segBytes, info.segOrigin,
+                                            dstRow, ct, consumerThreads, cache, refresh);
+            }
+            else
+            {
+                consume_columns<INTERP, DK>(p, co, info, info.g0, info.g1, 0, dstRow, ct, consumerThreads, cache,
+                                            refresh);
+            }
         }
         __syncwarp();
         if (lane == 0)
             mbar_arrive(&empty[s]);
+        if (++s == S)
+        {
+            s = 0;
+            fullParity ^= 1u;
+        }
     }
 }
 
