@@ -37,6 +37,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
         "--fmad=false", "--ftz=false", "--prec-div=true", "--prec-sqrt=true",
         "-Xcompiler", "-fPIC,-fvisibility=hidden,-Wall", "-shared",
         "-I" + os.path.join(ROOT, "include"), "-I" + CSRC,
+        "-Xlinker", "--version-script=" + os.path.join(CSRC, "exports.map"),
         "-o", LIB, *srcs, "-ldl",
     ]
     if verbose:

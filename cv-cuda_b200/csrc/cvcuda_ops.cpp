@@ -1,0 +1,512 @@
+// Handle-based operator entry points: the symbols the reference's libcvcuda exports for the fused pre-processing
+// path, implemented on top of the plain-C launch layer (library.cu).
+//
+// Tensor / image-batch handles belong to the reference's object-model library (libnvcv_types). This file never looks
+// inside them: it asks that library, found in the running process, to export their contents
+// (reference call sites: src/cvcuda/priv/OpResizeCropConvertReformat.cu:423-438,561-583,
+//  src/cvcuda/priv/OpCropFlipNormalizeReformat.cu:373-428).
+#include <cvcuda_b200/cvcuda_ops.h>
+
+#include <dlfcn.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <initializer_list>
+#include <mutex>
+#include <new>
+
+namespace {
+
+// ---------------------------------------------------------------------------------------------- object-model functions
+
+enum DataKind // NVCVDataKind (nvcv/DataLayout.h:260-267)
+{
+    KIND_UNSIGNED = 0,
+    KIND_SIGNED   = 1,
+    KIND_FLOAT    = 2,
+    KIND_COMPLEX  = 3
+};
+
+struct NvcvApi
+{
+    NVCVStatus (*tensorExportData)(NVCVTensorHandle, NVCVTensorData *)                     = nullptr;
+    NVCVStatus (*imageBatchExportData)(NVCVImageBatchHandle, cudaStream_t, NVCVImageBatchData *) = nullptr;
+    NVCVStatus (*dataTypeGetDataKind)(NVCVDataType, int *)                                  = nullptr;
+    NVCVStatus (*dataTypeGetBitsPerChannel)(NVCVDataType, int32_t *)                        = nullptr;
+    NVCVStatus (*imageFormatGetDataKind)(NVCVImageFormat, int *)                            = nullptr;
+    NVCVStatus (*imageFormatGetBitsPerChannel)(NVCVImageFormat, int32_t *)                  = nullptr;
+    NVCVStatus (*imageFormatGetNumChannels)(NVCVImageFormat, int32_t *)                     = nullptr;
+    NVCVStatus (*imageFormatGetNumPlanes)(NVCVImageFormat, int32_t *)                       = nullptr;
+    void (*setThreadStatus)(NVCVStatus, const char *, ...)                                  = nullptr;
+    bool ok                                                                                 = false;
+};
+
+const NvcvApi &nvcv()
+{
+    static NvcvApi        api;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        auto find = [](const char *name) -> void * {
+            if (void *p = dlsym(RTLD_DEFAULT, name))
+                return p;
+            // not yet in the process: load the object-model library the way libcvcuda depends on it
+            for (const char *lib : {"libnvcv_types.so.0", "libnvcv_types.so"})
+                if (void *h = dlopen(lib, RTLD_NOW | RTLD_GLOBAL))
+                    if (void *p = dlsym(h, name))
+                        return p;
+            return nullptr;
+        };
+#define B200_BIND(field, symbol) api.field = reinterpret_cast<decltype(api.field)>(find(symbol))
+        B200_BIND(tensorExportData, "nvcvTensorExportData");
+        B200_BIND(imageBatchExportData, "nvcvImageBatchExportData");
+        B200_BIND(dataTypeGetDataKind, "nvcvDataTypeGetDataKind");
+        B200_BIND(dataTypeGetBitsPerChannel, "nvcvDataTypeGetBitsPerChannel");
+        B200_BIND(imageFormatGetDataKind, "nvcvImageFormatGetDataKind");
+        B200_BIND(imageFormatGetBitsPerChannel, "nvcvImageFormatGetBitsPerChannel");
+        B200_BIND(imageFormatGetNumChannels, "nvcvImageFormatGetNumChannels");
+        B200_BIND(imageFormatGetNumPlanes, "nvcvImageFormatGetNumPlanes");
+        B200_BIND(setThreadStatus, "nvcvSetThreadStatus");
+#undef B200_BIND
+        api.ok = api.tensorExportData && api.imageBatchExportData && api.dataTypeGetDataKind
+              && api.dataTypeGetBitsPerChannel && api.imageFormatGetDataKind && api.imageFormatGetBitsPerChannel
+              && api.imageFormatGetNumChannels && api.imageFormatGetNumPlanes;
+    });
+    return api;
+}
+
+// Sets the thread's last status the way nvcv::ProtectCall does (nvcv/Exception.hpp:162-222) and returns it.
+NVCVStatus report(NVCVStatus status, const char *fmt, ...)
+{
+    char    msg[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(msg, sizeof(msg), fmt, ap);
+    va_end(ap);
+    if (nvcv().setThreadStatus)
+        nvcv().setThreadStatus(status, "%s", msg);
+    return status;
+}
+
+// Success leaves the thread's status untouched, as nvcv::ProtectCall does (nvcv/Exception.hpp:209-222).
+NVCVStatus forward(int status)
+{
+    if (status == B200PP_SUCCESS)
+        return B200PP_SUCCESS;
+    return report(status, "%s", b200ppGetLastErrorMessage());
+}
+
+// ---------------------------------------------------------------------------------------------- operator objects
+
+constexpr uint64_t kMagic = 0xB2000C0DA0F5ED01ull;
+
+enum OpKind
+{
+    OP_RESIZE_CROP_CONVERT_REFORMAT  = 1,
+    OP_CROP_FLIP_NORMALIZE_REFORMAT = 2
+};
+
+// The handle is the object pointer itself, as in the reference (src/cvcuda/priv/IOperator.hpp:37-40). Operators hold
+// no mutable state, so one handle may be used from any number of threads and streams.
+struct Operator
+{
+    uint64_t magic;
+    int      kind;
+};
+
+NVCVStatus create(NVCVOperatorHandle *handle, int kind)
+{
+    if (handle == nullptr)
+        return report(B200PP_ERROR_INVALID_ARGUMENT, "Pointer to NVCVOperator handle must not be NULL");
+    Operator *op = new (std::nothrow) Operator{kMagic, kind};
+    if (!op)
+        return report(7 /* NVCV_ERROR_OUT_OF_MEMORY */, "Not enough memory to create the operator");
+    *handle = reinterpret_cast<NVCVOperatorHandle>(op);
+    return forward(B200PP_SUCCESS);
+}
+
+// NULL -> INVALID_ARGUMENT, another operator's handle -> NOT_COMPATIBLE (src/cvcuda/priv/IOperator.hpp:56-73).
+NVCVStatus check_handle(NVCVOperatorHandle handle, int kind)
+{
+    if (handle == nullptr)
+        return report(B200PP_ERROR_INVALID_ARGUMENT, "Handle cannot be NULL");
+    const Operator *op = reinterpret_cast<const Operator *>(handle);
+    if (op->magic != kMagic || op->kind != kind)
+        return report(B200PP_ERROR_NOT_COMPATIBLE,
+                      "Handle doesn't correspond to the requested object or was already destroyed.");
+    return B200PP_SUCCESS;
+}
+
+// ---------------------------------------------------------------------------------------------- handle unpacking
+
+int element_type(int kind, int bits)
+{
+    if (kind == KIND_UNSIGNED)
+        return bits == 8 ? B200PP_U8 : bits == 16 ? B200PP_U16 : bits == 32 ? B200PP_U32 : -1;
+    if (kind == KIND_SIGNED)
+        return bits == 8 ? B200PP_S8 : bits == 16 ? B200PP_S16 : bits == 32 ? B200PP_S32 : -1;
+    if (kind == KIND_FLOAT)
+        return bits == 32 ? B200PP_F32 : bits == 16 ? B200PP_F16 : -1;
+    return -1;
+}
+
+// Image view of a tensor: the rules of nvcv::TensorDataAccessStridedImagePlanar
+// (nvcv/TensorDataAccess.hpp:389-458,564-605; accepted layouts nvcv/TensorShapeInfo.hpp:334-361).
+struct ImageView
+{
+    bool     valid = false;
+    int      samples = 1, channels = 1, rows = 1, cols = 1;
+    bool     channelLast = true; // interleaved
+    int64_t  sampleStride = 0, rowStride = 0, colStride = 0, chanStride = 0;
+    uint8_t *base = nullptr;
+    int      dtype = -1;
+    char     layout[NVCV_TENSOR_MAX_RANK + 1] = "";
+};
+
+bool export_tensor(NVCVTensorHandle h, ImageView &v, const char *what, NVCVStatus &status)
+{
+    NVCVTensorData d;
+    std::memset(&d, 0, sizeof(d));
+    if (h == nullptr || nvcv().tensorExportData(h, &d) != B200PP_SUCCESS || d.bufferType != 1)
+    {
+        status = report(B200PP_ERROR_INVALID_ARGUMENT, "%s must be a cuda-accessible, pitch-linear tensor", what);
+        return false;
+    }
+    int kind = -1, bits[4] = {0, 0, 0, 0};
+    nvcv().dataTypeGetDataKind(d.dtype, &kind);
+    nvcv().dataTypeGetBitsPerChannel(d.dtype, bits);
+    v.dtype = element_type(kind, bits[0]);
+    v.base  = d.strided.basePtr;
+    std::memcpy(v.layout, d.layout.data, sizeof(v.layout));
+    v.layout[NVCV_TENSOR_MAX_RANK] = 0;
+
+    int iN = -1, iC = -1, iH = -1, iW = -1;
+    for (int i = 0; i < d.rank; ++i)
+    {
+        switch (d.layout.data[i])
+        {
+        case 'N':
+            iN = i;
+            break;
+        case 'C':
+            iC = i;
+            break;
+        case 'H':
+            iH = i;
+            break;
+        case 'W':
+            iW = i;
+            break;
+        }
+    }
+    v.valid = d.rank >= 1 && iW >= 0 && (iN <= 0);
+    if (!v.valid)
+        return true; // exported, but not an image-like tensor: callers decide what that means
+    v.samples      = iN >= 0 ? static_cast<int>(d.shape[iN]) : 1;
+    v.channels     = iC >= 0 ? static_cast<int>(d.shape[iC]) : 1;
+    v.rows         = iH >= 0 ? static_cast<int>(d.shape[iH]) : 1;
+    v.cols         = static_cast<int>(d.shape[iW]);
+    v.channelLast  = iC < 0 || iC == d.rank - 1;
+    v.sampleStride = iN >= 0 ? d.strided.strides[iN] : 0;
+    v.rowStride    = iH >= 0 ? d.strided.strides[iH] : 0;
+    v.colStride    = d.strided.strides[iW];
+    v.chanStride   = iC >= 0 ? d.strided.strides[iC] : 0;
+    return true;
+}
+
+bool layout_is(const ImageView &v, const char *a, const char *b = nullptr, const char *c = nullptr,
+               const char *d = nullptr)
+{
+    for (const char *s : {a, b, c, d})
+        if (s && std::strcmp(v.layout, s) == 0)
+            return true;
+    return false;
+}
+
+void fill_dest(const ImageView &o, B200ppDest &d)
+{
+    d.base         = o.base;
+    d.dtype        = o.dtype;
+    d.channels     = o.channels;
+    d.width        = o.cols;
+    d.height       = o.rows;
+    d.sampleStride = o.sampleStride;
+    d.rowStride    = o.rowStride;
+    d.pixStride    = o.colStride;
+    d.chanStride   = o.chanStride;
+}
+
+// Output checks shared by both resize entry points
+// (src/cvcuda/priv/OpResizeCropConvertReformat.cu:446-498 / :591-640).
+NVCVStatus check_resize_output(const ImageView &o, int samples, int channels, bool allowHalf)
+{
+    if (samples != o.samples)
+        return report(B200PP_ERROR_INVALID_ARGUMENT,
+                      "Input and output must have the same batch size (i.e., same number of images): Provided %d "
+                      "input and %d output images / samples",
+                      samples, o.samples);
+    if (channels != o.channels)
+        return report(B200PP_ERROR_NOT_COMPATIBLE,
+                      "Input and output must have same number of channels: Provided %d input and %d output channels",
+                      channels, o.channels);
+    if (channels != 3)
+        return report(B200PP_ERROR_NOT_COMPATIBLE,
+                      "Only three-channel input is currently supported: Provided %d input channels", channels);
+    if (!(o.dtype == B200PP_U8 || o.dtype == B200PP_F32 || (allowHalf && o.dtype == B200PP_F16)))
+        return report(B200PP_ERROR_NOT_COMPATIBLE, "Output must be of data type uchar or float.");
+    return B200PP_SUCCESS;
+}
+
+NVCVStatus check_output_layout(const ImageView &o)
+{
+    if (!layout_is(o, "NHWC", "HWC", "NCHW", "CHW"))
+        return report(B200PP_ERROR_NOT_COMPATIBLE,
+                      "Output tensor must have 'NHWC', 'NCHW', 'HWC', or 'CHW' layout: Layout provided %s", o.layout);
+    return B200PP_SUCCESS;
+}
+
+NVCVStatus resize_tensor(NVCVOperatorHandle handle, cudaStream_t stream, NVCVTensorHandle in, NVCVTensorHandle out,
+                         const B200ppResizeOp &op, bool extended)
+{
+    if (NVCVStatus st = check_handle(handle, OP_RESIZE_CROP_CONVERT_REFORMAT))
+        return st;
+    if (!nvcv().ok)
+        return report(B200PP_ERROR_INTERNAL, "libnvcv_types is not loaded in this process");
+    NVCVStatus st = B200PP_SUCCESS;
+    ImageView  i, o;
+    if (!export_tensor(in, i, "Input", st) || !export_tensor(out, o, "Output", st))
+        return st;
+    if (!i.valid || !o.valid)
+        return report(B200PP_ERROR_NOT_COMPATIBLE, "Input and output must be image-like tensors");
+    if ((st = check_resize_output(o, i.samples, i.channels, extended)))
+        return st;
+    if (i.dtype != B200PP_U8)
+        return report(B200PP_ERROR_NOT_COMPATIBLE, "Input must be of data type uchar.");
+    if (!layout_is(i, "NHWC", "HWC"))
+        return report(B200PP_ERROR_NOT_COMPATIBLE, "Input tensor must have 'NHWC' or 'HWC' layout: Layout provided %s",
+                      i.layout);
+    if ((st = check_output_layout(o)))
+        return st;
+
+    B200ppSource s;
+    std::memset(&s, 0, sizeof(s));
+    s.dtype        = i.dtype;
+    s.channels     = i.channels;
+    s.planar       = 0;
+    s.numSamples   = i.samples;
+    s.base         = i.base;
+    s.sampleStride = i.sampleStride;
+    s.rowStride    = i.rowStride;
+    s.width        = i.cols;
+    s.height       = i.rows;
+    B200ppDest d;
+    fill_dest(o, d);
+    // Unlike the reference (src/cvcuda/priv/OpResizeCropConvertReformat.cu:515-519) inputs beyond 2 GiB are accepted:
+    // sample offsets are 64-bit.
+    return forward(b200ppResizeCropConvertReformat(&s, &d, &op, stream));
+}
+
+NVCVStatus resize_varshape(NVCVOperatorHandle handle, cudaStream_t stream, NVCVImageBatchHandle in,
+                           NVCVTensorHandle out, const B200ppResizeOp &op, bool extended)
+{
+    if (NVCVStatus st = check_handle(handle, OP_RESIZE_CROP_CONVERT_REFORMAT))
+        return st;
+    if (!nvcv().ok)
+        return report(B200PP_ERROR_INTERNAL, "libnvcv_types is not loaded in this process");
+    NVCVImageBatchData b;
+    std::memset(&b, 0, sizeof(b));
+    if (in == nullptr || nvcv().imageBatchExportData(in, stream, &b) != B200PP_SUCCESS || b.bufferType != 1)
+        return report(B200PP_ERROR_INVALID_ARGUMENT, "Input data must be a cuda-accessible, varshape image batch");
+    NVCVStatus st = B200PP_SUCCESS;
+    ImageView  o;
+    if (!export_tensor(out, o, "Output", st))
+        return st;
+    if (b.varShapeStrided.uniqueFormat == 0)
+        return report(B200PP_ERROR_INVALID_ARGUMENT,
+                      "All input images in a batch must have the same format (including number of channels)");
+    if (!o.valid)
+        return report(B200PP_ERROR_NOT_COMPATIBLE, "Output must be an image-like tensor");
+    int channels = 0, planes = 0, kind = -1, bits[4] = {0, 0, 0, 0};
+    nvcv().imageFormatGetNumChannels(b.varShapeStrided.uniqueFormat, &channels);
+    nvcv().imageFormatGetNumPlanes(b.varShapeStrided.uniqueFormat, &planes);
+    nvcv().imageFormatGetDataKind(b.varShapeStrided.uniqueFormat, &kind);
+    nvcv().imageFormatGetBitsPerChannel(b.varShapeStrided.uniqueFormat, bits);
+    if ((st = check_resize_output(o, b.numImages, channels, extended)))
+        return st;
+    if (element_type(kind, bits[0]) != B200PP_U8)
+        return report(B200PP_ERROR_NOT_COMPATIBLE, "Input must be of data type uchar.");
+    if (planes > 1)
+        return report(B200PP_ERROR_NOT_COMPATIBLE, "Input must be non-planar (i.e., interleaved).");
+    if ((st = check_output_layout(o)))
+        return st;
+
+    B200ppSource s;
+    std::memset(&s, 0, sizeof(s));
+    s.dtype      = B200PP_U8;
+    s.channels   = channels;
+    s.planar     = 0;
+    s.numSamples = b.numImages;
+    s.imageList  = b.varShapeStrided.imageList;
+    s.maxWidth   = b.varShapeStrided.maxWidth;
+    s.maxHeight  = b.varShapeStrided.maxHeight;
+    B200ppDest d;
+    fill_dest(o, d);
+    return forward(b200ppResizeCropConvertReformat(&s, &d, &op, stream));
+}
+
+B200ppResizeOp reference_op(NVCVSize2D resizeDim, int interp, int2 cropPos, int manip, float scale, float offset,
+                            bool srcCast)
+{
+    B200ppResizeOp op;
+    std::memset(&op, 0, sizeof(op));
+    op.resizeW = resizeDim.w;
+    op.resizeH = resizeDim.h;
+    op.cropX   = cropPos.x;
+    op.cropY   = cropPos.y;
+    op.interp  = interp;
+    op.srcCast = srcCast ? 1 : 0;
+    op.manip   = manip;
+    op.scale   = scale;
+    op.offset  = offset;
+    return op;
+}
+
+} // namespace
+
+// ================================================================================================ exported symbols
+
+extern "C" NVCVStatus cvcudaResizeCropConvertReformatCreate(NVCVOperatorHandle *handle)
+{
+    return create(handle, OP_RESIZE_CROP_CONVERT_REFORMAT);
+}
+
+extern "C" NVCVStatus cvcudaCropFlipNormalizeReformatCreate(NVCVOperatorHandle *handle)
+{
+    return create(handle, OP_CROP_FLIP_NORMALIZE_REFORMAT);
+}
+
+extern "C" void nvcvOperatorDestroy(NVCVOperatorHandle handle)
+{
+    Operator *op = reinterpret_cast<Operator *>(handle);
+    if (op && op->magic == kMagic)
+    {
+        op->magic = 0;
+        delete op;
+    }
+}
+
+extern "C" NVCVStatus cvcudaResizeCropConvertReformatSubmit(NVCVOperatorHandle handle, cudaStream_t stream,
+                                                            NVCVTensorHandle in, NVCVTensorHandle out,
+                                                            const NVCVSize2D resizeDim,
+                                                            const NVCVInterpolationType interpolation,
+                                                            const int2 cropPos, const NVCVChannelManip manip,
+                                                            const float scale, const float offset, const bool srcCast)
+{
+    return resize_tensor(handle, stream, in, out,
+                         reference_op(resizeDim, interpolation, cropPos, manip, scale, offset, srcCast), false);
+}
+
+extern "C" NVCVStatus cvcudaResizeCropConvertReformatVarShapeSubmit(NVCVOperatorHandle handle, cudaStream_t stream,
+                                                                    NVCVImageBatchHandle in, NVCVTensorHandle out,
+                                                                    const NVCVSize2D resizeDim,
+                                                                    const NVCVInterpolationType interpolation,
+                                                                    const int2 cropPos, const NVCVChannelManip manip,
+                                                                    const float scale, const float offset,
+                                                                    const bool srcCast)
+{
+    return resize_varshape(handle, stream, in, out,
+                           reference_op(resizeDim, interpolation, cropPos, manip, scale, offset, srcCast), false);
+}
+
+extern "C" NVCVStatus cvcudaB200FusedPreprocessSubmit(NVCVOperatorHandle handle, cudaStream_t stream,
+                                                      NVCVTensorHandle in, NVCVTensorHandle out,
+                                                      const B200ppResizeOp *op)
+{
+    if (!op)
+        return report(B200PP_ERROR_INVALID_ARGUMENT, "Null argument");
+    return resize_tensor(handle, stream, in, out, *op, true);
+}
+
+extern "C" NVCVStatus cvcudaB200FusedPreprocessVarShapeSubmit(NVCVOperatorHandle handle, cudaStream_t stream,
+                                                              NVCVImageBatchHandle in, NVCVTensorHandle out,
+                                                              const B200ppResizeOp *op)
+{
+    if (!op)
+        return report(B200PP_ERROR_INVALID_ARGUMENT, "Null argument");
+    return resize_varshape(handle, stream, in, out, *op, true);
+}
+
+extern "C" NVCVStatus cvcudaCropFlipNormalizeReformatSubmit(NVCVOperatorHandle handle, cudaStream_t stream,
+                                                            NVCVImageBatchHandle in, NVCVTensorHandle out,
+                                                            NVCVTensorHandle cropRect, NVCVBorderType borderMode,
+                                                            float borderValue, NVCVTensorHandle flipCode,
+                                                            NVCVTensorHandle base, NVCVTensorHandle scale,
+                                                            float global_scale, float shift, float epsilon,
+                                                            uint32_t flags)
+{
+    if (NVCVStatus st = check_handle(handle, OP_CROP_FLIP_NORMALIZE_REFORMAT))
+        return st;
+    if (!nvcv().ok)
+        return report(B200PP_ERROR_INTERNAL, "libnvcv_types is not loaded in this process");
+    NVCVImageBatchData b;
+    std::memset(&b, 0, sizeof(b));
+    if (in == nullptr || nvcv().imageBatchExportData(in, stream, &b) != B200PP_SUCCESS || b.bufferType != 1)
+        return report(B200PP_ERROR_INVALID_ARGUMENT, "Input must be cuda-accessible, pitch-linear tensor");
+    NVCVStatus st = B200PP_SUCCESS;
+    ImageView  o, fc, bs, sc, cr;
+    if (!export_tensor(out, o, "Output", st) || !export_tensor(flipCode, fc, "Input flipCode", st)
+        || !export_tensor(base, bs, "Input base", st) || !export_tensor(scale, sc, "Input scale", st)
+        || !export_tensor(cropRect, cr, "Input cropRect", st))
+        return st;
+    if (!o.valid || !bs.valid || !sc.valid || !cr.valid)
+        return report(B200PP_ERROR_INVALID_ARGUMENT, "Output, base, scale and cropRect must be image-like tensors");
+
+    int channels = 0, planes = 0, kind = -1, bits[4] = {0, 0, 0, 0};
+    nvcv().imageFormatGetNumChannels(b.varShapeStrided.uniqueFormat, &channels);
+    nvcv().imageFormatGetNumPlanes(b.varShapeStrided.uniqueFormat, &planes);
+    nvcv().imageFormatGetDataKind(b.varShapeStrided.uniqueFormat, &kind);
+    nvcv().imageFormatGetBitsPerChannel(b.varShapeStrided.uniqueFormat, bits);
+    if (kind == KIND_COMPLEX)
+        return report(B200PP_ERROR_INVALID_ARGUMENT, "Input DataKind must be unsigned, signed or float");
+    const int srcType = element_type(kind, bits[0]);
+    // float16 is no input type of the reference's dispatch table (OpCropFlipNormalizeReformat.cu:453-458)
+    if (srcType < 0 || srcType == B200PP_F16)
+        return report(B200PP_ERROR_INVALID_ARGUMENT, "Unsupported input data type");
+    // ... nor an output type (:335-341); the plain-C layer offers it as an addition
+    if (o.dtype < 0 || o.dtype == B200PP_F16)
+        return report(B200PP_ERROR_INVALID_ARGUMENT, "Unsupported output data type");
+    if (!layout_is(o, "NHWC", "NCHW"))
+        return report(B200PP_ERROR_INVALID_ARGUMENT, "Invalid tensor layout in output");
+
+    B200ppSource s;
+    std::memset(&s, 0, sizeof(s));
+    s.dtype      = srcType;
+    s.channels   = channels;
+    s.planar     = planes > 1;
+    s.numSamples = b.numImages;
+    s.imageList  = b.varShapeStrided.imageList;
+    s.maxWidth   = b.varShapeStrided.maxWidth;
+    s.maxHeight  = b.varShapeStrided.maxHeight;
+    B200ppDest d;
+    fill_dest(o, d);
+    d.channels = channels; // the kernel writes the input's channels (OpCropFlipNormalizeReformat.cu:264-267)
+
+    B200ppSliceOp op;
+    std::memset(&op, 0, sizeof(op));
+    op.cropRect        = reinterpret_cast<const int32_t *>(cr.base);
+    op.cropRectStride  = cr.sampleStride;
+    op.flipCode        = reinterpret_cast<const int32_t *>(fc.base);
+    op.border          = borderMode;
+    op.borderValue     = borderValue;
+    op.base            = reinterpret_cast<const float *>(bs.base);
+    op.baseChannels    = bs.channels;
+    op.baseChanStride  = bs.chanStride;
+    op.scale           = reinterpret_cast<const float *>(sc.base);
+    op.scaleChannels   = sc.channels;
+    op.scaleChanStride = sc.chanStride;
+    op.gscale          = global_scale;
+    op.shift           = shift;
+    op.epsilon         = epsilon;
+    op.flags           = flags;
+    return forward(b200ppCropFlipNormalizeReformat(&s, &d, &op, stream));
+}
