@@ -218,11 +218,7 @@ def run_native(args) -> int:
         torch.cuda.synchronize()
 
     def max_over_ranks(ms: float) -> float:
-        if world == 1:
-            return ms
-        t = torch.tensor([ms], dtype=torch.float64, device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
+        return pkg.sharding.max_over_ranks(ms, dev)
 
     # seeded synthetic batch, generated on the device (each rank its own shard of the global batch)
     gen = torch.Generator(device=dev)

@@ -86,33 +86,37 @@ static const DeviceFacts &device_facts(int dev)
     return it->second;
 }
 
-// Resident CTAs per SM of one staged-kernel instantiation for a block size and dynamic shared-memory size; also raises
-// the kernel's dynamic shared-memory limit the first time a size is seen on a device.
+// Resident CTAs per SM of one staged-kernel instantiation for a block size and dynamic shared-memory size. The first
+// use of a kernel on a device raises its dynamic shared-memory limit to the device maximum, once, so that launches with
+// different ring sizes never lower it again.
 template<typename K>
-static int staged_occupancy(K kernel, int dev, int kernelId, int block, int smemBytes)
+static int staged_occupancy(K kernel, int dev, int kernelId, int block, int smemBytes, int maxSmemOptin)
 {
     static std::mutex                                     mu;
     static std::map<std::tuple<int, int, int, int>, int> cache;
+    static std::map<std::pair<int, int>, bool>           raised;
     std::lock_guard<std::mutex>                           lock(mu);
+    auto rk = std::make_pair(dev, kernelId);
+    if (raised.find(rk) == raised.end())
+    {
+        const bool ok = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, maxSmemOptin) == cudaSuccess;
+        if (!ok)
+            cudaGetLastError();
+        raised[rk] = ok;
+    }
+    if (!raised[rk])
+        return 0;
     auto key = std::make_tuple(dev, kernelId, block, smemBytes);
     auto it  = cache.find(key);
     if (it == cache.end())
     {
-        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smemBytes) != cudaSuccess)
+        int n = 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, block, smemBytes) != cudaSuccess)
         {
             cudaGetLastError();
-            it = cache.emplace(key, 0).first;
+            n = 0;
         }
-        else
-        {
-            int n = 0;
-            if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, block, smemBytes) != cudaSuccess)
-            {
-                cudaGetLastError();
-                n = 0;
-            }
-            it = cache.emplace(key, n).first;
-        }
+        it = cache.emplace(key, n).first;
     }
     return it->second;
 }
@@ -196,7 +200,7 @@ static int launch_resize_staged(const ResizeKParams &kp, int srcWBound, cudaStre
     const int block         = kProducerThreads + consumers;
 
     auto      kernel = resize_staged_kernel<INTERP, DK>;
-    const int occ    = staged_occupancy(kernel, dev, INTERP * 4 + DK, block, smemBytes);
+    const int occ    = staged_occupancy(kernel, dev, INTERP * 4 + DK, block, smemBytes, facts.maxSmemOptin);
     if (occ <= 0)
         return 0;
     const int       perSm = tuning().maxCtasPerSm > 0 ? std::min(occ, tuning().maxCtasPerSm) : occ;

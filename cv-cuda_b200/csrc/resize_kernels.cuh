@@ -25,6 +25,8 @@ __device__ unsigned int g_deviceError;
 
 constexpr int                kProducerThreads = 32;
 constexpr unsigned long long kWaitLimitNs     = 2000000000ull; // 2 s
+// Upper bound of one hardware-suspended wait: a waiting warp sleeps instead of burning issue slots in a poll loop.
+constexpr unsigned           kSuspendHintNs   = 4000;
 
 // ------------------------------------------------------------------------------------------------ pixel maths
 //
@@ -190,10 +192,10 @@ __device__ __forceinline__ bool mbar_try_wait(unsigned addr, unsigned parity)
     unsigned done;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(done)
-        : "r"(addr), "r"(parity)
+        : "r"(addr), "r"(parity), "r"(kSuspendHintNs)
         : "memory");
     return done != 0;
 }
