@@ -123,12 +123,13 @@ static int staged_occupancy(K kernel, int dev, int kernelId, int block, int smem
 
 // Launch-shape overrides for tuning runs, read once from the environment:
 // B200PP_STAGES (ring depth), B200PP_MAX_CTAS_PER_SM (cap on resident CTAs per SM of the staged kernel) and
-// B200PP_BLOCK_UNITS (consecutive units dealt to a CTA at a time).
+// B200PP_BLOCK_UNITS (consecutive units dealt to a CTA at a time), B200PP_MAX_CONSUMERS (consumer threads per CTA).
 struct Tuning
 {
     int stages       = 0;
     int maxCtasPerSm = 0;
     int blockUnits   = 0;
+    int maxConsumers = 0;
 };
 
 static const Tuning &tuning()
@@ -143,6 +144,8 @@ static const Tuning &tuning()
             v.maxCtasPerSm = atoi(c);
         if (const char *b = getenv("B200PP_BLOCK_UNITS"))
             v.blockUnits = atoi(b);
+        if (const char *m = getenv("B200PP_MAX_CONSUMERS"))
+            v.maxConsumers = atoi(m);
         return v;
     }();
     return t;
@@ -194,13 +197,19 @@ static int launch_resize_staged(const ResizeKParams &kp, int srcWBound, cudaStre
     if (smemBytes > facts.maxSmemOptin)
         return 0;
 
-    const int colsPerThread = (cfg.chunkCols + 255) / 256;
+    const int maxConsumers  = tuning().maxConsumers > 0 ? std::min(480, tuning().maxConsumers / 32 * 32) : 256;
+    const int colsPerThread = (cfg.chunkCols + maxConsumers - 1) / maxConsumers;
     int       consumers     = ((cfg.chunkCols + colsPerThread - 1) / colsPerThread + 31) / 32 * 32;
     consumers               = std::max(32, std::min(consumers, 480));
     const int block         = kProducerThreads + consumers;
 
-    auto      kernel = resize_staged_kernel<INTERP, DK>;
-    const int occ    = staged_occupancy(kernel, dev, INTERP * 4 + DK, block, smemBytes, facts.maxSmemOptin);
+    // columns per consumer thread whose taps are kept in registers
+    const int perThread = (cfg.chunkCols + consumers - 1) / consumers;
+    const int kc        = std::min(3, std::max(1, perThread));
+    auto      kernel    = kc == 1   ? resize_staged_kernel<INTERP, DK, 1>
+                        : kc == 2 ? resize_staged_kernel<INTERP, DK, 2>
+                                  : resize_staged_kernel<INTERP, DK, 3>;
+    const int occ       = staged_occupancy(kernel, dev, (INTERP * 4 + DK) * 4 + kc, block, smemBytes, facts.maxSmemOptin);
     if (occ <= 0)
         return 0;
     const int       perSm = tuning().maxCtasPerSm > 0 ? std::min(occ, tuning().maxCtasPerSm) : occ;

@@ -306,18 +306,17 @@ __device__ __forceinline__ void consume_pixel(const ResizeKParams &p, const Chan
         linear_pixel<DK>(p, co, r0, r1, t.o0 - origin, t.o1 - origin, t.wx0s, t.wx1s, info.wy0s, info.wy1s, dstPix);
 }
 
-constexpr int kCachedCols = 2;
 
 // Columns [x0, x1) of one destination row, strided over the consumer threads so that a warp writes 32 adjacent pixels.
-// The taps of a thread's first kCachedCols columns stay in registers while consecutive units share a tap key, which
-// for a dense batch is the whole launch.
-template<int INTERP, int DK>
+// The taps of a thread's first KC columns stay in registers while consecutive units share a tap key, which for a dense
+// batch is the whole launch. KC is a template parameter because every cached column costs six registers.
+template<int INTERP, int DK, int KC>
 __device__ __forceinline__ void consume_columns(const ResizeKParams &p, const ChanOff &co, const UnitInfo &info,
                                                 const uint8_t *r0, const uint8_t *r1, int origin, uint8_t *dstRow,
-                                                int ct, int consumerThreads, ColTap (&cache)[kCachedCols], bool refresh)
+                                                int ct, int consumerThreads, ColTap (&cache)[KC], bool refresh)
 {
 #pragma unroll
-    for (int k = 0; k < kCachedCols; ++k)
+    for (int k = 0; k < KC; ++k)
     {
         const int x = info.x0 + ct + k * consumerThreads;
         if (x < info.x1)
@@ -327,7 +326,7 @@ __device__ __forceinline__ void consume_columns(const ResizeKParams &p, const Ch
             consume_pixel<INTERP, DK>(p, co, info, cache[k], r0, r1, origin, dstRow);
         }
     }
-    for (int x = info.x0 + ct + kCachedCols * consumerThreads; x < info.x1; x += consumerThreads)
+    for (int x = info.x0 + ct + KC * consumerThreads; x < info.x1; x += consumerThreads)
     {
         const ColTap t = make_tap<INTERP>(p, info, x);
         consume_pixel<INTERP, DK>(p, co, info, t, r0, r1, origin, dstRow);
@@ -363,7 +362,7 @@ struct UnitWalk
     }
 };
 
-template<int INTERP, int DK>
+template<int INTERP, int DK, int KC>
 __global__ void __launch_bounds__(512) resize_staged_kernel(const ResizeKParams p, const StagedCfg cfg)
 {
     extern __shared__ __align__(128) unsigned char smemRaw[];
@@ -545,7 +544,7 @@ __global__ void __launch_bounds__(512) resize_staged_kernel(const ResizeKParams 
     long long     cachedKey  = -1;
     int           s          = 0;
     unsigned      fullParity = 0;
-    ColTap        cache[kCachedCols];
+    ColTap        cache[KC];
     for (long long k = 0; k < walk.count; ++k)
     {
         if (!mbar_wait(&full[s], fullParity))
@@ -569,12 +568,12 @@ __global__ void __launch_bounds__(512) resize_staged_kernel(const ResizeKParams 
                 // Its own call site: the row pointers visibly derive from the shared-memory ring, so the tap reads
                 // compile to shared-memory loads.
                 const uint8_t *r0 = ring + s * slotBytes;
-                consume_columns<INTERP, DK>(p, co, info, r0, info.sameRow ? r0 : r0 + cfg.segBytes, info.segOrigin,
+                consume_columns<INTERP, DK, KC>(p, co, info, r0, info.sameRow ? r0 : r0 + cfg.segBytes, info.segOrigin,
                                             dstRow, ct, consumerThreads, cache, refresh);
             }
             else
             {
-                consume_columns<INTERP, DK>(p, co, info, info.g0, info.g1, 0, dstRow, ct, consumerThreads, cache,
+                consume_columns<INTERP, DK, KC>(p, co, info, info.g0, info.g1, 0, dstRow, ct, consumerThreads, cache,
                                             refresh);
             }
         }
