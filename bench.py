@@ -271,8 +271,15 @@ def run_native(args) -> int:
         step(out, host_src)
         host_out.copy_(out, non_blocking=True)
 
+    def e2e_zero_copy_step():
+        # one launch and nothing else: tapped source rows come in over PCIe by bulk copy, result rows go out as
+        # full-line stores into the page-locked host result
+        step(host_out, host_src)
+
     e2e_modes = {"h2d_copy+kernel+d2h": (e2e_copy_step, host_src.numel()),
-                 "kernel reads pinned host rows directly + d2h": (e2e_direct_step, ALG_SRC_BYTES * BATCH)}
+                 "kernel reads pinned host rows directly + d2h": (e2e_direct_step, ALG_SRC_BYTES * BATCH),
+                 "kernel reads pinned host rows and writes the pinned host result": (e2e_zero_copy_step,
+                                                                                    ALG_SRC_BYTES * BATCH)}
     e2e_results = {}
     for name, (fn, h2d_bytes) in e2e_modes.items():
         for _ in range(2):

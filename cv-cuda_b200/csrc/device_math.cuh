@@ -44,6 +44,13 @@ __device__ __forceinline__ short sat_s16(float v)
     return r;
 }
 
+// float(byte i of `word`) without a conversion instruction: selector 0x7540 + i makes PRMT build 0x4B0000bb, the float
+// 2^23 + bb, and the subtraction of 2^23 is exact.
+__device__ __forceinline__ float byte_as_float(unsigned word, unsigned selector)
+{
+    return __fsub_rn(__uint_as_float(__byte_perm(word, 0x4B000000u, selector)), 8388608.0f);
+}
+
 // Store one value of the resize path (uint8 / float32 / float16 destinations).
 template<int DK>
 __device__ __forceinline__ void store_elem(uint8_t *ptr, float v)

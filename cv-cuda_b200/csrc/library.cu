@@ -452,9 +452,30 @@ extern "C" int b200ppCropFlipNormalizeReformat(const B200ppSource *src, const B2
     kp.dstH    = dst->height;
 
     dim3 block(32, 8);
+    const int  path     = g_kernelPath.load(std::memory_order_relaxed);
+    const bool fastCase = src->dtype == B200PP_U8 && channels == 3 && !kp.srcPlanar
+                       && (dst->dtype == B200PP_U8 || dst->dtype == B200PP_F32 || dst->dtype == B200PP_F16);
+    if (fastCase && path != 1)
+    {
+        // four destination pixels per thread; one vector store per channel when the destination is planar and every
+        // address involved is a multiple of the vector size
+        const long long vec      = 4ll * elem_size(dst->dtype);
+        const int       vecStore = kp.dPix == elem_size(dst->dtype)
+                           && ((reinterpret_cast<unsigned long long>(kp.dst) | static_cast<unsigned long long>(kp.dRow)
+                                | static_cast<unsigned long long>(kp.dChan) | static_cast<unsigned long long>(kp.dSample))
+                               % vec)
+                                  == 0;
+        dim3 grid((kp.dstW + 127) / 128, (kp.dstH + 7) / 8, std::min(kp.numSamples, 32768));
+        if (dst->dtype == B200PP_F32)
+            slice_u8x3_kernel<DST_F32><<<grid, block, 0, stream>>>(kp, dst->dtype, vecStore);
+        else if (dst->dtype == B200PP_F16)
+            slice_u8x3_kernel<DST_F16><<<grid, block, 0, stream>>>(kp, dst->dtype, vecStore);
+        else
+            slice_u8x3_kernel<DST_U8><<<grid, block, 0, stream>>>(kp, dst->dtype, vecStore);
+        return check_launch("CropFlipNormalizeReformat (uint8 x 3)");
+    }
     dim3 grid((kp.dstW + 31) / 32, (kp.dstH + 7) / 8, std::min(kp.numSamples, 32768));
-    slice_gather_kernel<4><<<grid, block, 0, stream>>>(kp, src->dtype, dst->dtype, elem_size(src->dtype),
-                                                       elem_size(dst->dtype));
+    slice_gather_kernel<4><<<grid, block, 0, stream>>>(kp, src->dtype, dst->dtype, elem_size(src->dtype));
     return check_launch("CropFlipNormalizeReformat");
 }
 

@@ -36,100 +36,234 @@ __device__ __forceinline__ int border_index(int c, int size, int mode)
     }
 }
 
+// Per-channel constants of a launch: base value and multiplier (scale, or 1/sqrt(scale^2 + epsilon)).
 template<int MAXC>
-__global__ void __launch_bounds__(256) slice_gather_kernel(const SliceKParams p, const int srcType, const int dstType,
-                                                           const int srcElem, const int dstElem)
+__device__ __forceinline__ void load_constants(const SliceKParams &p, float (&base)[MAXC], float (&mul)[MAXC])
 {
-    const int j = blockIdx.x * blockDim.x + threadIdx.x;
-    const int i = blockIdx.y * blockDim.y + threadIdx.y;
-    if (j >= p.dstW || i >= p.dstH)
-        return;
+#pragma unroll
+    for (int k = 0; k < MAXC; ++k)
+    {
+        base[k] = 0.f;
+        mul[k]  = 0.f;
+        if (k < p.channels)
+        {
+            const int bk  = p.baseCh == 1 ? 0 : k;
+            const int sk  = p.scaleCh == 1 ? 0 : k;
+            base[k]       = *reinterpret_cast<const float *>(reinterpret_cast<const char *>(p.base) + bk * p.baseChanStride);
+            const float s = *reinterpret_cast<const float *>(reinterpret_cast<const char *>(p.scale) + sk * p.scaleChanStride);
+            mul[k]        = p.stddev ? __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fmul_rn(s, s), p.epsilon))) : s;
+        }
+    }
+}
 
-    // per-channel constants, identical for every pixel of the launch
-    float base[MAXC], mul[MAXC];
+// What a sample's descriptors say, read once per thread and sample.
+struct SliceSample
+{
+    const uint8_t *img;
+    long long      pitch, planeStride;
+    int            w, h;
+    int            cx, cy, cw, ch, flip;
+};
+
+__device__ __forceinline__ SliceSample load_slice_sample(const SliceKParams &p, int n)
+{
+    SliceSample s;
+    const int  *rect = reinterpret_cast<const int *>(reinterpret_cast<const char *>(p.cropRect) + n * p.cropRectStride);
+    s.cx   = rect[0];
+    s.cy   = rect[1];
+    s.cw   = rect[2];
+    s.ch   = rect[3];
+    s.flip = p.flip[n];
+    if (p.list)
+    {
+        const B200ppImagePlane &pl = p.list[n].planes[0];
+        s.img         = pl.basePtr;
+        s.pitch       = pl.rowStride;
+        s.w           = pl.width;
+        s.h           = pl.height;
+        s.planeStride = 0;
+    }
+    else
+    {
+        s.img         = p.srcBase + n * p.srcSampleStride;
+        s.pitch       = p.srcRowStride;
+        s.planeStride = p.srcPlaneStride;
+        s.w           = p.srcW;
+        s.h           = p.srcH;
+    }
+    return s;
+}
+
+// One destination pixel (j, i) of sample n, any element types, layout and border mode.
+template<int MAXC>
+__device__ __forceinline__ void slice_pixel(const SliceKParams &p, const SliceSample &s, int n, int i, int j, int srcType,
+                                            int dstType, int srcElem, const float (&base)[MAXC], const float (&mul)[MAXC])
+{
+    uint8_t *dstPix = p.dst + n * p.dSample + i * p.dRow + j * p.dPix;
+    if (i >= s.ch || j >= s.cw)
+    {
+#pragma unroll
+        for (int k = 0; k < MAXC; ++k)
+            if (k < p.channels)
+                store_any(dstPix + k * p.dChan, dstType, 0.f);
+        return;
+    }
+    int x = (s.flip == 1 || s.flip == -1) ? s.cw - 1 - j + s.cx : j + s.cx;
+    int y = (s.flip == 0 || s.flip == -1) ? s.ch - 1 - i + s.cy : i + s.cy;
+
+    bool inside = (x >= 0 && x < s.w && y >= 0 && y < s.h);
+    if (!inside && p.border != B200PP_BORDER_CONSTANT)
+    {
+        x      = border_index(x, s.w, p.border);
+        y      = border_index(y, s.h, p.border);
+        inside = true;
+    }
 #pragma unroll
     for (int k = 0; k < MAXC; ++k)
     {
         if (k < p.channels)
         {
-            const int bk = p.baseCh == 1 ? 0 : k;
-            const int sk = p.scaleCh == 1 ? 0 : k;
-            base[k]      = *reinterpret_cast<const float *>(reinterpret_cast<const char *>(p.base) + bk * p.baseChanStride);
-            const float s = *reinterpret_cast<const float *>(reinterpret_cast<const char *>(p.scale) + sk * p.scaleChanStride);
-            mul[k]        = p.stddev ? __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fmul_rn(s, s), p.epsilon))) : s;
+            float v = p.borderAsSrc;
+            if (inside)
+            {
+                const uint8_t *src;
+                if (p.srcPlanar)
+                {
+                    const uint8_t  *plane = p.list ? p.list[n].planes[k].basePtr : s.img + k * s.planeStride;
+                    const long long pp    = p.list ? p.list[n].planes[k].rowStride : s.pitch;
+                    src                   = plane + y * pp + static_cast<long long>(x) * srcElem;
+                }
+                else
+                {
+                    src = s.img + y * s.pitch + (static_cast<long long>(x) * p.channels + k) * srcElem;
+                }
+                v = load_any(src, srcType);
+            }
+            const float o = __fadd_rn(__fmul_rn(__fmul_rn(__fsub_rn(v, base[k]), mul[k]), p.gscale), p.shift);
+            store_any(dstPix + k * p.dChan, dstType, o);
         }
     }
+}
+
+// Generic kernel: one thread per destination pixel.
+template<int MAXC>
+__global__ void __launch_bounds__(256) slice_gather_kernel(const SliceKParams p, const int srcType, const int dstType,
+                                                           const int srcElem)
+{
+    const int j = blockIdx.x * blockDim.x + threadIdx.x;
+    const int i = blockIdx.y * blockDim.y + threadIdx.y;
+    if (j >= p.dstW || i >= p.dstH)
+        return;
+    float base[MAXC], mul[MAXC];
+    load_constants<MAXC>(p, base, mul);
+    for (int n = blockIdx.z; n < p.numSamples; n += gridDim.z)
+    {
+        const SliceSample s = load_slice_sample(p, n);
+        slice_pixel<MAXC>(p, s, n, i, j, srcType, dstType, srcElem, base, mul);
+    }
+}
+
+// Fast kernel for the pre-processing case: interleaved 3-channel uint8 sources to uint8 / float32 / float16.
+// A thread produces four adjacent destination pixels of one row. When they all lie inside the crop and their four
+// source pixels inside the image, the twelve source bytes come in as aligned words, bytes become floats with one PRMT
+// and one exact subtraction each, and -- for planar, suitably aligned destinations -- each channel leaves as one
+// vector store (a warp writes 512 contiguous bytes per channel). Anything else (crop edge, border, ragged end of a
+// row) goes through slice_pixel.
+template<int DK>
+__global__ void __launch_bounds__(256) slice_u8x3_kernel(const SliceKParams p, const int dstType, const int vecStore)
+{
+    const int j0 = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    const int i  = blockIdx.y * blockDim.y + threadIdx.y;
+    if (j0 >= p.dstW || i >= p.dstH)
+        return;
+    float base[3], mul[3];
+    load_constants<3>(p, base, mul);
+    const int cols = min(4, p.dstW - j0);
 
     for (int n = blockIdx.z; n < p.numSamples; n += gridDim.z)
     {
-        uint8_t *dstPix = p.dst + n * p.dSample + i * p.dRow + j * p.dPix;
+        const SliceSample s = load_slice_sample(p, n);
 
-        const int *rect = reinterpret_cast<const int *>(reinterpret_cast<const char *>(p.cropRect) + n * p.cropRectStride);
-        const int  cx = rect[0], cy = rect[1], cw = rect[2], ch = rect[3];
-        if (i >= ch || j >= cw)
+        const bool flipX = (s.flip == 1 || s.flip == -1);
+        const int  y     = (s.flip == 0 || s.flip == -1) ? s.ch - 1 - i + s.cy : i + s.cy;
+        const int  xlo   = flipX ? s.cw - 1 - (j0 + 3) + s.cx : j0 + s.cx; // leftmost of the four source pixels
+        const bool fast  = cols == 4 && i < s.ch && j0 + 3 < s.cw && y >= 0 && y < s.h && xlo >= 0 && xlo + 3 < s.w;
+        if (!fast)
         {
-#pragma unroll
-            for (int k = 0; k < MAXC; ++k)
-                if (k < p.channels)
-                    store_any(dstPix + k * p.dChan, dstType, 0.f);
+            for (int q = 0; q < cols; ++q) slice_pixel<3>(p, s, n, i, j0 + q, B200PP_U8, dstType, 1, base, mul);
             continue;
         }
-        const int fc = p.flip[n];
-        int       x  = (fc == 1 || fc == -1) ? cw - 1 - j + cx : j + cx;
-        int       y  = (fc == 0 || fc == -1) ? ch - 1 - i + cy : i + cy;
 
-        const uint8_t *img;
-        long long      pitch, planeStride;
-        int            w, h;
-        if (p.list)
+        // twelve source bytes as three words, byte 3q+c = channel c of source pixel xlo+q
+        const uint8_t *a = s.img + y * s.pitch + 3ll * xlo;
+        unsigned       w0, w1, w2;
+        const unsigned long long addr = reinterpret_cast<unsigned long long>(a);
+        const unsigned long long row  = reinterpret_cast<unsigned long long>(s.img + y * s.pitch);
+        if ((row & 3ull) == 0 && (s.pitch & 3ll) == 0 && (addr & ~3ull) + 16 <= row + static_cast<unsigned long long>(s.pitch))
         {
-            const B200ppImageBuffer &b = p.list[n];
-            img   = b.planes[0].basePtr;
-            pitch = b.planes[0].rowStride;
-            w     = b.planes[0].width;
-            h     = b.planes[0].height;
-            planeStride = 0;
+            // aligned window of four words inside the row's pitch; shift the twelve bytes into place
+            const unsigned *wp = reinterpret_cast<const unsigned *>(addr & ~3ull);
+            const unsigned  sh = static_cast<unsigned>(addr & 3ull) * 8;
+            const unsigned  t0 = __ldg(wp), t1 = __ldg(wp + 1), t2 = __ldg(wp + 2), t3 = __ldg(wp + 3);
+            w0 = __funnelshift_r(t0, t1, sh);
+            w1 = __funnelshift_r(t1, t2, sh);
+            w2 = __funnelshift_r(t2, t3, sh);
         }
         else
         {
-            img         = p.srcBase + n * p.srcSampleStride;
-            pitch       = p.srcRowStride;
-            planeStride = p.srcPlaneStride;
-            w           = p.srcW;
-            h           = p.srcH;
-        }
-
-        bool inside = (x >= 0 && x < w && y >= 0 && y < h);
-        if (!inside && p.border != B200PP_BORDER_CONSTANT)
-        {
-            x      = border_index(x, w, p.border);
-            y      = border_index(y, h, p.border);
-            inside = true;
-        }
+            unsigned b[12];
 #pragma unroll
-        for (int k = 0; k < MAXC; ++k)
-        {
-            if (k < p.channels)
+            for (int k = 0; k < 12; ++k) b[k] = a[k];
+            w0 = b[0] | b[1] << 8 | b[2] << 16 | b[3] << 24;
+            w1 = b[4] | b[5] << 8 | b[6] << 16 | b[7] << 24;
+            w2 = b[8] | b[9] << 8 | b[10] << 16 | b[11] << 24;
+        }
+        const unsigned words[3] = {w0, w1, w2};
+
+        float o[4][3]; // [destination column q][channel]
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+#pragma unroll
+            for (int c = 0; c < 3; ++c)
             {
-                float v = p.borderAsSrc;
-                if (inside)
-                {
-                    const uint8_t *src;
-                    if (p.srcPlanar)
-                    {
-                        const uint8_t *plane = p.list ? p.list[n].planes[k].basePtr : img + k * planeStride;
-                        const long long pp   = p.list ? p.list[n].planes[k].rowStride : pitch;
-                        src                  = plane + y * pp + static_cast<long long>(x) * srcElem;
-                    }
-                    else
-                    {
-                        src = img + y * pitch + (static_cast<long long>(x) * p.channels + k) * srcElem;
-                    }
-                    v = load_any(src, srcType);
-                }
-                const float o = __fadd_rn(__fmul_rn(__fmul_rn(__fsub_rn(v, base[k]), mul[k]), p.gscale), p.shift);
-                store_any(dstPix + k * p.dChan, dstType, o);
+                const int   byte = 3 * q + c;
+                const float v    = byte_as_float(words[byte >> 2], 0x7540u + (byte & 3));
+                const float r    = __fadd_rn(__fmul_rn(__fmul_rn(__fsub_rn(v, base[c]), mul[c]), p.gscale), p.shift);
+                // source pixel q lands in destination column q, or 3-q when mirrored
+                if (flipX)
+                    o[3 - q][c] = r;
+                else
+                    o[q][c] = r;
             }
+
+        uint8_t *dst = p.dst + n * p.dSample + i * p.dRow + j0 * p.dPix;
+        if (vecStore)
+        {
+#pragma unroll
+            for (int c = 0; c < 3; ++c)
+            {
+                uint8_t *d = dst + c * p.dChan;
+                if constexpr (DK == DST_F32)
+                    *reinterpret_cast<float4 *>(d) = make_float4(o[0][c], o[1][c], o[2][c], o[3][c]);
+                else if constexpr (DK == DST_F16)
+                {
+                    const __half2 lo = __floats2half2_rn(o[0][c], o[1][c]), hi = __floats2half2_rn(o[2][c], o[3][c]);
+                    uint2         v;
+                    v.x = *reinterpret_cast<const unsigned *>(&lo);
+                    v.y = *reinterpret_cast<const unsigned *>(&hi);
+                    *reinterpret_cast<uint2 *>(d) = v;
+                }
+                else
+                    *reinterpret_cast<unsigned *>(d) = sat_u8(o[0][c]) | sat_u8(o[1][c]) << 8 | sat_u8(o[2][c]) << 16
+                                                     | sat_u8(o[3][c]) << 24;
+            }
+        }
+        else
+        {
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+#pragma unroll
+                for (int c = 0; c < 3; ++c) store_elem<DK>(dst + q * p.dPix + c * p.dChan, o[q][c]);
         }
     }
 }

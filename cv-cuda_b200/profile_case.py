@@ -24,7 +24,7 @@ INV_STD = tuple(float(np.float32(1.0) / np.float32(s)) for s in (58.395, 57.12, 
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--case", default="classify", choices=("classify", "4k", "4k-nearest", "letterbox"))
+    ap.add_argument("--case", default="classify", choices=("classify", "4k", "4k-nearest", "letterbox", "cfnr"))
     ap.add_argument("--images", type=int, default=32)
     ap.add_argument("--path", type=int, default=0)
     ap.add_argument("--launches", type=int, default=5)
@@ -43,18 +43,35 @@ def main():
         out = torch.empty((n, 3, 448, 448), dtype=torch.float16, device="cuda")
         kw = dict(resize_dim=(512, 512), interp=int(a.case == "4k"), crop_pos=(32, 32), layout="NCHW", base=MEAN,
                   mul=INV_STD, srcCast=False)
-    else:
+    elif a.case == "letterbox":
         src = torch.randint(0, 256, (n, 1080, 1920, 3), dtype=torch.uint8, device="cuda", generator=g)
         out = torch.empty((n, 3, 640, 640), dtype=torch.float32, device="cuda")
         kw = dict(resize_dim=(640, 360), interp=1, layout="NCHW", manip=1, scale=1.0 / 255.0, srcCast=True,
                   dst_pos=(0, 140), region_size=(640, 360), pad_value=114.0)
+    if a.case == "cfnr":
+        # CropFlipNormalizeReformat on the reference benchmark's image size (bench/BenchCropFlipNormalizeReformat.cpp:
+        # 1080x1920, crop = full image, flip both axes), here 3-channel uint8 -> float32 NCHW with per-channel constants
+        imgs = [torch.randint(0, 256, (1080, 1920, 3), dtype=torch.uint8, device="cuda", generator=g) for _ in range(n)]
+        batch = pkg.ImageBatchVarShape(imgs)
+        out = torch.empty((n, 3, 1080, 1920), dtype=torch.float32, device="cuda")
+        rect = torch.tensor([[0, 0, 1920, 1080]] * n, dtype=torch.int32, device="cuda").reshape(n, 1, 1, 4)
+        flip = torch.full((n,), -1, dtype=torch.int32, device="cuda")
+        base = torch.tensor(MEAN, dtype=torch.float32, device="cuda").reshape(1, 1, 1, 3)
+        scale = torch.tensor(INV_STD, dtype=torch.float32, device="cuda").reshape(1, 1, 1, 3)
+
+        def run():
+            pkg.crop_flip_normalize_reformat_into(out, batch, rect, flip, base, scale, layout="NCHW",
+                                                  border=pkg.Border.REFLECT101)
+    else:
+        def run():
+            pkg.fused_preprocess_into(out, src, **kw)
     for _ in range(3):
-        pkg.fused_preprocess_into(out, src, **kw)
+        run()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(a.launches):
-        pkg.fused_preprocess_into(out, src, **kw)
+        run()
     e1.record()
     torch.cuda.synchronize()
     print(f"case {a.case} images {n} path {a.path}: {e0.elapsed_time(e1) / a.launches * 1000:.1f} us per launch, "

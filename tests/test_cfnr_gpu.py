@@ -6,7 +6,7 @@ import pytest
 import torch
 
 import ref_tables as T
-from gpu_util import _TORCH_DTYPE, assert_parity, padded_images, to_dev
+from gpu_util import _TORCH_DTYPE, assert_parity, kernel_path, padded_images, to_dev
 
 pytestmark = pytest.mark.gpu
 
@@ -37,9 +37,11 @@ def test_reference_table(pkg, oracle, idx):
         images, rects, flips, base, scale, osz = T.cfnr_case(row, seed)
         want = oracle.crop_flip_normalize(images, row.src_planar, rects, flips, osz, row.dst_dtype, row.dst_planar,
                                           row.border, 1.0, base, scale, row.gscale, row.gshift, row.eps, row.flags)
-        got = _run(pkg, images, row.src_planar, rects, flips, osz, row.dst_dtype, row.dst_planar, row.border, 1.0, base,
-                   scale, row.gscale, row.gshift, row.eps, row.flags)
-        assert_parity(got, want, what=f"row {idx} seed {seed}")
+        for path in (0, 1):  # 0: automatic (the four-pixel kernel where it applies), 1: per-pixel kernel
+            with kernel_path(pkg, path):
+                got = _run(pkg, images, row.src_planar, rects, flips, osz, row.dst_dtype, row.dst_planar, row.border,
+                           1.0, base, scale, row.gscale, row.gshift, row.eps, row.flags)
+            assert_parity(got, want, what=f"row {idx} seed {seed} path {path}")
 
 
 def test_golden_fixtures(pkg):
@@ -83,6 +85,32 @@ def test_dtype_and_border_matrix(pkg, oracle, border, src_dtype, dst_dtype):
             got = _run(pkg, images, src_planar, rects, flips, (50, 47), dst_dtype, dst_planar, border, 7.9, base, scale,
                        1.3, -2.5, eps, flags, pad_to=4, offset=4)
             assert_parity(got, want, what=f"border {border} planar {src_planar}->{dst_planar} flags {flags}")
+
+
+@pytest.mark.parametrize("border", range(5))
+@pytest.mark.parametrize("dst_dtype,dst_planar", [(np.float32, True), (np.float16, True), (np.uint8, True),
+                                                  (np.float32, False), (np.uint8, False)])
+def test_uint8_rgb_fast_kernel(pkg, oracle, border, dst_dtype, dst_planar):
+    """The four-pixels-per-thread kernel: every flip code, crops hanging over each image edge, widths that are not a
+    multiple of four, padded and unaligned source rows, against the oracle and against the per-pixel kernel."""
+    rng = np.random.default_rng(500 + border)
+    sizes = [(37, 23), (64, 16), (130, 9), (5, 41), (257, 3), (96, 96)]
+    images = [rng.integers(0, 256, (h, w, 3), dtype=np.uint8) for w, h in sizes]
+    rects = [(-3, -2, 30, 20), (0, 0, 64, 16), (7, 1, 140, 7), (1, 30, 9, 20), (250, -1, 20, 6), (8, 8, 80, 80)]
+    flips = np.array([1, 0, -1, 2, 1, -1], np.int32)
+    base = np.array([10.5, 20.25, 30.125], np.float32)
+    scale = np.array([0.5, 0.25, 1.5], np.float32)
+    for out_w, out_h in ((131, 40), (64, 16), (3, 5)):
+        want = oracle.crop_flip_normalize(images, False, rects, flips, (out_w, out_h), dst_dtype, dst_planar, border, 5.0,
+                                          base, scale, 1.25, -0.5, 0.0, 0)
+        for pad_to, offset in ((32, 0), (1, 1)):
+            got = {}
+            for path in (0, 1):
+                with kernel_path(pkg, path):
+                    got[path] = _run(pkg, images, False, rects, flips, (out_w, out_h), dst_dtype, dst_planar, border, 5.0,
+                                     base, scale, 1.25, -0.5, 0.0, 0, pad_to=pad_to, offset=offset)
+                assert_parity(got[path], want, what=f"{out_w}x{out_h} pad {pad_to} path {path}")
+            assert np.array_equal(got[0].view(np.uint8), got[1].view(np.uint8))
 
 
 def test_benchmark_shape_of_the_reference(pkg, oracle):
