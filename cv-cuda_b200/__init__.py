@@ -25,6 +25,7 @@ from .ops import (  # noqa: F401
     read_device_error,
     resize_crop_convert_reformat,
     resize_crop_convert_reformat_into,
+    self_test_wait_timeout,
     set_kernel_path,
 )
 

@@ -494,6 +494,14 @@ extern "C" uint64_t b200ppGetLaunchCount(void)
     return g_launchCount.load();
 }
 
+extern "C" int b200ppSelfTestWaitTimeout(uint32_t limitMs, cudaStream_t stream)
+{
+    if (limitMs == 0 || limitMs > 1000)
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "The wait limit of the self-test must be 1..1000 ms");
+    wait_timeout_probe_kernel<<<1, 32, 0, stream>>>(static_cast<unsigned long long>(limitMs) * 1000000ull);
+    return check_launch("wait self-test");
+}
+
 extern "C" int b200ppReadDeviceError(uint32_t *outError)
 {
     if (!outError)

@@ -20,7 +20,7 @@
 namespace b200pp {
 
 // Device error word. Bits: 1 = a consumer gave up waiting for a staged row, 2 = the producer gave up waiting
-// for a free ring slot, 4 = the producer gave up draining its copies at exit.
+// for a free ring slot, 4 = the producer gave up draining its copies at exit, 8 = the wait self-test gave up (expected).
 __device__ unsigned int g_deviceError;
 
 constexpr int                kProducerThreads = 32;
@@ -200,8 +200,9 @@ __device__ __forceinline__ bool mbar_try_wait(unsigned addr, unsigned parity)
     return done != 0;
 }
 
-// Bounded wait for the phase with the given parity: gives up (returns false) after kWaitLimitNs of wall time.
-__device__ __forceinline__ bool mbar_wait(unsigned long long *bar, unsigned parity)
+// Bounded wait for the phase with the given parity: gives up (returns false) after `limitNs` of wall time.
+__device__ __forceinline__ bool mbar_wait(unsigned long long *bar, unsigned parity,
+                                          unsigned long long limitNs = kWaitLimitNs)
 {
     const unsigned addr = smem_addr(bar);
     if (mbar_try_wait(addr, parity))
@@ -211,9 +212,24 @@ __device__ __forceinline__ bool mbar_wait(unsigned long long *bar, unsigned pari
     {
         if (mbar_try_wait(addr, parity))
             return true;
-        if ((spin & 63u) == 0 && globaltimer_ns() - t0 > kWaitLimitNs)
+        if ((spin & 63u) == 0 && globaltimer_ns() - t0 > limitNs)
             return false;
     }
+}
+
+// Self-test of the bounded wait: one warp waits on a barrier that nothing ever completes, with a short limit, and
+// must come back with the give-up bit (8) set in the device error word -- the same code path a stuck pipeline takes.
+__global__ void wait_timeout_probe_kernel(unsigned long long limitNs)
+{
+    __shared__ unsigned long long bar;
+    if (threadIdx.x == 0)
+    {
+        mbar_init(&bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (!mbar_wait(&bar, 0, limitNs) && threadIdx.x == 0)
+        atomicOr(&g_deviceError, 8u);
 }
 
 // Bulk asynchronous copy global -> shared, completion counted in bytes on `bar`.

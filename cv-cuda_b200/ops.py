@@ -159,6 +159,8 @@ def lib() -> C.CDLL:
         L.b200ppGetLaunchCount.restype = C.c_uint64
         L.b200ppReadDeviceError.restype = C.c_int
         L.b200ppReadDeviceError.argtypes = [C.POINTER(C.c_uint32)]
+        L.b200ppSelfTestWaitTimeout.restype = C.c_int
+        L.b200ppSelfTestWaitTimeout.argtypes = [C.c_uint32, C.c_void_p]
         _lib = L
     return _lib
 
@@ -180,6 +182,11 @@ def read_device_error() -> int:
     v = C.c_uint32(0)
     _check(lib().b200ppReadDeviceError(C.byref(v)))
     return int(v.value)
+
+
+def self_test_wait_timeout(limit_ms: int = 20, stream=None) -> None:
+    """Launches the bounded-wait self-test (a wait that must give up after `limit_ms`)."""
+    _check(lib().b200ppSelfTestWaitTimeout(int(limit_ms), _stream_handle(stream)))
 
 
 def _check(status: int) -> None:

@@ -24,7 +24,7 @@ INV_STD = tuple(float(np.float32(1.0) / np.float32(s)) for s in (58.395, 57.12, 
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--case", default="classify", choices=("classify", "4k", "4k-nearest", "letterbox", "cfnr"))
+    ap.add_argument("--case", default="classify", choices=("classify", "4k", "4k-nearest", "letterbox", "cfnr", "varshape"))
     ap.add_argument("--images", type=int, default=32)
     ap.add_argument("--path", type=int, default=0)
     ap.add_argument("--launches", type=int, default=5)
@@ -43,6 +43,27 @@ def main():
         out = torch.empty((n, 3, 448, 448), dtype=torch.float16, device="cuda")
         kw = dict(resize_dim=(512, 512), interp=int(a.case == "4k"), crop_pos=(32, 32), layout="NCHW", base=MEAN,
                   mul=INV_STD, srcCast=False)
+    elif a.case == "varshape":
+        # config 3: variable-shape RGB batch, one random rectangle per image -> 224x224 linear, horizontal flip p=0.5,
+        # mean/std, float16 NCHW
+        rng = np.random.default_rng(1234)
+        sizes = [(int(rng.integers(480, 3841)), int(rng.integers(360, 2161))) for _ in range(n)]
+        imgs = [torch.randint(0, 256, (h, (w * 3 + 31) // 32 * 32), dtype=torch.uint8, device="cuda", generator=g)
+                [:, : w * 3].unflatten(1, (w, 3)) for w, h in sizes]
+        src = pkg.ImageBatchVarShape(imgs)
+        rects = []
+        for w, h in sizes:
+            area = rng.uniform(0.08, 1.0) * w * h
+            ar = np.exp(rng.uniform(np.log(3 / 4), np.log(4 / 3)))
+            cw, ch = min(w, int(round(np.sqrt(area * ar)))), min(h, int(round(np.sqrt(area / ar))))
+            rects.append((int(rng.integers(0, w - cw + 1)), int(rng.integers(0, h - ch + 1)), cw, ch))
+        roi = torch.tensor(rects, dtype=torch.int32, device="cuda")
+        flip = torch.tensor(np.where(rng.random(n) < 0.5, 1, 2), dtype=torch.int32, device="cuda")
+        out = torch.empty((n, 3, 224, 224), dtype=torch.float16, device="cuda")
+        kw = dict(resize_dim=(224, 224), interp=1, layout="NCHW", base=MEAN, mul=INV_STD, srcCast=True, roi=roi,
+                  flip_code=flip)
+        src_bytes = sum(r[2] * r[3] * 3 for r in rects)
+        print(f"varshape: crop rectangles hold {src_bytes / 1e6:.1f} MB, output {out.numel() * 2 / 1e6:.1f} MB")
     elif a.case == "letterbox":
         src = torch.randint(0, 256, (n, 1080, 1920, 3), dtype=torch.uint8, device="cuda", generator=g)
         out = torch.empty((n, 3, 640, 640), dtype=torch.float32, device="cuda")

@@ -204,6 +204,11 @@ B200PP_PUBLIC uint64_t b200ppGetLaunchCount(void);
  * on a bounded wait; bit layout is documented next to the kernels. */
 B200PP_PUBLIC int b200ppReadDeviceError(uint32_t *outError);
 
+/* Self-test of the kernels' bounded waits: launches one warp that waits, for at most limitMs (1..1000) milliseconds, on a
+ * barrier nothing completes. The kernel then returns normally and bit 8 of the device error word is set; the context
+ * stays usable. No counterpart in the reference. */
+B200PP_PUBLIC int b200ppSelfTestWaitTimeout(uint32_t limitMs, cudaStream_t stream);
+
 #if defined(__cplusplus)
 }
 #endif

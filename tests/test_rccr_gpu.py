@@ -284,3 +284,46 @@ def test_negative_rows_return_the_reference_status(pkg, idx, varshape):
         pkg.resize_crop_convert_reformat_into(dst, src, r.resize, r.interp, r.crop, layout="NHWC")
     assert pkg.ops.Status(e.value.status).name == r.status, e.value.message
     assert pkg.launch_count() == before
+
+
+def test_bounded_wait_gives_up_and_reports(pkg, oracle):
+    """Failure detection without a fault: a wait nothing satisfies runs out after 20 ms, the kernel returns, the host
+    reads the give-up bit, and the context keeps working."""
+    import time
+    assert pkg.read_device_error() == 0
+    t0 = time.perf_counter()
+    pkg.self_test_wait_timeout(20)
+    torch.cuda.synchronize()
+    elapsed = time.perf_counter() - t0
+    assert 0.015 < elapsed < 1.0
+    assert pkg.read_device_error() == 8
+    assert pkg.read_device_error() == 0  # reading clears the word
+    src = np.random.default_rng(1).integers(0, 256, (1, 40, 60, 3), dtype=np.uint8)
+    spec = oracle.ResizeSpec(resize=(48, 32), out_size=(48, 32), interp=1, src_cast=False)
+    out = pkg.resize_crop_convert_reformat(to_dev(src), (48, 32), 1, (0, 0, 48, 32), layout="NCHW", data_type=torch.float32,
+                                           srcCast=False)
+    assert_parity(out.cpu().numpy(), oracle.resize_crop(list(src), spec, np.float32, True), what="after the self-test")
+
+
+def test_offsets_beyond_two_gib(pkg, oracle):
+    """400 x 1080p is 2.49 GB: the reference refuses it (sample offsets are 32-bit there); here the last sample of the
+    batch must come out right."""
+    n = 400
+    src = torch.zeros((n, 1080, 1920, 3), dtype=torch.uint8, device="cuda")
+    rng = np.random.default_rng(9)
+    last = rng.integers(0, 256, (1080, 1920, 3), dtype=np.uint8)
+    first = rng.integers(0, 256, (1080, 1920, 3), dtype=np.uint8)
+    src[n - 1].copy_(to_dev(last))
+    src[0].copy_(to_dev(first))
+    spec = oracle.ResizeSpec(resize=(256, 256), crop=(16, 16), out_size=(224, 224), interp=1, src_cast=False, manip=1,
+                             scale=1.0 / 255.0)
+    want = oracle.resize_crop([first, last], spec, np.float32, True, nthreads=2)
+    for path in PATHS:
+        with kernel_path(pkg, path):
+            out = pkg.resize_crop_convert_reformat(src, (256, 256), 1, (16, 16, 224, 224), layout="NCHW",
+                                                   data_type=torch.float32, manip=1, scale=1.0 / 255.0, srcCast=False)
+            torch.cuda.synchronize()
+        got = out[[0, n - 1]].cpu().numpy()
+        assert_parity(got, want, what=f"path {path}")
+        assert float(out[1:n - 1].abs().max()) == 0.0
+    del src
