@@ -69,15 +69,37 @@ __device__ __forceinline__ ChanOff chan_offsets(const ResizeKParams &p)
     return o;
 }
 
-// Affine step + cast + store of source channel c.
+// Cast + store of one finished value.
 template<int DK>
-__device__ __forceinline__ void emit(const ResizeKParams &p, int c, float v, uint8_t *dst)
+__device__ __forceinline__ void store_value(float v, uint8_t *dst)
 {
-    v = affine(p, c, v);
     if constexpr (DK == DST_U8)
         *dst = static_cast<uint8_t>(__float_as_uint(__fadd_rn(fminf(fmaxf(v, 0.0f), 255.0f), kRound)));
     else
         store_elem<DK>(dst, v);
+}
+
+// Affine step + cast + store of the three channels of one pixel. The two forms of the affine step are separate code
+// paths so that the choice costs one uniform branch per pixel, not one per channel.
+template<int DK>
+__device__ __forceinline__ void emit_pixel(const ResizeKParams &p, const ChanOff &co, float v0, float v1, float v2,
+                                           uint8_t *dstPix)
+{
+    if (p.perChannel)
+    {
+        v0 = __fadd_rn(__fmul_rn(__fmul_rn(__fsub_rn(v0, p.base[0]), p.mul[0]), p.gscale), p.shift);
+        v1 = __fadd_rn(__fmul_rn(__fmul_rn(__fsub_rn(v1, p.base[1]), p.mul[1]), p.gscale), p.shift);
+        v2 = __fadd_rn(__fmul_rn(__fmul_rn(__fsub_rn(v2, p.base[2]), p.mul[2]), p.gscale), p.shift);
+    }
+    else
+    {
+        v0 = __fadd_rn(__fmul_rn(p.scale, v0), p.offset);
+        v1 = __fadd_rn(__fmul_rn(p.scale, v1), p.offset);
+        v2 = __fadd_rn(__fmul_rn(p.scale, v2), p.offset);
+    }
+    store_value<DK>(v0, dstPix + co.c[0]);
+    store_value<DK>(v1, dstPix + co.c[1]);
+    store_value<DK>(v2, dstPix + co.c[2]);
 }
 
 // One destination pixel of the linear path. r0/r1 point at byte 0 of the two tapped source rows in whatever memory
@@ -88,31 +110,33 @@ __device__ __forceinline__ void linear_pixel(const ResizeKParams &p, const ChanO
                                              const uint8_t *r1, int o0, int o1, float wx0s, float wx1s, float wy0s,
                                              float wy1s, uint8_t *dstPix)
 {
+    float v[3];
 #pragma unroll
     for (int c = 0; c < 3; ++c)
+        v[c] = blend4(raw_byte(r0 + o0 + c), raw_byte(r0 + o1 + c), raw_byte(r1 + o0 + c), raw_byte(r1 + o1 + c), wx0s,
+                      wx1s, wy0s, wy1s);
+    if (p.srcCast)
     {
-        float v = blend4(raw_byte(r0 + o0 + c), raw_byte(r0 + o1 + c), raw_byte(r1 + o0 + c), raw_byte(r1 + o1 + c), wx0s,
-                         wx1s, wy0s, wy1s);
-        if (p.srcCast)
-            v = round_sat_u8(v);
-        emit<DK>(p, c, v, dstPix + co.c[c]);
+        v[0] = round_sat_u8(v[0]);
+        v[1] = round_sat_u8(v[1]);
+        v[2] = round_sat_u8(v[2]);
     }
+    emit_pixel<DK>(p, co, v[0], v[1], v[2], dstPix);
 }
 
 template<int DK>
 __device__ __forceinline__ void nearest_pixel(const ResizeKParams &p, const ChanOff &co, const uint8_t *r0, int o0,
                                               uint8_t *dstPix)
 {
-#pragma unroll
-    for (int c = 0; c < 3; ++c)
-        emit<DK>(p, c, __fmul_rn(__fmul_rn(raw_byte(r0 + o0 + c), kTwo127), kTwo22), dstPix + co.c[c]);
+    emit_pixel<DK>(p, co, __fmul_rn(__fmul_rn(raw_byte(r0 + o0), kTwo127), kTwo22),
+                   __fmul_rn(__fmul_rn(raw_byte(r0 + o0 + 1), kTwo127), kTwo22),
+                   __fmul_rn(__fmul_rn(raw_byte(r0 + o0 + 2), kTwo127), kTwo22), dstPix);
 }
 
 template<int DK>
 __device__ __forceinline__ void pad_pixel(const ResizeKParams &p, const ChanOff &co, uint8_t *dstPix)
 {
-#pragma unroll
-    for (int c = 0; c < 3; ++c) emit<DK>(p, c, p.padValue, dstPix + co.c[c]);
+    emit_pixel<DK>(p, co, p.padValue, p.padValue, p.padValue, dstPix);
 }
 
 // ------------------------------------------------------------------------------------------------ gather kernel
