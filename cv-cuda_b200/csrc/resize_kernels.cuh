@@ -133,10 +133,26 @@ __device__ __forceinline__ void nearest_pixel(const ResizeKParams &p, const Chan
                    __fmul_rn(__fmul_rn(raw_byte(r0 + o0 + 2), kTwo127), kTwo22), dstPix);
 }
 
-template<int DK>
-__device__ __forceinline__ void pad_pixel(const ResizeKParams &p, const ChanOff &co, uint8_t *dstPix)
+// Destination values of a pixel outside the placed region: the pad value pushed through the affine step, the same for
+// every such pixel of a launch, so each thread works them out once.
+struct PadValues
 {
-    emit_pixel<DK>(p, co, p.padValue, p.padValue, p.padValue, dstPix);
+    float v[3];
+};
+
+__device__ __forceinline__ PadValues pad_values(const ResizeKParams &p)
+{
+    PadValues pv;
+#pragma unroll
+    for (int c = 0; c < 3; ++c) pv.v[c] = affine(p, c, p.padValue);
+    return pv;
+}
+
+template<int DK>
+__device__ __forceinline__ void pad_pixel(const PadValues &pv, const ChanOff &co, uint8_t *dstPix)
+{
+#pragma unroll
+    for (int c = 0; c < 3; ++c) store_value<DK>(pv.v[c], dstPix + co.c[c]);
 }
 
 // ------------------------------------------------------------------------------------------------ gather kernel
@@ -148,7 +164,8 @@ __global__ void __launch_bounds__(256) resize_gather_kernel(const ResizeKParams 
     const int y = blockIdx.y * blockDim.y + threadIdx.y;
     if (x >= p.dstW || y >= p.dstH)
         return;
-    const ChanOff co = chan_offsets(p);
+    const ChanOff   co = chan_offsets(p);
+    const PadValues pv = pad_values(p);
 
     for (int n = blockIdx.z; n < p.numSamples; n += gridDim.z)
     {
@@ -156,7 +173,7 @@ __global__ void __launch_bounds__(256) resize_gather_kernel(const ResizeKParams 
         const int rx = x - p.dstX, ry = y - p.dstY;
         if (rx < 0 || ry < 0 || rx >= p.regionW || ry >= p.regionH)
         {
-            pad_pixel<DK>(p, co, dstPix);
+            pad_pixel<DK>(pv, co, dstPix);
             continue;
         }
         const Geom g  = load_geom(p, n);
@@ -333,13 +350,13 @@ __device__ __forceinline__ ColTap make_tap(const ResizeKParams &p, const UnitInf
 
 // One destination pixel from rows r0/r1 whose first byte is source-row byte `origin`.
 template<int INTERP, int DK>
-__device__ __forceinline__ void consume_pixel(const ResizeKParams &p, const ChanOff &co, const UnitInfo &info,
-                                              const ColTap &t, const uint8_t *r0, const uint8_t *r1, int origin,
-                                              uint8_t *dstRow)
+__device__ __forceinline__ void consume_pixel(const ResizeKParams &p, const ChanOff &co, const PadValues &pv,
+                                              const UnitInfo &info, const ColTap &t, const uint8_t *r0, const uint8_t *r1,
+                                              int origin, uint8_t *dstRow)
 {
     uint8_t *dstPix = dstRow + t.dstOff;
     if (t.o0 < 0)
-        pad_pixel<DK>(p, co, dstPix);
+        pad_pixel<DK>(pv, co, dstPix);
     else if constexpr (INTERP == B200PP_INTERP_NEAREST)
         nearest_pixel<DK>(p, co, r0, t.o0 - origin, dstPix);
     else
@@ -351,8 +368,8 @@ __device__ __forceinline__ void consume_pixel(const ResizeKParams &p, const Chan
 // The taps of a thread's first KC columns stay in registers while consecutive units share a tap key, which for a dense
 // batch is the whole launch. KC is a template parameter because every cached column costs six registers.
 template<int INTERP, int DK, int KC>
-__device__ __forceinline__ void consume_columns(const ResizeKParams &p, const ChanOff &co, const UnitInfo &info,
-                                                const uint8_t *r0, const uint8_t *r1, int origin, uint8_t *dstRow,
+__device__ __forceinline__ void consume_columns(const ResizeKParams &p, const ChanOff &co, const PadValues &pv,
+                                                const UnitInfo &info, const uint8_t *r0, const uint8_t *r1, int origin, uint8_t *dstRow,
                                                 int ct, int consumerThreads, ColTap (&cache)[KC], bool refresh)
 {
 #pragma unroll
@@ -363,13 +380,13 @@ __device__ __forceinline__ void consume_columns(const ResizeKParams &p, const Ch
         {
             if (refresh)
                 cache[k] = make_tap<INTERP>(p, info, x);
-            consume_pixel<INTERP, DK>(p, co, info, cache[k], r0, r1, origin, dstRow);
+            consume_pixel<INTERP, DK>(p, co, pv, info, cache[k], r0, r1, origin, dstRow);
         }
     }
     for (int x = info.x0 + ct + KC * consumerThreads; x < info.x1; x += consumerThreads)
     {
         const ColTap t = make_tap<INTERP>(p, info, x);
-        consume_pixel<INTERP, DK>(p, co, info, t, r0, r1, origin, dstRow);
+        consume_pixel<INTERP, DK>(p, co, pv, info, t, r0, r1, origin, dstRow);
     }
 }
 
@@ -580,7 +597,8 @@ __global__ void __launch_bounds__(512) resize_staged_kernel(const ResizeKParams 
 
     // ========================================================================= consumers
     const int     ct         = threadIdx.x - kProducerThreads;
-    const ChanOff co         = chan_offsets(p);
+    const ChanOff   co       = chan_offsets(p);
+    const PadValues pv       = pad_values(p);
     long long     cachedKey  = -1;
     int           s          = 0;
     unsigned      fullParity = 0;
@@ -597,7 +615,7 @@ __global__ void __launch_bounds__(512) resize_staged_kernel(const ResizeKParams 
 
         if (info.mode == UNIT_PAD)
         {
-            for (int x = info.x0 + ct; x < info.x1; x += consumerThreads) pad_pixel<DK>(p, co, dstRow + x * p.dPix);
+            for (int x = info.x0 + ct; x < info.x1; x += consumerThreads) pad_pixel<DK>(pv, co, dstRow + x * p.dPix);
         }
         else
         {
@@ -608,12 +626,12 @@ __global__ void __launch_bounds__(512) resize_staged_kernel(const ResizeKParams 
                 // Its own call site: the row pointers visibly derive from the shared-memory ring, so the tap reads
                 // compile to shared-memory loads.
                 const uint8_t *r0 = ring + s * slotBytes;
-                consume_columns<INTERP, DK, KC>(p, co, info, r0, info.sameRow ? r0 : r0 + cfg.segBytes, info.segOrigin,
+                consume_columns<INTERP, DK, KC>(p, co, pv, info, r0, info.sameRow ? r0 : r0 + cfg.segBytes, info.segOrigin,
                                             dstRow, ct, consumerThreads, cache, refresh);
             }
             else
             {
-                consume_columns<INTERP, DK, KC>(p, co, info, info.g0, info.g1, 0, dstRow, ct, consumerThreads, cache,
+                consume_columns<INTERP, DK, KC>(p, co, pv, info, info.g0, info.g1, 0, dstRow, ct, consumerThreads, cache,
                                             refresh);
             }
         }

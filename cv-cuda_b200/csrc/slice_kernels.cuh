@@ -170,7 +170,7 @@ __global__ void __launch_bounds__(256) slice_gather_kernel(const SliceKParams p,
 // vector store (a warp writes 512 contiguous bytes per channel). Anything else (crop edge, border, ragged end of a
 // row) goes through slice_pixel.
 template<int DK>
-__global__ void __launch_bounds__(256) slice_u8x3_kernel(const SliceKParams p, const int dstType, const int vecStore)
+__global__ void __launch_bounds__(256, 5) slice_u8x3_kernel(const SliceKParams p, const int dstType, const int vecStore)
 {
     const int j0 = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
     const int i  = blockIdx.y * blockDim.y + threadIdx.y;
