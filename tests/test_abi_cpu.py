@@ -60,3 +60,14 @@ def test_argument_checks_need_no_gpu(pkg):
     assert L.b200ppResizeCropConvertReformat(ctypes.byref(s), ctypes.byref(d), ctypes.byref(op), None) \
         == ops.Status.ERROR_INVALID_ARGUMENT
     assert pkg.launch_count() == 0 or True
+
+
+def test_public_headers_compile_as_c11_and_cxx11(tmp_path):
+    """Like the reference's header checks (tests/cvcuda/system/CMakeLists.txt:105-126): every public header is valid
+    C11 and C++11 on its own, without the CUDA toolkit on the include path."""
+    for name in sorted(os.listdir(INCLUDE)):
+        for compiler, std, ext in (("gcc", "-std=c11", "c"), ("g++", "-std=c++11", "cpp")):
+            src = tmp_path / f"use_{name.replace('.', '_')}.{ext}"
+            src.write_text(f'#include <cvcuda_b200/{name}>\nint main(void) {{ return 0; }}\n')
+            subprocess.check_call([compiler, std, "-Wall", "-Werror", "-pedantic-errors", "-fsyntax-only",
+                                   "-I" + os.path.join(ROOT, "include"), str(src)])

@@ -327,3 +327,89 @@ def test_offsets_beyond_two_gib(pkg, oracle):
         assert_parity(got, want, what=f"path {path}")
         assert float(out[1:n - 1].abs().max()) == 0.0
     del src
+
+
+def test_one_handle_many_threads_and_streams(pkg, oracle):
+    """Operators hold no mutable state: several host threads, each on its own stream, run different shapes at once."""
+    import threading
+    rng = np.random.default_rng(21)
+    cases = []
+    for k in range(4):
+        w, h = 200 + 37 * k, 150 + 21 * k
+        src = rng.integers(0, 256, (3, h, w, 3), dtype=np.uint8)
+        spec = oracle.ResizeSpec(resize=(96 + 8 * k, 80), crop=(k, 2 * k), out_size=(64, 48), interp=k % 2, src_cast=False,
+                                 manip=k % 2, scale=0.5, offset=float(k))
+        cases.append((src, spec, oracle.resize_crop(list(src), spec, np.float32, True)))
+    results, errors = [None] * 4, []
+
+    def work(k):
+        try:
+            src, spec, _ = cases[k]
+            stream = torch.cuda.Stream()
+            tsrc = to_dev(src)
+            torch.cuda.synchronize()
+            with torch.cuda.stream(stream):
+                for _ in range(20):
+                    out = pkg.resize_crop_convert_reformat(tsrc, spec.resize, spec.interp, (*spec.crop, 64, 48),
+                                                           layout="NCHW", data_type=torch.float32, manip=spec.manip,
+                                                           scale=0.5, offset=float(k), srcCast=False, stream=stream)
+            stream.synchronize()
+            results[k] = out.cpu().numpy()
+        except Exception as e:  # noqa: BLE001
+            errors.append(e)
+
+    threads = [threading.Thread(target=work, args=(k,)) for k in range(4)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors
+    for k in range(4):
+        assert_parity(results[k], cases[k][2], exact=(cases[k][1].interp == 0), what=f"thread {k}")
+    assert pkg.read_device_error() == 0
+
+
+@pytest.mark.parametrize("interp", [0, 1])
+@pytest.mark.parametrize("dtype,planar", [(np.uint8, False), (np.float16, True), (np.float32, False)])
+def test_region_placement_roi_and_all_flip_codes(pkg, oracle, interp, dtype, planar):
+    """A region placed off both edges of a larger canvas, per-sample regions of interest and every flip code,
+    on a variable-shape batch with odd pitches."""
+    rng = np.random.default_rng(77 + interp)
+    sizes = [(151, 93), (64, 200), (333, 47), (90, 90), (1203, 77)]
+    images = [rng.integers(0, 256, (h, w, 3), dtype=np.uint8) for w, h in sizes]
+    rois = np.array([(3, 5, 120, 80), (0, 0, 64, 200), (100, 7, 233, 40), (17, 29, 50, 33), (2, 1, 1200, 70)], np.int32)
+    flips = np.array([1, 0, -1, 2, 1], np.int32)
+    spec = oracle.ResizeSpec(resize=(66, 44), crop=(4, 3), out_size=(60, 40), interp=interp, src_cast=True, manip=1,
+                             base=(1.0, 2.0, 3.0), mul=(0.5, 0.25, 2.0), gscale=1.5, shift=-4.0, canvas=(100, 80),
+                             dst_pos=(13, 7), pad_value=114.0)
+    want = oracle.resize_crop(images, spec, dtype, planar, roi=rois, flip=flips)
+    for pad_to, offset in ((32, 0), (1, 3)):
+        batch = pkg.ImageBatchVarShape(padded_images(images, pad_to=pad_to, offset=offset))
+        for path in PATHS:
+            shape = (5, 3, 80, 100) if planar else (5, 80, 100, 3)
+            out = torch.zeros(shape, dtype=_torch_dtype(dtype), device="cuda")
+            with kernel_path(pkg, path):
+                pkg.fused_preprocess_into(out, batch, resize_dim=(66, 44), interp=interp, crop_pos=(4, 3),
+                                          layout="NCHW" if planar else "NHWC", manip=1, base=(1.0, 2.0, 3.0),
+                                          mul=(0.5, 0.25, 2.0), gscale=1.5, shift=-4.0, srcCast=True, roi=to_dev(rois),
+                                          flip_code=to_dev(flips), dst_pos=(13, 7), region_size=(60, 40), pad_value=114.0)
+                torch.cuda.synchronize()
+            assert_parity(out.cpu().numpy(), want, exact=(interp == 0), what=f"pad {pad_to} path {path}")
+    assert pkg.read_device_error() == 0
+
+
+def test_wide_rows_in_chunks_with_horizontal_flip(pkg, oracle):
+    """Rows whose source span exceeds a shared-memory slot are processed in column chunks; mirrored columns walk the
+    chunks from the other end."""
+    rng = np.random.default_rng(5)
+    src = rng.integers(0, 256, (2, 6, 20000, 3), dtype=np.uint8)
+    flips = np.array([1, -1], np.int32)
+    spec = oracle.ResizeSpec(resize=(5000, 6), crop=(10, 0), out_size=(4980, 6), interp=1, src_cast=False, scale=0.5)
+    want = oracle.resize_crop(list(src), spec, np.float32, True, flip=flips, nthreads=4)
+    for path in PATHS:
+        out = torch.empty((2, 3, 6, 4980), dtype=torch.float32, device="cuda")
+        with kernel_path(pkg, path):
+            pkg.fused_preprocess_into(out, to_dev(src), resize_dim=(5000, 6), interp=1, crop_pos=(10, 0), layout="NCHW",
+                                      scale=0.5, srcCast=False, flip_code=to_dev(flips))
+            torch.cuda.synchronize()
+        assert_parity(out.cpu().numpy(), want, what=f"path {path}")
