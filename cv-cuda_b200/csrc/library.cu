@@ -465,7 +465,8 @@ extern "C" int b200ppCropFlipNormalizeReformat(const B200ppSource *src, const B2
                                 | static_cast<unsigned long long>(kp.dChan) | static_cast<unsigned long long>(kp.dSample))
                                % vec)
                                   == 0;
-        dim3 grid((kp.dstW + 127) / 128, (kp.dstH + 7) / 8, std::min(kp.numSamples, 32768));
+        const int rowsPerBlock = 8 * kSliceRowsPerThread;
+        dim3      grid((kp.dstW + 127) / 128, (kp.dstH + rowsPerBlock - 1) / rowsPerBlock, std::min(kp.numSamples, 32768));
         if (dst->dtype == B200PP_F32)
             slice_u8x3_kernel<DST_F32><<<grid, block, 0, stream>>>(kp, dst->dtype, vecStore);
         else if (dst->dtype == B200PP_F16)

@@ -164,17 +164,37 @@ __global__ void __launch_bounds__(256) slice_gather_kernel(const SliceKParams p,
 }
 
 // Fast kernel for the pre-processing case: interleaved 3-channel uint8 sources to uint8 / float32 / float16.
-// A thread produces four adjacent destination pixels of one row. When they all lie inside the crop and their four
-// source pixels inside the image, the twelve source bytes come in as aligned words, bytes become floats with one PRMT
-// and one exact subtraction each, and -- for planar, suitably aligned destinations -- each channel leaves as one
-// vector store (a warp writes 512 contiguous bytes per channel). Anything else (crop edge, border, ragged end of a
-// row) goes through slice_pixel.
+// A thread produces four adjacent destination pixels in each of kSliceRowsPerThread rows (the per-launch constants and
+// the sample's descriptors are fetched once per thread, not once per pixel group). When the four pixels all lie
+// inside the crop and their source pixels inside the image, the twelve source bytes come in as aligned words, bytes
+// become floats with one PRMT and one exact subtraction each, and -- for planar, suitably aligned destinations -- each
+// channel leaves as one vector store (a warp writes 512 contiguous bytes per channel). Anything else (crop edge,
+// border, ragged end of a row) goes through slice_pixel.
+constexpr int kSliceRowsPerThread = 4;
+
+template<int DK>
+__device__ __forceinline__ void store_four(uint8_t *d, float a, float b, float c, float e)
+{
+    if constexpr (DK == DST_F32)
+        *reinterpret_cast<float4 *>(d) = make_float4(a, b, c, e);
+    else if constexpr (DK == DST_F16)
+    {
+        const __half2 lo = __floats2half2_rn(a, b), hi = __floats2half2_rn(c, e);
+        uint2         v;
+        v.x = *reinterpret_cast<const unsigned *>(&lo);
+        v.y = *reinterpret_cast<const unsigned *>(&hi);
+        *reinterpret_cast<uint2 *>(d) = v;
+    }
+    else
+        *reinterpret_cast<unsigned *>(d) = sat_u8(a) | sat_u8(b) << 8 | sat_u8(c) << 16 | sat_u8(e) << 24;
+}
+
 template<int DK>
 __global__ void __launch_bounds__(256, 5) slice_u8x3_kernel(const SliceKParams p, const int dstType, const int vecStore)
 {
     const int j0 = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
-    const int i  = blockIdx.y * blockDim.y + threadIdx.y;
-    if (j0 >= p.dstW || i >= p.dstH)
+    const int iBase = blockIdx.y * (blockDim.y * kSliceRowsPerThread) + threadIdx.y;
+    if (j0 >= p.dstW || iBase >= p.dstH)
         return;
     float base[3], mul[3];
     load_constants<3>(p, base, mul);
@@ -185,85 +205,82 @@ __global__ void __launch_bounds__(256, 5) slice_u8x3_kernel(const SliceKParams p
         const SliceSample s = load_slice_sample(p, n);
 
         const bool flipX = (s.flip == 1 || s.flip == -1);
-        const int  y     = (s.flip == 0 || s.flip == -1) ? s.ch - 1 - i + s.cy : i + s.cy;
+        const bool flipY = (s.flip == 0 || s.flip == -1);
         const int  xlo   = flipX ? s.cw - 1 - (j0 + 3) + s.cx : j0 + s.cx; // leftmost of the four source pixels
-        const bool fast  = cols == 4 && i < s.ch && j0 + 3 < s.cw && y >= 0 && y < s.h && xlo >= 0 && xlo + 3 < s.w;
-        if (!fast)
-        {
-            for (int q = 0; q < cols; ++q) slice_pixel<3>(p, s, n, i, j0 + q, B200PP_U8, dstType, 1, base, mul);
-            continue;
-        }
+        const bool colsFast = cols == 4 && j0 + 3 < s.cw && xlo >= 0 && xlo + 3 < s.w;
+        const bool rowAligned = (reinterpret_cast<unsigned long long>(s.img) & 3ull) == 0 && (s.pitch & 3ll) == 0;
 
-        // twelve source bytes as three words, byte 3q+c = channel c of source pixel xlo+q
-        const uint8_t *a = s.img + y * s.pitch + 3ll * xlo;
-        unsigned       w0, w1, w2;
-        const unsigned long long addr = reinterpret_cast<unsigned long long>(a);
-        const unsigned long long row  = reinterpret_cast<unsigned long long>(s.img + y * s.pitch);
-        if ((row & 3ull) == 0 && (s.pitch & 3ll) == 0 && (addr & ~3ull) + 16 <= row + static_cast<unsigned long long>(s.pitch))
+#pragma unroll 1
+        for (int r = 0; r < kSliceRowsPerThread; ++r)
         {
-            // aligned window of four words inside the row's pitch; shift the twelve bytes into place
-            const unsigned *wp = reinterpret_cast<const unsigned *>(addr & ~3ull);
-            const unsigned  sh = static_cast<unsigned>(addr & 3ull) * 8;
-            const unsigned  t0 = __ldg(wp), t1 = __ldg(wp + 1), t2 = __ldg(wp + 2), t3 = __ldg(wp + 3);
-            w0 = __funnelshift_r(t0, t1, sh);
-            w1 = __funnelshift_r(t1, t2, sh);
-            w2 = __funnelshift_r(t2, t3, sh);
-        }
-        else
-        {
-            unsigned b[12];
-#pragma unroll
-            for (int k = 0; k < 12; ++k) b[k] = a[k];
-            w0 = b[0] | b[1] << 8 | b[2] << 16 | b[3] << 24;
-            w1 = b[4] | b[5] << 8 | b[6] << 16 | b[7] << 24;
-            w2 = b[8] | b[9] << 8 | b[10] << 16 | b[11] << 24;
-        }
-        const unsigned words[3] = {w0, w1, w2};
-
-        float o[4][3]; // [destination column q][channel]
-#pragma unroll
-        for (int q = 0; q < 4; ++q)
-#pragma unroll
-            for (int c = 0; c < 3; ++c)
+            const int i = iBase + r * blockDim.y;
+            if (i >= p.dstH)
+                break;
+            const int y = flipY ? s.ch - 1 - i + s.cy : i + s.cy;
+            if (!(colsFast && i < s.ch && y >= 0 && y < s.h))
             {
-                const int   byte = 3 * q + c;
-                const float v    = byte_as_float(words[byte >> 2], 0x7540u + (byte & 3));
-                const float r    = __fadd_rn(__fmul_rn(__fmul_rn(__fsub_rn(v, base[c]), mul[c]), p.gscale), p.shift);
-                // source pixel q lands in destination column q, or 3-q when mirrored
-                if (flipX)
-                    o[3 - q][c] = r;
-                else
-                    o[q][c] = r;
+                for (int q = 0; q < cols; ++q) slice_pixel<3>(p, s, n, i, j0 + q, B200PP_U8, dstType, 1, base, mul);
+                continue;
             }
 
-        uint8_t *dst = p.dst + n * p.dSample + i * p.dRow + j0 * p.dPix;
-        if (vecStore)
-        {
-#pragma unroll
-            for (int c = 0; c < 3; ++c)
+            // twelve source bytes as three words, byte 3q+c = channel c of source pixel xlo+q
+            const uint8_t           *rowPtr = s.img + y * s.pitch;
+            const uint8_t           *a      = rowPtr + 3ll * xlo;
+            const unsigned long long addr   = reinterpret_cast<unsigned long long>(a);
+            unsigned                 w0, w1, w2;
+            if (rowAligned && (addr & ~3ull) + 16 <= reinterpret_cast<unsigned long long>(rowPtr) + static_cast<unsigned long long>(s.pitch))
             {
-                uint8_t *d = dst + c * p.dChan;
-                if constexpr (DK == DST_F32)
-                    *reinterpret_cast<float4 *>(d) = make_float4(o[0][c], o[1][c], o[2][c], o[3][c]);
-                else if constexpr (DK == DST_F16)
-                {
-                    const __half2 lo = __floats2half2_rn(o[0][c], o[1][c]), hi = __floats2half2_rn(o[2][c], o[3][c]);
-                    uint2         v;
-                    v.x = *reinterpret_cast<const unsigned *>(&lo);
-                    v.y = *reinterpret_cast<const unsigned *>(&hi);
-                    *reinterpret_cast<uint2 *>(d) = v;
-                }
-                else
-                    *reinterpret_cast<unsigned *>(d) = sat_u8(o[0][c]) | sat_u8(o[1][c]) << 8 | sat_u8(o[2][c]) << 16
-                                                     | sat_u8(o[3][c]) << 24;
+                // aligned window of four words inside the row's pitch; shift the twelve bytes into place
+                const unsigned *wp = reinterpret_cast<const unsigned *>(addr & ~3ull);
+                const unsigned  sh = static_cast<unsigned>(addr & 3ull) * 8;
+                const unsigned  t0 = __ldg(wp), t1 = __ldg(wp + 1), t2 = __ldg(wp + 2), t3 = __ldg(wp + 3);
+                w0 = __funnelshift_r(t0, t1, sh);
+                w1 = __funnelshift_r(t1, t2, sh);
+                w2 = __funnelshift_r(t2, t3, sh);
             }
-        }
-        else
-        {
+            else
+            {
+                unsigned b[12];
+#pragma unroll
+                for (int k = 0; k < 12; ++k) b[k] = a[k];
+                w0 = b[0] | b[1] << 8 | b[2] << 16 | b[3] << 24;
+                w1 = b[4] | b[5] << 8 | b[6] << 16 | b[7] << 24;
+                w2 = b[8] | b[9] << 8 | b[10] << 16 | b[11] << 24;
+            }
+            const unsigned words[3] = {w0, w1, w2};
+
+            float o[4][3]; // [source pixel q][channel]
 #pragma unroll
             for (int q = 0; q < 4; ++q)
 #pragma unroll
-                for (int c = 0; c < 3; ++c) store_elem<DK>(dst + q * p.dPix + c * p.dChan, o[q][c]);
+                for (int c = 0; c < 3; ++c)
+                {
+                    const int   byte = 3 * q + c;
+                    const float v    = byte_as_float(words[byte >> 2], 0x7540u + (byte & 3));
+                    o[q][c] = __fadd_rn(__fmul_rn(__fmul_rn(__fsub_rn(v, base[c]), mul[c]), p.gscale), p.shift);
+                }
+
+            // source pixel q lands in destination column q, or 3-q when mirrored
+            uint8_t *dst = p.dst + n * p.dSample + i * p.dRow + j0 * p.dPix;
+            if (vecStore)
+            {
+#pragma unroll
+                for (int c = 0; c < 3; ++c)
+                {
+                    if (flipX)
+                        store_four<DK>(dst + c * p.dChan, o[3][c], o[2][c], o[1][c], o[0][c]);
+                    else
+                        store_four<DK>(dst + c * p.dChan, o[0][c], o[1][c], o[2][c], o[3][c]);
+                }
+            }
+            else
+            {
+#pragma unroll
+                for (int q = 0; q < 4; ++q)
+#pragma unroll
+                    for (int c = 0; c < 3; ++c)
+                        store_elem<DK>(dst + (flipX ? 3 - q : q) * p.dPix + c * p.dChan, o[q][c]);
+            }
         }
     }
 }
