@@ -206,10 +206,20 @@ static int launch_resize_staged(const ResizeKParams &kp, int srcWBound, cudaStre
     // columns per consumer thread whose taps are kept in registers
     const int perThread = (cfg.chunkCols + consumers - 1) / consumers;
     const int kc        = std::min(3, std::max(1, perThread));
-    auto      kernel    = kc == 1   ? resize_staged_kernel<INTERP, DK, 1>
-                        : kc == 2 ? resize_staged_kernel<INTERP, DK, 2>
-                                  : resize_staged_kernel<INTERP, DK, 3>;
-    const int occ       = staged_occupancy(kernel, dev, (INTERP * 4 + DK) * 4 + kc, block, smemBytes, facts.maxSmemOptin);
+    // interleaved destinations (uint8 / float32) are written through the warp-transposing store
+    const int  elem = DK == DST_F32 ? 4 : (DK == DST_F16 ? 2 : 1);
+    const bool il   = DK != DST_F16 && kp.dPix == 3 * elem && kp.dChan == elem;
+    auto       kernel = resize_staged_kernel<INTERP, DK, 1, false>;
+    if (il)
+        kernel = kc == 1 ? resize_staged_kernel<INTERP, DK, 1, true>
+               : kc == 2 ? resize_staged_kernel<INTERP, DK, 2, true>
+                         : resize_staged_kernel<INTERP, DK, 3, true>;
+    else
+        kernel = kc == 1 ? resize_staged_kernel<INTERP, DK, 1, false>
+               : kc == 2 ? resize_staged_kernel<INTERP, DK, 2, false>
+                         : resize_staged_kernel<INTERP, DK, 3, false>;
+    const int occ = staged_occupancy(kernel, dev, ((INTERP * 4 + DK) * 4 + kc) * 2 + (il ? 1 : 0), block, smemBytes,
+                                     facts.maxSmemOptin);
     if (occ <= 0)
         return 0;
     const int       perSm = tuning().maxCtasPerSm > 0 ? std::min(occ, tuning().maxCtasPerSm) : occ;
@@ -230,7 +240,10 @@ static int run_resize(const ResizeKParams &kp, int srcWBound, cudaStream_t strea
 {
     const int path = g_kernelPath.load(std::memory_order_relaxed);
     // The staged kernel writes one destination row per unit with warp-contiguous stores; tiny outputs gain nothing.
-    const bool wantStaged = path == 2 || (path == 0 && kp.dstW >= 32);
+    // It also fetches whole row segments: beyond a 32x horizontal reduction (96 source bytes per destination column)
+    // the taps skip whole 32-byte sectors and the per-pixel gather moves fewer bytes.
+    const bool sparseTaps = static_cast<long long>(srcWBound) > 32ll * kp.resizeW;
+    const bool wantStaged = path == 2 || (path == 0 && kp.dstW >= 32 && !sparseTaps);
     if (wantStaged)
     {
         int status = B200PP_SUCCESS;

@@ -79,58 +79,46 @@ __device__ __forceinline__ void store_value(float v, uint8_t *dst)
         store_elem<DK>(dst, v);
 }
 
-// Affine step + cast + store of the three channels of one pixel. The two forms of the affine step are separate code
-// paths so that the choice costs one uniform branch per pixel, not one per channel.
-template<int DK>
-__device__ __forceinline__ void emit_pixel(const ResizeKParams &p, const ChanOff &co, float v0, float v1, float v2,
-                                           uint8_t *dstPix)
+// The affine step on the three channels of one pixel (v[c] belongs to source channel c). The two forms are separate
+// code paths so that the choice costs one uniform branch per pixel, not one per channel.
+__device__ __forceinline__ void affine3(const ResizeKParams &p, float (&v)[3])
 {
     if (p.perChannel)
     {
-        v0 = __fadd_rn(__fmul_rn(__fmul_rn(__fsub_rn(v0, p.base[0]), p.mul[0]), p.gscale), p.shift);
-        v1 = __fadd_rn(__fmul_rn(__fmul_rn(__fsub_rn(v1, p.base[1]), p.mul[1]), p.gscale), p.shift);
-        v2 = __fadd_rn(__fmul_rn(__fmul_rn(__fsub_rn(v2, p.base[2]), p.mul[2]), p.gscale), p.shift);
+#pragma unroll
+        for (int c = 0; c < 3; ++c)
+            v[c] = __fadd_rn(__fmul_rn(__fmul_rn(__fsub_rn(v[c], p.base[c]), p.mul[c]), p.gscale), p.shift);
     }
     else
     {
-        v0 = __fadd_rn(__fmul_rn(p.scale, v0), p.offset);
-        v1 = __fadd_rn(__fmul_rn(p.scale, v1), p.offset);
-        v2 = __fadd_rn(__fmul_rn(p.scale, v2), p.offset);
+#pragma unroll
+        for (int c = 0; c < 3; ++c) v[c] = __fadd_rn(__fmul_rn(p.scale, v[c]), p.offset);
     }
-    store_value<DK>(v0, dstPix + co.c[0]);
-    store_value<DK>(v1, dstPix + co.c[1]);
-    store_value<DK>(v2, dstPix + co.c[2]);
 }
 
-// One destination pixel of the linear path. r0/r1 point at byte 0 of the two tapped source rows in whatever memory
-// they live in; o0/o1 are the byte offsets of the left/right tap pixel. Weights are pre-scaled:
+// Final values of one destination pixel of the linear path. r0/r1 point at byte 0 of the two tapped source rows in
+// whatever memory they live in; o0/o1 are the byte offsets of the left/right tap pixel. Weights are pre-scaled:
 // wy*s = wy * 2^127, wx*s = wx * 2^22.
-template<int DK>
-__device__ __forceinline__ void linear_pixel(const ResizeKParams &p, const ChanOff &co, const uint8_t *r0,
-                                             const uint8_t *r1, int o0, int o1, float wx0s, float wx1s, float wy0s,
-                                             float wy1s, uint8_t *dstPix)
+__device__ __forceinline__ void linear_values(const ResizeKParams &p, const uint8_t *r0, const uint8_t *r1, int o0, int o1,
+                                              float wx0s, float wx1s, float wy0s, float wy1s, float (&v)[3])
 {
-    float v[3];
 #pragma unroll
     for (int c = 0; c < 3; ++c)
         v[c] = blend4(raw_byte(r0 + o0 + c), raw_byte(r0 + o1 + c), raw_byte(r1 + o0 + c), raw_byte(r1 + o1 + c), wx0s,
                       wx1s, wy0s, wy1s);
     if (p.srcCast)
     {
-        v[0] = round_sat_u8(v[0]);
-        v[1] = round_sat_u8(v[1]);
-        v[2] = round_sat_u8(v[2]);
+#pragma unroll
+        for (int c = 0; c < 3; ++c) v[c] = round_sat_u8(v[c]);
     }
-    emit_pixel<DK>(p, co, v[0], v[1], v[2], dstPix);
+    affine3(p, v);
 }
 
-template<int DK>
-__device__ __forceinline__ void nearest_pixel(const ResizeKParams &p, const ChanOff &co, const uint8_t *r0, int o0,
-                                              uint8_t *dstPix)
+__device__ __forceinline__ void nearest_values(const ResizeKParams &p, const uint8_t *r0, int o0, float (&v)[3])
 {
-    emit_pixel<DK>(p, co, __fmul_rn(__fmul_rn(raw_byte(r0 + o0), kTwo127), kTwo22),
-                   __fmul_rn(__fmul_rn(raw_byte(r0 + o0 + 1), kTwo127), kTwo22),
-                   __fmul_rn(__fmul_rn(raw_byte(r0 + o0 + 2), kTwo127), kTwo22), dstPix);
+#pragma unroll
+    for (int c = 0; c < 3; ++c) v[c] = __fmul_rn(__fmul_rn(raw_byte(r0 + o0 + c), kTwo127), kTwo22);
+    affine3(p, v);
 }
 
 // Destination values of a pixel outside the placed region: the pad value pushed through the affine step, the same for
@@ -144,15 +132,55 @@ __device__ __forceinline__ PadValues pad_values(const ResizeKParams &p)
 {
     PadValues pv;
 #pragma unroll
-    for (int c = 0; c < 3; ++c) pv.v[c] = affine(p, c, p.padValue);
+    for (int c = 0; c < 3; ++c) pv.v[c] = p.padValue;
+    affine3(p, pv.v);
     return pv;
 }
 
+// Cast + store of the three channels of one pixel through the generic strides (any layout).
 template<int DK>
-__device__ __forceinline__ void pad_pixel(const PadValues &pv, const ChanOff &co, uint8_t *dstPix)
+__device__ __forceinline__ void store_pixel(const float (&v)[3], const ChanOff &co, uint8_t *dstPix)
 {
 #pragma unroll
-    for (int c = 0; c < 3; ++c) store_value<DK>(pv.v[c], dstPix + co.c[c]);
+    for (int c = 0; c < 3; ++c) store_value<DK>(v[c], dstPix + co.c[c]);
+}
+
+// Interleaved (NHWC) destinations: a warp's 32 pixels are 96 consecutive elements in memory, but each lane holds the
+// three channels of one pixel. The channels are transposed across the warp with shuffles so that every store
+// instruction writes consecutive 32-bit words: three fully coalesced stores for float32 (lane L writes elements L,
+// 32+L, 64+L), one for uint8 (lanes 0..23 write the 96 bytes as 24 words). `warpBase` is the address of lane 0's pixel.
+// All 32 lanes must call this.
+template<int DK>
+__device__ __forceinline__ void store_interleaved_warp(const float (&d)[3] /* destination channel order */,
+                                                       uint8_t *warpBase, int lane)
+{
+    if constexpr (DK == DST_F32)
+    {
+#pragma unroll
+        for (int k = 0; k < 3; ++k)
+        {
+            const int   e   = 32 * k + lane; // element index within the warp's 96
+            const int   src = (e * 43) >> 7; // e / 3 for e < 128
+            const int   c   = e - 3 * src;
+            const float a = __shfl_sync(0xffffffffu, d[0], src), b = __shfl_sync(0xffffffffu, d[1], src),
+                        g = __shfl_sync(0xffffffffu, d[2], src);
+            reinterpret_cast<float *>(warpBase)[e] = c == 0 ? a : (c == 1 ? b : g);
+        }
+    }
+    else
+    {
+        // pack this lane's pixel into 24 bits, then word j = bytes 4j..4j+3 straddles pixels p0 = 4j/3 and p0+1
+        const unsigned w = (__float_as_uint(__fadd_rn(fminf(fmaxf(d[0], 0.0f), 255.0f), kRound)) & 0xffu)
+                         | (__float_as_uint(__fadd_rn(fminf(fmaxf(d[1], 0.0f), 255.0f), kRound)) & 0xffu) << 8
+                         | (__float_as_uint(__fadd_rn(fminf(fmaxf(d[2], 0.0f), 255.0f), kRound)) & 0xffu) << 16;
+        const int      b0  = 4 * lane;
+        const int      p0  = (b0 * 43) >> 7; // b0 / 3 (b0 < 128)
+        const int      off = b0 - 3 * p0;
+        const unsigned lo  = __shfl_sync(0xffffffffu, w, p0 & 31);
+        const unsigned hi  = __shfl_sync(0xffffffffu, w, (p0 + 1) & 31);
+        if (lane < 24)
+            reinterpret_cast<unsigned *>(warpBase)[lane] = (lo >> (8 * off)) | (hi << (8 * (3 - off)));
+    }
 }
 
 // ------------------------------------------------------------------------------------------------ gather kernel
@@ -173,7 +201,7 @@ __global__ void __launch_bounds__(256) resize_gather_kernel(const ResizeKParams 
         const int rx = x - p.dstX, ry = y - p.dstY;
         if (rx < 0 || ry < 0 || rx >= p.regionW || ry >= p.regionH)
         {
-            pad_pixel<DK>(pv, co, dstPix);
+            store_pixel<DK>(pv.v, co, dstPix);
             continue;
         }
         const Geom g  = load_geom(p, n);
@@ -184,7 +212,9 @@ __global__ void __launch_bounds__(256) resize_gather_kernel(const ResizeKParams 
         {
             const int sx = nearest_tap(g.scaleW, dx, g.w);
             const int sy = nearest_tap(g.scaleH, dy, g.h);
-            nearest_pixel<DK>(p, co, g.base + sy * g.pitch, 3 * sx, dstPix);
+            float v[3];
+            nearest_values(p, g.base + sy * g.pitch, 3 * sx, v);
+            store_pixel<DK>(v, co, dstPix);
         }
         else
         {
@@ -192,9 +222,11 @@ __global__ void __launch_bounds__(256) resize_gather_kernel(const ResizeKParams 
             float wx1, wy1;
             linear_tap(g.scaleW, dx, g.w, sx0, sx1, wx1);
             linear_tap(g.scaleH, dy, g.h, sy0, sy1, wy1);
-            linear_pixel<DK>(p, co, g.base + sy0 * g.pitch, g.base + sy1 * g.pitch, 3 * sx0, 3 * sx1,
-                             __fmul_rn(__fsub_rn(1.0f, wx1), kTwo22), __fmul_rn(wx1, kTwo22),
-                             __fmul_rn(__fsub_rn(1.0f, wy1), kTwo127), __fmul_rn(wy1, kTwo127), dstPix);
+            float v[3];
+            linear_values(p, g.base + sy0 * g.pitch, g.base + sy1 * g.pitch, 3 * sx0, 3 * sx1,
+                          __fmul_rn(__fsub_rn(1.0f, wx1), kTwo22), __fmul_rn(wx1, kTwo22),
+                          __fmul_rn(__fsub_rn(1.0f, wy1), kTwo127), __fmul_rn(wy1, kTwo127), v);
+            store_pixel<DK>(v, co, dstPix);
         }
     }
 }
@@ -348,45 +380,88 @@ __device__ __forceinline__ ColTap make_tap(const ResizeKParams &p, const UnitInf
     return t;
 }
 
-// One destination pixel from rows r0/r1 whose first byte is source-row byte `origin`.
-template<int INTERP, int DK>
-__device__ __forceinline__ void consume_pixel(const ResizeKParams &p, const ChanOff &co, const PadValues &pv,
-                                              const UnitInfo &info, const ColTap &t, const uint8_t *r0, const uint8_t *r1,
-                                              int origin, uint8_t *dstRow)
+// Final values of one destination pixel from rows r0/r1 whose first byte is source-row byte `origin`.
+template<int INTERP>
+__device__ __forceinline__ void pixel_values(const ResizeKParams &p, const PadValues &pv, const UnitInfo &info,
+                                             const ColTap &t, const uint8_t *r0, const uint8_t *r1, int origin,
+                                             float (&v)[3])
 {
-    uint8_t *dstPix = dstRow + t.dstOff;
     if (t.o0 < 0)
-        pad_pixel<DK>(pv, co, dstPix);
+    {
+#pragma unroll
+        for (int c = 0; c < 3; ++c) v[c] = pv.v[c];
+    }
     else if constexpr (INTERP == B200PP_INTERP_NEAREST)
-        nearest_pixel<DK>(p, co, r0, t.o0 - origin, dstPix);
+        nearest_values(p, r0, t.o0 - origin, v);
     else
-        linear_pixel<DK>(p, co, r0, r1, t.o0 - origin, t.o1 - origin, t.wx0s, t.wx1s, info.wy0s, info.wy1s, dstPix);
+        linear_values(p, r0, r1, t.o0 - origin, t.o1 - origin, t.wx0s, t.wx1s, info.wy0s, info.wy1s, v);
 }
 
+// How a consumer warp writes its pixels.
+struct StorePlan
+{
+    ChanOff co;
+    bool    interleaved; // destination has the three channels of a pixel adjacent: transpose across the warp
+    bool    reversed;    // channel order reversed
+};
+
+// Stores one pixel per lane of a warp. `x` is this lane's column (lanes hold consecutive columns), `valid` whether it
+// exists. Every lane of the warp must call this.
+template<int DK, bool IL>
+__device__ __forceinline__ void store_warp(const ResizeKParams &p, const StorePlan &plan, const float (&v)[3],
+                                           uint8_t *dstRow, int x, bool valid, int lane)
+{
+    if constexpr (IL && DK != DST_F16)
+    {
+        uint8_t   *warpBase = dstRow + (x - lane) * p.dPix;
+        const bool full     = __all_sync(0xffffffffu, valid) && (reinterpret_cast<unsigned long long>(warpBase) & 3ull) == 0;
+        if (full)
+        {
+            const float d[3] = {plan.reversed ? v[2] : v[0], v[1], plan.reversed ? v[0] : v[2]};
+            store_interleaved_warp<DK>(d, warpBase, lane);
+            return;
+        }
+    }
+    if (valid)
+        store_pixel<DK>(v, plan.co, dstRow + x * p.dPix);
+}
 
 // Columns [x0, x1) of one destination row, strided over the consumer threads so that a warp writes 32 adjacent pixels.
 // The taps of a thread's first KC columns stay in registers while consecutive units share a tap key, which for a dense
 // batch is the whole launch. KC is a template parameter because every cached column costs six registers.
-template<int INTERP, int DK, int KC>
-__device__ __forceinline__ void consume_columns(const ResizeKParams &p, const ChanOff &co, const PadValues &pv,
-                                                const UnitInfo &info, const uint8_t *r0, const uint8_t *r1, int origin, uint8_t *dstRow,
-                                                int ct, int consumerThreads, ColTap (&cache)[KC], bool refresh)
+// Loop trip counts are uniform across a warp (the stores vote and shuffle). IL selects the transposing store for
+// interleaved destinations; planar destinations compile without it.
+template<int INTERP, int DK, int KC, bool IL>
+__device__ __forceinline__ void consume_columns(const ResizeKParams &p, const StorePlan &plan, const PadValues &pv,
+                                                const UnitInfo &info, const uint8_t *r0, const uint8_t *r1, int origin,
+                                                uint8_t *dstRow, int ct, int lane, int consumerThreads,
+                                                ColTap (&cache)[KC], bool refresh)
 {
 #pragma unroll
     for (int k = 0; k < KC; ++k)
     {
-        const int x = info.x0 + ct + k * consumerThreads;
-        if (x < info.x1)
+        const int  x     = info.x0 + ct + k * consumerThreads;
+        const bool valid = x < info.x1;
+        float      v[3]  = {0.f, 0.f, 0.f};
+        if (valid)
         {
             if (refresh)
                 cache[k] = make_tap<INTERP>(p, info, x);
-            consume_pixel<INTERP, DK>(p, co, pv, info, cache[k], r0, r1, origin, dstRow);
+            pixel_values<INTERP>(p, pv, info, cache[k], r0, r1, origin, v);
         }
+        store_warp<DK, IL>(p, plan, v, dstRow, x, valid, lane);
     }
-    for (int x = info.x0 + ct + KC * consumerThreads; x < info.x1; x += consumerThreads)
+    for (int xw = info.x0 + (ct - lane) + KC * consumerThreads; xw < info.x1; xw += consumerThreads)
     {
-        const ColTap t = make_tap<INTERP>(p, info, x);
-        consume_pixel<INTERP, DK>(p, co, pv, info, t, r0, r1, origin, dstRow);
+        const int  x     = xw + lane;
+        const bool valid = x < info.x1;
+        float      v[3]  = {0.f, 0.f, 0.f};
+        if (valid)
+        {
+            const ColTap t = make_tap<INTERP>(p, info, x);
+            pixel_values<INTERP>(p, pv, info, t, r0, r1, origin, v);
+        }
+        store_warp<DK, IL>(p, plan, v, dstRow, x, valid, lane);
     }
 }
 
@@ -419,7 +494,8 @@ struct UnitWalk
     }
 };
 
-template<int INTERP, int DK, int KC>
+// IL: the destination is interleaved (three adjacent channels per pixel) and is written with the transposing store.
+template<int INTERP, int DK, int KC, bool IL>
 __global__ void __launch_bounds__(512) resize_staged_kernel(const ResizeKParams p, const StagedCfg cfg)
 {
     extern __shared__ __align__(128) unsigned char smemRaw[];
@@ -597,8 +673,11 @@ __global__ void __launch_bounds__(512) resize_staged_kernel(const ResizeKParams 
 
     // ========================================================================= consumers
     const int     ct         = threadIdx.x - kProducerThreads;
-    const ChanOff   co       = chan_offsets(p);
     const PadValues pv       = pad_values(p);
+    StorePlan       plan;
+    plan.co          = chan_offsets(p);
+    plan.interleaved = IL;
+    plan.reversed    = p.mapC[0] == 2;
     long long     cachedKey  = -1;
     int           s          = 0;
     unsigned      fullParity = 0;
@@ -615,7 +694,8 @@ __global__ void __launch_bounds__(512) resize_staged_kernel(const ResizeKParams 
 
         if (info.mode == UNIT_PAD)
         {
-            for (int x = info.x0 + ct; x < info.x1; x += consumerThreads) pad_pixel<DK>(pv, co, dstRow + x * p.dPix);
+            for (int xw = info.x0 + (ct - lane); xw < info.x1; xw += consumerThreads)
+                store_warp<DK, IL>(p, plan, pv.v, dstRow, xw + lane, xw + lane < info.x1, lane);
         }
         else
         {
@@ -626,13 +706,14 @@ __global__ void __launch_bounds__(512) resize_staged_kernel(const ResizeKParams 
                 // Its own call site: the row pointers visibly derive from the shared-memory ring, so the tap reads
                 // compile to shared-memory loads.
                 const uint8_t *r0 = ring + s * slotBytes;
-                consume_columns<INTERP, DK, KC>(p, co, pv, info, r0, info.sameRow ? r0 : r0 + cfg.segBytes, info.segOrigin,
-                                            dstRow, ct, consumerThreads, cache, refresh);
+                const uint8_t *r1 = info.sameRow ? r0 : r0 + cfg.segBytes;
+                consume_columns<INTERP, DK, KC, IL>(p, plan, pv, info, r0, r1, info.segOrigin, dstRow, ct, lane,
+                                                    consumerThreads, cache, refresh);
             }
             else
             {
-                consume_columns<INTERP, DK, KC>(p, co, pv, info, info.g0, info.g1, 0, dstRow, ct, consumerThreads, cache,
-                                            refresh);
+                consume_columns<INTERP, DK, KC, IL>(p, plan, pv, info, info.g0, info.g1, 0, dstRow, ct, lane,
+                                                    consumerThreads, cache, refresh);
             }
         }
         __syncwarp();

@@ -233,6 +233,18 @@ class ImageBatchVarShape:
             self._images.append(im)
         self._table = None
 
+    def popback(self, count: int = 1) -> None:
+        """Removes the last `count` images (nvcv.ImageBatchVarShape.popback)."""
+        if count < 0 or count > len(self._images):
+            raise Error(Status.ERROR_INVALID_ARGUMENT, "Cannot remove more images than the batch holds")
+        if count:
+            del self._images[-count:]
+            self._table = None
+
+    def clear(self) -> None:
+        self._images = []
+        self._table = None
+
     def _channels(self, im: torch.Tensor) -> int:
         return im.shape[0] if self.planar else im.shape[2]
 
