@@ -102,10 +102,38 @@ __device__ __forceinline__ void affine3(const ResizeKParams &p, float (&v)[3])
 __device__ __forceinline__ void linear_values(const ResizeKParams &p, const uint8_t *r0, const uint8_t *r1, int o0, int o1,
                                               float wx0s, float wx1s, float wy0s, float wy1s, float (&v)[3])
 {
+    // A tap whose weight is exactly zero contributes +0 to the golden's left-to-right sum of non-negative products, so
+    // it is neither read nor multiplied (integer scale factors: every second tap; the producer does not even fetch a
+    // source row whose weight is zero).
+    if (wy1s == 0.0f)
+    {
+        if (wx1s == 0.0f)
+        {
 #pragma unroll
-    for (int c = 0; c < 3; ++c)
-        v[c] = blend4(raw_byte(r0 + o0 + c), raw_byte(r0 + o1 + c), raw_byte(r1 + o0 + c), raw_byte(r1 + o1 + c), wx0s,
-                      wx1s, wy0s, wy1s);
+            for (int c = 0; c < 3; ++c) v[c] = __fmul_rn(__fmul_rn(raw_byte(r0 + o0 + c), wy0s), wx0s);
+        }
+        else
+        {
+#pragma unroll
+            for (int c = 0; c < 3; ++c)
+                v[c] = __fadd_rn(__fmul_rn(__fmul_rn(raw_byte(r0 + o0 + c), wy0s), wx0s),
+                                 __fmul_rn(__fmul_rn(raw_byte(r0 + o1 + c), wy0s), wx1s));
+        }
+    }
+    else if (wx1s == 0.0f)
+    {
+#pragma unroll
+        for (int c = 0; c < 3; ++c)
+            v[c] = __fadd_rn(__fmul_rn(__fmul_rn(raw_byte(r0 + o0 + c), wy0s), wx0s),
+                             __fmul_rn(__fmul_rn(raw_byte(r1 + o0 + c), wy1s), wx0s));
+    }
+    else
+    {
+#pragma unroll
+        for (int c = 0; c < 3; ++c)
+            v[c] = blend4(raw_byte(r0 + o0 + c), raw_byte(r0 + o1 + c), raw_byte(r1 + o0 + c), raw_byte(r1 + o1 + c),
+                          wx0s, wx1s, wy0s, wy1s);
+    }
     if (p.srcCast)
     {
 #pragma unroll
@@ -596,7 +624,7 @@ __global__ void __launch_bounds__(512) resize_staged_kernel(const ResizeKParams 
                     }
                     info.g0      = g.base + sy0 * g.pitch;
                     info.g1      = g.base + sy1 * g.pitch;
-                    info.sameRow = (sy0 == sy1);
+                    info.sameRow = (sy0 == sy1) || info.wy1s == 0.0f; // a lower row of weight zero is never read
                     rowDelta     = (sy1 - sy0) * g.pitch;
 
                     const unsigned long long a0 = reinterpret_cast<unsigned long long>(info.g0) + 3ull * sxmin;

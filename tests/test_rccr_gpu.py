@@ -413,3 +413,28 @@ def test_wide_rows_in_chunks_with_horizontal_flip(pkg, oracle):
                                       scale=0.5, srcCast=False, flip_code=to_dev(flips))
             torch.cuda.synchronize()
         assert_parity(out.cpu().numpy(), want, what=f"path {path}")
+
+
+@pytest.mark.parametrize("factor", [(1, 1), (2, 2), (3, 1), (1, 4), (5, 3)])
+def test_integer_reduction_factors(pkg, oracle, factor):
+    """Whole-number scale factors put every sample point on a pixel centre or exactly between two (weights 0 or 0.5);
+    taps of weight zero are skipped by the kernels and must not change a bit."""
+    fx, fy = factor
+    ow, oh = 96, 40
+    rng = np.random.default_rng(fx * 10 + fy)
+    src = rng.integers(0, 256, (2, oh * fy, ow * fx, 3), dtype=np.uint8)
+    for dtype, planar, cast in ((np.float32, True, False), (np.uint8, False, True), (np.float16, True, True)):
+        spec = oracle.ResizeSpec(resize=(ow, oh), crop=(3, 2), out_size=(ow - 5, oh - 4), interp=1, src_cast=cast,
+                                 manip=1, scale=0.75, offset=-1.5)
+        want = oracle.resize_crop(list(src), spec, dtype, planar)
+        for path in PATHS:
+            shape = (2, 3, oh - 4, ow - 5) if planar else (2, oh - 4, ow - 5, 3)
+            out = torch.empty(shape, dtype=_torch_dtype(dtype), device="cuda")
+            with kernel_path(pkg, path):
+                pkg.fused_preprocess_into(out, to_dev(src), resize_dim=(ow, oh), interp=1, crop_pos=(3, 2),
+                                          layout="NCHW" if planar else "NHWC", manip=1, scale=0.75, offset=-1.5,
+                                          srcCast=cast)
+                torch.cuda.synchronize()
+            got = out.cpu().numpy()
+            assert_parity(got, want, what=f"factor {factor} {np.dtype(dtype).name} path {path}")
+            assert np.array_equal(got.view(np.uint8), want.view(np.uint8))
