@@ -92,6 +92,54 @@ def build_ref(ref_root: str = DEFAULT_REF_ROOT, force: bool = False) -> str | No
     return REF_SO
 
 
+REF_CUDA_SO = os.path.join(REF_DIR, "libref_cuda_kernels.so")
+REF_CUDA_WRAP = os.path.join(HERE, "ref_cuda_wrap.cu")
+
+
+def _cut_between(path: str, first_marker: str, last_marker: str, start_at_template: bool = True) -> str:
+    """Lines from the `template<...>` line above the first line containing `first_marker` to the line that closes the
+    definition containing `last_marker` (the first line starting with '}' after it)."""
+    with open(path, "r", encoding="utf-8") as f:
+        lines = f.read().split("\n")
+    first = next(i for i, ln in enumerate(lines) if first_marker in ln)
+    start = first
+    if start_at_template:
+        while not lines[start].lstrip().startswith("template"):
+            start -= 1
+    last = next(i for i, ln in enumerate(lines) if last_marker in ln)
+    end = next(i for i in range(last, len(lines)) if lines[i].startswith("}"))
+    return "\n".join(lines[start : end + 1]) + "\n"
+
+
+def build_ref_cuda(ref_root: str = DEFAULT_REF_ROOT, force: bool = False) -> str | None:
+    """Compile the reference's own CUDA kernels of the path for sm_100a into oracle/_ref/ (baseline and cross-check).
+    Returns None when the reference tree is absent and no earlier build exists."""
+    rccr = os.path.join(ref_root, "src/cvcuda/priv/OpResizeCropConvertReformat.cu")
+    cfnr = os.path.join(ref_root, "src/cvcuda/priv/OpCropFlipNormalizeReformat.cu")
+    if not (os.path.exists(rccr) and os.path.exists(cfnr)):
+        return REF_CUDA_SO if os.path.exists(REF_CUDA_SO) else None
+    if not (force or _stale(REF_CUDA_SO, REF_CUDA_WRAP, rccr, cfnr)):
+        return REF_CUDA_SO
+    os.makedirs(REF_DIR, exist_ok=True)
+    scratch = tempfile.mkdtemp(prefix="refcuda_")
+    try:
+        with open(os.path.join(scratch, "rccr_kernels.inc"), "w") as f:
+            f.write(_cut_between(rccr, "uchar4 remapC(const NVCVChannelManip manip)", "__global__ void resizeCrop_bilinear_varShape("))
+        with open(os.path.join(scratch, "cfnr_kernels.inc"), "w") as f:
+            f.write(_cut_between(cfnr, "__device__ float get_base_value(", "__global__ void slice_flip_normalize("))
+        cmd = [
+            os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc"), "-std=c++17", "-O3", "-gencode",
+            "arch=compute_100a,code=sm_100a", "-lineinfo", "-w", "-DNDEBUG", "-Xcompiler", "-fPIC", "-shared",
+            '-DREF_CUDA_RCCR_INC="rccr_kernels.inc"', '-DREF_CUDA_CFNR_INC="cfnr_kernels.inc"',
+            "-I" + os.path.join(ref_root, "src/cvcuda/include"), "-I" + os.path.join(ref_root, "src/nvcv/src/include"),
+            "-I" + scratch, "-o", REF_CUDA_SO, REF_CUDA_WRAP,
+        ]
+        subprocess.check_call(cmd)
+    finally:
+        shutil.rmtree(scratch, ignore_errors=True)
+    return REF_CUDA_SO
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--ref-root", default=DEFAULT_REF_ROOT)
@@ -99,6 +147,7 @@ def main() -> int:
     a = ap.parse_args()
     print("oracle:", build_oracle(a.force))
     print("reference golden:", build_ref(a.ref_root, a.force) or "reference tree absent, not built")
+    print("reference CUDA kernels:", build_ref_cuda(a.ref_root, a.force) or "reference tree absent, not built")
     return 0
 
 
