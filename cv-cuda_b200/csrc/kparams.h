@@ -52,10 +52,11 @@ struct StagedCfg
 {
     int       stages;       // ring depth
     int       segBytes;     // shared-memory bytes reserved per staged source row (multiple of 128)
-    int       rowsPerStage; // 2 for linear, 1 for nearest
+    int       rowsPerStage; // source row segments per destination row: 2 for linear, 1 for nearest
+    int       unitRows;     // destination rows per work unit (1..4)
     int       chunkCols;    // destination columns per work unit
     int       chunksPerRow;
-    long long totalUnits;   // numSamples * dstH * chunksPerRow
+    long long totalUnits;   // numSamples * ceil(dstH / unitRows) * chunksPerRow
     long long blockUnits;   // consecutive units dealt to a CTA at a time
 };
 

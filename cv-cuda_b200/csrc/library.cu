@@ -123,13 +123,17 @@ static int staged_occupancy(K kernel, int dev, int kernelId, int block, int smem
 
 // Launch-shape overrides for tuning runs, read once from the environment:
 // B200PP_STAGES (ring depth), B200PP_MAX_CTAS_PER_SM (cap on resident CTAs per SM of the staged kernel) and
-// B200PP_BLOCK_UNITS (consecutive units dealt to a CTA at a time), B200PP_MAX_CONSUMERS (consumer threads per CTA).
+// B200PP_BLOCK_UNITS (consecutive units dealt to a CTA at a time), B200PP_MAX_CONSUMERS (consumer threads per CTA),
+// B200PP_UNIT_ROWS (destination rows per work unit of the staged kernel), B200PP_WALK_ROWS (rows per CTA of the
+// row-walk kernel).
 struct Tuning
 {
     int stages       = 0;
     int maxCtasPerSm = 0;
     int blockUnits   = 0;
     int maxConsumers = 0;
+    int unitRows     = 0;
+    int walkRows     = 0;
 };
 
 static const Tuning &tuning()
@@ -146,6 +150,10 @@ static const Tuning &tuning()
             v.blockUnits = atoi(b);
         if (const char *m = getenv("B200PP_MAX_CONSUMERS"))
             v.maxConsumers = atoi(m);
+        if (const char *r = getenv("B200PP_UNIT_ROWS"))
+            v.unitRows = atoi(r);
+        if (const char *w = getenv("B200PP_WALK_ROWS"))
+            v.walkRows = atoi(w);
         return v;
     }();
     return t;
@@ -160,6 +168,26 @@ static int launch_resize_gather(const ResizeKParams &kp, cudaStream_t stream)
     dim3 grid((kp.dstW + 31) / 32, (kp.dstH + 7) / 8, std::min(kp.numSamples, 32768));
     resize_gather_kernel<INTERP, DK><<<grid, block, 0, stream>>>(kp);
     return check_launch("ResizeCropConvertReformat (gather)");
+}
+
+template<int INTERP, int DK>
+static int launch_resize_rowwalk(const ResizeKParams &kp, cudaStream_t stream)
+{
+    const int block  = std::min(256, (kp.dstW + 31) / 32 * 32);
+    const int chunks = (kp.dstW + block - 1) / block;
+    int       rows   = tuning().walkRows > 0 ? tuning().walkRows : 8;
+    rows             = std::max(1, std::min({rows, kWalkRowsMax, kp.dstH}));
+    const long long gx = static_cast<long long>(chunks) * ((kp.dstH + rows - 1) / rows);
+    if (gx > 0x7fffffffll)
+        return launch_resize_gather<INTERP, DK>(kp, stream);
+    const int  elem = DK == DST_F32 ? 4 : (DK == DST_F16 ? 2 : 1);
+    const bool il   = DK != DST_F16 && kp.dPix == 3 * elem && kp.dChan == elem;
+    dim3       grid(static_cast<unsigned>(gx), static_cast<unsigned>(std::min(kp.numSamples, 65535)));
+    if (il)
+        resize_rowwalk_kernel<INTERP, DK, true><<<grid, block, 0, stream>>>(kp, rows, chunks);
+    else
+        resize_rowwalk_kernel<INTERP, DK, false><<<grid, block, 0, stream>>>(kp, rows, chunks);
+    return check_launch("ResizeCropConvertReformat (row walk)");
 }
 
 // Returns 1 when the staged kernel was launched, 0 when it does not apply (caller falls back), <0 never.
@@ -186,14 +214,22 @@ static int launch_resize_staged(const ResizeKParams &kp, int srcWBound, cudaStre
     while (cfg.chunkCols > 32 && seg_for(cfg.chunkCols) > kMaxSeg) cfg.chunkCols = (cfg.chunkCols + 1) / 2;
     cfg.segBytes     = std::min(seg_for(cfg.chunkCols), kMaxSeg);
     cfg.chunksPerRow = (kp.dstW + cfg.chunkCols - 1) / cfg.chunkCols;
-    cfg.totalUnits   = static_cast<long long>(kp.numSamples) * kp.dstH * cfg.chunksPerRow;
 
-    const int stageBytes = cfg.segBytes * cfg.rowsPerStage;
+    // Destination rows per unit: a ring slot (one barrier phase) should move 10 KB or more, about 20 KB where rows are
+    // short. Measured on B200 with 5 KB row segments (1080p -> 224, nearest): 96 / 77 / 71 / 68 us at 1 / 2 / 3 / 4 rows.
+    const int rowBytes = cfg.segBytes * cfg.rowsPerStage;
+    cfg.unitRows       = std::max(1, std::min({kMaxUnitRows, (24 * 1024 + rowBytes / 2) / rowBytes, kp.dstH}));
+    if (tuning().unitRows > 0)
+        cfg.unitRows = std::max(1, std::min({kMaxUnitRows, tuning().unitRows, kp.dstH}));
+    cfg.totalUnits = static_cast<long long>(kp.numSamples) * ((kp.dstH + cfg.unitRows - 1) / cfg.unitRows) * cfg.chunksPerRow;
+
+    const int stageBytes = rowBytes * cfg.unitRows;
     // About 30 KB of copies in flight per CTA (four CTAs per SM): measured best on B200; deeper rings were slower.
     cfg.stages           = std::max(2, std::min(8, (32 * 1024) / stageBytes));
     if (tuning().stages > 0)
         cfg.stages = std::max(2, std::min(16, tuning().stages));
-    const int smemBytes  = cfg.stages * stageBytes + cfg.stages * (int)sizeof(UnitInfo) + cfg.stages * 16 + 128;
+    const int smemBytes  = cfg.stages * stageBytes + cfg.stages * (int)sizeof(UnitInfo) + cfg.stages * 16
+                         + kProducerThreads * (int)sizeof(Staged) + 128;
     if (smemBytes > facts.maxSmemOptin)
         return 0;
 
@@ -243,6 +279,8 @@ static int run_resize(const ResizeKParams &kp, int srcWBound, cudaStream_t strea
     // It also fetches whole row segments: beyond a 32x horizontal reduction (96 source bytes per destination column)
     // the taps skip whole 32-byte sectors and the per-pixel gather moves fewer bytes.
     const bool sparseTaps = static_cast<long long>(srcWBound) > 32ll * kp.resizeW;
+    if (path == 3)
+        return launch_resize_rowwalk<INTERP, DK>(kp, stream);
     const bool wantStaged = path == 2 || (path == 0 && kp.dstW >= 32 && !sparseTaps);
     if (wantStaged)
     {

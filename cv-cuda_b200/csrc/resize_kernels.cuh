@@ -2,6 +2,8 @@
 //
 //  * resize_gather_kernel  -- one thread per destination pixel, taps read straight from global memory.
 //                             Handles every argument combination; the fallback and the cross-check.
+//  * resize_rowwalk_kernel -- a thread keeps one destination column's taps in registers and walks down a group of
+//                             rows, reading from global memory through the L1: the leanest instruction stream.
 //  * resize_staged_kernel  -- persistent, warp-specialised pipeline. A work unit is one destination row segment of
 //                             one sample. A producer thread copies the one or two source row segments that the unit
 //                             taps into a shared-memory ring with bulk asynchronous copies (cp.async.bulk, completion
@@ -43,9 +45,34 @@ constexpr float kTwo127 = 1.7014118346046923e38f; // 2^127
 constexpr float kTwo22  = 4194304.0f;             // 2^22
 constexpr float kRound  = 12582912.0f;            // 1.5 * 2^23
 
-__device__ __forceinline__ float raw_byte(const uint8_t *p)
+// A tapped source row segment: either a 32-bit shared-memory address (staged rows; explicit ld.shared with the channel
+// as an immediate offset, 32-bit address arithmetic) or a pointer into global memory.
+struct SmemRow
 {
-    return __uint_as_float(static_cast<unsigned>(*p));
+    unsigned a;
+};
+
+__device__ __forceinline__ SmemRow operator+(SmemRow r, int byteOff)
+{
+    return SmemRow{r.a + static_cast<unsigned>(byteOff)};
+}
+
+// The three channel bytes of the pixel at `r`, each as the float whose bit pattern is the byte.
+__device__ __forceinline__ void tap3(SmemRow r, float (&b)[3])
+{
+    unsigned x, y, z;
+    asm volatile("ld.shared.u8 %0, [%1];" : "=r"(x) : "r"(r.a));
+    asm volatile("ld.shared.u8 %0, [%1+1];" : "=r"(y) : "r"(r.a));
+    asm volatile("ld.shared.u8 %0, [%1+2];" : "=r"(z) : "r"(r.a));
+    b[0] = __uint_as_float(x);
+    b[1] = __uint_as_float(y);
+    b[2] = __uint_as_float(z);
+}
+
+__device__ __forceinline__ void tap3(const uint8_t *r, float (&b)[3])
+{
+#pragma unroll
+    for (int c = 0; c < 3; ++c) b[c] = __uint_as_float(static_cast<unsigned>(r[c]));
 }
 
 // float(SaturateCast<uint8_t>(v)) for finite v
@@ -96,43 +123,50 @@ __device__ __forceinline__ void affine3(const ResizeKParams &p, float (&v)[3])
     }
 }
 
-// Final values of one destination pixel of the linear path. r0/r1 point at byte 0 of the two tapped source rows in
-// whatever memory they live in; o0/o1 are the byte offsets of the left/right tap pixel. Weights are pre-scaled:
-// wy*s = wy * 2^127, wx*s = wx * 2^22.
-__device__ __forceinline__ void linear_values(const ResizeKParams &p, const uint8_t *r0, const uint8_t *r1, int o0, int o1,
-                                              float wx0s, float wx1s, float wy0s, float wy1s, float (&v)[3])
+// Final values of one destination pixel of the linear path. r0/r1 address byte 0 of the two tapped source rows in
+// whatever memory they live in (SmemRow or a global pointer); o0/o1 are the byte offsets of the left/right tap pixel.
+// Weights are pre-scaled: wy*s = wy * 2^127, wx*s = wx * 2^22.
+template<class Row>
+__device__ __forceinline__ void linear_values(const ResizeKParams &p, Row r0, Row r1, int o0, int o1, float wx0s,
+                                              float wx1s, float wy0s, float wy1s, float (&v)[3])
 {
     // A tap whose weight is exactly zero contributes +0 to the golden's left-to-right sum of non-negative products, so
     // it is neither read nor multiplied (integer scale factors: every second tap; the producer does not even fetch a
     // source row whose weight is zero).
+    float a[3], b[3];
     if (wy1s == 0.0f)
     {
+        tap3(r0 + o0, a);
         if (wx1s == 0.0f)
         {
 #pragma unroll
-            for (int c = 0; c < 3; ++c) v[c] = __fmul_rn(__fmul_rn(raw_byte(r0 + o0 + c), wy0s), wx0s);
+            for (int c = 0; c < 3; ++c) v[c] = __fmul_rn(__fmul_rn(a[c], wy0s), wx0s);
         }
         else
         {
+            tap3(r0 + o1, b);
 #pragma unroll
             for (int c = 0; c < 3; ++c)
-                v[c] = __fadd_rn(__fmul_rn(__fmul_rn(raw_byte(r0 + o0 + c), wy0s), wx0s),
-                                 __fmul_rn(__fmul_rn(raw_byte(r0 + o1 + c), wy0s), wx1s));
+                v[c] = __fadd_rn(__fmul_rn(__fmul_rn(a[c], wy0s), wx0s), __fmul_rn(__fmul_rn(b[c], wy0s), wx1s));
         }
     }
     else if (wx1s == 0.0f)
     {
+        tap3(r0 + o0, a);
+        tap3(r1 + o0, b);
 #pragma unroll
         for (int c = 0; c < 3; ++c)
-            v[c] = __fadd_rn(__fmul_rn(__fmul_rn(raw_byte(r0 + o0 + c), wy0s), wx0s),
-                             __fmul_rn(__fmul_rn(raw_byte(r1 + o0 + c), wy1s), wx0s));
+            v[c] = __fadd_rn(__fmul_rn(__fmul_rn(a[c], wy0s), wx0s), __fmul_rn(__fmul_rn(b[c], wy1s), wx0s));
     }
     else
     {
+        float c2[3], d[3];
+        tap3(r0 + o0, a);
+        tap3(r0 + o1, b);
+        tap3(r1 + o0, c2);
+        tap3(r1 + o1, d);
 #pragma unroll
-        for (int c = 0; c < 3; ++c)
-            v[c] = blend4(raw_byte(r0 + o0 + c), raw_byte(r0 + o1 + c), raw_byte(r1 + o0 + c), raw_byte(r1 + o1 + c),
-                          wx0s, wx1s, wy0s, wy1s);
+        for (int c = 0; c < 3; ++c) v[c] = blend4(a[c], b[c], c2[c], d[c], wx0s, wx1s, wy0s, wy1s);
     }
     if (p.srcCast)
     {
@@ -142,10 +176,13 @@ __device__ __forceinline__ void linear_values(const ResizeKParams &p, const uint
     affine3(p, v);
 }
 
-__device__ __forceinline__ void nearest_values(const ResizeKParams &p, const uint8_t *r0, int o0, float (&v)[3])
+template<class Row>
+__device__ __forceinline__ void nearest_values(const ResizeKParams &p, Row r0, int o0, float (&v)[3])
 {
+    float a[3];
+    tap3(r0 + o0, a);
 #pragma unroll
-    for (int c = 0; c < 3; ++c) v[c] = __fmul_rn(__fmul_rn(raw_byte(r0 + o0 + c), kTwo127), kTwo22);
+    for (int c = 0; c < 3; ++c) v[c] = __fmul_rn(__fmul_rn(a[c], kTwo127), kTwo22);
     affine3(p, v);
 }
 
@@ -176,11 +213,11 @@ __device__ __forceinline__ void store_pixel(const float (&v)[3], const ChanOff &
 // Interleaved (NHWC) destinations: a warp's 32 pixels are 96 consecutive elements in memory, but each lane holds the
 // three channels of one pixel. The channels are transposed across the warp with shuffles so that every store
 // instruction writes consecutive 32-bit words: three fully coalesced stores for float32 (lane L writes elements L,
-// 32+L, 64+L), one for uint8 (lanes 0..23 write the 96 bytes as 24 words). `warpBase` is the address of lane 0's pixel.
-// All 32 lanes must call this.
+// 32+L, 64+L), one for uint8 (lanes 0..23 write the 96 bytes as 24 words). `lanePtr` is the address of word `lane` of
+// the warp's segment (the address of lane 0's pixel + 4*lane). All 32 lanes must call this.
 template<int DK>
 __device__ __forceinline__ void store_interleaved_warp(const float (&d)[3] /* destination channel order */,
-                                                       uint8_t *warpBase, int lane)
+                                                       uint8_t *lanePtr, int lane)
 {
     if constexpr (DK == DST_F32)
     {
@@ -192,7 +229,7 @@ __device__ __forceinline__ void store_interleaved_warp(const float (&d)[3] /* de
             const int   c   = e - 3 * src;
             const float a = __shfl_sync(0xffffffffu, d[0], src), b = __shfl_sync(0xffffffffu, d[1], src),
                         g = __shfl_sync(0xffffffffu, d[2], src);
-            reinterpret_cast<float *>(warpBase)[e] = c == 0 ? a : (c == 1 ? b : g);
+            reinterpret_cast<float *>(lanePtr)[32 * k] = c == 0 ? a : (c == 1 ? b : g);
         }
     }
     else
@@ -207,7 +244,7 @@ __device__ __forceinline__ void store_interleaved_warp(const float (&d)[3] /* de
         const unsigned lo  = __shfl_sync(0xffffffffu, w, p0 & 31);
         const unsigned hi  = __shfl_sync(0xffffffffu, w, (p0 + 1) & 31);
         if (lane < 24)
-            reinterpret_cast<unsigned *>(warpBase)[lane] = (lo >> (8 * off)) | (hi << (8 * (3 - off)));
+            *reinterpret_cast<unsigned *>(lanePtr) = (lo >> (8 * off)) | (hi << (8 * (3 - off)));
     }
 }
 
@@ -281,6 +318,12 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(unsigned long long *bar, u
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
 }
 
+// Adds to the bytes the current phase waits for, without arriving.
+__device__ __forceinline__ void mbar_expect_tx(unsigned long long *bar, unsigned bytes)
+{
+    asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
+}
+
 __device__ __forceinline__ unsigned long long globaltimer_ns()
 {
     unsigned long long t;
@@ -302,10 +345,8 @@ __device__ __forceinline__ bool mbar_try_wait(unsigned addr, unsigned parity)
 }
 
 // Bounded wait for the phase with the given parity: gives up (returns false) after `limitNs` of wall time.
-__device__ __forceinline__ bool mbar_wait(unsigned long long *bar, unsigned parity,
-                                          unsigned long long limitNs = kWaitLimitNs)
+__device__ __forceinline__ bool mbar_wait_addr(unsigned addr, unsigned parity, unsigned long long limitNs = kWaitLimitNs)
 {
-    const unsigned addr = smem_addr(bar);
     if (mbar_try_wait(addr, parity))
         return true;
     const unsigned long long t0 = globaltimer_ns();
@@ -316,6 +357,17 @@ __device__ __forceinline__ bool mbar_wait(unsigned long long *bar, unsigned pari
         if ((spin & 63u) == 0 && globaltimer_ns() - t0 > limitNs)
             return false;
     }
+}
+
+__device__ __forceinline__ bool mbar_wait(unsigned long long *bar, unsigned parity,
+                                          unsigned long long limitNs = kWaitLimitNs)
+{
+    return mbar_wait_addr(smem_addr(bar), parity, limitNs);
+}
+
+__device__ __forceinline__ void mbar_arrive_addr(unsigned addr)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(addr) : "memory");
 }
 
 // Self-test of the bounded wait: one warp waits on a barrier that nothing ever completes, with a short limit, and
@@ -345,22 +397,6 @@ __device__ __forceinline__ void bulk_load(void *smemDst, const void *gmemSrc, un
 
 // ------------------------------------------------------------------------------------------------ staged kernel
 
-// What the producer tells the consumers about the unit staged in one ring slot.
-struct UnitInfo
-{
-    int            mode; // UNIT_*
-    int            x0, x1;
-    int            flipX;
-    int            srcW;
-    int            segOrigin; // source-row byte offset that shared-memory offset 0 of the slot corresponds to
-    int            sameRow;   // linear: both taps come from one source row
-    float          scaleW;
-    float          wy0s, wy1s; // vertical weights * 2^127
-    long long      dstRowOff;
-    long long      tapKey; // units with equal keys have identical column taps (same sample geometry, chunk and flip)
-    const uint8_t *g0, *g1; // tapped source rows in global memory (byte 0 of the row of the sub-view)
-};
-
 enum
 {
     UNIT_PAD    = 0, // nothing to sample: the row lies outside the placed region
@@ -368,17 +404,69 @@ enum
     UNIT_DIRECT = 2  // read the rows from global memory (unaligned image, or a segment larger than a slot)
 };
 
-// Horizontal taps of one destination column: byte offsets of the left/right source pixel within the source row
-// (o0 < 0 marks a column outside the placed region), the weights * 2^22 and the column's destination byte offset.
+// A work unit is up to kMaxUnitRows consecutive destination rows of one column chunk of one sample. Rows are grouped
+// so that one ring slot (one barrier phase) moves 10 KB or more: below that the per-phase cost of the pipeline, not
+// HBM, sets the pace.
+constexpr int kMaxUnitRows = 4;
+
+// One destination row of a unit (two 16-byte words; consumers read the second only for UNIT_DIRECT rows).
+struct alignas(16) RowInfo
+{
+    int            mode;       // UNIT_* in bits 0-7; bit 8: the second tap row has its own segment (off0 + segBytes)
+    int            off0;       // byte offset of the row's first segment inside the slot
+    float          wy0s, wy1s; // vertical weights * 2^127
+    const uint8_t *g0, *g1;    // tapped source rows in global memory (byte 0 of the row of the sub-view)
+};
+
+// What the producer tells the consumers about the unit staged in one ring slot: three 16-byte header words (the third
+// is read only when cached column taps go stale) and one RowInfo per destination row.
+struct alignas(16) UnitInfo
+{
+    // word 0
+    int x0, x1;   // destination columns [x0, x1)
+    int origin;   // source-row byte offset that offset 0 of a staged segment corresponds to (0 for UNIT_DIRECT)
+    int flipRows; // bit 0: horizontal flip; bit 1: at least one row is sampled; bits 8..: number of rows
+    // word 1
+    long long dstRowOff; // of the unit's first row
+    long long tapKey;    // units with equal keys have identical column taps (sample geometry, chunk, flip, origin)
+    // word 2
+    int   srcW;
+    float scaleW;
+    int   pad0, pad1;
+    RowInfo row[kMaxUnitRows];
+};
+
+static_assert(sizeof(RowInfo) == 32 && sizeof(UnitInfo) == 48 + 32 * kMaxUnitRows, "UnitInfo layout is read by offset");
+
+__device__ __forceinline__ uint4 lds128(unsigned addr)
+{
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+
+__device__ __forceinline__ long long join64(unsigned lo, unsigned hi)
+{
+    return static_cast<long long>((static_cast<unsigned long long>(hi) << 32) | lo);
+}
+
+// Horizontal taps of one destination column: byte offsets of the left/right source pixel relative to the unit's
+// origin (or one of the two codes below), the weights * 2^22 and the column's destination byte offset.
 struct ColTap
 {
-    int       o0, o1;
+    int       rel0, rel1;
     float     wx0s, wx1s;
     long long dstOff;
 };
 
+enum
+{
+    TAP_PAD  = -1, // column outside the placed region: gets the pad value
+    TAP_NONE = -2  // the thread has no such column
+};
+
 template<int INTERP>
-__device__ __forceinline__ ColTap make_tap(const ResizeKParams &p, const UnitInfo &info, int x)
+__device__ __forceinline__ ColTap make_tap(const ResizeKParams &p, int flipX, int srcW, float scaleW, int origin, int x)
 {
     ColTap t;
     t.dstOff     = x * p.dPix;
@@ -387,54 +475,54 @@ __device__ __forceinline__ ColTap make_tap(const ResizeKParams &p, const UnitInf
     const int rx = x - p.dstX;
     if (rx < 0 || rx >= p.regionW)
     {
-        t.o0 = t.o1 = -1;
+        t.rel0 = t.rel1 = TAP_PAD;
         return t;
     }
-    const int dx = (info.flipX ? p.regionW - 1 - rx : rx) + p.cropX;
+    const int dx = (flipX ? p.regionW - 1 - rx : rx) + p.cropX;
     if constexpr (INTERP == B200PP_INTERP_NEAREST)
     {
-        t.o0 = t.o1 = 3 * nearest_tap(info.scaleW, dx, info.srcW);
+        t.rel0 = t.rel1 = 3 * nearest_tap(scaleW, dx, srcW) - origin;
     }
     else
     {
         int   s0, s1;
         float wx1;
-        linear_tap(info.scaleW, dx, info.srcW, s0, s1, wx1);
-        t.o0   = 3 * s0;
-        t.o1   = 3 * s1;
+        linear_tap(scaleW, dx, srcW, s0, s1, wx1);
+        t.rel0 = 3 * s0 - origin;
+        t.rel1 = 3 * s1 - origin;
         t.wx0s = __fmul_rn(__fsub_rn(1.0f, wx1), kTwo22);
         t.wx1s = __fmul_rn(wx1, kTwo22);
     }
     return t;
 }
 
-// Final values of one destination pixel from rows r0/r1 whose first byte is source-row byte `origin`.
-template<int INTERP>
-__device__ __forceinline__ void pixel_values(const ResizeKParams &p, const PadValues &pv, const UnitInfo &info,
-                                             const ColTap &t, const uint8_t *r0, const uint8_t *r1, int origin,
-                                             float (&v)[3])
+// Final values of one destination pixel from rows r0/r1 (addressed from the unit's origin).
+template<int INTERP, class Row>
+__device__ __forceinline__ void pixel_values(const ResizeKParams &p, const PadValues &pv, const ColTap &t, Row r0, Row r1,
+                                             float wy0s, float wy1s, float (&v)[3])
 {
-    if (t.o0 < 0)
+    if (t.rel0 < 0)
     {
 #pragma unroll
         for (int c = 0; c < 3; ++c) v[c] = pv.v[c];
     }
     else if constexpr (INTERP == B200PP_INTERP_NEAREST)
-        nearest_values(p, r0, t.o0 - origin, v);
+        nearest_values(p, r0, t.rel0, v);
     else
-        linear_values(p, r0, r1, t.o0 - origin, t.o1 - origin, t.wx0s, t.wx1s, info.wy0s, info.wy1s, v);
+        linear_values(p, r0, r1, t.rel0, t.rel1, t.wx0s, t.wx1s, wy0s, wy1s, v);
 }
 
-// How a consumer warp writes its pixels.
+// How a consumer thread writes its pixels.
 struct StorePlan
 {
-    ChanOff co;
-    bool    interleaved; // destination has the three channels of a pixel adjacent: transpose across the warp
-    bool    reversed;    // channel order reversed
+    ChanOff   co;
+    bool      reversed; // channel order reversed
+    long long ilAdj;    // interleaved destinations: from a lane's pixel address to the word(s) it writes in the
+                        // transposed warp store (-8*lane for float32, +lane for uint8)
 };
 
-// Stores one pixel per lane of a warp. `x` is this lane's column (lanes hold consecutive columns), `valid` whether it
-// exists. Every lane of the warp must call this.
+// Stores one pixel per lane of a warp, deciding per call whether the warp can use the transposing store. `x` is this
+// lane's column (lanes hold consecutive columns), `valid` whether it exists. Every lane of the warp must call this.
 template<int DK, bool IL>
 __device__ __forceinline__ void store_warp(const ResizeKParams &p, const StorePlan &plan, const float (&v)[3],
                                            uint8_t *dstRow, int x, bool valid, int lane)
@@ -446,7 +534,7 @@ __device__ __forceinline__ void store_warp(const ResizeKParams &p, const StorePl
         if (full)
         {
             const float d[3] = {plan.reversed ? v[2] : v[0], v[1], plan.reversed ? v[0] : v[2]};
-            store_interleaved_warp<DK>(d, warpBase, lane);
+            store_interleaved_warp<DK>(d, dstRow + x * p.dPix + plan.ilAdj, lane);
             return;
         }
     }
@@ -454,43 +542,176 @@ __device__ __forceinline__ void store_warp(const ResizeKParams &p, const StorePl
         store_pixel<DK>(v, plan.co, dstRow + x * p.dPix);
 }
 
-// Columns [x0, x1) of one destination row, strided over the consumer threads so that a warp writes 32 adjacent pixels.
-// The taps of a thread's first KC columns stay in registers while consecutive units share a tap key, which for a dense
-// batch is the whole launch. KC is a template parameter because every cached column costs six registers.
-// Loop trip counts are uniform across a warp (the stores vote and shuffle). IL selects the transposing store for
-// interleaved destinations; planar destinations compile without it.
-template<int INTERP, int DK, int KC, bool IL>
-__device__ __forceinline__ void consume_columns(const ResizeKParams &p, const StorePlan &plan, const PadValues &pv,
-                                                const UnitInfo &info, const uint8_t *r0, const uint8_t *r1, int origin,
-                                                uint8_t *dstRow, int ct, int lane, int consumerThreads,
-                                                ColTap (&cache)[KC], bool refresh)
+// The cached columns of one unit: taps, validity and the choice of store were settled when the cache was filled.
+template<int INTERP, int DK, int KC, bool IL, class Row>
+__device__ __forceinline__ void consume_cached(const ResizeKParams &p, const StorePlan &plan, const PadValues &pv, Row r0,
+                                               Row r1, float wy0s, float wy1s, uint8_t *dstRow, const ColTap (&cache)[KC],
+                                               unsigned fastMask, int lane)
 {
 #pragma unroll
     for (int k = 0; k < KC; ++k)
     {
-        const int  x     = info.x0 + ct + k * consumerThreads;
-        const bool valid = x < info.x1;
-        float      v[3]  = {0.f, 0.f, 0.f};
-        if (valid)
+        float v[3];
+        pixel_values<INTERP>(p, pv, cache[k], r0, r1, wy0s, wy1s, v);
+        uint8_t *pix = dstRow + cache[k].dstOff;
+        if constexpr (IL && DK != DST_F16)
         {
-            if (refresh)
-                cache[k] = make_tap<INTERP>(p, info, x);
-            pixel_values<INTERP>(p, pv, info, cache[k], r0, r1, origin, v);
+            if (fastMask & (1u << k)) // uniform across the warp
+            {
+                const float d[3] = {plan.reversed ? v[2] : v[0], v[1], plan.reversed ? v[0] : v[2]};
+                store_interleaved_warp<DK>(d, pix + plan.ilAdj, lane);
+                continue;
+            }
         }
-        store_warp<DK, IL>(p, plan, v, dstRow, x, valid, lane);
+        if (cache[k].rel0 != TAP_NONE)
+            store_pixel<DK>(v, plan.co, pix);
     }
-    for (int xw = info.x0 + (ct - lane) + KC * consumerThreads; xw < info.x1; xw += consumerThreads)
+}
+
+// Columns beyond the cached ones (rows wider than KC columns per consumer thread): taps are worked out on the fly.
+template<int INTERP, int DK, int KC, bool IL, class Row>
+__device__ __forceinline__ void consume_tail(const ResizeKParams &p, const StorePlan &plan, const PadValues &pv, Row r0,
+                                             Row r1, float wy0s, float wy1s, uint8_t *dstRow, int x0, int x1, int flipX,
+                                             int origin, unsigned infoAddr, int ct, int lane, int consumerThreads)
+{
+    int xw = x0 + (ct - lane) + KC * consumerThreads;
+    if (xw >= x1)
+        return;
+    const uint4 w3     = lds128(infoAddr + 32);
+    const int   srcW   = static_cast<int>(w3.x);
+    const float scaleW = __uint_as_float(w3.y);
+    for (; xw < x1; xw += consumerThreads)
     {
         const int  x     = xw + lane;
-        const bool valid = x < info.x1;
+        const bool valid = x < x1;
         float      v[3]  = {0.f, 0.f, 0.f};
         if (valid)
         {
-            const ColTap t = make_tap<INTERP>(p, info, x);
-            pixel_values<INTERP>(p, pv, info, t, r0, r1, origin, v);
+            const ColTap t = make_tap<INTERP>(p, flipX, srcW, scaleW, origin, x);
+            pixel_values<INTERP>(p, pv, t, r0, r1, wy0s, wy1s, v);
         }
         store_warp<DK, IL>(p, plan, v, dstRow, x, valid, lane);
     }
+}
+
+// A unit as the producer stages it: the description the consumers get, plus what the copies need.
+struct alignas(16) Staged
+{
+    UnitInfo  info;
+    long long colOff;  // from byte 0 of a tapped source row to the 16-byte aligned start of the copied span
+    unsigned  nb;      // bytes per copied row segment
+    unsigned  pad;
+};
+
+static_assert(sizeof(Staged) == sizeof(UnitInfo) + 16, "Staged tail is read as one 16-byte word");
+
+__device__ __forceinline__ void sts128(unsigned addr, uint4 v)
+{
+    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+// Everything about work unit `u`: which sample, rows and columns, what they tap and where the tapped bytes lie.
+template<int INTERP>
+__device__ __forceinline__ void describe_unit(const ResizeKParams &p, const StagedCfg &cfg, long long u, bool perSampleTaps,
+                                              int unitsPerSample, int rowBytes, Staged &out)
+{
+    const int  n     = static_cast<int>(u / unitsPerSample);
+    const int  rem   = static_cast<int>(u - static_cast<long long>(n) * unitsPerSample);
+    const int  yg    = rem / cfg.chunksPerRow;
+    const int  chunk = rem - yg * cfg.chunksPerRow;
+    const Geom g     = load_geom(p, n);
+    const bool aligned
+        = ((reinterpret_cast<unsigned long long>(g.image) | static_cast<unsigned long long>(g.pitch)) & 15ull) == 0;
+
+    const int  y0    = yg * cfg.unitRows;
+    const int  nRows = min(cfg.unitRows, p.dstH - y0);
+    const int  x0    = chunk * cfg.chunkCols;
+    const int  x1    = min(x0 + cfg.chunkCols, p.dstW);
+    const int  flipX = (g.flip == 1 || g.flip == -1);
+    const bool flipY = (g.flip == 0 || g.flip == -1);
+    long long  tapKey = (((perSampleTaps ? static_cast<long long>(n) + 1 : 0) * cfg.chunksPerRow + chunk) * 2 + flipX) * 32;
+    int        unitMode = UNIT_PAD, origin = 0;
+    long long  colOff = 0;
+    unsigned   nb     = 0;
+
+    const int rx0 = max(x0 - p.dstX, 0);
+    const int rx1 = min(x1 - p.dstX, p.regionW) - 1; // inclusive
+    if (rx1 >= rx0)
+    {
+        const int dlo = (flipX ? p.regionW - 1 - rx1 : rx0) + p.cropX;
+        const int dhi = (flipX ? p.regionW - 1 - rx0 : rx1) + p.cropX;
+        int       sxmin, sxmax;
+        if constexpr (INTERP == B200PP_INTERP_NEAREST)
+        {
+            sxmin = nearest_tap(g.scaleW, dlo, g.w);
+            sxmax = nearest_tap(g.scaleW, dhi, g.w);
+        }
+        else
+        {
+            float w;
+            int   t;
+            linear_tap(g.scaleW, dlo, g.w, sxmin, t, w);
+            linear_tap(g.scaleW, dhi, g.w, t, sxmax, w);
+        }
+        // with a 16-byte aligned image and pitch the low address bits are the same in every row
+        const unsigned long long a0 = reinterpret_cast<unsigned long long>(g.base) + 3ull * sxmin;
+        const unsigned long long a1 = reinterpret_cast<unsigned long long>(g.base) + 3ull * (sxmax + 1);
+        colOff                      = 3ll * sxmin - static_cast<long long>(a0 & 15ull);
+        nb                          = static_cast<unsigned>(((a1 + 15ull) & ~15ull) - (a0 & ~15ull));
+        if (!aligned || nb > static_cast<unsigned>(cfg.segBytes))
+        {
+            unitMode = UNIT_DIRECT;
+        }
+        else
+        {
+            unitMode = UNIT_STAGED;
+            origin   = static_cast<int>(colOff);
+            // cached taps are relative to the origin, whose alignment part is not implied by the geometry
+            tapKey += 16 + static_cast<long long>(a0 & 15ull);
+        }
+    }
+
+    int sampled = 0;
+    for (int r = 0; r < nRows; ++r)
+    {
+        RowInfo   ri{};
+        const int ry = y0 + r - p.dstY;
+        ri.mode      = UNIT_PAD;
+        ri.off0      = r * rowBytes;
+        if (unitMode != UNIT_PAD && ry >= 0 && ry < p.regionH)
+        {
+            const int dy = (flipY ? p.regionH - 1 - ry : ry) + p.cropY;
+            int       sy0, sy1;
+            bool      twoRow = false;
+            if constexpr (INTERP == B200PP_INTERP_NEAREST)
+            {
+                sy0 = sy1 = nearest_tap(g.scaleH, dy, g.h);
+            }
+            else
+            {
+                float wy1;
+                linear_tap(g.scaleH, dy, g.h, sy0, sy1, wy1);
+                ri.wy0s = __fmul_rn(__fsub_rn(1.0f, wy1), kTwo127);
+                ri.wy1s = __fmul_rn(wy1, kTwo127);
+                twoRow  = sy0 != sy1 && ri.wy1s != 0.0f; // a lower row of weight zero is never read
+            }
+            ri.g0   = g.base + sy0 * g.pitch;
+            ri.g1   = g.base + sy1 * g.pitch;
+            ri.mode = unitMode | (twoRow && unitMode == UNIT_STAGED ? 0x100 : 0);
+            sampled = 2;
+        }
+        out.info.row[r] = ri;
+    }
+    out.info.x0        = x0;
+    out.info.x1        = x1;
+    out.info.origin    = origin;
+    out.info.flipRows  = flipX | sampled | (nRows << 8);
+    out.info.dstRowOff = n * p.dSample + y0 * p.dRow;
+    out.info.tapKey    = tapKey;
+    out.info.srcW      = g.w;
+    out.info.scaleW    = g.scaleW;
+    out.colOff         = colOff;
+    out.nb             = nb;
 }
 
 // Units are dealt to CTAs in blocks of cfg.blockUnits consecutive units, round-robin over the CTAs.
@@ -524,12 +745,12 @@ struct UnitWalk
 
 // IL: the destination is interleaved (three adjacent channels per pixel) and is written with the transposing store.
 template<int INTERP, int DK, int KC, bool IL>
-__global__ void __launch_bounds__(512) resize_staged_kernel(const ResizeKParams p, const StagedCfg cfg)
+__global__ void __launch_bounds__(512, 2) resize_staged_kernel(const ResizeKParams p, const StagedCfg cfg)
 {
     extern __shared__ __align__(128) unsigned char smemRaw[];
 
     const int       S         = cfg.stages;
-    const long long slotBytes = static_cast<long long>(cfg.rowsPerStage) * cfg.segBytes;
+    const long long slotBytes = static_cast<long long>(cfg.unitRows) * cfg.rowsPerStage * cfg.segBytes;
     unsigned char  *ring      = smemRaw;
     UnitInfo       *infos     = reinterpret_cast<UnitInfo *>(ring + S * slotBytes);
     auto           *full      = reinterpret_cast<unsigned long long *>(infos + S);
@@ -556,11 +777,15 @@ __global__ void __launch_bounds__(512) resize_staged_kernel(const ResizeKParams 
     if (threadIdx.x < kProducerThreads)
     {
         // ===================================================================== producer warp
-        // Geometry of 32 consecutive units is worked out by the 32 lanes side by side (sample descriptors, row taps,
-        // tapped span, copy addresses); the lanes then take turns, in unit order, to claim a ring slot, publish the
-        // unit and issue its bulk copies.
-        const bool perSampleTaps = p.list != nullptr || p.roi != nullptr;
-        const int  unitsPerSample = p.dstH * cfg.chunksPerRow;
+        // Phase A: the 32 lanes describe 32 consecutive units side by side (sample descriptor, column span, row taps,
+        // copy addresses) into a staging array in shared memory. Phase B: unit by unit, in order, lane 0 claims a ring
+        // slot, eleven lanes move the description into the slot's UnitInfo and up to eight lanes issue one bulk copy
+        // each; lane 0 then arrives on the slot's barrier.
+        Staged    *staging        = reinterpret_cast<Staged *>(empty + S);
+        const bool perSampleTaps  = p.list != nullptr || p.roi != nullptr;
+        const int  groupsPerImage = (p.dstH + cfg.unitRows - 1) / cfg.unitRows;
+        const int  unitsPerSample = groupsPerImage * cfg.chunksPerRow;
+        const int  rowBytes       = cfg.rowsPerStage * cfg.segBytes;
         int        s           = 0;
         unsigned   emptyParity = 1; // phase the consumers complete when they release the slot's previous use
         bool       failed      = false;
@@ -568,115 +793,51 @@ __global__ void __launch_bounds__(512) resize_staged_kernel(const ResizeKParams 
 
         for (long long kb = 0; kb < walk.count && !failed; kb += 32)
         {
-            const long long k     = kb + lane;
-            const bool      valid = k < walk.count;
-            UnitInfo           info{};
-            unsigned long long copySrc = 0;
-            long long          rowDelta = 0;
-            unsigned           nb = 0;
-            if (valid)
-            {
-                const long long u     = walk.unit(k);
-                const int       n     = static_cast<int>(u / unitsPerSample);
-                const int       rem   = static_cast<int>(u - static_cast<long long>(n) * unitsPerSample);
-                const int       y     = rem / cfg.chunksPerRow;
-                const int       chunk = rem - y * cfg.chunksPerRow;
-                const Geom      g     = load_geom(p, n);
-                const bool      aligned
-                    = ((reinterpret_cast<unsigned long long>(g.image) | static_cast<unsigned long long>(g.pitch)) & 15ull) == 0;
-
-                info.x0        = chunk * cfg.chunkCols;
-                info.x1        = min(info.x0 + cfg.chunkCols, p.dstW);
-                info.dstRowOff = n * p.dSample + y * p.dRow;
-                info.flipX     = (g.flip == 1 || g.flip == -1);
-                info.tapKey    = ((perSampleTaps ? static_cast<long long>(n) + 1 : 0) * cfg.chunksPerRow + chunk) * 2 + info.flipX;
-                info.srcW      = g.w;
-                info.scaleW    = g.scaleW;
-
-                const int ry  = y - p.dstY;
-                const int rx0 = max(info.x0 - p.dstX, 0);
-                const int rx1 = min(info.x1 - p.dstX, p.regionW) - 1; // inclusive
-                if (ry < 0 || ry >= p.regionH || rx1 < rx0)
-                {
-                    info.mode = UNIT_PAD;
-                }
-                else
-                {
-                    const int dy  = ((g.flip == 0 || g.flip == -1) ? p.regionH - 1 - ry : ry) + p.cropY;
-                    const int dlo = (info.flipX ? p.regionW - 1 - rx1 : rx0) + p.cropX;
-                    const int dhi = (info.flipX ? p.regionW - 1 - rx0 : rx1) + p.cropX;
-                    int       sy0, sy1, sxmin, sxmax;
-                    if constexpr (INTERP == B200PP_INTERP_NEAREST)
-                    {
-                        sy0 = sy1 = nearest_tap(g.scaleH, dy, g.h);
-                        sxmin     = nearest_tap(g.scaleW, dlo, g.w);
-                        sxmax     = nearest_tap(g.scaleW, dhi, g.w);
-                    }
-                    else
-                    {
-                        float w, wy1;
-                        int   t;
-                        linear_tap(g.scaleH, dy, g.h, sy0, sy1, wy1);
-                        info.wy0s = __fmul_rn(__fsub_rn(1.0f, wy1), kTwo127);
-                        info.wy1s = __fmul_rn(wy1, kTwo127);
-                        linear_tap(g.scaleW, dlo, g.w, sxmin, t, w);
-                        linear_tap(g.scaleW, dhi, g.w, t, sxmax, w);
-                    }
-                    info.g0      = g.base + sy0 * g.pitch;
-                    info.g1      = g.base + sy1 * g.pitch;
-                    info.sameRow = (sy0 == sy1) || info.wy1s == 0.0f; // a lower row of weight zero is never read
-                    rowDelta     = (sy1 - sy0) * g.pitch;
-
-                    const unsigned long long a0 = reinterpret_cast<unsigned long long>(info.g0) + 3ull * sxmin;
-                    const unsigned long long a1 = reinterpret_cast<unsigned long long>(info.g0) + 3ull * (sxmax + 1);
-                    copySrc                     = a0 & ~15ull;
-                    nb                          = static_cast<unsigned>(((a1 + 15ull) & ~15ull) - copySrc);
-                    if (!aligned || nb > static_cast<unsigned>(cfg.segBytes))
-                    {
-                        info.mode = UNIT_DIRECT;
-                    }
-                    else
-                    {
-                        info.mode      = UNIT_STAGED;
-                        info.segOrigin = 3 * sxmin - static_cast<int>(a0 & 15ull);
-                    }
-                }
-            }
+            const long long k = kb + lane;
+            if (k < walk.count)
+                describe_unit<INTERP>(p, cfg, walk.unit(k), perSampleTaps, unitsPerSample, rowBytes, staging[lane]);
+            __syncwarp();
 
             const int batch = static_cast<int>(min(32ll, walk.count - kb));
             for (int j = 0; j < batch; ++j)
             {
+                // Everything the publication needs is read from the staging array before the wait for the slot, so
+                // that the copies go out as soon as the slot is free.
+                const unsigned from = smem_addr(&staging[j]), to = smem_addr(&infos[s]);
+                const uint4    word = lds128(from + 16u * min(lane, static_cast<int>(sizeof(Staged) / 16) - 1));
+                const int      r = (lane >> 1) & (kMaxUnitRows - 1), second = lane & 1;
+                const uint4    ra   = lds128(from + 48u + 32u * r);
+                const uint4    rb   = lds128(from + 64u + 32u * r);
+                const uint4    tail = lds128(from + static_cast<unsigned>(sizeof(UnitInfo)));
+                const int      rows = static_cast<int>(lds128(from).w >> 8);
+                // lane 2r copies the first tapped row of destination row r, lane 2r+1 the second
+                const bool copies = lane < 2 * kMaxUnitRows && r < rows && (ra.x & 0xffu) == UNIT_STAGED
+                                 && (!second || (ra.x & 0x100u));
+                const void *src = reinterpret_cast<const void *>((second ? join64(rb.z, rb.w) : join64(rb.x, rb.y))
+                                                                 + join64(tail.x, tail.y));
+                unsigned char *dstSeg = ring + s * slotBytes + ra.y + (second ? cfg.segBytes : 0);
+
                 bool bad = false;
-                if (lane == j)
+                if (lane == 0 && kb + j >= S && !mbar_wait(&empty[s], emptyParity))
                 {
-                    if (kb + j >= S && !mbar_wait(&empty[s], emptyParity))
-                    {
-                        atomicOr(&g_deviceError, 2u);
-                        bad = true;
-                    }
-                    else
-                    {
-                        infos[s] = info;
-                        if (info.mode == UNIT_STAGED)
-                        {
-                            unsigned char *slot   = ring + s * slotBytes;
-                            const bool     twoRow = (INTERP == B200PP_INTERP_LINEAR) && !info.sameRow;
-                            mbar_arrive_expect_tx(&full[s], twoRow ? 2u * nb : nb);
-                            bulk_load(slot, reinterpret_cast<const void *>(copySrc), nb, &full[s]);
-                            if (twoRow)
-                                bulk_load(slot + cfg.segBytes, reinterpret_cast<const void *>(copySrc + rowDelta), nb, &full[s]);
-                        }
-                        else
-                        {
-                            mbar_arrive(&full[s]);
-                        }
-                    }
+                    atomicOr(&g_deviceError, 2u);
+                    bad = true;
                 }
                 if (__any_sync(0xffffffffu, bad))
                 {
                     failed = true;
                     break;
                 }
+                if (lane < static_cast<int>(sizeof(UnitInfo) / 16))
+                    sts128(to + 16u * lane, word);
+                if (copies)
+                {
+                    mbar_expect_tx(&full[s], tail.z);
+                    bulk_load(dstSeg, src, tail.z, &full[s]);
+                }
+                __syncwarp();
+                if (lane == 0)
+                    mbar_arrive(&full[s]); // the phase completes once this arrival and all expected bytes are in
                 ++issued;
                 if (++s == S)
                 {
@@ -684,6 +845,7 @@ __global__ void __launch_bounds__(512) resize_staged_kernel(const ResizeKParams 
                     emptyParity ^= 1u;
                 }
             }
+            __syncwarp();
         }
         if (failed && lane == 0)
         {
@@ -700,58 +862,213 @@ __global__ void __launch_bounds__(512) resize_staged_kernel(const ResizeKParams 
     }
 
     // ========================================================================= consumers
-    const int     ct         = threadIdx.x - kProducerThreads;
-    const PadValues pv       = pad_values(p);
+    // A unit's header arrives in two vector loads and each of its rows in one; the column taps, their validity and the
+    // choice of store stay in registers while consecutive units share a tap key, which for a dense batch is the
+    // whole launch.
+    const int       ct = threadIdx.x - kProducerThreads;
+    const PadValues pv = pad_values(p);
     StorePlan       plan;
-    plan.co          = chan_offsets(p);
-    plan.interleaved = IL;
-    plan.reversed    = p.mapC[0] == 2;
-    long long     cachedKey  = -1;
-    int           s          = 0;
-    unsigned      fullParity = 0;
-    ColTap        cache[KC];
+    plan.co       = chan_offsets(p);
+    plan.reversed = p.mapC[0] == 2;
+    plan.ilAdj    = DK == DST_F32 ? -8 * lane : lane;
+
+    const unsigned ringA = smem_addr(ring), infoA = smem_addr(infos), fullA = smem_addr(full), emptyA = smem_addr(empty);
+    const unsigned slotStep = static_cast<unsigned>(slotBytes);
+    const unsigned segStep  = static_cast<unsigned>(cfg.segBytes);
+
+    long long cachedKey  = -1;
+    unsigned  fullMask   = 0; // bit k: all 32 lanes of this warp have a k-th cached column
+    int       s          = 0;
+    unsigned  fullParity = 0;
+    ColTap    cache[KC];
     for (long long k = 0; k < walk.count; ++k)
     {
-        if (!mbar_wait(&full[s], fullParity))
+        if (!mbar_wait_addr(fullA + 8u * s, fullParity))
         {
             atomicOr(&g_deviceError, 1u);
             return;
         }
-        const UnitInfo info   = infos[s];
-        uint8_t       *dstRow = p.dst + info.dstRowOff;
+        const unsigned infoAddr = infoA + static_cast<unsigned>(s) * static_cast<unsigned>(sizeof(UnitInfo));
+        const unsigned slotA    = ringA + static_cast<unsigned>(s) * slotStep;
+        const uint4    w0       = lds128(infoAddr);
+        const uint4    w1       = lds128(infoAddr + 16);
+        const int      x0 = static_cast<int>(w0.x), x1 = static_cast<int>(w0.y), origin = static_cast<int>(w0.z);
+        const int      flipX = static_cast<int>(w0.w & 1u), nRows = static_cast<int>(w0.w >> 8);
+        uint8_t       *dstRow = p.dst + join64(w1.x, w1.y);
 
-        if (info.mode == UNIT_PAD)
+        if (w0.w & 2u) // some row is sampled: the cached taps must match this unit
         {
-            for (int xw = info.x0 + (ct - lane); xw < info.x1; xw += consumerThreads)
-                store_warp<DK, IL>(p, plan, pv.v, dstRow, xw + lane, xw + lane < info.x1, lane);
-        }
-        else
-        {
-            const bool refresh = info.tapKey != cachedKey;
-            cachedKey          = info.tapKey;
-            if (info.mode == UNIT_STAGED)
+            const long long key = join64(w1.z, w1.w);
+            if (key != cachedKey) // uniform across the CTA
             {
-                // Its own call site: the row pointers visibly derive from the shared-memory ring, so the tap reads
-                // compile to shared-memory loads.
-                const uint8_t *r0 = ring + s * slotBytes;
-                const uint8_t *r1 = info.sameRow ? r0 : r0 + cfg.segBytes;
-                consume_columns<INTERP, DK, KC, IL>(p, plan, pv, info, r0, r1, info.segOrigin, dstRow, ct, lane,
-                                                    consumerThreads, cache, refresh);
+                cachedKey          = key;
+                const uint4 w2     = lds128(infoAddr + 32);
+                const int   srcW   = static_cast<int>(w2.x);
+                const float scaleW = __uint_as_float(w2.y);
+                fullMask           = 0;
+#pragma unroll
+                for (int c = 0; c < KC; ++c)
+                {
+                    const int  x     = x0 + ct + c * consumerThreads;
+                    const bool valid = x < x1;
+                    if (valid)
+                        cache[c] = make_tap<INTERP>(p, flipX, srcW, scaleW, origin, x);
+                    else
+                    {
+                        cache[c].rel0 = cache[c].rel1 = TAP_NONE;
+                        cache[c].wx0s = cache[c].wx1s = 0.f;
+                        cache[c].dstOff               = 0;
+                    }
+                    if (__all_sync(0xffffffffu, valid))
+                        fullMask |= 1u << c;
+                }
+            }
+        }
+
+        for (int r = 0; r < nRows; ++r, dstRow += p.dRow)
+        {
+            const uint4 ra   = lds128(infoAddr + 48u + 32u * r);
+            const int   mode = static_cast<int>(ra.x & 0xffu);
+            if (mode == UNIT_PAD)
+            {
+                for (int xw = x0 + (ct - lane); xw < x1; xw += consumerThreads)
+                    store_warp<DK, IL>(p, plan, pv.v, dstRow, xw + lane, xw + lane < x1, lane);
+                continue;
+            }
+            const float wy0s = __uint_as_float(ra.z), wy1s = __uint_as_float(ra.w);
+            // the transposing store needs word-aligned warp segments; lane 0 of every warp sits 32*m columns from x0
+            unsigned fastMask = 0;
+            if constexpr (IL && DK != DST_F16)
+            {
+                const unsigned long long rowBits = reinterpret_cast<unsigned long long>(dstRow) + (DK == DST_U8 ? 3ull * x0 : 0ull);
+                fastMask                         = (rowBits & 3ull) == 0 ? fullMask : 0u;
+            }
+            if (mode == UNIT_STAGED)
+            {
+                const SmemRow r0{slotA + ra.y};
+                const SmemRow r1{r0.a + ((ra.x & 0x100u) ? segStep : 0u)};
+                consume_cached<INTERP, DK, KC, IL>(p, plan, pv, r0, r1, wy0s, wy1s, dstRow, cache, fastMask, lane);
+                consume_tail<INTERP, DK, KC, IL>(p, plan, pv, r0, r1, wy0s, wy1s, dstRow, x0, x1, flipX, origin, infoAddr,
+                                                 ct, lane, consumerThreads);
             }
             else
             {
-                consume_columns<INTERP, DK, KC, IL>(p, plan, pv, info, info.g0, info.g1, 0, dstRow, ct, lane,
-                                                    consumerThreads, cache, refresh);
+                const uint4    rb = lds128(infoAddr + 64u + 32u * r);
+                const uint8_t *g0 = reinterpret_cast<const uint8_t *>(join64(rb.x, rb.y));
+                const uint8_t *g1 = reinterpret_cast<const uint8_t *>(join64(rb.z, rb.w));
+                consume_cached<INTERP, DK, KC, IL>(p, plan, pv, g0, g1, wy0s, wy1s, dstRow, cache, fastMask, lane);
+                consume_tail<INTERP, DK, KC, IL>(p, plan, pv, g0, g1, wy0s, wy1s, dstRow, x0, x1, flipX, origin, infoAddr,
+                                                 ct, lane, consumerThreads);
             }
         }
         __syncwarp();
         if (lane == 0)
-            mbar_arrive(&empty[s]);
+            mbar_arrive_addr(emptyA + 8u * s);
         if (++s == S)
         {
             s = 0;
             fullParity ^= 1u;
         }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ row-walk kernel
+//
+// One CTA = up to blockDim.x destination columns x `rowsPerCta` consecutive destination rows of one sample. A thread
+// keeps the taps of its column in registers and walks down the rows, reading the tapped bytes straight from global
+// memory: a warp's 32 columns touch one short contiguous span per source row, which the L1 fetches sector by sector,
+// once. No pipeline machinery, so the fewest instructions per destination pixel of the three kernels; it wins where the
+// staged kernel is bound by instruction issue rather than by HBM (small element types, nearest neighbour).
+constexpr int kWalkRowsMax = 16;
+
+struct alignas(16) WalkRow
+{
+    long long off0, off1; // byte offsets of the two tapped rows from the first byte of the sample's (sub-)image
+    float     wy0s, wy1s; // vertical weights * 2^127
+    int       mode;       // UNIT_PAD or UNIT_DIRECT
+    int       pad;
+};
+
+template<int INTERP, int DK, bool IL>
+__global__ void __launch_bounds__(256) resize_rowwalk_kernel(const ResizeKParams p, const int rowsPerCta, const int chunksPerRow)
+{
+    __shared__ WalkRow rows[kWalkRowsMax];
+
+    const int chunk = blockIdx.x % chunksPerRow;
+    const int y0    = (blockIdx.x / chunksPerRow) * rowsPerCta;
+    const int nRows = min(rowsPerCta, p.dstH - y0);
+    const int lane  = threadIdx.x & 31;
+    const int x     = chunk * blockDim.x + threadIdx.x;
+    const bool valid = x < p.dstW;
+
+    const PadValues pv = pad_values(p);
+    StorePlan       plan;
+    plan.co       = chan_offsets(p);
+    plan.reversed = p.mapC[0] == 2;
+    plan.ilAdj    = DK == DST_F32 ? -8 * lane : lane;
+    const unsigned fullMask = __all_sync(0xffffffffu, valid) ? 1u : 0u;
+
+    for (int n = blockIdx.y; n < p.numSamples; n += gridDim.y)
+    {
+        const Geom g     = load_geom(p, n);
+        const int  flipX = (g.flip == 1 || g.flip == -1);
+        if (threadIdx.x < nRows)
+        {
+            WalkRow   wr{};
+            const int ry = y0 + static_cast<int>(threadIdx.x) - p.dstY;
+            wr.mode      = UNIT_PAD;
+            if (ry >= 0 && ry < p.regionH)
+            {
+                const int dy = ((g.flip == 0 || g.flip == -1) ? p.regionH - 1 - ry : ry) + p.cropY;
+                int       sy0, sy1;
+                if constexpr (INTERP == B200PP_INTERP_NEAREST)
+                {
+                    sy0 = sy1 = nearest_tap(g.scaleH, dy, g.h);
+                }
+                else
+                {
+                    float wy1;
+                    linear_tap(g.scaleH, dy, g.h, sy0, sy1, wy1);
+                    wr.wy0s = __fmul_rn(__fsub_rn(1.0f, wy1), kTwo127);
+                    wr.wy1s = __fmul_rn(wy1, kTwo127);
+                }
+                wr.off0 = sy0 * g.pitch;
+                wr.off1 = sy1 * g.pitch;
+                wr.mode = UNIT_DIRECT;
+            }
+            rows[threadIdx.x] = wr;
+        }
+        ColTap cache[1];
+        if (valid)
+            cache[0] = make_tap<INTERP>(p, flipX, g.w, g.scaleW, 0, x);
+        else
+        {
+            cache[0].rel0 = cache[0].rel1 = TAP_NONE;
+            cache[0].wx0s = cache[0].wx1s = 0.f;
+            cache[0].dstOff               = 0;
+        }
+        __syncthreads();
+
+        uint8_t *dstRow = p.dst + n * p.dSample + y0 * p.dRow;
+        for (int r = 0; r < nRows; ++r, dstRow += p.dRow)
+        {
+            const WalkRow wr = rows[r];
+            if (wr.mode == UNIT_PAD)
+            {
+                if (valid)
+                    store_pixel<DK>(pv.v, plan.co, dstRow + cache[0].dstOff);
+                continue;
+            }
+            unsigned fastMask = 0;
+            if constexpr (IL && DK != DST_F16)
+            {
+                // the transposing store needs word-aligned warp segments; lane 0 of every warp sits 32*m columns from 0
+                fastMask = (reinterpret_cast<unsigned long long>(dstRow) & 3ull) == 0 ? fullMask : 0u;
+            }
+            consume_cached<INTERP, DK, 1, IL>(p, plan, pv, g.base + wr.off0, g.base + wr.off1, wr.wy0s, wr.wy1s, dstRow, cache,
+                                              fastMask, lane);
+        }
+        __syncthreads();
     }
 }
 

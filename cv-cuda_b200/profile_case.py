@@ -24,7 +24,7 @@ INV_STD = tuple(float(np.float32(1.0) / np.float32(s)) for s in (58.395, 57.12, 
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--case", default="classify", choices=("classify", "classify-nhwc-u8", "classify-nhwc-f32", "4k", "4k-nearest", "letterbox", "cfnr", "varshape"))
+    ap.add_argument("--case", default="classify", choices=("classify", "classify-nhwc-u8", "classify-nhwc-f32", "classify-nhwc-u8-nearest", "4k", "4k-nearest", "letterbox", "cfnr", "varshape"))
     ap.add_argument("--images", type=int, default=32)
     ap.add_argument("--path", type=int, default=0)
     ap.add_argument("--launches", type=int, default=5)
@@ -38,12 +38,12 @@ def main():
         src = torch.randint(0, 256, (n, 1080, 1920, 3), dtype=torch.uint8, device="cuda", generator=g)
         out = torch.empty((n, 3, 224, 224), dtype=torch.float32, device="cuda")
         kw = dict(resize_dim=(256, 256), interp=1, crop_pos=(16, 16), layout="NCHW", base=MEAN, mul=INV_STD, srcCast=False)
-    elif a.case in ("classify-nhwc-u8", "classify-nhwc-f32"):
+    elif a.case in ("classify-nhwc-u8", "classify-nhwc-f32", "classify-nhwc-u8-nearest"):
         # the reference's Python operator benchmark: resize 256x256 linear, centre crop 224x224, channel reverse,
         # interleaved output (bench/python/all_ops/op_resize_crop_convert_reformat.py:25-45)
         src = torch.randint(0, 256, (n, 1080, 1920, 3), dtype=torch.uint8, device="cuda", generator=g)
-        out = torch.empty((n, 224, 224, 3), dtype=torch.uint8 if a.case.endswith("u8") else torch.float32, device="cuda")
-        kw = dict(resize_dim=(256, 256), interp=1, crop_pos=(16, 16), layout="NHWC", manip=1, srcCast=True)
+        out = torch.empty((n, 224, 224, 3), dtype=torch.float32 if a.case.endswith("f32") else torch.uint8, device="cuda")
+        kw = dict(resize_dim=(256, 256), interp=int(not a.case.endswith("nearest")), crop_pos=(16, 16), layout="NHWC", manip=1, srcCast=True)
     elif a.case in ("4k", "4k-nearest"):
         src = torch.randint(0, 256, (n, 2160, 3840, 3), dtype=torch.uint8, device="cuda", generator=g)
         out = torch.empty((n, 3, 448, 448), dtype=torch.float16, device="cuda")

@@ -77,7 +77,7 @@ def test_random_resize_cases(pkg, oracle, seed):
         kw["roi"] = to_dev(c["rois"])
     if c["flips"] is not None:
         kw["flip_code"] = to_dev(c["flips"])
-    for path in (1, 2):
+    for path in (1, 2, 3):
         out = torch.zeros(shape, dtype=TORCH[c["dtype"]], device="cuda")
         with kernel_path(pkg, path):
             pkg.fused_preprocess_into(out, src, **kw)

@@ -9,7 +9,7 @@ from gpu_util import assert_parity, kernel_path, padded_images, to_dev
 
 pytestmark = pytest.mark.gpu
 
-PATHS = (1, 2)
+PATHS = (1, 2, 3)  # per-pixel gather, staged pipeline, row walk
 MEAN = (123.675, 116.28, 103.53)
 STD = (58.395, 57.12, 57.375)
 INV_STD = tuple(float(np.float32(1.0) / np.float32(s)) for s in STD)
