@@ -195,9 +195,17 @@ __device__ __forceinline__ Geom load_geom(const ResizeKParams &p, int n)
         g.w = r[2];
         g.h = r[3];
     }
-    g.flip   = p.flip ? p.flip[n] : 2;
-    g.scaleW = __fdiv_rn(static_cast<float>(g.w), static_cast<float>(p.resizeW));
-    g.scaleH = __fdiv_rn(static_cast<float>(g.h), static_cast<float>(p.resizeH));
+    g.flip = p.flip ? p.flip[n] : 2;
+    if (p.list || p.roi)
+    {
+        g.scaleW = __fdiv_rn(static_cast<float>(g.w), static_cast<float>(p.resizeW));
+        g.scaleH = __fdiv_rn(static_cast<float>(g.h), static_cast<float>(p.resizeH));
+    }
+    else
+    {
+        g.scaleW = p.denseScaleW;
+        g.scaleH = p.denseScaleH;
+    }
     return g;
 }
 

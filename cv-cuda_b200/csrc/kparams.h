@@ -28,6 +28,9 @@ struct ResizeKParams
     long long                roiStride; // bytes
     const int               *flip;
     int                      numSamples;
+    // srcW / resizeW and srcH / resizeH in float32, worked out on the host for sources without per-sample sizes
+    // (the same correctly rounded quotient the device would compute)
+    float                    denseScaleW, denseScaleH;
 
     // geometry
     int   resizeW, resizeH, cropX, cropY, srcCast;
@@ -54,7 +57,9 @@ struct StagedCfg
     int       segBytes;     // shared-memory bytes reserved per staged source row (multiple of 128)
     int       rowsPerStage; // source row segments per destination row: 2 for linear, 1 for nearest
     int       unitRows;     // destination rows per work unit (1..4)
-    int       chunkCols;    // destination columns per work unit
+    int       chunkCols;    // destination columns per work unit (at most 128 * colBlocks)
+    int       colBlocks;    // 128-column blocks per unit; the warps of a consumer team are a multiple of it
+    int       teams;        // consumer teams per CTA; team t consumes the CTA's units t, t + teams, ...
     int       chunksPerRow;
     long long totalUnits;   // numSamples * ceil(dstH / unitRows) * chunksPerRow
     long long blockUnits;   // consecutive units dealt to a CTA at a time

@@ -134,6 +134,7 @@ struct Tuning
     int maxConsumers = 0;
     int unitRows     = 0;
     int walkRows     = 0;
+    int teams        = 0;
 };
 
 static const Tuning &tuning()
@@ -154,6 +155,8 @@ static const Tuning &tuning()
             v.unitRows = atoi(r);
         if (const char *w = getenv("B200PP_WALK_ROWS"))
             v.walkRows = atoi(w);
+        if (const char *t = getenv("B200PP_TEAMS"))
+            v.teams = atoi(t);
         return v;
     }();
     return t;
@@ -211,7 +214,9 @@ static int launch_resize_staged(const ResizeKParams &kp, int srcWBound, cudaStre
     };
     const int kMaxSeg = 32 * 1024;
     cfg.chunkCols     = kp.dstW;
-    while (cfg.chunkCols > 32 && seg_for(cfg.chunkCols) > kMaxSeg) cfg.chunkCols = (cfg.chunkCols + 1) / 2;
+    // a consumer warp covers 128 columns (four per lane) and a CTA has at most eight consumer warps
+    while (cfg.chunkCols > 32 && (cfg.chunkCols > 1024 || seg_for(cfg.chunkCols) > kMaxSeg))
+        cfg.chunkCols = ((cfg.chunkCols + 1) / 2 + 3) / 4 * 4;
     cfg.segBytes     = std::min(seg_for(cfg.chunkCols), kMaxSeg);
     cfg.chunksPerRow = (kp.dstW + cfg.chunkCols - 1) / cfg.chunkCols;
 
@@ -224,7 +229,7 @@ static int launch_resize_staged(const ResizeKParams &kp, int srcWBound, cudaStre
     cfg.totalUnits = static_cast<long long>(kp.numSamples) * ((kp.dstH + cfg.unitRows - 1) / cfg.unitRows) * cfg.chunksPerRow;
 
     const int stageBytes = rowBytes * cfg.unitRows;
-    // About 30 KB of copies in flight per CTA (four CTAs per SM): measured best on B200; deeper rings were slower.
+    // About 30-40 KB of copies in flight per CTA (four CTAs per SM): measured best on B200; deeper rings were slower.
     cfg.stages           = std::max(2, std::min(8, (32 * 1024) / stageBytes));
     if (tuning().stages > 0)
         cfg.stages = std::max(2, std::min(16, tuning().stages));
@@ -233,28 +238,25 @@ static int launch_resize_staged(const ResizeKParams &kp, int srcWBound, cudaStre
     if (smemBytes > facts.maxSmemOptin)
         return 0;
 
-    const int maxConsumers  = tuning().maxConsumers > 0 ? std::min(480, tuning().maxConsumers / 32 * 32) : 256;
-    const int colsPerThread = (cfg.chunkCols + maxConsumers - 1) / maxConsumers;
-    int       consumers     = ((cfg.chunkCols + colsPerThread - 1) / colsPerThread + 31) / 32 * 32;
-    consumers               = std::max(32, std::min(consumers, 480));
-    const int block         = kProducerThreads + consumers;
-
-    // columns per consumer thread whose taps are kept in registers
-    const int perThread = (cfg.chunkCols + consumers - 1) / consumers;
-    const int kc        = std::min(3, std::max(1, perThread));
-    // interleaved destinations (uint8 / float32) are written through the warp-transposing store
-    const int  elem = DK == DST_F32 ? 4 : (DK == DST_F16 ? 2 : 1);
-    const bool il   = DK != DST_F16 && kp.dPix == 3 * elem && kp.dChan == elem;
-    auto       kernel = resize_staged_kernel<INTERP, DK, 1, false>;
-    if (il)
-        kernel = kc == 1 ? resize_staged_kernel<INTERP, DK, 1, true>
-               : kc == 2 ? resize_staged_kernel<INTERP, DK, 2, true>
-                         : resize_staged_kernel<INTERP, DK, 3, true>;
-    else
-        kernel = kc == 1 ? resize_staged_kernel<INTERP, DK, 1, false>
-               : kc == 2 ? resize_staged_kernel<INTERP, DK, 2, false>
-                         : resize_staged_kernel<INTERP, DK, 3, false>;
-    const int occ = staged_occupancy(kernel, dev, ((INTERP * 4 + DK) * 4 + kc) * 2 + (il ? 1 : 0), block, smemBytes,
+    // Consumer warps: a team has one warp per 128-column block, times as many rows of a unit as fit; teams (each on
+    // its own unit) fill the CTA up to its warp budget. The budget keeps four CTAs resident per SM for the linear
+    // kernels (about 90 registers per thread) and three for the nearest ones (72).
+    cfg.colBlocks          = (cfg.chunkCols + 127) / 128;
+    const int budget       = INTERP == B200PP_INTERP_LINEAR ? 4 : 8;
+    const int maxWarps     = std::max(cfg.colBlocks, tuning().maxConsumers > 0 ? std::min(8, tuning().maxConsumers / 32) : budget);
+    const int rowWarps     = std::max(1, std::min(cfg.unitRows, maxWarps / cfg.colBlocks));
+    cfg.teams              = std::max(1, std::min(cfg.stages / 2, maxWarps / (cfg.colBlocks * rowWarps)));
+    if (tuning().teams > 0)
+        cfg.teams = std::max(1, std::min({cfg.stages, tuning().teams, 8 / (cfg.colBlocks * rowWarps)}));
+    // A ring slot must always be consumed by the same team: a team that did not consume a slot's previous phase could
+    // run two phases ahead of it, and a parity wait cannot tell those apart. So the team count divides the ring depth.
+    while (cfg.stages % cfg.teams != 0) --cfg.teams;
+    const int block        = kProducerThreads + 32 * cfg.colBlocks * rowWarps * cfg.teams;
+    // interleaved destinations: the three channels of a pixel are adjacent
+    const int  elem   = DK == DST_F32 ? 4 : (DK == DST_F16 ? 2 : 1);
+    const bool il     = kp.dPix == 3 * elem && kp.dChan == elem;
+    auto       kernel = il ? resize_staged_kernel<INTERP, DK, true> : resize_staged_kernel<INTERP, DK, false>;
+    const int occ = staged_occupancy(kernel, dev, (INTERP * 4 + DK) * 2 + (il ? 1 : 0), block, smemBytes,
                                      facts.maxSmemOptin);
     if (occ <= 0)
         return 0;
@@ -279,7 +281,11 @@ static int run_resize(const ResizeKParams &kp, int srcWBound, cudaStream_t strea
     // It also fetches whole row segments: beyond a 32x horizontal reduction (96 source bytes per destination column)
     // the taps skip whole 32-byte sectors and the per-pixel gather moves fewer bytes.
     const bool sparseTaps = static_cast<long long>(srcWBound) > 32ll * kp.resizeW;
-    if (path == 3)
+    // Batches with per-sample geometry (image lists, regions of interest) have short, uneven runs of units per CTA:
+    // the row-walk kernel, with no pipeline to fill and drain, is the faster one there (measured 45 vs 65 us on a
+    // 64-image random-crop batch).
+    const bool perSample = kp.list != nullptr || kp.roi != nullptr;
+    if (path == 3 || (path == 0 && perSample && kp.dstW >= 32))
         return launch_resize_rowwalk<INTERP, DK>(kp, stream);
     const bool wantStaged = path == 2 || (path == 0 && kp.dstW >= 32 && !sparseTaps);
     if (wantStaged)
@@ -375,6 +381,8 @@ extern "C" int b200ppResizeCropConvertReformat(const B200ppSource *src, const B2
     kp.roiStride       = op->roiStride ? op->roiStride : 16;
     kp.flip            = op->flipCode;
     kp.numSamples      = src->numSamples;
+    kp.denseScaleW     = static_cast<float>(src->width) / static_cast<float>(op->resizeW);
+    kp.denseScaleH     = static_cast<float>(src->height) / static_cast<float>(op->resizeH);
     kp.resizeW         = op->resizeW;
     kp.resizeH         = op->resizeH;
     kp.cropX           = op->cropX;

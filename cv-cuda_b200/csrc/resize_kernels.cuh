@@ -22,7 +22,8 @@
 namespace b200pp {
 
 // Device error word. Bits: 1 = a consumer gave up waiting for a staged row, 2 = the producer gave up waiting
-// for a free ring slot, 4 = the producer gave up draining its copies at exit, 8 = the wait self-test gave up (expected).
+// for a free ring slot, 4 = the producer gave up draining its copies at exit, 8 = the wait self-test gave up (expected),
+// 16 = the staged kernel was launched with a shape it refuses (nothing was written).
 __device__ unsigned int g_deviceError;
 
 constexpr int                kProducerThreads = 32;
@@ -594,6 +595,168 @@ __device__ __forceinline__ void consume_tail(const ResizeKParams &p, const Store
     }
 }
 
+// ------------------------------------------------------------------------------------------------ quads
+//
+// A consumer thread of the staged kernel produces four adjacent destination pixels of one row (a quad): the per-row
+// and per-unit bookkeeping is shared by four pixels, and the twelve finished values leave as vectors -- one 4-element
+// store per channel into planar destinations, three into interleaved ones -- with no cross-lane traffic.
+
+// Horizontal taps of a quad. rel0[i]: byte offset of column i's left source pixel relative to the unit's origin, or
+// TAP_PAD / TAP_NONE; the right source pixel is the same one or the next (bit i of `flags`). Bit 8 of `flags`: all
+// four columns exist.
+struct QuadTaps
+{
+    int       rel0[4];
+    float     wx0s[4], wx1s[4]; // horizontal weights * 2^22
+    unsigned  flags;
+    long long dstOff; // destination byte offset of column 0 within the row
+};
+
+constexpr unsigned kQuadFull = 0x100u;
+
+template<int INTERP>
+__device__ __forceinline__ void make_quad(const ResizeKParams &p, int flipX, int srcW, float scaleW, int origin, int xq,
+                                          int x1, QuadTaps &q)
+{
+    q.dstOff = xq * p.dPix;
+    q.flags  = xq + 3 < x1 ? kQuadFull : 0u;
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+    {
+        if (xq + i < x1)
+        {
+            const ColTap t = make_tap<INTERP>(p, flipX, srcW, scaleW, origin, xq + i);
+            q.rel0[i]      = t.rel0;
+            q.wx0s[i]      = t.wx0s;
+            q.wx1s[i]      = t.wx1s;
+            if (t.rel1 != t.rel0)
+                q.flags |= 1u << i;
+        }
+        else
+        {
+            q.rel0[i] = TAP_NONE;
+            q.wx0s[i] = q.wx1s[i] = 0.f;
+        }
+    }
+}
+
+// Taps of a quad in a row that is all padding: only validity and the destination offset matter.
+__device__ __forceinline__ void make_pad_quad(const ResizeKParams &p, int xq, int x1, QuadTaps &q)
+{
+    q.dstOff = xq * p.dPix;
+    q.flags  = xq + 3 < x1 ? kQuadFull : 0u;
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+    {
+        q.rel0[i] = xq + i < x1 ? TAP_PAD : TAP_NONE;
+        q.wx0s[i] = q.wx1s[i] = 0.f;
+    }
+}
+
+// The finished values of the four pixels of a quad: v[i][c], c = source channel.
+template<int INTERP, class Row>
+__device__ __forceinline__ void quad_values(const ResizeKParams &p, const PadValues &pv, const QuadTaps &q, Row r0, Row r1,
+                                            float wy0s, float wy1s, float (&v)[4][3])
+{
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+    {
+        if (q.rel0[i] < 0)
+        {
+#pragma unroll
+            for (int c = 0; c < 3; ++c) v[i][c] = pv.v[c];
+        }
+        else if constexpr (INTERP == B200PP_INTERP_NEAREST)
+            nearest_values(p, r0, q.rel0[i], v[i]);
+        else
+            linear_values(p, r0, r1, q.rel0[i], q.rel0[i] + ((q.flags >> i) & 1u ? 3 : 0), q.wx0s[i], q.wx1s[i], wy0s, wy1s,
+                          v[i]);
+    }
+}
+
+// Four finished values as one vector of the destination element type; `dst` is aligned to the vector size.
+template<int DK>
+__device__ __forceinline__ void store_vec4(uint8_t *dst, float a, float b, float c, float d)
+{
+    if constexpr (DK == DST_F32)
+    {
+        *reinterpret_cast<float4 *>(dst) = make_float4(a, b, c, d);
+    }
+    else if constexpr (DK == DST_F16)
+    {
+        const __half2 lo = __halves2half2(__float2half_rn(a), __float2half_rn(b));
+        const __half2 hi = __halves2half2(__float2half_rn(c), __float2half_rn(d));
+        uint2         w;
+        w.x = *reinterpret_cast<const unsigned *>(&lo);
+        w.y = *reinterpret_cast<const unsigned *>(&hi);
+        *reinterpret_cast<uint2 *>(dst) = w;
+    }
+    else
+    {
+        // round-half-even + clamp leaves the byte in bits 0-7 of each sum; two byte permutes gather the four
+        const unsigned ua = __float_as_uint(__fadd_rn(fminf(fmaxf(a, 0.0f), 255.0f), kRound));
+        const unsigned ub = __float_as_uint(__fadd_rn(fminf(fmaxf(b, 0.0f), 255.0f), kRound));
+        const unsigned uc = __float_as_uint(__fadd_rn(fminf(fmaxf(c, 0.0f), 255.0f), kRound));
+        const unsigned ud = __float_as_uint(__fadd_rn(fminf(fmaxf(d, 0.0f), 255.0f), kRound));
+        *reinterpret_cast<unsigned *>(dst) = __byte_perm(__byte_perm(ua, ub, 0x0040), __byte_perm(uc, ud, 0x0040), 0x5410);
+    }
+}
+
+template<int DK>
+__device__ __forceinline__ constexpr int elem_bytes()
+{
+    return DK == DST_F32 ? 4 : (DK == DST_F16 ? 2 : 1);
+}
+
+// How a consumer thread writes its quads.
+struct QuadStore
+{
+    ChanOff co;
+    bool    reversed;  // channel order reversed
+    bool    planarVec; // channels are planes whose distance keeps vector alignment, pixels of a row are adjacent
+};
+
+// Writes a quad. IL: the destination has the three channels of a pixel adjacent (twelve consecutive elements).
+template<int DK, bool IL>
+__device__ __forceinline__ void store_quad(const ResizeKParams &p, const QuadStore &qs, const QuadTaps &q,
+                                           const float (&v)[4][3], uint8_t *dstRow)
+{
+    constexpr int      kVec = 4 * elem_bytes<DK>();
+    uint8_t           *base = dstRow + q.dstOff;
+    const bool         aligned = (q.flags & kQuadFull) && (reinterpret_cast<unsigned long long>(base) & (kVec - 1)) == 0;
+    if constexpr (IL)
+    {
+        if (aligned)
+        {
+            // destination order: pixel-major, channel-minor
+            float e[12];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+            {
+                e[3 * i + 0] = qs.reversed ? v[i][2] : v[i][0];
+                e[3 * i + 1] = v[i][1];
+                e[3 * i + 2] = qs.reversed ? v[i][0] : v[i][2];
+            }
+#pragma unroll
+            for (int k = 0; k < 3; ++k) store_vec4<DK>(base + k * kVec, e[4 * k], e[4 * k + 1], e[4 * k + 2], e[4 * k + 3]);
+            return;
+        }
+    }
+    else
+    {
+        if (aligned && qs.planarVec)
+        {
+#pragma unroll
+            for (int c = 0; c < 3; ++c) store_vec4<DK>(base + qs.co.c[c], v[0][c], v[1][c], v[2][c], v[3][c]);
+            return;
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+        if (q.rel0[i] != TAP_NONE)
+            store_pixel<DK>(v[i], qs.co, base + i * p.dPix);
+}
+
 // A unit as the producer stages it: the description the consumers get, plus what the copies need.
 struct alignas(16) Staged
 {
@@ -613,9 +776,11 @@ __device__ __forceinline__ void sts128(unsigned addr, uint4 v)
 // Everything about work unit `u`: which sample, rows and columns, what they tap and where the tapped bytes lie.
 template<int INTERP>
 __device__ __forceinline__ void describe_unit(const ResizeKParams &p, const StagedCfg &cfg, long long u, bool perSampleTaps,
-                                              int unitsPerSample, int rowBytes, Staged &out)
+                                              int unitsPerSample, Staged &out)
 {
-    const int  n     = static_cast<int>(u / unitsPerSample);
+    // 64-bit division is a long subroutine; launches of fewer than 2^31 units (all but absurd ones) do without
+    const int  n     = u < 0x7fffffffll ? static_cast<int>(static_cast<unsigned>(u) / static_cast<unsigned>(unitsPerSample))
+                                         : static_cast<int>(u / unitsPerSample);
     const int  rem   = static_cast<int>(u - static_cast<long long>(n) * unitsPerSample);
     const int  yg    = rem / cfg.chunksPerRow;
     const int  chunk = rem - yg * cfg.chunksPerRow;
@@ -671,7 +836,8 @@ __device__ __forceinline__ void describe_unit(const ResizeKParams &p, const Stag
         }
     }
 
-    int sampled = 0;
+    const int      rowBytes  = cfg.rowsPerStage * cfg.segBytes;
+    int            sampled   = 0;
     for (int r = 0; r < nRows; ++r)
     {
         RowInfo   ri{};
@@ -712,6 +878,7 @@ __device__ __forceinline__ void describe_unit(const ResizeKParams &p, const Stag
     out.info.scaleW    = g.scaleW;
     out.colOff         = colOff;
     out.nb             = nb;
+    out.pad            = 0;
 }
 
 // Units are dealt to CTAs in blocks of cfg.blockUnits consecutive units, round-robin over the CTAs.
@@ -738,34 +905,47 @@ struct UnitWalk
     // global index of this CTA's k-th unit
     __device__ __forceinline__ long long unit(long long k) const
     {
+        if (blockUnits == 1)
+            return first + k * stride;
         const long long j = k / blockUnits;
         return first + j * stride + (k - j * blockUnits);
     }
 };
 
 // IL: the destination is interleaved (three adjacent channels per pixel) and is written with the transposing store.
-template<int INTERP, int DK, int KC, bool IL>
-__global__ void __launch_bounds__(512, 2) resize_staged_kernel(const ResizeKParams p, const StagedCfg cfg)
+template<int INTERP, int DK, bool IL>
+__global__ void __launch_bounds__(288, INTERP == B200PP_INTERP_NEAREST ? 3 : 2) resize_staged_kernel(const ResizeKParams p, const StagedCfg cfg)
 {
     extern __shared__ __align__(128) unsigned char smemRaw[];
 
-    const int       S         = cfg.stages;
-    const long long slotBytes = static_cast<long long>(cfg.unitRows) * cfg.rowsPerStage * cfg.segBytes;
-    unsigned char  *ring      = smemRaw;
-    UnitInfo       *infos     = reinterpret_cast<UnitInfo *>(ring + S * slotBytes);
-    auto           *full      = reinterpret_cast<unsigned long long *>(infos + S);
-    unsigned long long *empty = full + S;
+    // Shared memory: the ring of cfg.stages slots (each holds the row segments of one unit), then per slot a UnitInfo
+    // and a full / empty barrier pair, then the producer's staging array.
+    const int           S         = cfg.stages;
+    const long long     slotBytes = static_cast<long long>(cfg.unitRows) * cfg.rowsPerStage * cfg.segBytes;
+    unsigned char      *ring      = smemRaw;
+    UnitInfo           *infos     = reinterpret_cast<UnitInfo *>(ring + S * slotBytes);
+    unsigned long long *full      = reinterpret_cast<unsigned long long *>(infos + S);
+    unsigned long long *empty     = full + S;
 
     const int consumerThreads = blockDim.x - kProducerThreads;
     const int consumerWarps   = consumerThreads / 32;
     const int lane            = threadIdx.x & 31;
+
+    // A ring slot must always be consumed by the same team (see the host code): refuse any other shape.
+    if (cfg.teams < 1 || S % cfg.teams != 0 || consumerWarps % cfg.teams != 0
+        || (consumerWarps / cfg.teams) % cfg.colBlocks != 0)
+    {
+        if (threadIdx.x == 0)
+            atomicOr(&g_deviceError, 16u);
+        return;
+    }
 
     if (threadIdx.x == 0)
     {
         for (int s = 0; s < S; ++s)
         {
             mbar_init(&full[s], 1);
-            mbar_init(&empty[s], consumerWarps);
+            mbar_init(&empty[s], consumerWarps / cfg.teams); // a unit is consumed by one team of warps
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -785,7 +965,6 @@ __global__ void __launch_bounds__(512, 2) resize_staged_kernel(const ResizeKPara
         const bool perSampleTaps  = p.list != nullptr || p.roi != nullptr;
         const int  groupsPerImage = (p.dstH + cfg.unitRows - 1) / cfg.unitRows;
         const int  unitsPerSample = groupsPerImage * cfg.chunksPerRow;
-        const int  rowBytes       = cfg.rowsPerStage * cfg.segBytes;
         int        s           = 0;
         unsigned   emptyParity = 1; // phase the consumers complete when they release the slot's previous use
         bool       failed      = false;
@@ -795,7 +974,7 @@ __global__ void __launch_bounds__(512, 2) resize_staged_kernel(const ResizeKPara
         {
             const long long k = kb + lane;
             if (k < walk.count)
-                describe_unit<INTERP>(p, cfg, walk.unit(k), perSampleTaps, unitsPerSample, rowBytes, staging[lane]);
+                describe_unit<INTERP>(p, cfg, walk.unit(k), perSampleTaps, unitsPerSample, staging[lane]);
             __syncwarp();
 
             const int batch = static_cast<int>(min(32ll, walk.count - kb));
@@ -862,26 +1041,33 @@ __global__ void __launch_bounds__(512, 2) resize_staged_kernel(const ResizeKPara
     }
 
     // ========================================================================= consumers
-    // A unit's header arrives in two vector loads and each of its rows in one; the column taps, their validity and the
-    // choice of store stay in registers while consecutive units share a tap key, which for a dense batch is the
-    // whole launch.
-    const int       ct = threadIdx.x - kProducerThreads;
-    const PadValues pv = pad_values(p);
-    StorePlan       plan;
-    plan.co       = chan_offsets(p);
-    plan.reversed = p.mapC[0] == 2;
-    plan.ilAdj    = DK == DST_F32 ? -8 * lane : lane;
+    // The consumer warps form cfg.teams teams; team t consumes units t, t + teams, ... of this CTA, so that several
+    // ring slots are worked on at once. Within a team, warp w works on column block w % colBlocks (128 columns, four
+    // per lane) of the unit's rows w / colBlocks, + teamWarps/colBlocks, ... A unit's header arrives in two vector loads
+    // and each row in one; the taps of the thread's four columns stay in registers while consecutive units share a tap
+    // key, which for a dense batch is the whole launch.
+    const int       teamWarps = consumerWarps / cfg.teams;
+    const int       cwarp     = (threadIdx.x - kProducerThreads) >> 5;
+    const int       team      = cwarp / teamWarps;
+    const int       warp      = cwarp - team * teamWarps;
+    const int       cb        = warp % cfg.colBlocks;
+    const int       rowLane   = warp / cfg.colBlocks;
+    const int       rowStep   = teamWarps / cfg.colBlocks;
+    const PadValues pv      = pad_values(p);
+    QuadStore       qs;
+    qs.co        = chan_offsets(p);
+    qs.reversed  = p.mapC[0] == 2;
+    qs.planarVec = p.dPix == elem_bytes<DK>() && (p.dChan & (4 * elem_bytes<DK>() - 1)) == 0;
 
     const unsigned ringA = smem_addr(ring), infoA = smem_addr(infos), fullA = smem_addr(full), emptyA = smem_addr(empty);
     const unsigned slotStep = static_cast<unsigned>(slotBytes);
     const unsigned segStep  = static_cast<unsigned>(cfg.segBytes);
 
     long long cachedKey  = -1;
-    unsigned  fullMask   = 0; // bit k: all 32 lanes of this warp have a k-th cached column
-    int       s          = 0;
-    unsigned  fullParity = 0;
-    ColTap    cache[KC];
-    for (long long k = 0; k < walk.count; ++k)
+    int       s          = team % S; // slot of unit `team`
+    unsigned  fullParity = static_cast<unsigned>(team / S) & 1u;
+    QuadTaps  quad;
+    for (long long k = team; k < walk.count; k += cfg.teams)
     {
         if (!mbar_wait_addr(fullA + 8u * s, fullParity))
         {
@@ -892,81 +1078,62 @@ __global__ void __launch_bounds__(512, 2) resize_staged_kernel(const ResizeKPara
         const unsigned slotA    = ringA + static_cast<unsigned>(s) * slotStep;
         const uint4    w0       = lds128(infoAddr);
         const uint4    w1       = lds128(infoAddr + 16);
-        const int      x0 = static_cast<int>(w0.x), x1 = static_cast<int>(w0.y), origin = static_cast<int>(w0.z);
-        const int      flipX = static_cast<int>(w0.w & 1u), nRows = static_cast<int>(w0.w >> 8);
-        uint8_t       *dstRow = p.dst + join64(w1.x, w1.y);
+        const int      x1 = static_cast<int>(w0.y), nRows = static_cast<int>(w0.w >> 8);
+        const int      xq = static_cast<int>(w0.x) + 128 * cb + 4 * lane; // first column of this thread's quad
+        uint8_t       *dstBase = p.dst + join64(w1.x, w1.y);
 
         if (w0.w & 2u) // some row is sampled: the cached taps must match this unit
         {
             const long long key = join64(w1.z, w1.w);
             if (key != cachedKey) // uniform across the CTA
             {
-                cachedKey          = key;
-                const uint4 w2     = lds128(infoAddr + 32);
-                const int   srcW   = static_cast<int>(w2.x);
-                const float scaleW = __uint_as_float(w2.y);
-                fullMask           = 0;
-#pragma unroll
-                for (int c = 0; c < KC; ++c)
-                {
-                    const int  x     = x0 + ct + c * consumerThreads;
-                    const bool valid = x < x1;
-                    if (valid)
-                        cache[c] = make_tap<INTERP>(p, flipX, srcW, scaleW, origin, x);
-                    else
-                    {
-                        cache[c].rel0 = cache[c].rel1 = TAP_NONE;
-                        cache[c].wx0s = cache[c].wx1s = 0.f;
-                        cache[c].dstOff               = 0;
-                    }
-                    if (__all_sync(0xffffffffu, valid))
-                        fullMask |= 1u << c;
-                }
+                cachedKey      = key;
+                const uint4 w2 = lds128(infoAddr + 32);
+                make_quad<INTERP>(p, static_cast<int>(w0.w & 1u), static_cast<int>(w2.x), __uint_as_float(w2.y),
+                                  static_cast<int>(w0.z), xq, x1, quad);
             }
         }
 
-        for (int r = 0; r < nRows; ++r, dstRow += p.dRow)
+        for (int r = rowLane; r < nRows; r += rowStep)
         {
-            const uint4 ra   = lds128(infoAddr + 48u + 32u * r);
-            const int   mode = static_cast<int>(ra.x & 0xffu);
+            const uint4 ra     = lds128(infoAddr + 48u + 32u * r);
+            const int   mode   = static_cast<int>(ra.x & 0xffu);
+            uint8_t    *dstRow = dstBase + r * p.dRow;
+            float       v[4][3];
             if (mode == UNIT_PAD)
             {
-                for (int xw = x0 + (ct - lane); xw < x1; xw += consumerThreads)
-                    store_warp<DK, IL>(p, plan, pv.v, dstRow, xw + lane, xw + lane < x1, lane);
+                QuadTaps padQuad;
+                make_pad_quad(p, xq, x1, padQuad);
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+#pragma unroll
+                    for (int c = 0; c < 3; ++c) v[i][c] = pv.v[c];
+                store_quad<DK, IL>(p, qs, padQuad, v, dstRow);
                 continue;
             }
             const float wy0s = __uint_as_float(ra.z), wy1s = __uint_as_float(ra.w);
-            // the transposing store needs word-aligned warp segments; lane 0 of every warp sits 32*m columns from x0
-            unsigned fastMask = 0;
-            if constexpr (IL && DK != DST_F16)
-            {
-                const unsigned long long rowBits = reinterpret_cast<unsigned long long>(dstRow) + (DK == DST_U8 ? 3ull * x0 : 0ull);
-                fastMask                         = (rowBits & 3ull) == 0 ? fullMask : 0u;
-            }
             if (mode == UNIT_STAGED)
             {
                 const SmemRow r0{slotA + ra.y};
                 const SmemRow r1{r0.a + ((ra.x & 0x100u) ? segStep : 0u)};
-                consume_cached<INTERP, DK, KC, IL>(p, plan, pv, r0, r1, wy0s, wy1s, dstRow, cache, fastMask, lane);
-                consume_tail<INTERP, DK, KC, IL>(p, plan, pv, r0, r1, wy0s, wy1s, dstRow, x0, x1, flipX, origin, infoAddr,
-                                                 ct, lane, consumerThreads);
+                quad_values<INTERP>(p, pv, quad, r0, r1, wy0s, wy1s, v);
             }
             else
             {
                 const uint4    rb = lds128(infoAddr + 64u + 32u * r);
                 const uint8_t *g0 = reinterpret_cast<const uint8_t *>(join64(rb.x, rb.y));
                 const uint8_t *g1 = reinterpret_cast<const uint8_t *>(join64(rb.z, rb.w));
-                consume_cached<INTERP, DK, KC, IL>(p, plan, pv, g0, g1, wy0s, wy1s, dstRow, cache, fastMask, lane);
-                consume_tail<INTERP, DK, KC, IL>(p, plan, pv, g0, g1, wy0s, wy1s, dstRow, x0, x1, flipX, origin, infoAddr,
-                                                 ct, lane, consumerThreads);
+                quad_values<INTERP>(p, pv, quad, g0, g1, wy0s, wy1s, v);
             }
+            store_quad<DK, IL>(p, qs, quad, v, dstRow);
         }
         __syncwarp();
         if (lane == 0)
             mbar_arrive_addr(emptyA + 8u * s);
-        if (++s == S)
+        s += cfg.teams;
+        while (s >= S)
         {
-            s = 0;
+            s -= S;
             fullParity ^= 1u;
         }
     }
