@@ -49,7 +49,7 @@ ALG_OUT_BYTES = 3 * 224 * 224 * 4
 ALG_BYTES = ALG_SRC_BYTES + ALG_OUT_BYTES
 # DRAM traffic per image of the staged kernel from the ncu capture summarised in
 # profiles/resize_staged_linear_f32_1080p_to_224.md (full-size launch of 256 images, one-pass capture).
-NCU_TRAFFIC_BYTES_PER_IMAGE = 737738496 / 256
+NCU_TRAFFIC_BYTES_PER_IMAGE = 736412928 / 256
 FALLBACK_HBM_GBS = 6650.0
 
 
@@ -298,6 +298,35 @@ def run_native(args) -> int:
     check = host_out[:2].numpy().copy()
     best = max(e2e_results, key=lambda k: e2e_results[k]["value"])
 
+    # ---- the reference project's own CUDA kernel (compiled for sm_100a from the reference sources into oracle/_ref),
+    # same GPU, same source batch: a reported baseline, like the CPU one. Its operator has one scalar scale/offset, so
+    # channel 0's constants stand in and the per-channel Normalize pass its pipeline would still need is not timed.
+    ref_cuda = None
+    if rank == 0:
+        from oracle import ref_cuda as RC
+        if RC.lib() is not None:
+            out_ref = torch.empty_like(out)
+            n_ref = max(3, min(args.steps, 50))
+
+            def ref_step():
+                RC.rccr_tensor(src, out_ref, True, RESIZE, 1, CROP, 0, mul[0], -MEAN[0] * mul[0], False)
+
+            for _ in range(3):
+                ref_step()
+            torch.cuda.synchronize()
+            e0.record()
+            for _ in range(n_ref):
+                ref_step()
+            e1.record()
+            torch.cuda.synchronize()
+            ref_ms = e0.elapsed_time(e1) / n_ref
+            ref_cuda = {"value": BATCH / (ref_ms / 1000.0), "unit": UNIT + " on one GPU", "ms_per_step": ref_ms,
+                        "launches": n_ref,
+                        "kind": "reference resizeCrop_bilinear kernel (src/cvcuda/priv/OpResizeCropConvertReformat.cu:158-198), "
+                                "its 16x16 launch shape, built for sm_100a; scalar scale/offset of channel 0, float32 NCHW; "
+                                "the Normalize pass its pipeline needs for per-channel constants is not included"}
+            del out_ref
+
     clock_info = clocks.stop() if rank == 0 else None
     if world > 1:
         dist.barrier()
@@ -327,10 +356,11 @@ def run_native(args) -> int:
                          "peak_kind": peak_kind, "frac_of_nominal_8000": achieved / 8000.0,
                          "alg_bytes_per_image": ALG_BYTES, "images_per_launch": BATCH,
                          "traffic": NCU_TRAFFIC_BYTES_PER_IMAGE * BATCH if NCU_TRAFFIC_BYTES_PER_IMAGE else None,
-                         "kernel": "resize_staged_kernel<LINEAR,F32>"},
+                         "kernel": "resize_staged_kernel<LINEAR,F32,planar>"},
             "e2e": {"value": e2e_results[best]["value"], "unit": UNIT, "mode": best,
                     "h2d_bytes_per_step": e2e_results[best]["h2d_bytes_per_step"],
                     "d2h_bytes_per_step": int(host_out.numel() * 4), "steps": e2e_steps, "all_modes": e2e_results},
+            "reference_cuda_baseline": ref_cuda,
             "cpu_baseline": {"value": statistics.mean(cpu_rates), "unit": UNIT, "cores": cores, "kind": kind,
                              "sample": sample},
             "gpu_launches": int(launches), "clocks": clock_info, "parity_max_abs_diff": parity,

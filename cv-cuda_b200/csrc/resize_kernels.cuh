@@ -763,7 +763,7 @@ struct alignas(16) Staged
     UnitInfo  info;
     long long colOff;  // from byte 0 of a tapped source row to the 16-byte aligned start of the copied span
     unsigned  nb;      // bytes per copied row segment
-    unsigned  pad;
+    unsigned  txBytes; // bytes all copies of the unit deliver
 };
 
 static_assert(sizeof(Staged) == sizeof(UnitInfo) + 16, "Staged tail is read as one 16-byte word");
@@ -838,6 +838,7 @@ __device__ __forceinline__ void describe_unit(const ResizeKParams &p, const Stag
 
     const int      rowBytes  = cfg.rowsPerStage * cfg.segBytes;
     int            sampled   = 0;
+    unsigned       txBytes   = 0;
     for (int r = 0; r < nRows; ++r)
     {
         RowInfo   ri{};
@@ -865,6 +866,8 @@ __device__ __forceinline__ void describe_unit(const ResizeKParams &p, const Stag
             ri.g1   = g.base + sy1 * g.pitch;
             ri.mode = unitMode | (twoRow && unitMode == UNIT_STAGED ? 0x100 : 0);
             sampled = 2;
+            if (unitMode == UNIT_STAGED)
+                txBytes += twoRow ? 2u * nb : nb;
         }
         out.info.row[r] = ri;
     }
@@ -878,7 +881,7 @@ __device__ __forceinline__ void describe_unit(const ResizeKParams &p, const Stag
     out.info.scaleW    = g.scaleW;
     out.colOff         = colOff;
     out.nb             = nb;
-    out.pad            = 0;
+    out.txBytes        = txBytes;
 }
 
 // Units are dealt to CTAs in blocks of cfg.blockUnits consecutive units, round-robin over the CTAs.
@@ -1010,13 +1013,17 @@ __global__ void __launch_bounds__(288, INTERP == B200PP_INTERP_NEAREST ? 3 : 2) 
                 if (lane < static_cast<int>(sizeof(UnitInfo) / 16))
                     sts128(to + 16u * lane, word);
                 if (copies)
-                {
-                    mbar_expect_tx(&full[s], tail.z);
                     bulk_load(dstSeg, src, tail.z, &full[s]);
-                }
                 __syncwarp();
+                // One arrival carrying the byte count of all the unit's copies: the phase completes once it and the
+                // bytes are in (bytes that land before it only run the transaction count negative for a moment).
                 if (lane == 0)
-                    mbar_arrive(&full[s]); // the phase completes once this arrival and all expected bytes are in
+                {
+                    if (tail.w)
+                        mbar_arrive_expect_tx(&full[s], tail.w);
+                    else
+                        mbar_arrive(&full[s]);
+                }
                 ++issued;
                 if (++s == S)
                 {
