@@ -3,13 +3,16 @@
 //  * resize_gather_kernel  -- one thread per destination pixel, taps read straight from global memory.
 //                             Handles every argument combination; the fallback and the cross-check.
 //  * resize_rowwalk_kernel -- a thread keeps one destination column's taps in registers and walks down a group of
-//                             rows, reading from global memory through the L1: the leanest instruction stream.
-//  * resize_staged_kernel  -- persistent, warp-specialised pipeline. A work unit is one destination row segment of
-//                             one sample. A producer thread copies the one or two source row segments that the unit
-//                             taps into a shared-memory ring with bulk asynchronous copies (cp.async.bulk, completion
-//                             on an mbarrier); the consumer warps interpolate out of shared memory and write
-//                             warp-contiguous destination rows. HBM sees only long contiguous reads and full-sector
-//                             writes; the byte-granular gather happens in shared memory.
+//                             rows, reading from global memory through the L1. No pipeline to fill or drain: the kernel
+//                             for batches with per-sample geometry (image lists, regions of interest).
+//  * resize_staged_kernel  -- persistent, warp-specialised pipeline for dense batches. A work unit is one to four
+//                             destination rows of one column chunk of one sample. A producer warp describes units 32
+//                             at a time and publishes them in order: the source row segments a unit taps go into a
+//                             shared-memory ring by bulk asynchronous copies (cp.async.bulk, completion counted in
+//                             bytes on an mbarrier). Consumer warps interpolate out of shared memory, four adjacent
+//                             pixels per thread, and write the rows with 4-element vector stores. HBM sees only long
+//                             contiguous reads and full-sector writes; the byte-granular gather happens in shared
+//                             memory.
 //
 // Replaces resizeCrop_NN / resizeCrop_bilinear / *_varShape of the reference
 // (src/cvcuda/priv/OpResizeCropConvertReformat.cu:137-278); arithmetic follows the reference's CPU golden
@@ -513,7 +516,7 @@ __device__ __forceinline__ void pixel_values(const ResizeKParams &p, const PadVa
         linear_values(p, r0, r1, t.rel0, t.rel1, t.wx0s, t.wx1s, wy0s, wy1s, v);
 }
 
-// How a consumer thread writes its pixels.
+// How a thread of the row-walk kernel writes its pixels.
 struct StorePlan
 {
     ChanOff   co;
@@ -522,28 +525,8 @@ struct StorePlan
                         // transposed warp store (-8*lane for float32, +lane for uint8)
 };
 
-// Stores one pixel per lane of a warp, deciding per call whether the warp can use the transposing store. `x` is this
-// lane's column (lanes hold consecutive columns), `valid` whether it exists. Every lane of the warp must call this.
-template<int DK, bool IL>
-__device__ __forceinline__ void store_warp(const ResizeKParams &p, const StorePlan &plan, const float (&v)[3],
-                                           uint8_t *dstRow, int x, bool valid, int lane)
-{
-    if constexpr (IL && DK != DST_F16)
-    {
-        uint8_t   *warpBase = dstRow + (x - lane) * p.dPix;
-        const bool full     = __all_sync(0xffffffffu, valid) && (reinterpret_cast<unsigned long long>(warpBase) & 3ull) == 0;
-        if (full)
-        {
-            const float d[3] = {plan.reversed ? v[2] : v[0], v[1], plan.reversed ? v[0] : v[2]};
-            store_interleaved_warp<DK>(d, dstRow + x * p.dPix + plan.ilAdj, lane);
-            return;
-        }
-    }
-    if (valid)
-        store_pixel<DK>(v, plan.co, dstRow + x * p.dPix);
-}
-
-// The cached columns of one unit: taps, validity and the choice of store were settled when the cache was filled.
+// The cached columns of one row (row-walk kernel): taps, validity and the choice of store were settled when the cache
+// was filled.
 template<int INTERP, int DK, int KC, bool IL, class Row>
 __device__ __forceinline__ void consume_cached(const ResizeKParams &p, const StorePlan &plan, const PadValues &pv, Row r0,
                                                Row r1, float wy0s, float wy1s, uint8_t *dstRow, const ColTap (&cache)[KC],
@@ -566,32 +549,6 @@ __device__ __forceinline__ void consume_cached(const ResizeKParams &p, const Sto
         }
         if (cache[k].rel0 != TAP_NONE)
             store_pixel<DK>(v, plan.co, pix);
-    }
-}
-
-// Columns beyond the cached ones (rows wider than KC columns per consumer thread): taps are worked out on the fly.
-template<int INTERP, int DK, int KC, bool IL, class Row>
-__device__ __forceinline__ void consume_tail(const ResizeKParams &p, const StorePlan &plan, const PadValues &pv, Row r0,
-                                             Row r1, float wy0s, float wy1s, uint8_t *dstRow, int x0, int x1, int flipX,
-                                             int origin, unsigned infoAddr, int ct, int lane, int consumerThreads)
-{
-    int xw = x0 + (ct - lane) + KC * consumerThreads;
-    if (xw >= x1)
-        return;
-    const uint4 w3     = lds128(infoAddr + 32);
-    const int   srcW   = static_cast<int>(w3.x);
-    const float scaleW = __uint_as_float(w3.y);
-    for (; xw < x1; xw += consumerThreads)
-    {
-        const int  x     = xw + lane;
-        const bool valid = x < x1;
-        float      v[3]  = {0.f, 0.f, 0.f};
-        if (valid)
-        {
-            const ColTap t = make_tap<INTERP>(p, flipX, srcW, scaleW, origin, x);
-            pixel_values<INTERP>(p, pv, t, r0, r1, wy0s, wy1s, v);
-        }
-        store_warp<DK, IL>(p, plan, v, dstRow, x, valid, lane);
     }
 }
 
