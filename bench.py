@@ -49,7 +49,7 @@ ALG_OUT_BYTES = 3 * 224 * 224 * 4
 ALG_BYTES = ALG_SRC_BYTES + ALG_OUT_BYTES
 # DRAM traffic per image of the staged kernel from the ncu capture summarised in
 # profiles/resize_staged_linear_f32_1080p_to_224.md (full-size launch of 256 images, one-pass capture).
-NCU_TRAFFIC_BYTES_PER_IMAGE = 736412928 / 256
+NCU_TRAFFIC_BYTES_PER_IMAGE = 736304128 / 256
 FALLBACK_HBM_GBS = 6650.0
 
 
