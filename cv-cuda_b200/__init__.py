@@ -23,6 +23,8 @@ from .ops import (  # noqa: F401
     lib,
     lib_path,
     read_device_error,
+    resize,
+    resize_into,
     resize_crop_convert_reformat,
     resize_crop_convert_reformat_into,
     self_test_wait_timeout,

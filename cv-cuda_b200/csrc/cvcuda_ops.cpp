@@ -103,7 +103,8 @@ constexpr uint64_t kMagic = 0xB2000C0DA0F5ED01ull;
 enum OpKind
 {
     OP_RESIZE_CROP_CONVERT_REFORMAT  = 1,
-    OP_CROP_FLIP_NORMALIZE_REFORMAT = 2
+    OP_CROP_FLIP_NORMALIZE_REFORMAT = 2,
+    OP_RESIZE                       = 3
 };
 
 // The handle is the object pointer itself, as in the reference (src/cvcuda/priv/IOperator.hpp:37-40). Operators hold
@@ -160,6 +161,7 @@ struct ImageView
     int64_t  sampleStride = 0, rowStride = 0, colStride = 0, chanStride = 0;
     uint8_t *base = nullptr;
     int      dtype = -1;
+    int      elemChannels = 1; // channels carried by the element type itself (3U8 -> 3)
     char     layout[NVCV_TENSOR_MAX_RANK + 1] = "";
 };
 
@@ -176,6 +178,7 @@ bool export_tensor(NVCVTensorHandle h, ImageView &v, const char *what, NVCVStatu
     nvcv().dataTypeGetDataKind(d.dtype, &kind);
     nvcv().dataTypeGetBitsPerChannel(d.dtype, bits);
     v.dtype = element_type(kind, bits[0]);
+    for (int k = 1; k < 4; ++k) v.elemChannels += bits[k] != 0;
     v.base  = d.strided.basePtr;
     std::memcpy(v.layout, d.layout.data, sizeof(v.layout));
     v.layout[NVCV_TENSOR_MAX_RANK] = 0;
@@ -371,9 +374,110 @@ B200ppResizeOp reference_op(NVCVSize2D resizeDim, int interp, int2 cropPos, int 
     return op;
 }
 
+// ---------------------------------------------------------------------------------------------- stand-alone Resize
+
+// The reference accepts the channel count either in the tensor shape or baked into the element type (3U8 ...),
+// src/cvcuda/priv/OpResize.cu:455-486: ImageView::elemChannels carries the latter.
+NVCVStatus plain_resize_tensor(NVCVOperatorHandle handle, cudaStream_t stream, NVCVTensorHandle in, NVCVTensorHandle out,
+                               int interp)
+{
+    if (NVCVStatus st = check_handle(handle, OP_RESIZE))
+        return st;
+    if (!nvcv().ok)
+        return report(B200PP_ERROR_INTERNAL, "libnvcv_types is not loaded in this process");
+    NVCVStatus st = B200PP_SUCCESS;
+    ImageView  i, o;
+    if (!export_tensor(in, i, "Input", st) || !export_tensor(out, o, "Output", st))
+        return st;
+    // order and codes of src/cvcuda/priv/OpResize.cu:501-541
+    if (i.dtype != o.dtype || i.elemChannels != o.elemChannels)
+        return report(B200PP_ERROR_INVALID_ARGUMENT, "Input and output data type are different");
+    if (std::strcmp(i.layout, o.layout) != 0)
+        return report(B200PP_ERROR_INVALID_ARGUMENT, "Input and output data layout are different");
+    if (!layout_is(i, "HWC", "NHWC"))
+        return report(B200PP_ERROR_INVALID_ARGUMENT, "Input must have (N)HWC layout");
+    if (!i.valid || !o.valid)
+        return report(B200PP_ERROR_INVALID_ARGUMENT, "Input and output must be image-like tensors");
+    B200ppImageSet s, d;
+    std::memset(&s, 0, sizeof(s));
+    std::memset(&d, 0, sizeof(d));
+    const ImageView *views[2] = {&i, &o};
+    B200ppImageSet  *sets[2]  = {&s, &d};
+    for (int k = 0; k < 2; ++k)
+    {
+        sets[k]->base         = views[k]->base;
+        sets[k]->dtype        = views[k]->dtype;
+        sets[k]->channels     = views[k]->channels * views[k]->elemChannels;
+        sets[k]->numSamples   = views[k]->samples;
+        sets[k]->width        = views[k]->cols;
+        sets[k]->height       = views[k]->rows;
+        sets[k]->rowStride    = views[k]->rowStride;
+        sets[k]->sampleStride = views[k]->sampleStride;
+    }
+    return forward(b200ppResize(&s, &d, interp, stream));
+}
+
+NVCVStatus plain_resize_varshape(NVCVOperatorHandle handle, cudaStream_t stream, NVCVImageBatchHandle in,
+                                 NVCVImageBatchHandle out, int interp)
+{
+    if (NVCVStatus st = check_handle(handle, OP_RESIZE))
+        return st;
+    if (!nvcv().ok)
+        return report(B200PP_ERROR_INTERNAL, "libnvcv_types is not loaded in this process");
+    NVCVImageBatchData bi, bo;
+    std::memset(&bi, 0, sizeof(bi));
+    std::memset(&bo, 0, sizeof(bo));
+    if (in == nullptr || nvcv().imageBatchExportData(in, stream, &bi) != B200PP_SUCCESS || bi.bufferType != 1)
+        return report(B200PP_ERROR_INVALID_ARGUMENT, "Input must be cuda-accessible, varshape pitch-linear image batch");
+    if (out == nullptr || nvcv().imageBatchExportData(out, stream, &bo) != B200PP_SUCCESS || bo.bufferType != 1)
+        return report(B200PP_ERROR_INVALID_ARGUMENT, "Output must be cuda-accessible, varshape pitch-linear image batch");
+    if (bi.varShapeStrided.uniqueFormat == 0 || bo.varShapeStrided.uniqueFormat == 0)
+        return report(B200PP_ERROR_INVALID_ARGUMENT, "Images in the input and output batches must all have the same format");
+    if (bi.varShapeStrided.uniqueFormat != bo.varShapeStrided.uniqueFormat)
+        return report(B200PP_ERROR_INVALID_ARGUMENT, "Input and output data type are different");
+    int channels = 0, planes = 0, kind = -1, bits[4] = {0, 0, 0, 0};
+    nvcv().imageFormatGetNumChannels(bi.varShapeStrided.uniqueFormat, &channels);
+    nvcv().imageFormatGetNumPlanes(bi.varShapeStrided.uniqueFormat, &planes);
+    nvcv().imageFormatGetDataKind(bi.varShapeStrided.uniqueFormat, &kind);
+    nvcv().imageFormatGetBitsPerChannel(bi.varShapeStrided.uniqueFormat, bits);
+    if (planes > 1)
+        return report(B200PP_ERROR_INVALID_ARGUMENT, "Image batches must hold interleaved (single-plane) images");
+    B200ppImageSet s, d;
+    std::memset(&s, 0, sizeof(s));
+    std::memset(&d, 0, sizeof(d));
+    s.dtype = d.dtype = element_type(kind, bits[0]);
+    s.channels = d.channels = channels;
+    s.numSamples            = bi.numImages;
+    d.numSamples            = bo.numImages;
+    s.imageList             = bi.varShapeStrided.imageList;
+    d.imageList             = bo.varShapeStrided.imageList;
+    s.maxWidth              = bi.varShapeStrided.maxWidth;
+    s.maxHeight             = bi.varShapeStrided.maxHeight;
+    d.maxWidth              = bo.varShapeStrided.maxWidth;
+    d.maxHeight             = bo.varShapeStrided.maxHeight;
+    return forward(b200ppResize(&s, &d, interp, stream));
+}
+
 } // namespace
 
 // ================================================================================================ exported symbols
+
+extern "C" NVCVStatus cvcudaResizeCreate(NVCVOperatorHandle *handle)
+{
+    return create(handle, OP_RESIZE);
+}
+
+extern "C" NVCVStatus cvcudaResizeSubmit(NVCVOperatorHandle handle, cudaStream_t stream, NVCVTensorHandle in,
+                                         NVCVTensorHandle out, const NVCVInterpolationType interpolation)
+{
+    return plain_resize_tensor(handle, stream, in, out, static_cast<int>(interpolation));
+}
+
+extern "C" NVCVStatus cvcudaResizeVarShapeSubmit(NVCVOperatorHandle handle, cudaStream_t stream, NVCVImageBatchHandle in,
+                                                 NVCVImageBatchHandle out, const NVCVInterpolationType interpolation)
+{
+    return plain_resize_varshape(handle, stream, in, out, static_cast<int>(interpolation));
+}
 
 extern "C" NVCVStatus cvcudaResizeCropConvertReformatCreate(NVCVOperatorHandle *handle)
 {

@@ -1,5 +1,6 @@
 // Host side of the plain-C launch layer: argument validation, kernel selection and launch.
 // The single translation unit that contains all device code of the library.
+#include "plain_resize_kernels.cuh"
 #include "resize_kernels.cuh"
 #include "slice_kernels.cuh"
 
@@ -542,6 +543,106 @@ extern "C" int b200ppCropFlipNormalizeReformat(const B200ppSource *src, const B2
     dim3 grid((kp.dstW + 31) / 32, (kp.dstH + 7) / 8, std::min(kp.numSamples, 32768));
     slice_gather_kernel<4><<<grid, block, 0, stream>>>(kp, src->dtype, dst->dtype, elem_size(src->dtype));
     return check_launch("CropFlipNormalizeReformat");
+}
+
+// ================================================================================================ stand-alone Resize
+
+namespace b200pp {
+
+template<typename T, int C>
+static void launch_plain(int interp, dim3 grid, dim3 block, cudaStream_t stream, const PlainResizeKParams &kp)
+{
+    if (interp == B200PP_INTERP_NEAREST)
+        resize_plain_kernel<T, C, B200PP_INTERP_NEAREST><<<grid, block, 0, stream>>>(kp);
+    else
+        resize_plain_kernel<T, C, B200PP_INTERP_LINEAR><<<grid, block, 0, stream>>>(kp);
+}
+
+template<typename T>
+static void launch_plain_channels(int channels, int interp, dim3 grid, dim3 block, cudaStream_t stream,
+                                  const PlainResizeKParams &kp)
+{
+    if (channels == 1)
+        launch_plain<T, 1>(interp, grid, block, stream, kp);
+    else if (channels == 3)
+        launch_plain<T, 3>(interp, grid, block, stream, kp);
+    else
+        launch_plain<T, 4>(interp, grid, block, stream, kp);
+}
+
+static PlainSide plain_side(const B200ppImageSet *s)
+{
+    PlainSide p{};
+    p.base         = static_cast<uint8_t *>(s->base);
+    p.list         = s->imageList;
+    p.sampleStride = s->sampleStride;
+    p.rowStride    = s->rowStride;
+    p.width        = s->width;
+    p.height       = s->height;
+    return p;
+}
+
+} // namespace b200pp
+
+extern "C" int b200ppResize(const B200ppImageSet *src, const B200ppImageSet *dst, int32_t interp, cudaStream_t stream)
+{
+    if (!src || !dst)
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "Null argument");
+    // Checks, order and status codes of the reference operator (src/cvcuda/priv/OpResize.cu:501-555, :455-486).
+    if (src->dtype != dst->dtype)
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "Input and output data type are different");
+    if (src->numSamples != dst->numSamples)
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "Input and output samples are different");
+    if (src->channels != dst->channels)
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "Input and output channels are different");
+    if (src->channels > 4 || src->channels < 1)
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "Invalid number of channels");
+    if (interp == 2 /* NVCV_INTERP_CUBIC */ || interp == 3 /* NVCV_INTERP_AREA */)
+        return fail(B200PP_ERROR_NOT_IMPLEMENTED, "Interpolation not implemented: %s",
+                    interp == 2 ? "NVCV_INTERP_CUBIC" : "NVCV_INTERP_AREA");
+    if (interp != B200PP_INTERP_NEAREST && interp != B200PP_INTERP_LINEAR)
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "Invalid interpolation");
+    const bool knownType = src->dtype == B200PP_U8 || src->dtype == B200PP_U16 || src->dtype == B200PP_S16
+                        || src->dtype == B200PP_F32;
+    if (!knownType || src->channels == 2)
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "Invalid input data type");
+    if (src->numSamples < 0)
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "Negative batch size");
+    if (src->numSamples == 0)
+        return B200PP_SUCCESS;
+    if ((!src->base && !src->imageList) || (!dst->base && !dst->imageList))
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "Input and output must be cuda-accessible, pitch-linear memory");
+    if ((!src->imageList && (src->width < 1 || src->height < 1)) || (!dst->imageList && (dst->width < 1 || dst->height < 1)))
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "Invalid image size");
+
+    PlainResizeKParams kp{};
+    kp.src        = plain_side(src);
+    kp.dst        = plain_side(dst);
+    kp.numSamples = src->numSamples;
+    const int gw = dst->imageList ? dst->maxWidth : dst->width, gh = dst->imageList ? dst->maxHeight : dst->height;
+    if (gw < 1 || gh < 1)
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "Output image list needs its maximum width and height");
+    dim3 block(32, 8);
+    const int tile = 32 * (interp == B200PP_INTERP_NEAREST ? kPlainCols<B200PP_INTERP_NEAREST> : kPlainCols<B200PP_INTERP_LINEAR>);
+    dim3      grid((gw + tile - 1) / tile, (gh + 7) / 8, std::min(src->numSamples, 65535));
+    if (grid.y > 65535u)
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "Input or output tensors are too large");
+    switch (src->dtype)
+    {
+    case B200PP_U8:
+        launch_plain_channels<uint8_t>(src->channels, interp, grid, block, stream, kp);
+        break;
+    case B200PP_U16:
+        launch_plain_channels<uint16_t>(src->channels, interp, grid, block, stream, kp);
+        break;
+    case B200PP_S16:
+        launch_plain_channels<int16_t>(src->channels, interp, grid, block, stream, kp);
+        break;
+    default:
+        launch_plain_channels<float>(src->channels, interp, grid, block, stream, kp);
+        break;
+    }
+    return check_launch("Resize");
 }
 
 extern "C" const char *b200ppGetLastErrorMessage(void)

@@ -121,6 +121,12 @@ class _SliceOp(C.Structure):
                 ("gscale", C.c_float), ("shift", C.c_float), ("epsilon", C.c_float), ("flags", C.c_uint32)]
 
 
+class _ImageSet(C.Structure):
+    _fields_ = [("base", C.c_void_p), ("imageList", C.c_void_p), ("dtype", C.c_int32), ("channels", C.c_int32),
+                ("numSamples", C.c_int32), ("width", C.c_int32), ("height", C.c_int32), ("maxWidth", C.c_int32),
+                ("maxHeight", C.c_int32), ("rowStride", C.c_int64), ("sampleStride", C.c_int64)]
+
+
 assert C.sizeof(_ImagePlane) == 24 and C.sizeof(_ImageBuffer) == 152  # NVCVImageBufferStrided layout
 
 _DTYPE_CODE = {torch.uint8: 0, torch.int8: 1, torch.int16: 3, torch.int32: 5, torch.float32: 6, torch.float16: 7}
@@ -155,6 +161,8 @@ def lib() -> C.CDLL:
                                                       C.c_void_p]
         L.b200ppGetLastErrorMessage.restype = C.c_char_p
         L.b200ppSetKernelPath.restype = C.c_int
+        L.b200ppResize.restype = C.c_int
+        L.b200ppResize.argtypes = [C.POINTER(_ImageSet), C.POINTER(_ImageSet), C.c_int32, C.c_void_p]
         L.b200ppSetKernelPath.argtypes = [C.c_int]
         L.b200ppGetLaunchCount.restype = C.c_uint64
         L.b200ppReadDeviceError.restype = C.c_int
@@ -515,3 +523,61 @@ def crop_flip_normalize_reformat(src: ImageBatchVarShape, out_shape: Sequence[in
     dst = torch.empty(tuple(out_shape), dtype=out_dtype, device=src.device)
     return crop_flip_normalize_reformat_into(dst, src, rect, flip_code, base, scale, globalscale, globalshift, epsilon,
                                              flags, border, bvalue, layout=out_layout, stream=stream)
+
+
+# ------------------------------------------------------------------------------------------------ stand-alone Resize
+
+def _image_set(x: Union[torch.Tensor, ImageBatchVarShape], what: str):
+    """_ImageSet of a dense (N)HWC tensor or an image batch, plus the objects that must stay alive."""
+    s = _ImageSet()
+    if isinstance(x, ImageBatchVarShape):
+        if x.planar:
+            raise Error(Status.ERROR_INVALID_ARGUMENT, f"{what} images must be interleaved")
+        if len(x) == 0:
+            s.numSamples = 0
+            return s, None
+        table = x.descriptor_table()
+        s.imageList = table.data_ptr()
+        s.dtype, s.channels, s.numSamples = _DTYPE_CODE.get(x.dtype, -1), x.channels, len(x)
+        s.maxWidth, s.maxHeight = x.max_size
+        return s, table
+    if x.dim() not in (3, 4):
+        raise Error(Status.ERROR_INVALID_ARGUMENT, f"{what} must have (N)HWC layout")
+    if not _device_accessible(x) or x.stride(-1) != 1 or x.stride(-2) != x.shape[-1]:
+        raise Error(Status.ERROR_INVALID_ARGUMENT, f"{what} must be a cuda-accessible, pitch-linear tensor")
+    es = x.element_size()
+    s.base, s.dtype, s.channels = x.data_ptr(), _DTYPE_CODE.get(x.dtype, -1), x.shape[-1]
+    s.numSamples = x.shape[0] if x.dim() == 4 else 1
+    s.height, s.width = x.shape[-3], x.shape[-2]
+    s.rowStride = x.stride(-3) * es
+    s.sampleStride = x.stride(0) * es if x.dim() == 4 else 0
+    return s, x
+
+
+def resize_into(dst: Union[torch.Tensor, ImageBatchVarShape], src: Union[torch.Tensor, ImageBatchVarShape],
+                interp: Interp = Interp.LINEAR, *, stream=None):
+    """cvcuda.resize_into for tensors and image batches (python/mod_cvcuda/OpResize.cpp:32-49,58-76): every image of
+    ``src`` is resized to the size of the corresponding image of ``dst``. Nearest and linear interpolation."""
+    if isinstance(src, ImageBatchVarShape) != isinstance(dst, ImageBatchVarShape):
+        raise Error(Status.ERROR_INVALID_ARGUMENT, "Input and output must both be tensors or both be image batches")
+    if not isinstance(src, ImageBatchVarShape) and src.dim() != dst.dim():
+        raise Error(Status.ERROR_INVALID_ARGUMENT, "Input and output data layout are different")
+    s, keep_s = _image_set(src, "Input")
+    d, keep_d = _image_set(dst, "Output")
+    _check(lib().b200ppResize(C.byref(s), C.byref(d), int(interp), _stream_handle(stream)))
+    return dst
+
+
+def resize(src: Union[torch.Tensor, ImageBatchVarShape], shape_or_sizes, interp: Interp = Interp.LINEAR, *, stream=None):
+    """cvcuda.resize (python/mod_cvcuda/OpResize.cpp:51-56,78-97). For a tensor, ``shape_or_sizes`` is the output shape
+    ((N)HWC); for an image batch, a list of (width, height) per image. Allocates the output."""
+    if isinstance(src, ImageBatchVarShape):
+        sizes = list(shape_or_sizes)
+        if len(sizes) != len(src):
+            raise Error(Status.ERROR_INVALID_ARGUMENT, "Invalid outputs sizes, must be equal to input batch size")
+        out = ImageBatchVarShape([torch.empty((int(h), int(w), src.channels), dtype=src.dtype, device=src.device)
+                                  for (w, h) in sizes])
+        return resize_into(out, src, interp, stream=stream)
+    dev = src.device if src.is_cuda else torch.device("cuda", torch.cuda.current_device())
+    out = torch.empty(tuple(int(v) for v in shape_or_sizes), dtype=src.dtype, device=dev)
+    return resize_into(out, src, interp, stream=stream)

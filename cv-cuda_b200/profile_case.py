@@ -24,7 +24,7 @@ INV_STD = tuple(float(np.float32(1.0) / np.float32(s)) for s in (58.395, 57.12, 
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--case", default="classify", choices=("classify", "classify-nhwc-u8", "classify-nhwc-f32", "classify-nhwc-u8-nearest", "4k", "4k-nearest", "letterbox", "cfnr", "varshape"))
+    ap.add_argument("--case", default="classify", choices=("classify", "classify-nhwc-u8", "classify-nhwc-f32", "classify-nhwc-u8-nearest", "4k", "4k-nearest", "letterbox", "cfnr", "varshape", "resize-rgba", "resize-rgba-nearest", "resize-rgb"))
     ap.add_argument("--images", type=int, default=32)
     ap.add_argument("--path", type=int, default=0)
     ap.add_argument("--launches", type=int, default=5)
@@ -75,7 +75,18 @@ def main():
         out = torch.empty((n, 3, 640, 640), dtype=torch.float32, device="cuda")
         kw = dict(resize_dim=(640, 360), interp=1, layout="NCHW", manip=1, scale=1.0 / 255.0, srcCast=True,
                   dst_pos=(0, 140), region_size=(640, 360), pad_value=114.0)
-    if a.case == "cfnr":
+    if a.case.startswith("resize-"):
+        # stand-alone Resize on a shape of the reference's test table (1080 wide x 1920 high -> 720 x 1280,
+        # tests/cvcuda/system/TestOpResize.cpp:70), RGBA8 or RGB8, n images per launch
+        ch = 3 if a.case == "resize-rgb" else 4
+        src = torch.randint(0, 256, (n, 1920, 1080, ch), dtype=torch.uint8, device="cuda", generator=g)
+        out = torch.empty((n, 1280, 720, ch), dtype=torch.uint8, device="cuda")
+        interp = 0 if a.case.endswith("nearest") else 1
+        print(f"resize: {src.numel() / 1e6:.1f} MB in, {out.numel() / 1e6:.1f} MB out")
+
+        def run():
+            pkg.resize_into(out, src, interp)
+    elif a.case == "cfnr":
         # CropFlipNormalizeReformat on the reference benchmark's image size (bench/BenchCropFlipNormalizeReformat.cpp:
         # 1080x1920, crop = full image, flip both axes), here 3-channel uint8 -> float32 NCHW with per-channel constants
         imgs = [torch.randint(0, 256, (1080, 1920, 3), dtype=torch.uint8, device="cuda", generator=g) for _ in range(n)]

@@ -145,6 +145,17 @@ extern "C"
 {
 #endif
 
+/* Stand-alone Resize, nearest and linear interpolation (cubic and area: NVCV_ERROR_NOT_IMPLEMENTED).
+ * Replace cvcudaResizeCreate / cvcudaResizeSubmit / cvcudaResizeVarShapeSubmit (reference:
+ * src/cvcuda/OpResize.cpp:29-71, declared in src/cvcuda/include/cvcuda/OpResize.h:52,115-120; validation and status codes
+ * of src/cvcuda/priv/OpResize.cu:501-555). Same ownership, threading and error rules as the entry points above. */
+B200PP_PUBLIC NVCVStatus cvcudaResizeCreate(NVCVOperatorHandle *handle);
+B200PP_PUBLIC NVCVStatus cvcudaResizeSubmit(NVCVOperatorHandle handle, cudaStream_t stream, NVCVTensorHandle in,
+                                            NVCVTensorHandle out, const NVCVInterpolationType interpolation);
+B200PP_PUBLIC NVCVStatus cvcudaResizeVarShapeSubmit(NVCVOperatorHandle handle, cudaStream_t stream,
+                                                    NVCVImageBatchHandle in, NVCVImageBatchHandle out,
+                                                    const NVCVInterpolationType interpolation);
+
 /* Additions (no counterpart in the reference): the whole fused pass -- per-channel normalisation, float16 output,
  * per-sample regions of interest and flip codes, letterbox placement -- on tensor / image-batch handles. `op` is the
  * B200ppResizeOp of preproc.h; its roi / flipCode pointers are device memory. The operator handle is the one

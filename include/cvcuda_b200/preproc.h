@@ -178,6 +178,21 @@ typedef struct B200ppSliceOp
     uint32_t       flags;
 } B200ppSliceOp;
 
+/* A batch of interleaved images of one element type and channel count, for the stand-alone Resize: a dense tensor
+ * [numSamples, height, width, channels] (base and byte strides), or -- when imageList is not NULL -- a device array of
+ * numSamples image descriptors with per-image sizes (plane 0 of each is used). */
+typedef struct B200ppImageSet
+{
+    void                    *base;
+    const B200ppImageBuffer *imageList;
+    int32_t                  dtype;    /* B200PP_U8, _U16, _S16 or _F32 */
+    int32_t                  channels; /* 1, 3 or 4 */
+    int32_t                  numSamples;
+    int32_t                  width, height;       /* dense only */
+    int32_t                  maxWidth, maxHeight; /* image lists: upper bounds of the image sizes (sizes the launch) */
+    int64_t                  rowStride, sampleStride; /* dense only, bytes */
+} B200ppImageSet;
+
 /* Replaces: cvcuda::priv::ResizeCropConvertReformat::operator() (tensor and var-shape),
  * src/cvcuda/priv/OpResizeCropConvertReformat.cu:418-554 and :556-683, minus the handle unpacking.
  * Sources must be interleaved 3-channel uint8; destination uint8, float32 or float16. */
@@ -189,12 +204,20 @@ B200PP_PUBLIC int b200ppResizeCropConvertReformat(const B200ppSource *src, const
 B200PP_PUBLIC int b200ppCropFlipNormalizeReformat(const B200ppSource *src, const B200ppDest *dst,
                                                   const B200ppSliceOp *op, cudaStream_t stream);
 
+/* Stand-alone Resize, nearest or linear: dst[i] = src[i] resized to the size of dst[i], element type and channel
+ * count unchanged. Replaces cvcuda::priv::Resize::operator() for tensors (src/cvcuda/priv/OpResize.cu:501-560) and for
+ * variable-shape batches (src/cvcuda/priv/legacy/resize_var_shape.cu), minus the handle unpacking; results follow the
+ * reference's CPU golden (tests/cvcuda/system/ResizeUtils.cpp:189-241) bit for bit for the integer element types.
+ * Cubic and area interpolation are not implemented (B200PP_ERROR_NOT_IMPLEMENTED). */
+B200PP_PUBLIC int b200ppResize(const B200ppImageSet *src, const B200ppImageSet *dst, int32_t interp, cudaStream_t stream);
+
 /* Message of the last failed call on this thread ("" if none). Mirrors nvcvPeekAtLastStatusMessage
  * (src/nvcv/src/include/nvcv/Status.h). */
 B200PP_PUBLIC const char *b200ppGetLastErrorMessage(void);
 
 /* Kernel selection for tests and profiling: 0 automatic (default), 1 force the per-pixel gather kernels,
- * 2 force the staged (bulk-copy pipelined) kernels where they apply. Process-wide. Returns the previous value. */
+ * 2 force the staged (bulk-copy pipelined) kernel where it applies, 3 force the row-walk kernel. Process-wide. Returns
+ * the previous value. */
 B200PP_PUBLIC int b200ppSetKernelPath(int path);
 
 /* Number of kernels this library has launched in this process (all threads). */

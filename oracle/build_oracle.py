@@ -22,6 +22,7 @@ import tempfile
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ORACLE_SRC = os.path.join(HERE, "preproc_oracle.c")
+ORACLE_RESIZE_SRC = os.path.join(HERE, "resize_oracle.c")
 ORACLE_SO = os.path.join(HERE, "liboracle.so")
 REF_DIR = os.path.join(HERE, "_ref")
 REF_SO = os.path.join(REF_DIR, "libref_golden.so")
@@ -40,8 +41,9 @@ def _stale(target: str, *sources: str) -> bool:
 
 
 def build_oracle(force: bool = False) -> str:
-    if force or _stale(ORACLE_SO, ORACLE_SRC, os.path.join(HERE, "preproc_oracle.h")):
-        cmd = ["gcc", "-std=c11", *CFLAGS, "-o", ORACLE_SO, ORACLE_SRC, "-lm"]
+    if force or _stale(ORACLE_SO, ORACLE_SRC, ORACLE_RESIZE_SRC, os.path.join(HERE, "preproc_oracle.h"),
+                       os.path.join(HERE, "resize_oracle.h")):
+        cmd = ["gcc", "-std=c11", *CFLAGS, "-o", ORACLE_SO, ORACLE_SRC, ORACLE_RESIZE_SRC, "-lm"]
         subprocess.check_call(cmd)
     return ORACLE_SO
 
@@ -63,9 +65,10 @@ def build_ref(ref_root: str = DEFAULT_REF_ROOT, force: bool = False) -> str | No
     """Compile the reference's golden functions into oracle/_ref/. Returns None when the tree is absent."""
     rccr_tu = os.path.join(ref_root, "tests/cvcuda/system/TestOpResizeCropConvertReformat.cpp")
     cfnr_tu = os.path.join(ref_root, "tests/cvcuda/system/TestOpCropFlipNormalizeReformat.cpp")
-    if not (os.path.exists(rccr_tu) and os.path.exists(cfnr_tu)):
+    resize_tu = os.path.join(ref_root, "tests/cvcuda/system/ResizeUtils.cpp")
+    if not (os.path.exists(rccr_tu) and os.path.exists(cfnr_tu) and os.path.exists(resize_tu)):
         return REF_SO if os.path.exists(REF_SO) else None
-    if not (force or _stale(REF_SO, REF_WRAP, rccr_tu, cfnr_tu)):
+    if not (force or _stale(REF_SO, REF_WRAP, rccr_tu, cfnr_tu, resize_tu)):
         return REF_SO
     os.makedirs(REF_DIR, exist_ok=True)
     scratch = tempfile.mkdtemp(prefix="refgold_")
@@ -74,6 +77,8 @@ def build_ref(ref_root: str = DEFAULT_REF_ROOT, force: bool = False) -> str | No
             f.write(_cut_function(rccr_tu, "void ResizeCropConvert(      DstT *dst,"))
         with open(os.path.join(scratch, "cfnr.inc"), "w") as f:
             f.write(_cut_function(cfnr_tu, "static void CropFlipNormalizeReformat("))
+        with open(os.path.join(scratch, "resize.inc"), "w") as f:
+            f.write(_cut_function(resize_tu, "void resizedCrop(T *dstPtr"))
         inc = [
             "-I" + os.path.join(ref_root, "tests"),
             "-I" + os.path.join(ref_root, "src/cvcuda/include"),
@@ -83,7 +88,7 @@ def build_ref(ref_root: str = DEFAULT_REF_ROOT, force: bool = False) -> str | No
         ]
         cmd = [
             "g++", "-std=c++17", *CFLAGS, "-w",
-            '-DREF_GOLDEN_RCCR_INC="rccr.inc"', '-DREF_GOLDEN_CFNR_INC="cfnr.inc"',
+            '-DREF_GOLDEN_RCCR_INC="rccr.inc"', '-DREF_GOLDEN_CFNR_INC="cfnr.inc"', '-DREF_GOLDEN_RESIZE_INC="resize.inc"',
             *inc, "-o", REF_SO, REF_WRAP,
         ]
         subprocess.check_call(cmd)

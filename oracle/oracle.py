@@ -74,6 +74,8 @@ def lib() -> C.CDLL:
         L.oracle_resize_source_bytes.restype = C.c_int64
         L.oracle_resize_source_bytes.argtypes = [C.c_int32, C.c_int32, C.c_int64, C.c_void_p,
                                                  C.POINTER(_ResizeParams)]
+        L.oracle_resize_plain.restype = C.c_int
+        L.oracle_resize_plain.argtypes = [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32]
         L.oracle_sat_u8.restype = C.c_uint8
         L.oracle_sat_u8.argtypes = [C.c_float]
         L.oracle_sat_s16.restype = C.c_int16
@@ -101,6 +103,10 @@ def ref() -> Optional[C.CDLL]:
         R.ref_cfnr.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int,
                                C.c_int, C.c_int, C.c_int, C.c_float, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
                                C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_float, C.c_float, C.c_float, C.c_uint32]
+        if hasattr(R, "ref_resize"):
+            R.ref_resize.restype = C.c_int
+            R.ref_resize.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int,
+                                     C.c_int, C.c_int]
         for name, rt in (("ref_sat_u8_f32", C.c_uint8), ("ref_sat_s32_f32", C.c_int32), ("ref_sat_s16_f32", C.c_int16)):
             f = getattr(R, name)
             f.restype = rt
@@ -266,5 +272,44 @@ def ref_cfnr(image: np.ndarray, src_planar: bool, rect, flip: int, out_size, out
                     DTYPE_CODE[image.dtype], int(src_planar), w, h, ch, border, border_value, flip,
                     int(rect[0]), int(rect[1]), int(rect[2]), int(rect[3]), base.ctypes.data, base.size,
                     scale.ctypes.data, scale.size, gscale, shift, epsilon, flags)
+    assert rc == 0
+    return out
+
+
+# ------------------------------------------------------------------------------------------------ stand-alone Resize
+
+class _PlainImage(C.Structure):
+    _fields_ = [("base", C.c_void_p), ("width", C.c_int32), ("height", C.c_int32), ("rowStride", C.c_int64)]
+
+
+def resize_plain(images: Sequence[np.ndarray], out_sizes: Sequence[tuple], interp: int,
+                 golden_float: bool = False) -> list:
+    """Stand-alone Resize restatement (resize_oracle.h) on packed HxWxC images (C = 1..4; uint8, uint16, int16 or
+    float32); out_sizes are (w, h) per image. Returns the resized images."""
+    imgs = [np.ascontiguousarray(im) for im in images]
+    n = len(imgs)
+    dt = imgs[0].dtype
+    ch = imgs[0].shape[2]
+    outs = [np.empty((h, w, ch), dtype=dt) for (w, h) in out_sizes]
+    S = (_PlainImage * n)()
+    D = (_PlainImage * n)()
+    for i in range(n):
+        h, w, _ = imgs[i].shape
+        S[i] = _PlainImage(imgs[i].ctypes.data, w, h, imgs[i].strides[0])
+        D[i] = _PlainImage(outs[i].ctypes.data, out_sizes[i][0], out_sizes[i][1], outs[i].strides[0])
+    rc = lib().oracle_resize_plain(S, D, n, DTYPE_CODE[np.dtype(dt)], ch, interp, int(golden_float))
+    assert rc == 0
+    return outs
+
+
+def ref_resize(image: np.ndarray, out_size: tuple, interp: int) -> np.ndarray:
+    """The reference's own Resize golden (test::resizedCrop as test::Resize calls it) on one packed HxWxC image."""
+    R = ref()
+    assert R is not None and hasattr(R, "ref_resize")
+    image = np.ascontiguousarray(image)
+    h, w, ch = image.shape
+    ow, oh = out_size
+    out = np.empty((oh, ow, ch), dtype=image.dtype)
+    rc = R.ref_resize(out.ctypes.data, ow * ch, ow, oh, image.ctypes.data, w * ch, w, h, ch, DTYPE_CODE[image.dtype], interp)
     assert rc == 0
     return out

@@ -11,6 +11,7 @@
 //
 //   tests/cvcuda/system/TestOpResizeCropConvertReformat.cpp:76-172   ResizeCropConvert<DstT,SrcT>
 //   tests/cvcuda/system/TestOpCropFlipNormalizeReformat.cpp:43-149   CropFlipNormalizeReformat<T_Src,T_Dst,B>
+//   tests/cvcuda/system/ResizeUtils.cpp:189-300                      test::resizedCrop<T> (stand-alone Resize golden)
 //   tests/common/InterpUtils.hpp:38-89                               test::ValueAt
 //   tests/common/BorderUtils.cpp:24-137                              test::IsInside + border index rules
 //   cvcuda/cuda_tools/SaturateCast.hpp                               cuda::SaturateCast (host path)
@@ -62,6 +63,13 @@ namespace cuda = nvcv::cuda;
 
 #include REF_GOLDEN_RCCR_INC
 #include REF_GOLDEN_CFNR_INC
+
+// tests/cvcuda/system/ResizeUtils.cpp:189-300  nvcv::test::resizedCrop<T> (nearest / linear / cubic), cut by signature
+#include <cassert>
+#include <limits>
+namespace nvcv::test {
+#include REF_GOLDEN_RESIZE_INC
+} // namespace nvcv::test
 
 namespace {
 
@@ -243,4 +251,39 @@ int16_t ref_sat_s16_f32(float v)
 {
     return cuda::SaturateCast<int16_t>(v);
 }
+}
+
+namespace {
+template<typename T>
+void ref_resize_t(void *dst, int dstStepElems, int dstW, int dstH, const void *src, int srcStepElems, int srcW, int srcH,
+                  int channels, int interp)
+{
+    // the call test::Resize makes for nearest / linear / cubic (ResizeUtils.cpp:320-323)
+    nvcv::test::resizedCrop<T>(static_cast<T *>(dst), dstStepElems, nvcv::Size2D{dstW, dstH}, static_cast<const T *>(src),
+                               srcStepElems, nvcv::Size2D{srcW, srcH}, 0, 0, srcH, srcW, nvcv::ImageFormat{channels, 1},
+                               static_cast<NVCVInterpolationType>(interp), std::numeric_limits<T>::min(),
+                               std::numeric_limits<T>::max());
+}
+} // namespace
+
+// dtype: 0 uint8, 2 uint16, 3 int16, 6 float32. Steps in elements, as the golden takes them.
+extern "C" int ref_resize(void *dst, int dstStepElems, int dstW, int dstH, const void *src, int srcStepElems, int srcW,
+                          int srcH, int channels, int dtype, int interp)
+{
+    switch (dtype)
+    {
+    case 0:
+        ref_resize_t<uint8_t>(dst, dstStepElems, dstW, dstH, src, srcStepElems, srcW, srcH, channels, interp);
+        return 0;
+    case 2:
+        ref_resize_t<uint16_t>(dst, dstStepElems, dstW, dstH, src, srcStepElems, srcW, srcH, channels, interp);
+        return 0;
+    case 3:
+        ref_resize_t<int16_t>(dst, dstStepElems, dstW, dstH, src, srcStepElems, srcW, srcH, channels, interp);
+        return 0;
+    case 6:
+        ref_resize_t<float>(dst, dstStepElems, dstW, dstH, src, srcStepElems, srcW, srcH, channels, interp);
+        return 0;
+    }
+    return -1;
 }

@@ -1,0 +1,43 @@
+/* TEST INFRASTRUCTURE ONLY.
+ *
+ * CPU restatement of the reference project's golden code for the stand-alone Resize operator, nearest and linear
+ * interpolation (tests/cvcuda/system/ResizeUtils.cpp:189-241: `resizedCrop` with top = left = 0 and the crop equal to
+ * the whole source, which is what `test::Resize` calls for these two interpolations, :320-330). The product library
+ * never links, loads or calls it.
+ *
+ * Parity is pinned: tests compare this restatement element-for-element with the reference's own function (compiled
+ * from the reference tree into oracle/_ref by build_oracle.py) over the shapes of the reference's test table.
+ *
+ * Element types: 0 = uint8, 2 = uint16, 3 = int16, 6 = float32 (the codes of preproc_oracle.h); 1 to 4 interleaved
+ * channels. Strides in BYTES.
+ */
+#ifndef RESIZE_ORACLE_H
+#define RESIZE_ORACLE_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C"
+{
+#endif
+
+typedef struct OraclePlainImage
+{
+    void   *base;
+    int32_t width, height;
+    int64_t rowStride;
+} OraclePlainImage;
+
+/* dst[i] = resize(src[i]) for i < n. interp: 0 nearest, 1 linear. `goldenFloat`: for float32 elements and linear
+ * interpolation the reference golden rounds the blend to an integer and clamps it to [FLT_MIN, FLT_MAX]
+ * (ResizeUtils.cpp:226-234 with std::numeric_limits<float>::min()); with goldenFloat == 0 the blend is stored as
+ * computed, which is what the reference's CUDA operator does (src/cvcuda/priv/OpResize.cu:228-262) and what the
+ * product implements. Returns 0, or -1 for arguments it does not cover. */
+int oracle_resize_plain(const OraclePlainImage *src, const OraclePlainImage *dst, int32_t n, int32_t dtype,
+                        int32_t channels, int32_t interp, int32_t goldenFloat);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif

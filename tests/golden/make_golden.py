@@ -66,8 +66,32 @@ def cfnr_cases():
     return out
 
 
+def resize_cases():
+    """Stand-alone Resize golden (nearest / linear) on small seeded images of every element type and channel count."""
+    rng = np.random.default_rng(4321)
+    out = {}
+    k = 0
+    shapes = [((26, 30), (15, 16)), ((11, 13), (22, 26)), ((19, 9), (7, 20)), ((8, 8), (8, 8))]
+    for (sw, sh), (dw, dh) in shapes:
+        for dt in (np.uint8, np.uint16, np.int16, np.float32):
+            for ch in (1, 3, 4):
+                for interp in (0, 1):
+                    if dt == np.float32:
+                        im = rng.uniform(0.0, 300.0, (sh, sw, ch)).astype(np.float32)
+                    else:
+                        info = np.iinfo(dt)
+                        im = rng.integers(info.min, info.max + 1, (sh, sw, ch)).astype(dt)
+                    out[f"resize{k}_src"] = im
+                    out[f"resize{k}_ref"] = O.ref_resize(im, (dw, dh), interp)
+                    out[f"resize{k}_par"] = np.array([dw, dh, interp], np.int32)
+                    k += 1
+    out["resize_count"] = np.array(k)
+    return out
+
+
 if __name__ == "__main__":
     assert build_oracle.build_ref() is not None, "reference tree not available"
     np.savez_compressed(os.path.join(HERE, "rccr_golden.npz"), **rccr_cases())
     np.savez_compressed(os.path.join(HERE, "cfnr_golden.npz"), **cfnr_cases())
+    np.savez_compressed(os.path.join(HERE, "resize_golden.npz"), **resize_cases())
     print("written", [f for f in os.listdir(HERE) if f.endswith(".npz")])

@@ -124,6 +124,12 @@ def bind_operators(lib_path: str):
         f = getattr(L, name)
         f.restype = C.c_int
         f.argtypes = [H, C.c_void_p, H, H, Size2D, C.c_int, Int2, C.c_int, C.c_float, C.c_float, C.c_bool]
+    L.cvcudaResizeCreate.restype = C.c_int
+    L.cvcudaResizeCreate.argtypes = [C.POINTER(H)]
+    for name in ("cvcudaResizeSubmit", "cvcudaResizeVarShapeSubmit"):
+        f = getattr(L, name)
+        f.restype = C.c_int
+        f.argtypes = [H, C.c_void_p, H, H, C.c_int]
     L.cvcudaCropFlipNormalizeReformatSubmit.restype = C.c_int
     L.cvcudaCropFlipNormalizeReformatSubmit.argtypes = [H, C.c_void_p, H, H, H, C.c_int, C.c_float, H, H, H, C.c_float,
                                                         C.c_float, C.c_float, C.c_uint32]

@@ -205,3 +205,38 @@ def cfnr_case(row: CfnrRow, seed: int):
     sizes = [((im.shape[2], im.shape[1]) if row.src_planar else (im.shape[1], im.shape[0])) for im in images]
     out = (max(s[0] for s in sizes), max(s[1] for s in sizes))
     return images, np.array(rects, np.int32), flips, base, scale, out
+
+
+# ------------------------------------------------------------------------------------------------ stand-alone Resize
+
+class ResizeRow(NamedTuple):
+    src_w: int
+    src_h: int
+    dst_w: int
+    dst_h: int
+    interp: int  # 0 nearest, 1 linear
+    images: int
+    channels: int
+    dtype: type
+
+
+def _resize_rows():
+    """The nearest / linear rows of the reference's Resize table (tests/cvcuda/system/TestOpResize.cpp:49-91): same
+    shapes, interpolations, image counts and formats. Its cubic and area rows (:60-69, :71-78 in part) are not covered:
+    those interpolations are not implemented here. The variable-shape test draws each image's source and destination
+    size from 0.8x to 1.1x of the row's (:211-226); test code here does the same with its own generator."""
+    u8, u16, s16, f32 = np.uint8, np.uint16, np.int16, np.float32
+    rows = [
+        (42, 48, 23, 24, 0, 1, 4, u8), (113, 12, 12, 36, 0, 1, 4, u8), (421, 148, 223, 124, 0, 2, 4, u8),
+        (313, 212, 412, 336, 0, 3, 4, u8), (42, 40, 21, 20, 1, 1, 4, u8), (21, 21, 42, 42, 1, 1, 4, u8),
+        (420, 420, 210, 210, 1, 4, 4, u8), (210, 210, 420, 420, 1, 5, 4, u8), (1080, 1920, 720, 1280, 1, 1, 4, u8),
+        (2160, 3840, 1080, 1920, 1, 1, 4, u8), (2160, 3840, 1440, 2560, 1, 1, 4, u8),
+    ]
+    for dt in (u8, u16, s16, f32):
+        for ch in (1, 3, 4):
+            rows.append((42, 48, 23, 24, 0, 1, ch, dt))
+    return [ResizeRow(*r) for r in rows]
+
+
+RESIZE_ROWS = _resize_rows()
+assert len(RESIZE_ROWS) == 23
