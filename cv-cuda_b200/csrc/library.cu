@@ -623,8 +623,8 @@ extern "C" int b200ppResize(const B200ppImageSet *src, const B200ppImageSet *dst
     if (gw < 1 || gh < 1)
         return fail(B200PP_ERROR_INVALID_ARGUMENT, "Output image list needs its maximum width and height");
     dim3 block(32, 8);
-    const int tile = 32 * (interp == B200PP_INTERP_NEAREST ? kPlainCols<B200PP_INTERP_NEAREST> : kPlainCols<B200PP_INTERP_LINEAR>);
-    dim3      grid((gw + tile - 1) / tile, (gh + 7) / 8, std::min(src->numSamples, 65535));
+    dim3 grid((gw + 32 * kPlainCols - 1) / (32 * kPlainCols), (gh + 8 * kPlainRows - 1) / (8 * kPlainRows),
+              std::min(src->numSamples, 65535));
     if (grid.y > 65535u)
         return fail(B200PP_ERROR_INVALID_ARGUMENT, "Input or output tensors are too large");
     switch (src->dtype)
