@@ -15,6 +15,8 @@
 
 #include "kparams.h"
 
+#include <type_traits>
+
 namespace b200pp {
 
 // One side of a stand-alone resize: dense [N, H, W, C] or a device array of image descriptors.
@@ -133,6 +135,40 @@ __device__ __forceinline__ float byte_to_float(uint8_t b)
     return __fsub_rn(__uint_as_float(0x4B000000u | b), 8388608.0f);
 }
 
+// uint8 pixels of 1, 3 or 4 channels as one packed word (channel c in byte c): a quarter of the registers of
+// unpacked bytes, and a byte goes from the word into a float's mantissa with a single byte permute.
+template<int C>
+__device__ __forceinline__ unsigned load_packed(const uint8_t *p, bool vector)
+{
+    if (C == 4 && vector)
+        return *reinterpret_cast<const unsigned *>(p);
+    unsigned w = p[0];
+    if (C > 1)
+        w |= static_cast<unsigned>(p[1]) << 8 | static_cast<unsigned>(p[2]) << 16;
+    if (C > 3)
+        w |= static_cast<unsigned>(p[3]) << 24;
+    return w;
+}
+
+template<int C>
+__device__ __forceinline__ void store_packed(uint8_t *p, unsigned w, bool vector)
+{
+    if (C == 4 && vector)
+    {
+        *reinterpret_cast<unsigned *>(p) = w;
+        return;
+    }
+#pragma unroll
+    for (int c = 0; c < C; ++c) p[c] = static_cast<uint8_t>(w >> (8 * c));
+}
+
+// float(byte c of w): the byte becomes the low mantissa bits of 2^23
+template<int CH>
+__device__ __forceinline__ float packed_byte_to_float(unsigned w)
+{
+    return __fsub_rn(__uint_as_float(__byte_perm(w, 0x4B000000u, 0x7650 | CH)), 8388608.0f);
+}
+
 __device__ __forceinline__ bool is_multiple_of_2_to_minus_8(double w)
 {
     const double t = __dmul_rn(w, 256.0);
@@ -163,7 +199,7 @@ __device__ __forceinline__ void linear_tap_exact(float scale, int d, int size, i
 }
 
 template<typename T, int C, int INTERP>
-__global__ void __launch_bounds__(256) resize_plain_kernel(const PlainResizeKParams p)
+__global__ void __launch_bounds__(256, INTERP == B200PP_INTERP_LINEAR && sizeof(T) == 1 ? 3 : 1) resize_plain_kernel(const PlainResizeKParams p)
 {
     const int     dx0  = blockIdx.x * (32 * kPlainCols) + threadIdx.x;
     const int     dy0  = blockIdx.y * (8 * kPlainRows) + threadIdx.y;
@@ -187,7 +223,7 @@ __global__ void __launch_bounds__(256) resize_plain_kernel(const PlainResizeKPar
 
         // ---- columns: source byte offsets and weights, once per thread and sample
         int    off0[kPlainCols], off1[kPlainCols];
-        float  wx0f[kPlainCols], wx1f[kPlainCols];  // uint8 fast path
+        float  wx1f[kPlainCols];                    // uint8 fast path
         double wx1d[kPlainCols];                    // other element types
         unsigned exactCols = 0; // bit k: column k's weights are multiples of 2^-8
 #pragma unroll
@@ -208,7 +244,6 @@ __global__ void __launch_bounds__(256) resize_plain_kernel(const PlainResizeKPar
                 off1[k] = s1 * kPix;
                 if constexpr (kFast)
                 {
-                    wx0f[k] = static_cast<float>(__dsub_rn(1.0, w1));
                     wx1f[k] = static_cast<float>(w1);
                     if (is_multiple_of_2_to_minus_8(w1))
                         exactCols |= 1u << k;
@@ -247,45 +282,43 @@ __global__ void __launch_bounds__(256) resize_plain_kernel(const PlainResizeKPar
                 const double   wy0 = __dsub_rn(1.0, fy);
                 const uint8_t *r0 = S.base + sy * S.pitch, *r1 = S.base + sy1 * S.pitch;
 
-                PlainPixel<T, C> p00[kPlainCols], p10[kPlainCols], p01[kPlainCols], p11[kPlainCols];
-#pragma unroll
-                for (int k = 0; k < kPlainCols; ++k)
+                if constexpr (kFast)
                 {
-                    p00[k] = load_plain<T, C>(r0 + off0[k], vector);
-                    p10[k] = load_plain<T, C>(r1 + off0[k], vector);
-                    p01[k] = load_plain<T, C>(r0 + off1[k], vector);
-                    p11[k] = load_plain<T, C>(r1 + off1[k], vector);
-                }
-                [[maybe_unused]] const float wy0f = static_cast<float>(wy0), wy1f = static_cast<float>(fy);
-                // Weights that are multiples of 2^-8 on both axes (whole-number and simple fractional scale factors)
-                // make the float32 blend exact (8 + 8 + 8 bits; a fused multiply-add rounds once), ties included:
-                // nothing to redo.
-                [[maybe_unused]] const unsigned exactHere = is_multiple_of_2_to_minus_8(fy) ? exactCols : 0u;
+                    // uint8. Blend in float32 first (separable form, fused multiply-adds). Its error against the
+                    // golden's double-precision sum is below 2.4e-4 (three fused multiply-adds on values of at most 255
+                    // and three rounded weights), so unless the float32 sum lies within 2^-10 of a rounding boundary
+                    // both round to the same integer; the values that do are blended again exactly -- unless the
+                    // weights make the float32 blend exact anyway (with a 1.5x reduction one value in sixteen is an
+                    // exact tie). Adding 1.5 * 2^23 rounds half-to-even and leaves the integer in the low mantissa
+                    // bits: no conversion instruction anywhere.
+                    unsigned q00[kPlainCols], q10[kPlainCols], q01[kPlainCols], q11[kPlainCols];
 #pragma unroll
-                for (int k = 0; k < kPlainCols; ++k)
-                {
-                    PlainPixel<T, C> out;
-                    if constexpr (kFast)
+                    for (int k = 0; k < kPlainCols; ++k)
                     {
-                        // Blend in float32 first. Its error against the golden's double-precision sum is below 2.4e-4
-                        // (three fused multiply-adds on values of at most 255 and three rounded weights), so unless the
-                        // float32 sum lies within 2^-10 of a rounding boundary both round to the same integer; the
-                        // values that do are blended again exactly -- unless the weights make the float32 blend exact
-                        // anyway (with a 1.5x reduction one value in sixteen is an exact tie). Adding 1.5 * 2^23 rounds half-to-even and leaves the
-                        // integer in the low mantissa bits: no conversion instruction.
+                        q00[k] = load_packed<C>(r0 + off0[k], vector);
+                        q10[k] = load_packed<C>(r1 + off0[k], vector);
+                        q01[k] = load_packed<C>(r0 + off1[k], vector);
+                        q11[k] = load_packed<C>(r1 + off1[k], vector);
+                    }
+                    const float wy1f = static_cast<float>(fy);
+                    // Weights that are multiples of 2^-8 on both axes (whole-number and simple fractional scale
+                    // factors) make the float32 blend exact (8 + 8 + 8 bits; a fused multiply-add rounds once), ties
+                    // included: nothing to redo.
+                    const unsigned exactHere = is_multiple_of_2_to_minus_8(fy) ? exactCols : 0u;
 #pragma unroll
-                        for (int c = 0; c < C; ++c)
-                        {
-                            // separable form with fused multiply-adds: cheaper than the golden's order and just as
-                            // good here, where only the size of the error matters (and exact when the weights are)
-                            const float f00 = byte_to_float(p00[k].v[c]), f10 = byte_to_float(p10[k].v[c]);
-                            const float top = __fmaf_rn(wx1f[k], diff_to_float(p01[k].v[c], p00[k].v[c]), f00);
-                            const float bot = __fmaf_rn(wx1f[k], diff_to_float(p11[k].v[c], p10[k].v[c]), f10);
-                            const float sum = __fmaf_rn(wy1f, __fsub_rn(bot, top), top);
-                            const float biased = __fadd_rn(sum, 12582912.0f);
-                            const float r      = __fsub_rn(biased, 12582912.0f);
-                            out.v[c]           = static_cast<uint8_t>(__float_as_uint(biased) & 0xffu);
-                            if (fabsf(__fsub_rn(sum, r)) > 0.5f - 0.0009765625f && !((exactHere >> k) & 1u))
+                    for (int k = 0; k < kPlainCols; ++k)
+                    {
+                        unsigned   u[4] = {0u, 0u, 0u, 0u};
+                        const bool redo = !((exactHere >> k) & 1u);
+                        auto channel = [&](auto ch) {
+                            constexpr int c   = decltype(ch)::value;
+                            const float   f00 = packed_byte_to_float<c>(q00[k]), f10 = packed_byte_to_float<c>(q10[k]);
+                            const float   top = __fmaf_rn(wx1f[k], __fsub_rn(packed_byte_to_float<c>(q01[k]), f00), f00);
+                            const float   bot = __fmaf_rn(wx1f[k], __fsub_rn(packed_byte_to_float<c>(q11[k]), f10), f10);
+                            const float   sum = __fmaf_rn(wy1f, __fsub_rn(bot, top), top);
+                            const float   biased = __fadd_rn(sum, 12582912.0f);
+                            u[c]                 = __float_as_uint(biased);
+                            if (redo && fabsf(__fsub_rn(sum, __fsub_rn(biased, 12582912.0f))) > 0.5f - 0.0009765625f)
                             {
                                 // a real branch: the empty asm keeps the compiler from turning the redo into a select,
                                 // which would run the double-precision blend for every value
@@ -293,20 +326,47 @@ __global__ void __launch_bounds__(256) resize_plain_kernel(const PlainResizeKPar
                                 int    s0, s1;
                                 double w1;
                                 linear_tap_exact(scaleW, min(dx0 + 32 * k, D.w - 1), S.w, s0, s1, w1);
-                                out.v[c] = blend_exact<T>(p00[k].v[c], p10[k].v[c], p01[k].v[c], p11[k].v[c], wy0, fy,
-                                                          __dsub_rn(1.0, w1), w1);
+                                u[c] = blend_exact<uint8_t>((q00[k] >> (8 * c)) & 0xffu, (q10[k] >> (8 * c)) & 0xffu,
+                                                            (q01[k] >> (8 * c)) & 0xffu, (q11[k] >> (8 * c)) & 0xffu, wy0, fy,
+                                                            __dsub_rn(1.0, w1), w1);
                             }
+                        };
+                        channel(std::integral_constant<int, 0>{});
+                        if constexpr (C > 1)
+                        {
+                            channel(std::integral_constant<int, 1>{});
+                            channel(std::integral_constant<int, 2>{});
                         }
+                        if constexpr (C > 3)
+                            channel(std::integral_constant<int, 3>{});
+                        // byte 0 of each of the four words, gathered with byte permutes
+                        const unsigned word = __byte_perm(__byte_perm(u[0], u[1], 0x0040), __byte_perm(u[2], u[3], 0x0040), 0x5410);
+                        if (dx0 + 32 * k < D.w)
+                            store_packed<C>(drow + static_cast<long long>(dx0 + 32 * k) * kPix, word, vector);
                     }
-                    else
+                }
+                else
+                {
+                    PlainPixel<T, C> p00[kPlainCols], p10[kPlainCols], p01[kPlainCols], p11[kPlainCols];
+#pragma unroll
+                    for (int k = 0; k < kPlainCols; ++k)
                     {
-                        const double wx0 = __dsub_rn(1.0, wx1d[k]);
+                        p00[k] = load_plain<T, C>(r0 + off0[k], vector);
+                        p10[k] = load_plain<T, C>(r1 + off0[k], vector);
+                        p01[k] = load_plain<T, C>(r0 + off1[k], vector);
+                        p11[k] = load_plain<T, C>(r1 + off1[k], vector);
+                    }
+#pragma unroll
+                    for (int k = 0; k < kPlainCols; ++k)
+                    {
+                        PlainPixel<T, C> out;
+                        const double     wx0 = __dsub_rn(1.0, wx1d[k]);
 #pragma unroll
                         for (int c = 0; c < C; ++c)
                             out.v[c] = blend_exact<T>(p00[k].v[c], p10[k].v[c], p01[k].v[c], p11[k].v[c], wy0, fy, wx0, wx1d[k]);
+                        if (dx0 + 32 * k < D.w)
+                            store_plain<T, C>(drow + static_cast<long long>(dx0 + 32 * k) * kPix, out, vector);
                     }
-                    if (dx0 + 32 * k < D.w)
-                        store_plain<T, C>(drow + static_cast<long long>(dx0 + 32 * k) * kPix, out, vector);
                 }
             }
         }
