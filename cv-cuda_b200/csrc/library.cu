@@ -283,7 +283,7 @@ template<int INTERP, int DK>
 static int run_resize(const ResizeKParams &kp, int srcWBound, cudaStream_t stream)
 {
     const int path = g_kernelPath.load(std::memory_order_relaxed);
-    // The staged kernel writes one destination row per unit with warp-contiguous stores; tiny outputs gain nothing.
+    // The staged kernel works on 128-column blocks of destination rows with vector stores; tiny outputs gain nothing.
     // It also fetches whole row segments: beyond a 32x horizontal reduction (96 source bytes per destination column)
     // the taps skip whole 32-byte sectors and the per-pixel gather moves fewer bytes.
     const bool sparseTaps = static_cast<long long>(srcWBound) > 32ll * kp.resizeW;
