@@ -22,6 +22,8 @@ from .ops import (  # noqa: F401
     launch_count,
     lib,
     lib_path,
+    normalize,
+    normalize_into,
     read_device_error,
     resize,
     resize_into,

@@ -104,7 +104,8 @@ enum OpKind
 {
     OP_RESIZE_CROP_CONVERT_REFORMAT  = 1,
     OP_CROP_FLIP_NORMALIZE_REFORMAT = 2,
-    OP_RESIZE                       = 3
+    OP_RESIZE                       = 3,
+    OP_NORMALIZE                    = 4
 };
 
 // The handle is the object pointer itself, as in the reference (src/cvcuda/priv/IOperator.hpp:37-40). Operators hold
@@ -458,9 +459,153 @@ NVCVStatus plain_resize_varshape(NVCVOperatorHandle handle, cudaStream_t stream,
     return forward(b200ppResize(&s, &d, interp, stream));
 }
 
+// ---------------------------------------------------------------------------------------------- stand-alone Normalize
+
+// base / scale tensor -> pointer and the four broadcast strides (a dimension of extent 1 gets stride 0).
+bool param_tensor(NVCVTensorHandle h, const char *what, int samples, int channels, const float *&ptr, int64_t (&stride)[4],
+                  NVCVStatus &status)
+{
+    ImageView v;
+    char      msg[96];
+    std::snprintf(msg, sizeof(msg), "Input %s", what);
+    if (!export_tensor(h, v, msg, status))
+        return false;
+    if (!v.valid || v.dtype != B200PP_F32 || !v.channelLast)
+    {
+        status = report(B200PP_ERROR_INVALID_ARGUMENT, "Input %s must be a float32 (N)HWC tensor", what);
+        return false;
+    }
+    if (!(v.samples == 1 || v.samples >= samples) || !(v.channels == 1 || v.channels >= channels))
+    {
+        status = report(B200PP_ERROR_INVALID_ARGUMENT, "Input %s cannot be broadcast to the input's samples / channels", what);
+        return false;
+    }
+    ptr       = reinterpret_cast<const float *>(v.base);
+    stride[0] = v.samples == 1 ? 0 : v.sampleStride;
+    stride[1] = v.rows == 1 ? 0 : v.rowStride;
+    stride[2] = v.cols == 1 ? 0 : v.colStride;
+    stride[3] = v.channels == 1 ? 0 : v.chanStride;
+    return true;
+}
+
+NVCVStatus normalize_common(NVCVOperatorHandle handle, cudaStream_t stream, const B200ppImageSet &s, const B200ppImageSet &d,
+                            NVCVTensorHandle base, NVCVTensorHandle scale, float gscale, float shift, float epsilon,
+                            uint32_t flags)
+{
+    (void)handle;
+    NVCVStatus        st = B200PP_SUCCESS;
+    B200ppNormalizeOp op;
+    std::memset(&op, 0, sizeof(op));
+    if (!param_tensor(base, "base", s.numSamples, s.channels, op.base, op.baseStride, st)
+        || !param_tensor(scale, "scale", s.numSamples, s.channels, op.scale, op.scaleStride, st))
+        return st;
+    op.gscale  = gscale;
+    op.shift   = shift;
+    op.epsilon = epsilon;
+    op.flags   = flags;
+    return forward(b200ppNormalize(&s, &d, &op, stream));
+}
+
+NVCVStatus normalize_tensor(NVCVOperatorHandle handle, cudaStream_t stream, NVCVTensorHandle in, NVCVTensorHandle base,
+                            NVCVTensorHandle scale, NVCVTensorHandle out, float gscale, float shift, float epsilon,
+                            uint32_t flags)
+{
+    if (NVCVStatus st = check_handle(handle, OP_NORMALIZE))
+        return st;
+    if (!nvcv().ok)
+        return report(B200PP_ERROR_INTERNAL, "libnvcv_types is not loaded in this process");
+    NVCVStatus st = B200PP_SUCCESS;
+    ImageView  i, o;
+    if (!export_tensor(in, i, "Input", st) || !export_tensor(out, o, "Output", st))
+        return st;
+    // src/cvcuda/priv/legacy/normalize.cu:314-326
+    if (std::strcmp(i.layout, o.layout) != 0)
+        return report(B200PP_ERROR_INVALID_ARGUMENT, "Invalid DataFormat between input (%s) and output (%s)", i.layout, o.layout);
+    if (!layout_is(i, "NHWC", "HWC") || !i.valid || !o.valid)
+        return report(B200PP_ERROR_INVALID_ARGUMENT, "Invalid input DataFormat %s, the valid DataFormats are: \"NHWC\", \"HWC\"",
+                      i.layout);
+    B200ppImageSet s, d;
+    std::memset(&s, 0, sizeof(s));
+    std::memset(&d, 0, sizeof(d));
+    const ImageView *views[2] = {&i, &o};
+    B200ppImageSet  *sets[2]  = {&s, &d};
+    for (int k = 0; k < 2; ++k)
+    {
+        sets[k]->base         = views[k]->base;
+        sets[k]->dtype        = views[k]->dtype;
+        sets[k]->channels     = views[k]->channels * views[k]->elemChannels;
+        sets[k]->numSamples   = views[k]->samples;
+        sets[k]->width        = views[k]->cols;
+        sets[k]->height       = views[k]->rows;
+        sets[k]->rowStride    = views[k]->rowStride;
+        sets[k]->sampleStride = views[k]->sampleStride;
+    }
+    return normalize_common(handle, stream, s, d, base, scale, gscale, shift, epsilon, flags);
+}
+
+NVCVStatus normalize_varshape(NVCVOperatorHandle handle, cudaStream_t stream, NVCVImageBatchHandle in, NVCVTensorHandle base,
+                              NVCVTensorHandle scale, NVCVImageBatchHandle out, float gscale, float shift, float epsilon,
+                              uint32_t flags)
+{
+    if (NVCVStatus st = check_handle(handle, OP_NORMALIZE))
+        return st;
+    if (!nvcv().ok)
+        return report(B200PP_ERROR_INTERNAL, "libnvcv_types is not loaded in this process");
+    NVCVImageBatchData bi, bo;
+    std::memset(&bi, 0, sizeof(bi));
+    std::memset(&bo, 0, sizeof(bo));
+    if (in == nullptr || nvcv().imageBatchExportData(in, stream, &bi) != B200PP_SUCCESS || bi.bufferType != 1)
+        return report(B200PP_ERROR_INVALID_ARGUMENT, "Input must be cuda-accessible, varshape pitch-linear image batch");
+    if (out == nullptr || nvcv().imageBatchExportData(out, stream, &bo) != B200PP_SUCCESS || bo.bufferType != 1)
+        return report(B200PP_ERROR_INVALID_ARGUMENT, "Output must be cuda-accessible, varshape pitch-linear image batch");
+    if (bi.varShapeStrided.uniqueFormat == 0 || bo.varShapeStrided.uniqueFormat == 0)
+        return report(B200PP_ERROR_INVALID_ARGUMENT, "Images in the input and output batches must all have the same format");
+    B200ppImageSet s, d;
+    std::memset(&s, 0, sizeof(s));
+    std::memset(&d, 0, sizeof(d));
+    const NVCVImageBatchData *batches[2] = {&bi, &bo};
+    B200ppImageSet           *sets[2]    = {&s, &d};
+    for (int k = 0; k < 2; ++k)
+    {
+        int channels = 0, planes = 0, kind = -1, bits[4] = {0, 0, 0, 0};
+        nvcv().imageFormatGetNumChannels(batches[k]->varShapeStrided.uniqueFormat, &channels);
+        nvcv().imageFormatGetNumPlanes(batches[k]->varShapeStrided.uniqueFormat, &planes);
+        nvcv().imageFormatGetDataKind(batches[k]->varShapeStrided.uniqueFormat, &kind);
+        nvcv().imageFormatGetBitsPerChannel(batches[k]->varShapeStrided.uniqueFormat, bits);
+        if (planes > 1)
+            return report(B200PP_ERROR_INVALID_ARGUMENT, "Image batches must hold interleaved (single-plane) images");
+        sets[k]->dtype      = element_type(kind, bits[0]);
+        sets[k]->channels   = channels;
+        sets[k]->numSamples = batches[k]->numImages;
+        sets[k]->imageList  = batches[k]->varShapeStrided.imageList;
+        sets[k]->maxWidth   = batches[k]->varShapeStrided.maxWidth;
+        sets[k]->maxHeight  = batches[k]->varShapeStrided.maxHeight;
+    }
+    return normalize_common(handle, stream, s, d, base, scale, gscale, shift, epsilon, flags);
+}
+
 } // namespace
 
 // ================================================================================================ exported symbols
+
+extern "C" NVCVStatus cvcudaNormalizeCreate(NVCVOperatorHandle *handle)
+{
+    return create(handle, OP_NORMALIZE);
+}
+
+extern "C" NVCVStatus cvcudaNormalizeSubmit(NVCVOperatorHandle handle, cudaStream_t stream, NVCVTensorHandle in,
+                                            NVCVTensorHandle base, NVCVTensorHandle scale, NVCVTensorHandle out,
+                                            float global_scale, float shift, float epsilon, uint32_t flags)
+{
+    return normalize_tensor(handle, stream, in, base, scale, out, global_scale, shift, epsilon, flags);
+}
+
+extern "C" NVCVStatus cvcudaNormalizeVarShapeSubmit(NVCVOperatorHandle handle, cudaStream_t stream, NVCVImageBatchHandle in,
+                                                    NVCVTensorHandle base, NVCVTensorHandle scale, NVCVImageBatchHandle out,
+                                                    float global_scale, float shift, float epsilon, uint32_t flags)
+{
+    return normalize_varshape(handle, stream, in, base, scale, out, global_scale, shift, epsilon, flags);
+}
 
 extern "C" NVCVStatus cvcudaResizeCreate(NVCVOperatorHandle *handle)
 {

@@ -1,5 +1,6 @@
 // Host side of the plain-C launch layer: argument validation, kernel selection and launch.
 // The single translation unit that contains all device code of the library.
+#include "normalize_kernels.cuh"
 #include "plain_resize_kernels.cuh"
 #include "resize_kernels.cuh"
 #include "slice_kernels.cuh"
@@ -643,6 +644,68 @@ extern "C" int b200ppResize(const B200ppImageSet *src, const B200ppImageSet *dst
         break;
     }
     return check_launch("Resize");
+}
+
+// ================================================================================================ stand-alone Normalize
+
+extern "C" int b200ppNormalize(const B200ppImageSet *src, const B200ppImageSet *dst, const B200ppNormalizeOp *op,
+                               cudaStream_t stream)
+{
+    if (!src || !dst || !op)
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "Null argument");
+    // Checks of the reference operator (src/cvcuda/priv/legacy/normalize.cu:314-373): same layout on both sides is
+    // implied by the argument types here; channel count and element types as there.
+    if (src->numSamples != dst->numSamples)
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "Input and output samples are different");
+    if (src->channels != dst->channels)
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "Input and output channels are different");
+    if (src->channels > 4 || src->channels < 1)
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "Invalid channel number %d", src->channels);
+    auto known = [](int t) {
+        return t == B200PP_U8 || t == B200PP_S8 || t == B200PP_U16 || t == B200PP_S16 || t == B200PP_S32 || t == B200PP_F32;
+    };
+    if (!known(src->dtype) || !known(dst->dtype))
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "Invalid DataType");
+    if (src->numSamples < 0)
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "Negative batch size");
+    if (src->numSamples == 0)
+        return B200PP_SUCCESS;
+    if (!op->base || !op->scale)
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "Input base and scale must be cuda-accessible, pitch-linear tensors");
+    if ((!src->base && !src->imageList) || (!dst->base && !dst->imageList))
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "Input and output must be cuda-accessible, pitch-linear memory");
+    if (!src->imageList && !dst->imageList && (src->width != dst->width || src->height != dst->height))
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "Input and output sizes are different");
+
+    NormalizeKParams kp{};
+    kp.src        = plain_side(src);
+    kp.dst        = plain_side(dst);
+    kp.numSamples = src->numSamples;
+    kp.channels   = src->channels;
+    kp.srcType    = src->dtype;
+    kp.dstType    = dst->dtype;
+    kp.srcElem    = elem_size(src->dtype);
+    kp.dstElem    = elem_size(dst->dtype);
+    kp.base       = op->base;
+    kp.scale      = op->scale;
+    for (int k = 0; k < 4; ++k)
+    {
+        kp.baseStride[k]  = op->baseStride[k];
+        kp.scaleStride[k] = op->scaleStride[k];
+    }
+    kp.gscale  = op->gscale;
+    kp.shift   = op->shift;
+    kp.epsilon = op->epsilon;
+    kp.stddev  = (op->flags & B200PP_NORMALIZE_SCALE_IS_STDDEV) != 0;
+    const int gw = dst->imageList ? dst->maxWidth : dst->width, gh = dst->imageList ? dst->maxHeight : dst->height;
+    if (gw < 1 || gh < 1)
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "Invalid image size");
+    dim3 block(32, 8);
+    dim3 grid((gw + 31) / 32, (gh + 15) / 16, std::min(src->numSamples, 65535));
+    if (grid.y > 65535u)
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "Input or output tensors are too large");
+    normalize_kernel<<<grid, block, 0, stream>>>(kp);
+    return check_launch("Normalize");
 }
 
 extern "C" const char *b200ppGetLastErrorMessage(void)

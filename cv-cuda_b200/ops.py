@@ -127,6 +127,11 @@ class _ImageSet(C.Structure):
                 ("maxHeight", C.c_int32), ("rowStride", C.c_int64), ("sampleStride", C.c_int64)]
 
 
+class _NormalizeOp(C.Structure):
+    _fields_ = [("base", C.c_void_p), ("baseStride", C.c_int64 * 4), ("scale", C.c_void_p), ("scaleStride", C.c_int64 * 4),
+                ("gscale", C.c_float), ("shift", C.c_float), ("epsilon", C.c_float), ("flags", C.c_uint32)]
+
+
 assert C.sizeof(_ImagePlane) == 24 and C.sizeof(_ImageBuffer) == 152  # NVCVImageBufferStrided layout
 
 _DTYPE_CODE = {torch.uint8: 0, torch.int8: 1, torch.int16: 3, torch.int32: 5, torch.float32: 6, torch.float16: 7}
@@ -163,6 +168,8 @@ def lib() -> C.CDLL:
         L.b200ppSetKernelPath.restype = C.c_int
         L.b200ppResize.restype = C.c_int
         L.b200ppResize.argtypes = [C.POINTER(_ImageSet), C.POINTER(_ImageSet), C.c_int32, C.c_void_p]
+        L.b200ppNormalize.restype = C.c_int
+        L.b200ppNormalize.argtypes = [C.POINTER(_ImageSet), C.POINTER(_ImageSet), C.POINTER(_NormalizeOp), C.c_void_p]
         L.b200ppSetKernelPath.argtypes = [C.c_int]
         L.b200ppGetLaunchCount.restype = C.c_uint64
         L.b200ppReadDeviceError.restype = C.c_int
@@ -581,3 +588,44 @@ def resize(src: Union[torch.Tensor, ImageBatchVarShape], shape_or_sizes, interp:
     dev = src.device if src.is_cuda else torch.device("cuda", torch.cuda.current_device())
     out = torch.empty(tuple(int(v) for v in shape_or_sizes), dtype=src.dtype, device=dev)
     return resize_into(out, src, interp, stream=stream)
+
+
+# ------------------------------------------------------------------------------------------------ stand-alone Normalize
+
+def _broadcast_param(t: torch.Tensor, what: str):
+    """Pointer and the four byte strides (sample, row, column, channel; 0 where the extent is 1) of a float32 CUDA
+    parameter tensor of rank 1 to 4, aligned to the right ((N)HWC)."""
+    if not t.is_cuda or t.dtype != torch.float32 or t.dim() < 1 or t.dim() > 4:
+        raise Error(Status.ERROR_INVALID_ARGUMENT, f"Input {what} must be cuda-accessible, pitch-linear tensor")
+    shape = (1,) * (4 - t.dim()) + tuple(t.shape)
+    stride = (0,) * (4 - t.dim()) + tuple(t.stride())
+    return t.data_ptr(), (C.c_int64 * 4)(*[0 if shape[k] == 1 else stride[k] * 4 for k in range(4)])
+
+
+def normalize_into(dst, src, base: torch.Tensor, scale: torch.Tensor, flags: Optional[int] = None,
+                   globalscale: float = 1.0, globalshift: float = 0.0, epsilon: float = 0.0, *, stream=None):
+    """cvcuda.normalize_into for tensors and image batches (python/mod_cvcuda/OpNormalize.cpp): dst = (src - base) * mul *
+    globalscale + globalshift, mul = scale, or 1 / sqrt(scale^2 + epsilon) with NORMALIZE_SCALE_IS_STDDEV."""
+    if isinstance(src, ImageBatchVarShape) != isinstance(dst, ImageBatchVarShape):
+        raise Error(Status.ERROR_INVALID_ARGUMENT, "Input and output must both be tensors or both be image batches")
+    if not isinstance(src, ImageBatchVarShape) and src.dim() != dst.dim():
+        raise Error(Status.ERROR_INVALID_ARGUMENT, "Invalid DataFormat between input and output")
+    s, keep_s = _image_set(src, "Input")
+    d, keep_d = _image_set(dst, "Output")
+    op = _NormalizeOp()
+    op.base, op.baseStride = _broadcast_param(base, "base")
+    op.scale, op.scaleStride = _broadcast_param(scale, "scale")
+    op.gscale, op.shift, op.epsilon, op.flags = float(globalscale), float(globalshift), float(epsilon), int(flags or 0)
+    _check(lib().b200ppNormalize(C.byref(s), C.byref(d), C.byref(op), _stream_handle(stream)))
+    return dst
+
+
+def normalize(src, base: torch.Tensor, scale: torch.Tensor, flags: Optional[int] = None, globalscale: float = 1.0,
+              globalshift: float = 0.0, epsilon: float = 0.0, *, stream=None):
+    """cvcuda.normalize: allocates an output like the input (same sizes, element type and layout)."""
+    if isinstance(src, ImageBatchVarShape):
+        out = ImageBatchVarShape([torch.empty(tuple(im.shape), dtype=im.dtype, device=src.device) for im in src._images])
+    else:
+        dev = src.device if src.is_cuda else torch.device("cuda", torch.cuda.current_device())
+        out = torch.empty(tuple(src.shape), dtype=src.dtype, device=dev)
+    return normalize_into(out, src, base, scale, flags, globalscale, globalshift, epsilon, stream=stream)

@@ -1,7 +1,7 @@
 /*
  * Handle-based operator API: the drop-in replacement for the reference's C operators of the fused pre-processing path.
  *
- * The six entry points below have the names, signatures, status codes and ownership rules of the reference library's
+ * The entry points below have the names, signatures, status codes and ownership rules of the reference library's
  * (libcvcuda) exports, so a program, the reference's C++ wrappers (cvcuda/Op*.hpp) or its Python module can bind to
  * this library instead. Tensor and image-batch handles are unpacked with the object-model library of the reference
  * (libnvcv_types: nvcvTensorExportData, nvcvImageBatchExportData, nvcvDataTypeGet*, nvcvImageFormatGet*,
@@ -90,7 +90,7 @@ typedef struct NVCVImageBatchData /* nvcv/ImageBatchData.h:26-111 */
     } varShapeStrided;
 } NVCVImageBatchData;
 
-/* ---- the six exported operator entry points ------------------------------------------------------------------------ */
+/* ---- the exported operator entry points ---------------------------------------------------------------------------- */
 
 /* Replaces cvcudaResizeCropConvertReformatCreate (reference: src/cvcuda/OpResizeCropConvertReformat.cpp:29-42,
  * declared in src/cvcuda/include/cvcuda/OpResizeCropConvertReformat.h:54). NULL handle pointer: INVALID_ARGUMENT.
@@ -155,6 +155,19 @@ B200PP_PUBLIC NVCVStatus cvcudaResizeSubmit(NVCVOperatorHandle handle, cudaStrea
 B200PP_PUBLIC NVCVStatus cvcudaResizeVarShapeSubmit(NVCVOperatorHandle handle, cudaStream_t stream,
                                                     NVCVImageBatchHandle in, NVCVImageBatchHandle out,
                                                     const NVCVInterpolationType interpolation);
+
+/* Stand-alone Normalize. Replace cvcudaNormalizeCreate / cvcudaNormalizeSubmit / cvcudaNormalizeVarShapeSubmit (reference:
+ * src/cvcuda/OpNormalize.cpp:29-71, declared in src/cvcuda/include/cvcuda/OpNormalize.h:54,128-163; operator
+ * src/cvcuda/priv/OpNormalize.cpp:38-108). base and scale are float32 (N)HWC tensors whose sample, row, column and channel
+ * extents are each 1 (broadcast) or the input's. */
+B200PP_PUBLIC NVCVStatus cvcudaNormalizeCreate(NVCVOperatorHandle *handle);
+B200PP_PUBLIC NVCVStatus cvcudaNormalizeSubmit(NVCVOperatorHandle handle, cudaStream_t stream, NVCVTensorHandle in,
+                                               NVCVTensorHandle base, NVCVTensorHandle scale, NVCVTensorHandle out,
+                                               float global_scale, float shift, float epsilon, uint32_t flags);
+B200PP_PUBLIC NVCVStatus cvcudaNormalizeVarShapeSubmit(NVCVOperatorHandle handle, cudaStream_t stream,
+                                                       NVCVImageBatchHandle in, NVCVTensorHandle base,
+                                                       NVCVTensorHandle scale, NVCVImageBatchHandle out,
+                                                       float global_scale, float shift, float epsilon, uint32_t flags);
 
 /* Additions (no counterpart in the reference): the whole fused pass -- per-channel normalisation, float16 output,
  * per-sample regions of interest and flip codes, letterbox placement -- on tensor / image-batch handles. `op` is the

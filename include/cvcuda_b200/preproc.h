@@ -211,6 +211,26 @@ B200PP_PUBLIC int b200ppCropFlipNormalizeReformat(const B200ppSource *src, const
  * Cubic and area interpolation are not implemented (B200PP_ERROR_NOT_IMPLEMENTED). */
 B200PP_PUBLIC int b200ppResize(const B200ppImageSet *src, const B200ppImageSet *dst, int32_t interp, cudaStream_t stream);
 
+/* Parameters of the stand-alone Normalize. base and scale are float32 device tensors addressed as
+ * ptr + n*stride[0] + y*stride[1] + x*stride[2] + c*stride[3] (bytes); a stride of 0 broadcasts along that dimension. */
+typedef struct B200ppNormalizeOp
+{
+    const float *base;
+    int64_t      baseStride[4];
+    const float *scale;
+    int64_t      scaleStride[4];
+    float        gscale, shift, epsilon;
+    uint32_t     flags; /* B200PP_NORMALIZE_SCALE_IS_STDDEV: mul = 1 / sqrt(scale^2 + epsilon) */
+} B200ppNormalizeOp;
+
+/* Stand-alone Normalize: dst = SaturateCast((src - base) * mul * gscale + shift), same image sizes and channel count on
+ * both sides (1 to 4 interleaved channels; uint8, int8, uint16, int16, int32 or float32 elements; the destination may
+ * have another element type). Replaces cvcuda::priv::Normalize::operator() for tensors and variable-shape batches
+ * (src/cvcuda/priv/OpNormalize.cpp:38-108, kernels src/cvcuda/priv/legacy/normalize.cu), minus the handle unpacking;
+ * results follow the reference's CPU golden (tests/cvcuda/system/TestOpNormalize.cpp:34-77) bit for bit. */
+B200PP_PUBLIC int b200ppNormalize(const B200ppImageSet *src, const B200ppImageSet *dst, const B200ppNormalizeOp *op,
+                                  cudaStream_t stream);
+
 /* Message of the last failed call on this thread ("" if none). Mirrors nvcvPeekAtLastStatusMessage
  * (src/nvcv/src/include/nvcv/Status.h). */
 B200PP_PUBLIC const char *b200ppGetLastErrorMessage(void);

@@ -23,6 +23,7 @@ import tempfile
 HERE = os.path.dirname(os.path.abspath(__file__))
 ORACLE_SRC = os.path.join(HERE, "preproc_oracle.c")
 ORACLE_RESIZE_SRC = os.path.join(HERE, "resize_oracle.c")
+ORACLE_NORMALIZE_SRC = os.path.join(HERE, "normalize_oracle.c")
 ORACLE_SO = os.path.join(HERE, "liboracle.so")
 REF_DIR = os.path.join(HERE, "_ref")
 REF_SO = os.path.join(REF_DIR, "libref_golden.so")
@@ -41,21 +42,21 @@ def _stale(target: str, *sources: str) -> bool:
 
 
 def build_oracle(force: bool = False) -> str:
-    if force or _stale(ORACLE_SO, ORACLE_SRC, ORACLE_RESIZE_SRC, os.path.join(HERE, "preproc_oracle.h"),
+    if force or _stale(ORACLE_SO, ORACLE_SRC, ORACLE_RESIZE_SRC, ORACLE_NORMALIZE_SRC, os.path.join(HERE, "preproc_oracle.h"),
                        os.path.join(HERE, "resize_oracle.h")):
-        cmd = ["gcc", "-std=c11", *CFLAGS, "-o", ORACLE_SO, ORACLE_SRC, ORACLE_RESIZE_SRC, "-lm"]
+        cmd = ["gcc", "-std=c11", *CFLAGS, "-o", ORACLE_SO, ORACLE_SRC, ORACLE_RESIZE_SRC, ORACLE_NORMALIZE_SRC, "-lm"]
         subprocess.check_call(cmd)
     return ORACLE_SO
 
 
-def _cut_function(path: str, marker: str) -> str:
-    """Return the text of the top-level function template whose signature contains `marker`:
-    from the `template<...>` line above it to the first line that is exactly '}'."""
+def _cut_function(path: str, marker: str, start_at_template: bool = True) -> str:
+    """Return the text of the top-level function (template) whose signature contains `marker`: from the
+    `template<...>` line above it (or from the marker's own line) to the first line that is exactly '}'."""
     with open(path, "r", encoding="utf-8") as f:
         lines = f.read().split("\n")
     hit = next(i for i, ln in enumerate(lines) if marker in ln)
     start = hit
-    while not lines[start].lstrip().startswith("template<"):
+    while start_at_template and not lines[start].lstrip().startswith("template<"):
         start -= 1
     end = next(i for i in range(hit, len(lines)) if lines[i] == "}")
     return "\n".join(lines[start : end + 1]) + "\n"
@@ -66,9 +67,10 @@ def build_ref(ref_root: str = DEFAULT_REF_ROOT, force: bool = False) -> str | No
     rccr_tu = os.path.join(ref_root, "tests/cvcuda/system/TestOpResizeCropConvertReformat.cpp")
     cfnr_tu = os.path.join(ref_root, "tests/cvcuda/system/TestOpCropFlipNormalizeReformat.cpp")
     resize_tu = os.path.join(ref_root, "tests/cvcuda/system/ResizeUtils.cpp")
-    if not (os.path.exists(rccr_tu) and os.path.exists(cfnr_tu) and os.path.exists(resize_tu)):
+    norm_tu = os.path.join(ref_root, "tests/cvcuda/system/TestOpNormalize.cpp")
+    if not all(os.path.exists(f) for f in (rccr_tu, cfnr_tu, resize_tu, norm_tu)):
         return REF_SO if os.path.exists(REF_SO) else None
-    if not (force or _stale(REF_SO, REF_WRAP, rccr_tu, cfnr_tu, resize_tu)):
+    if not (force or _stale(REF_SO, REF_WRAP, rccr_tu, cfnr_tu, resize_tu, norm_tu)):
         return REF_SO
     os.makedirs(REF_DIR, exist_ok=True)
     scratch = tempfile.mkdtemp(prefix="refgold_")
@@ -79,6 +81,8 @@ def build_ref(ref_root: str = DEFAULT_REF_ROOT, force: bool = False) -> str | No
             f.write(_cut_function(cfnr_tu, "static void CropFlipNormalizeReformat("))
         with open(os.path.join(scratch, "resize.inc"), "w") as f:
             f.write(_cut_function(resize_tu, "void resizedCrop(T *dstPtr"))
+        with open(os.path.join(scratch, "normalize.inc"), "w") as f:
+            f.write(_cut_function(norm_tu, "static void Normalize(std::vector<uint8_t> &hDst", start_at_template=False))
         inc = [
             "-I" + os.path.join(ref_root, "tests"),
             "-I" + os.path.join(ref_root, "src/cvcuda/include"),
@@ -89,6 +93,7 @@ def build_ref(ref_root: str = DEFAULT_REF_ROOT, force: bool = False) -> str | No
         cmd = [
             "g++", "-std=c++17", *CFLAGS, "-w",
             '-DREF_GOLDEN_RCCR_INC="rccr.inc"', '-DREF_GOLDEN_CFNR_INC="cfnr.inc"', '-DREF_GOLDEN_RESIZE_INC="resize.inc"',
+            '-DREF_GOLDEN_NORMALIZE_INC="normalize.inc"',
             *inc, "-o", REF_SO, REF_WRAP,
         ]
         subprocess.check_call(cmd)

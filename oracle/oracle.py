@@ -76,6 +76,9 @@ def lib() -> C.CDLL:
                                                  C.POINTER(_ResizeParams)]
         L.oracle_resize_plain.restype = C.c_int
         L.oracle_resize_plain.argtypes = [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32]
+        L.oracle_normalize.restype = C.c_int
+        L.oracle_normalize.argtypes = [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p,
+                                       C.c_void_p, C.c_void_p, C.c_void_p, C.c_float, C.c_float, C.c_float, C.c_uint32]
         L.oracle_sat_u8.restype = C.c_uint8
         L.oracle_sat_u8.argtypes = [C.c_float]
         L.oracle_sat_s16.restype = C.c_int16
@@ -107,6 +110,10 @@ def ref() -> Optional[C.CDLL]:
             R.ref_resize.restype = C.c_int
             R.ref_resize.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int,
                                      C.c_int, C.c_int]
+        if hasattr(R, "ref_normalize"):
+            R.ref_normalize.restype = C.c_int
+            R.ref_normalize.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_void_p,
+                                        C.c_int, C.c_float, C.c_float, C.c_float, C.c_uint32]
         for name, rt in (("ref_sat_u8_f32", C.c_uint8), ("ref_sat_s32_f32", C.c_int32), ("ref_sat_s16_f32", C.c_int16)):
             f = getattr(R, name)
             f.restype = rt
@@ -311,5 +318,53 @@ def ref_resize(image: np.ndarray, out_size: tuple, interp: int) -> np.ndarray:
     ow, oh = out_size
     out = np.empty((oh, ow, ch), dtype=image.dtype)
     rc = R.ref_resize(out.ctypes.data, ow * ch, ow, oh, image.ctypes.data, w * ch, w, h, ch, DTYPE_CODE[image.dtype], interp)
+    assert rc == 0
+    return out
+
+
+# ------------------------------------------------------------------------------------------------ stand-alone Normalize
+
+def _broadcast_strides(t: np.ndarray):
+    """Byte strides of a float32 [N, H, W, C] parameter tensor with 0 for every dimension of extent 1."""
+    assert t.ndim == 4 and t.dtype == np.float32
+    return (C.c_int64 * 4)(*[0 if t.shape[k] == 1 else t.strides[k] for k in range(4)])
+
+
+def normalize(images: Sequence[np.ndarray], base: np.ndarray, scale: np.ndarray, out_dtype=None, gscale: float = 1.0,
+              shift: float = 0.0, epsilon: float = 0.0, flags: int = 0) -> list:
+    """Stand-alone Normalize restatement on packed HxWxC images; base / scale are float32 [N|1, H|1, W|1, C|1] (full
+    extents only make sense when all images have the same size)."""
+    imgs = [np.ascontiguousarray(im) for im in images]
+    n = len(imgs)
+    dt = imgs[0].dtype
+    od = np.dtype(out_dtype or dt)
+    ch = imgs[0].shape[2]
+    outs = [np.empty(im.shape, dtype=od) for im in imgs]
+    S = (_PlainImage * n)()
+    D = (_PlainImage * n)()
+    for i in range(n):
+        h, w, _ = imgs[i].shape
+        S[i] = _PlainImage(imgs[i].ctypes.data, w, h, imgs[i].strides[0])
+        D[i] = _PlainImage(outs[i].ctypes.data, w, h, outs[i].strides[0])
+    base = np.ascontiguousarray(base, dtype=np.float32)
+    scale = np.ascontiguousarray(scale, dtype=np.float32)
+    rc = lib().oracle_normalize(S, D, n, DTYPE_CODE[np.dtype(dt)], DTYPE_CODE[od], ch, base.ctypes.data,
+                                _broadcast_strides(base), scale.ctypes.data, _broadcast_strides(scale), gscale, shift,
+                                epsilon, flags)
+    assert rc == 0
+    return outs
+
+
+def ref_normalize(image: np.ndarray, base: np.ndarray, scale: np.ndarray, gscale, shift, epsilon, flags) -> np.ndarray:
+    """The reference's own Normalize golden on one packed uint8 HxWxC image; base / scale hold one value or HxWxC."""
+    R = ref()
+    assert R is not None and hasattr(R, "ref_normalize")
+    image = np.ascontiguousarray(image, dtype=np.uint8)
+    h, w, ch = image.shape
+    base = np.ascontiguousarray(base, dtype=np.float32)
+    scale = np.ascontiguousarray(scale, dtype=np.float32)
+    out = np.empty_like(image)
+    rc = R.ref_normalize(out.ctypes.data, image.ctypes.data, w, h, ch, base.ctypes.data, int(base.size > 1),
+                         scale.ctypes.data, int(scale.size > 1), gscale, shift, epsilon, flags)
     assert rc == 0
     return out

@@ -253,6 +253,26 @@ int16_t ref_sat_s16_f32(float v)
 }
 }
 
+// tests/cvcuda/system/TestOpNormalize.cpp:34-77  Normalize (uint8 images, float32 base / scale), cut by signature
+#include REF_GOLDEN_NORMALIZE_INC
+
+// One uint8 image of `channels` interleaved channels; base / scale are either one value or a full w x h x channels
+// float32 image (the two forms the reference's test uses).
+extern "C" int ref_normalize(uint8_t *dst, const uint8_t *src, int w, int h, int channels, const float *base, int baseFull,
+                             const float *scale, int scaleFull, float gscale, float shift, float epsilon, uint32_t flags)
+{
+    std::vector<uint8_t> hSrc(src, src + static_cast<size_t>(w) * h * channels), hDst(hSrc.size());
+    std::vector<float>   hBase(base, base + (baseFull ? static_cast<size_t>(w) * h * channels : 1));
+    std::vector<float>   hScale(scale, scale + (scaleFull ? static_cast<size_t>(w) * h * channels : 1));
+    Normalize(hDst, w * channels, hSrc, w * channels, nvcv::Size2D{w, h}, nvcv::ImageFormat{channels, 1}, hBase,
+              baseFull ? w * channels : 1, baseFull ? nvcv::Size2D{w, h} : nvcv::Size2D{1, 1},
+              nvcv::ImageFormat{baseFull ? channels : 1, 1}, hScale, scaleFull ? w * channels : 1,
+              scaleFull ? nvcv::Size2D{w, h} : nvcv::Size2D{1, 1}, nvcv::ImageFormat{scaleFull ? channels : 1, 1}, gscale,
+              shift, epsilon, flags);
+    std::memcpy(dst, hDst.data(), hDst.size());
+    return 0;
+}
+
 namespace {
 template<typename T>
 void ref_resize_t(void *dst, int dstStepElems, int dstW, int dstH, const void *src, int srcStepElems, int srcW, int srcH,

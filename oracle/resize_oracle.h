@@ -36,6 +36,14 @@ typedef struct OraclePlainImage
 int oracle_resize_plain(const OraclePlainImage *src, const OraclePlainImage *dst, int32_t n, int32_t dtype,
                         int32_t channels, int32_t interp, int32_t goldenFloat);
 
+/* Stand-alone Normalize golden (tests/cvcuda/system/TestOpNormalize.cpp:34-77), element types as in preproc_oracle.h
+ * (source: U8, S8, U16, S16, S32, F32; destination the same set). base / scale: float32, addressed as
+ * ptr + n*stride[0] + y*stride[1] + x*stride[2] + c*stride[3] (bytes; 0 broadcasts). flags bit 0: scale holds standard
+ * deviations. Image i of dst has the size of image i of src. */
+int oracle_normalize(const OraclePlainImage *src, const OraclePlainImage *dst, int32_t n, int32_t srcType, int32_t dstType,
+                     int32_t channels, const float *base, const int64_t *baseStride, const float *scale,
+                     const int64_t *scaleStride, float gscale, float shift, float epsilon, uint32_t flags);
+
 #ifdef __cplusplus
 }
 #endif

@@ -130,6 +130,12 @@ def bind_operators(lib_path: str):
         f = getattr(L, name)
         f.restype = C.c_int
         f.argtypes = [H, C.c_void_p, H, H, C.c_int]
+    L.cvcudaNormalizeCreate.restype = C.c_int
+    L.cvcudaNormalizeCreate.argtypes = [C.POINTER(H)]
+    for name in ("cvcudaNormalizeSubmit", "cvcudaNormalizeVarShapeSubmit"):
+        f = getattr(L, name)
+        f.restype = C.c_int
+        f.argtypes = [H, C.c_void_p, H, H, H, H, C.c_float, C.c_float, C.c_float, C.c_uint32]
     L.cvcudaCropFlipNormalizeReformatSubmit.restype = C.c_int
     L.cvcudaCropFlipNormalizeReformatSubmit.argtypes = [H, C.c_void_p, H, H, H, C.c_int, C.c_float, H, H, H, C.c_float,
                                                         C.c_float, C.c_float, C.c_uint32]

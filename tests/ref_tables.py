@@ -240,3 +240,42 @@ def _resize_rows():
 
 RESIZE_ROWS = _resize_rows()
 assert len(RESIZE_ROWS) == 23
+
+
+# ------------------------------------------------------------------------------------------------ stand-alone Normalize
+
+class NormalizeRow(NamedTuple):
+    width: int
+    height: int
+    images: int
+    scalar_base: bool
+    scalar_scale: bool
+    flags: int
+    gscale: float
+    gshift: float
+    eps: float
+
+
+# tests/cvcuda/system/TestOpNormalize.cpp:84-98 (RGBA8 images; scalar parameters are 1x1x1 float32, the others
+# RGBAf32 tensors of the image size, one per image)
+NORMALIZE_ROWS = [NormalizeRow(*r) for r in [
+    (32, 33, 1, True, True, 0, 0.0, 0.0, 0.0), (66, 55, 1, True, True, 0, 1.0, 0.0, 0.0),
+    (122, 212, 2, True, True, 0, 1.234, 43.21, 0.0), (211, 102, 3, False, False, 0, 1.1, 0.1, 0.0),
+    (21, 12, 5, True, True, 1, 1.2, 0.2, 0.0), (22, 12, 5, False, True, 1, 1.3, 0.3, 0.0),
+    (55, 23, 5, True, False, 1, 1.2, 0.2, 0.0), (72, 88, 5, False, False, 1, 1.2, 0.2, 0.0),
+    (63, 32, 7, False, True, 0, 1.3, 0.3, 0.0), (22, 13, 9, True, False, 0, 1.4, 0.4, 0.0),
+    (55, 33, 2, True, False, 1, 2.1, 1.1, 1.23), (444, 222, 4, True, False, 1, 2.2, 2.2, 12.3),
+]]
+assert len(NORMALIZE_ROWS) == 12
+
+
+def normalize_case(row: NormalizeRow, seed: int):
+    """Images, base and scale of one table row: uint8 RGBA images, base ~U(0, 255), scale ~U(0, 1) as the reference's
+    test draws them (TestOpNormalize.cpp:141-199), from this file's own generator."""
+    rng = np.random.default_rng(seed)
+    images = [rng.integers(0, 256, (row.height, row.width, 4), dtype=np.uint8) for _ in range(row.images)]
+    bshape = (1, 1, 1, 1) if row.scalar_base else (row.images, row.height, row.width, 4)
+    sshape = (1, 1, 1, 1) if row.scalar_scale else (row.images, row.height, row.width, 4)
+    base = rng.uniform(0.0, 255.0, bshape).astype(np.float32)
+    scale = rng.uniform(0.0, 1.0, sshape).astype(np.float32)
+    return images, base, scale
