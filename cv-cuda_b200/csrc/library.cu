@@ -701,10 +701,16 @@ extern "C" int b200ppNormalize(const B200ppImageSet *src, const B200ppImageSet *
     if (gw < 1 || gh < 1)
         return fail(B200PP_ERROR_INVALID_ARGUMENT, "Invalid image size");
     dim3 block(32, 8);
-    dim3 grid((gw + 31) / 32, (gh + 15) / 16, std::min(src->numSamples, 65535));
+    dim3 grid((gw + 32 * kNormCols - 1) / (32 * kNormCols), (gh + 8 * kNormRows - 1) / (8 * kNormRows),
+              std::min(src->numSamples, 65535));
     if (grid.y > 65535u)
         return fail(B200PP_ERROR_INVALID_ARGUMENT, "Input or output tensors are too large");
-    normalize_kernel<<<grid, block, 0, stream>>>(kp);
+    if (src->dtype == B200PP_U8 && dst->dtype == B200PP_U8)
+        normalize_kernel<B200PP_U8, B200PP_U8><<<grid, block, 0, stream>>>(kp);
+    else if (src->dtype == B200PP_U8 && dst->dtype == B200PP_F32)
+        normalize_kernel<B200PP_U8, B200PP_F32><<<grid, block, 0, stream>>>(kp);
+    else
+        normalize_kernel<-1, -1><<<grid, block, 0, stream>>>(kp);
     return check_launch("Normalize");
 }
 

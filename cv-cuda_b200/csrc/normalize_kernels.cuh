@@ -26,34 +26,117 @@ struct NormalizeKParams
     int          stddev;
 };
 
-// One thread per pixel (all channels), two rows per thread for a little more memory-level parallelism.
+__device__ __forceinline__ float normalize_mul(const NormalizeKParams &p, float s)
+{
+    return p.stddev ? __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fmul_rn(s, s), p.epsilon))) : s;
+}
+
+// A thread produces kNormRows x kNormCols pixels (rows 8 apart, columns 32 apart, so that loads and stores stay
+// coalesced across the warp). When base and scale vary only by channel -- the usual mean / standard-deviation case --
+// the per-channel constants, including the division and square root of the standard-deviation form, are worked out
+// once per thread instead of once per element. uint8 pixels of four channels move as one word.
+constexpr int kNormRows = 4;
+constexpr int kNormCols = 2;
+
+// SRC / DST: the element type when it is one of the common ones (B200PP_U8 source; B200PP_U8 or B200PP_F32
+// destination), which removes the run-time type dispatch and the conversion instructions from the element loop; -1: any.
+template<int SRC, int DST>
 __global__ void __launch_bounds__(256) normalize_kernel(const NormalizeKParams p)
 {
-    const int x  = blockIdx.x * blockDim.x + threadIdx.x;
-    const int y0 = (blockIdx.y * blockDim.y + threadIdx.y) * 2;
+    const int x0 = blockIdx.x * (32 * kNormCols) + threadIdx.x;
+    const int y0 = blockIdx.y * (8 * kNormRows) + threadIdx.y;
+    const bool perChannel = (p.baseStride[0] | p.baseStride[1] | p.baseStride[2] | p.scaleStride[0] | p.scaleStride[1]
+                             | p.scaleStride[2])
+                         == 0;
+    float cb[4] = {0.f, 0.f, 0.f, 0.f}, cm[4] = {0.f, 0.f, 0.f, 0.f};
+    if (perChannel)
+    {
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+            if (c < p.channels)
+            {
+                cb[c] = *reinterpret_cast<const float *>(reinterpret_cast<const char *>(p.base) + c * p.baseStride[3]);
+                cm[c] = normalize_mul(p, *reinterpret_cast<const float *>(reinterpret_cast<const char *>(p.scale) + c * p.scaleStride[3]));
+            }
+    }
     for (int n = blockIdx.z; n < p.numSamples; n += gridDim.z)
     {
         const PlainView S = plain_view(p.src, n), D = plain_view(p.dst, n);
         const int       w = min(S.w, D.w), h = min(S.h, D.h);
-        if (x >= w)
-            continue;
-#pragma unroll
-        for (int r = 0; r < 2; ++r)
+        const bool      words = SRC == B200PP_U8 && p.channels == 4
+                        && ((reinterpret_cast<unsigned long long>(S.base) | static_cast<unsigned long long>(S.pitch)) & 3ull) == 0;
+        const bool      wordsOut = DST == B200PP_U8 && p.channels == 4
+                           && ((reinterpret_cast<unsigned long long>(D.base) | static_cast<unsigned long long>(D.pitch)) & 3ull) == 0;
+        // uint8 sources: all of the thread's pixels are loaded (as packed words) before any arithmetic, so that eight
+        // loads are in flight per thread instead of one
+        unsigned packed[kNormRows][kNormCols];
+        if constexpr (SRC == B200PP_U8)
         {
-            const int y = y0 + r;
+#pragma unroll
+            for (int r = 0; r < kNormRows; ++r)
+#pragma unroll
+                for (int k = 0; k < kNormCols; ++k)
+                {
+                    const int y = min(y0 + 8 * r, h - 1), x = min(x0 + 32 * k, w - 1); // clamped, stored only if inside
+                    const uint8_t *sp = S.base + y * S.pitch + static_cast<long long>(x) * p.channels;
+                    unsigned       v  = 0;
+                    if (w > 0 && h > 0)
+                    {
+                        if (words)
+                            v = *reinterpret_cast<const unsigned *>(sp);
+                        else
+                            for (int c = 0; c < p.channels; ++c) v |= static_cast<unsigned>(sp[c]) << (8 * c);
+                    }
+                    packed[r][k] = v;
+                }
+        }
+#pragma unroll
+        for (int r = 0; r < kNormRows; ++r)
+        {
+            const int y = y0 + 8 * r;
             if (y >= h)
                 break;
-            const uint8_t *sp = S.base + y * S.pitch + static_cast<long long>(x) * p.channels * p.srcElem;
-            uint8_t       *dp = D.base + y * D.pitch + static_cast<long long>(x) * p.channels * p.dstElem;
-            const char    *bp = reinterpret_cast<const char *>(p.base) + n * p.baseStride[0] + y * p.baseStride[1] + x * p.baseStride[2];
-            const char    *cp = reinterpret_cast<const char *>(p.scale) + n * p.scaleStride[0] + y * p.scaleStride[1] + x * p.scaleStride[2];
-            for (int c = 0; c < p.channels; ++c)
+#pragma unroll
+            for (int k = 0; k < kNormCols; ++k)
             {
-                const float v = load_any(sp + c * p.srcElem, p.srcType);
-                const float b = *reinterpret_cast<const float *>(bp + c * p.baseStride[3]);
-                const float s = *reinterpret_cast<const float *>(cp + c * p.scaleStride[3]);
-                const float m = p.stddev ? __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fmul_rn(s, s), p.epsilon))) : s;
-                store_any(dp + c * p.dstElem, p.dstType, __fadd_rn(__fmul_rn(__fmul_rn(__fsub_rn(v, b), m), p.gscale), p.shift));
+                const int x = x0 + 32 * k;
+                if (x >= w)
+                    continue;
+                const uint8_t *sp = S.base + y * S.pitch + static_cast<long long>(x) * p.channels * p.srcElem;
+                uint8_t       *dp = D.base + y * D.pitch + static_cast<long long>(x) * p.channels * p.dstElem;
+                const char    *bp = reinterpret_cast<const char *>(p.base) + n * p.baseStride[0] + y * p.baseStride[1] + x * p.baseStride[2];
+                const char    *cp = reinterpret_cast<const char *>(p.scale) + n * p.scaleStride[0] + y * p.scaleStride[1] + x * p.scaleStride[2];
+                unsigned       outWord = 0;
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+                {
+                    if (c >= p.channels)
+                        break;
+                    float v;
+                    if constexpr (SRC == B200PP_U8)
+                        // float(byte) without a conversion instruction: the byte becomes the low mantissa bits of 2^23
+                        v = __fsub_rn(__uint_as_float(0x4B000000u | ((packed[r][k] >> (8 * c)) & 0xffu)), 8388608.0f);
+                    else
+                        v = load_any(sp + c * p.srcElem, p.srcType);
+                    const float b = perChannel ? cb[c] : *reinterpret_cast<const float *>(bp + c * p.baseStride[3]);
+                    const float m = perChannel ? cm[c] : normalize_mul(p, *reinterpret_cast<const float *>(cp + c * p.scaleStride[3]));
+                    const float o = __fadd_rn(__fmul_rn(__fmul_rn(__fsub_rn(v, b), m), p.gscale), p.shift);
+                    if constexpr (DST == B200PP_U8)
+                    {
+                        // round half to even + clamp through the mantissa of 1.5 * 2^23
+                        const unsigned b8 = __float_as_uint(__fadd_rn(fminf(fmaxf(o, 0.0f), 255.0f), 12582912.0f)) & 0xffu;
+                        if (wordsOut)
+                            outWord |= b8 << (8 * c);
+                        else
+                            dp[c] = static_cast<uint8_t>(b8);
+                    }
+                    else if constexpr (DST == B200PP_F32)
+                        reinterpret_cast<float *>(dp)[c] = o;
+                    else
+                        store_any(dp + c * p.dstElem, p.dstType, o);
+                }
+                if (wordsOut)
+                    *reinterpret_cast<unsigned *>(dp) = outWord;
             }
         }
     }

@@ -24,7 +24,7 @@ INV_STD = tuple(float(np.float32(1.0) / np.float32(s)) for s in (58.395, 57.12, 
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--case", default="classify", choices=("classify", "classify-nhwc-u8", "classify-nhwc-f32", "classify-nhwc-u8-nearest", "4k", "4k-nearest", "letterbox", "cfnr", "varshape", "resize-rgba", "resize-rgba-nearest", "resize-rgb"))
+    ap.add_argument("--case", default="classify", choices=("classify", "classify-nhwc-u8", "classify-nhwc-f32", "classify-nhwc-u8-nearest", "4k", "4k-nearest", "letterbox", "cfnr", "varshape", "resize-rgba", "resize-rgba-nearest", "resize-rgb", "normalize-rgba", "normalize-rgb-f32"))
     ap.add_argument("--images", type=int, default=32)
     ap.add_argument("--path", type=int, default=0)
     ap.add_argument("--launches", type=int, default=5)
@@ -86,6 +86,19 @@ def main():
 
         def run():
             pkg.resize_into(out, src, interp)
+    elif a.case.startswith("normalize-"):
+        # stand-alone Normalize on 1080x1920 images with per-channel mean / standard deviation: RGBA8 -> RGBA8 (the
+        # reference test's format) or RGB8 -> float32 (the step a classification pipeline runs after its resize)
+        ch = 4 if a.case == "normalize-rgba" else 3
+        src = torch.randint(0, 256, (n, 1080, 1920, ch), dtype=torch.uint8, device="cuda", generator=g)
+        out = torch.empty((n, 1080, 1920, ch), dtype=torch.uint8 if ch == 4 else torch.float32, device="cuda")
+        base = torch.tensor((MEAN + (127.5,))[:ch], dtype=torch.float32, device="cuda").reshape(1, 1, 1, ch)
+        scale = torch.tensor(((58.395, 57.12, 57.375) + (64.0,))[:ch], dtype=torch.float32, device="cuda").reshape(1, 1, 1, ch)
+        print(f"normalize: {src.numel() / 1e6:.1f} MB in, {out.numel() * out.element_size() / 1e6:.1f} MB out")
+
+        def run():
+            pkg.normalize_into(out, src, base, scale, pkg.NORMALIZE_SCALE_IS_STDDEV, 64.0 if ch == 4 else 1.0,
+                               128.0 if ch == 4 else 0.0, 0.0)
     elif a.case == "cfnr":
         # CropFlipNormalizeReformat on the reference benchmark's image size (bench/BenchCropFlipNormalizeReformat.cpp:
         # 1080x1920, crop = full image, flip both axes), here 3-channel uint8 -> float32 NCHW with per-channel constants

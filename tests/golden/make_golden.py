@@ -89,9 +89,25 @@ def resize_cases():
     return out
 
 
+def normalize_cases():
+    """Stand-alone Normalize golden on small versions of the reference's table rows (one image each)."""
+    out = {}
+    for k, row in enumerate(T.NORMALIZE_ROWS):
+        small = row._replace(images=1, width=min(row.width, 23), height=min(row.height, 17))
+        images, base, scale = T.normalize_case(small, 900 + k)
+        out[f"norm{k}_src"] = images[0]
+        out[f"norm{k}_base"] = base
+        out[f"norm{k}_scale"] = scale
+        out[f"norm{k}_par"] = np.array([small.gscale, small.gshift, small.eps, small.flags], np.float32)
+        out[f"norm{k}_ref"] = O.ref_normalize(images[0], base, scale, small.gscale, small.gshift, small.eps, small.flags)
+    out["norm_count"] = np.array(len(T.NORMALIZE_ROWS))
+    return out
+
+
 if __name__ == "__main__":
     assert build_oracle.build_ref() is not None, "reference tree not available"
     np.savez_compressed(os.path.join(HERE, "rccr_golden.npz"), **rccr_cases())
     np.savez_compressed(os.path.join(HERE, "cfnr_golden.npz"), **cfnr_cases())
     np.savez_compressed(os.path.join(HERE, "resize_golden.npz"), **resize_cases())
+    np.savez_compressed(os.path.join(HERE, "normalize_golden.npz"), **normalize_cases())
     print("written", [f for f in os.listdir(HERE) if f.endswith(".npz")])

@@ -1,9 +1,13 @@
 """CPU: the stand-alone Normalize restatement (oracle/normalize_oracle.c) against the reference's own golden function
 (compiled into oracle/_ref where the reference tree is present) over the reference's test table."""
+import os
+
 import numpy as np
 import pytest
 
 import ref_tables as T
+
+HERE = os.path.dirname(os.path.abspath(__file__))
 
 
 @pytest.mark.parametrize("idx", range(len(T.NORMALIZE_ROWS)))
@@ -18,6 +22,17 @@ def test_restatement_matches_the_reference_golden_on_its_test_table(oracle, idx)
         s = scale if row.scalar_scale else scale[i:i + 1]
         ref = oracle.ref_normalize(im, b, s, row.gscale, row.gshift, row.eps, row.flags)
         assert np.array_equal(got[i], ref), f"image {i}"
+
+
+def test_restatement_matches_the_committed_reference_outputs(oracle):
+    g = np.load(os.path.join(HERE, "golden", "normalize_golden.npz"))
+    n = int(g["norm_count"])
+    assert n == len(T.NORMALIZE_ROWS)
+    for k in range(n):
+        gs, sh, eps, flags = g[f"norm{k}_par"]
+        got = oracle.normalize([g[f"norm{k}_src"]], g[f"norm{k}_base"], g[f"norm{k}_scale"], None, float(gs), float(sh),
+                               float(eps), int(flags))[0]
+        assert np.array_equal(got, g[f"norm{k}_ref"]), f"fixture {k}"
 
 
 def test_known_values(oracle):
