@@ -25,6 +25,8 @@ from .ops import (  # noqa: F401
     normalize,
     normalize_into,
     read_device_error,
+    reformat,
+    reformat_into,
     resize,
     resize_into,
     resize_crop_convert_reformat,

@@ -105,7 +105,8 @@ enum OpKind
     OP_RESIZE_CROP_CONVERT_REFORMAT  = 1,
     OP_CROP_FLIP_NORMALIZE_REFORMAT = 2,
     OP_RESIZE                       = 3,
-    OP_NORMALIZE                    = 4
+    OP_NORMALIZE                    = 4,
+    OP_REFORMAT                     = 5
 };
 
 // The handle is the object pointer itself, as in the reference (src/cvcuda/priv/IOperator.hpp:37-40). Operators hold
@@ -584,9 +585,49 @@ NVCVStatus normalize_varshape(NVCVOperatorHandle handle, cudaStream_t stream, NV
     return normalize_common(handle, stream, s, d, base, scale, gscale, shift, epsilon, flags);
 }
 
+// ---------------------------------------------------------------------------------------------- stand-alone Reformat
+
+NVCVStatus reformat_tensor(NVCVOperatorHandle handle, cudaStream_t stream, NVCVTensorHandle in, NVCVTensorHandle out)
+{
+    if (NVCVStatus st = check_handle(handle, OP_REFORMAT))
+        return st;
+    if (!nvcv().ok)
+        return report(B200PP_ERROR_INTERNAL, "libnvcv_types is not loaded in this process");
+    NVCVStatus st = B200PP_SUCCESS;
+    ImageView  i, o;
+    if (!export_tensor(in, i, "Input", st) || !export_tensor(out, o, "Output", st))
+        return st;
+    // layouts and combinations of src/cvcuda/priv/legacy/reformat.cu:120-179
+    if (!layout_is(i, "NHWC", "HWC", "NCHW", "CHW") || !layout_is(o, "NHWC", "HWC", "NCHW", "CHW") || !i.valid || !o.valid
+        || (std::strlen(i.layout) != std::strlen(o.layout)))
+        return report(B200PP_ERROR_INVALID_ARGUMENT, "Invalid combination of input format %s and output format %s", i.layout,
+                      o.layout);
+    if (i.dtype != o.dtype || i.elemChannels != o.elemChannels)
+        return report(B200PP_ERROR_INVALID_ARGUMENT, "DataType of input and output must be equal");
+    if (i.samples != o.samples)
+        return report(B200PP_ERROR_INVALID_ARGUMENT, "Input and output samples are different");
+    if (i.elemChannels != 1)
+        return report(B200PP_ERROR_INVALID_ARGUMENT, "Invalid DataType: channels must be a tensor dimension");
+    B200ppDest s, d;
+    fill_dest(i, s);
+    fill_dest(o, d);
+    return forward(b200ppReformat(&s, &d, i.samples, stream));
+}
+
 } // namespace
 
 // ================================================================================================ exported symbols
+
+extern "C" NVCVStatus cvcudaReformatCreate(NVCVOperatorHandle *handle)
+{
+    return create(handle, OP_REFORMAT);
+}
+
+extern "C" NVCVStatus cvcudaReformatSubmit(NVCVOperatorHandle handle, cudaStream_t stream, NVCVTensorHandle in,
+                                           NVCVTensorHandle out)
+{
+    return reformat_tensor(handle, stream, in, out);
+}
 
 extern "C" NVCVStatus cvcudaNormalizeCreate(NVCVOperatorHandle *handle)
 {

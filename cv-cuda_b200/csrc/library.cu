@@ -2,6 +2,7 @@
 // The single translation unit that contains all device code of the library.
 #include "normalize_kernels.cuh"
 #include "plain_resize_kernels.cuh"
+#include "reformat_kernels.cuh"
 #include "resize_kernels.cuh"
 #include "slice_kernels.cuh"
 
@@ -712,6 +713,59 @@ extern "C" int b200ppNormalize(const B200ppImageSet *src, const B200ppImageSet *
     else
         normalize_kernel<-1, -1><<<grid, block, 0, stream>>>(kp);
     return check_launch("Normalize");
+}
+
+// ================================================================================================ stand-alone Reformat
+
+extern "C" int b200ppReformat(const B200ppDest *src, const B200ppDest *dst, int32_t numSamples, cudaStream_t stream)
+{
+    if (!src || !dst)
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "Null argument");
+    if (src->dtype != dst->dtype)
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "Input and output data type are different");
+    if (src->channels != dst->channels || src->width != dst->width || src->height != dst->height)
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "Input and output shapes are different");
+    if (src->dtype < B200PP_U8 || src->dtype > B200PP_F16)
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "Invalid DataType");
+    if (numSamples < 0 || src->channels < 1 || src->width < 0 || src->height < 0)
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "Invalid shape");
+    if (numSamples == 0 || src->width == 0 || src->height == 0)
+        return B200PP_SUCCESS;
+    if (!src->base || !dst->base)
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "Input and output must be cuda-accessible, pitch-linear memory");
+    ReformatKParams kp{};
+    kp.src        = static_cast<const uint8_t *>(src->base);
+    kp.dst        = static_cast<uint8_t *>(dst->base);
+    kp.sSample    = src->sampleStride;
+    kp.sRow       = src->rowStride;
+    kp.sPix       = src->pixStride;
+    kp.sChan      = src->chanStride;
+    kp.dSample    = dst->sampleStride;
+    kp.dRow       = dst->rowStride;
+    kp.dPix       = dst->pixStride;
+    kp.dChan      = dst->chanStride;
+    kp.numSamples = numSamples;
+    kp.channels   = src->channels;
+    kp.width      = src->width;
+    kp.height     = src->height;
+    dim3      block(32, 8);
+    const int perThread = 4 / std::min(4, elem_size(src->dtype)); // pixels per thread: one 32-bit word per channel
+    dim3      grid((kp.width + 32 * perThread - 1) / (32 * perThread), (kp.height + 31) / 32, std::min(numSamples, 65535));
+    if (grid.y > 65535u)
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "Input or output tensors are too large");
+    switch (elem_size(src->dtype))
+    {
+    case 1:
+        reformat_kernel<uint8_t><<<grid, block, 0, stream>>>(kp);
+        break;
+    case 2:
+        reformat_kernel<uint16_t><<<grid, block, 0, stream>>>(kp);
+        break;
+    default:
+        reformat_kernel<uint32_t><<<grid, block, 0, stream>>>(kp);
+        break;
+    }
+    return check_launch("Reformat");
 }
 
 extern "C" const char *b200ppGetLastErrorMessage(void)

@@ -170,6 +170,8 @@ def lib() -> C.CDLL:
         L.b200ppResize.argtypes = [C.POINTER(_ImageSet), C.POINTER(_ImageSet), C.c_int32, C.c_void_p]
         L.b200ppNormalize.restype = C.c_int
         L.b200ppNormalize.argtypes = [C.POINTER(_ImageSet), C.POINTER(_ImageSet), C.POINTER(_NormalizeOp), C.c_void_p]
+        L.b200ppReformat.restype = C.c_int
+        L.b200ppReformat.argtypes = [C.POINTER(_Dest), C.POINTER(_Dest), C.c_int32, C.c_void_p]
         L.b200ppSetKernelPath.argtypes = [C.c_int]
         L.b200ppGetLaunchCount.restype = C.c_uint64
         L.b200ppReadDeviceError.restype = C.c_int
@@ -629,3 +631,35 @@ def normalize(src, base: torch.Tensor, scale: torch.Tensor, flags: Optional[int]
         dev = src.device if src.is_cuda else torch.device("cuda", torch.cuda.current_device())
         out = torch.empty(tuple(src.shape), dtype=src.dtype, device=dev)
     return normalize_into(out, src, base, scale, flags, globalscale, globalshift, epsilon, stream=stream)
+
+
+# ------------------------------------------------------------------------------------------------ stand-alone Reformat
+
+def reformat_into(dst: torch.Tensor, src: torch.Tensor, *, src_layout: str = "", dst_layout: str = "", stream=None):
+    """cvcuda.reformat_into (python/mod_cvcuda/OpReformat.cpp): copies ``src`` into ``dst`` changing between the NHWC / HWC
+    and NCHW / CHW layouts (a torch tensor carries no layout, so both are named; default (N)HWC by rank)."""
+    src_layout, dst_layout = _default_layout(src, src_layout), _default_layout(dst, dst_layout)
+    if len(src_layout) != len(dst_layout) or src_layout not in ("NHWC", "HWC", "NCHW", "CHW") \
+            or dst_layout not in ("NHWC", "HWC", "NCHW", "CHW"):
+        raise Error(Status.ERROR_INVALID_ARGUMENT,
+                    f"Invalid combination of input format {src_layout} and output format {dst_layout}")
+    if not _device_accessible(src):
+        raise Error(Status.ERROR_INVALID_ARGUMENT, "Input must be cuda-accessible, pitch-linear tensor")
+    s, n_in = _dest_of(src, src_layout)
+    d, n_out = _dest_of(dst, dst_layout)
+    if n_in != n_out:
+        raise Error(Status.ERROR_INVALID_ARGUMENT, "Input and output samples are different")
+    _check(lib().b200ppReformat(C.byref(s), C.byref(d), n_in, _stream_handle(stream)))
+    return dst
+
+
+def reformat(src: torch.Tensor, dst_layout: str, *, src_layout: str = "", stream=None) -> torch.Tensor:
+    """cvcuda.reformat: allocates the output in ``dst_layout``."""
+    src_layout = _default_layout(src, src_layout)
+    if len(src_layout) != len(dst_layout):
+        raise Error(Status.ERROR_INVALID_ARGUMENT,
+                    f"Invalid combination of input format {src_layout} and output format {dst_layout}")
+    dims = dict(zip(src_layout, src.shape))
+    dev = src.device if src.is_cuda else torch.device("cuda", torch.cuda.current_device())
+    out = torch.empty(tuple(dims[k] for k in dst_layout), dtype=src.dtype, device=dev)
+    return reformat_into(out, src, src_layout=src_layout, dst_layout=dst_layout, stream=stream)

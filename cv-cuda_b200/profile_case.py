@@ -24,7 +24,7 @@ INV_STD = tuple(float(np.float32(1.0) / np.float32(s)) for s in (58.395, 57.12, 
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--case", default="classify", choices=("classify", "classify-nhwc-u8", "classify-nhwc-f32", "classify-nhwc-u8-nearest", "4k", "4k-nearest", "letterbox", "cfnr", "varshape", "resize-rgba", "resize-rgba-nearest", "resize-rgb", "normalize-rgba", "normalize-rgb-f32"))
+    ap.add_argument("--case", default="classify", choices=("classify", "classify-nhwc-u8", "classify-nhwc-f32", "classify-nhwc-u8-nearest", "4k", "4k-nearest", "letterbox", "cfnr", "varshape", "resize-rgba", "resize-rgba-nearest", "resize-rgb", "normalize-rgba", "normalize-rgb-f32", "reformat-u8", "reformat-f32"))
     ap.add_argument("--images", type=int, default=32)
     ap.add_argument("--path", type=int, default=0)
     ap.add_argument("--launches", type=int, default=5)
@@ -99,6 +99,15 @@ def main():
         def run():
             pkg.normalize_into(out, src, base, scale, pkg.NORMALIZE_SCALE_IS_STDDEV, 64.0 if ch == 4 else 1.0,
                                128.0 if ch == 4 else 0.0, 0.0)
+    elif a.case.startswith("reformat-"):
+        # stand-alone Reformat, 1080x1920 RGB, NHWC -> NCHW
+        dt = torch.uint8 if a.case.endswith("u8") else torch.float32
+        src = torch.randint(0, 256, (n, 1080, 1920, 3), dtype=torch.uint8, device="cuda", generator=g).to(dt)
+        out = torch.empty((n, 3, 1080, 1920), dtype=dt, device="cuda")
+        print(f"reformat: {2 * src.numel() * src.element_size() / 1e6:.1f} MB in + out")
+
+        def run():
+            pkg.reformat_into(out, src, src_layout="NHWC", dst_layout="NCHW")
     elif a.case == "cfnr":
         # CropFlipNormalizeReformat on the reference benchmark's image size (bench/BenchCropFlipNormalizeReformat.cpp:
         # 1080x1920, crop = full image, flip both axes), here 3-channel uint8 -> float32 NCHW with per-channel constants

@@ -169,6 +169,12 @@ B200PP_PUBLIC NVCVStatus cvcudaNormalizeVarShapeSubmit(NVCVOperatorHandle handle
                                                        NVCVTensorHandle scale, NVCVImageBatchHandle out,
                                                        float global_scale, float shift, float epsilon, uint32_t flags);
 
+/* Stand-alone Reformat (NHWC / HWC <-> NCHW / CHW, or a strided copy within one layout). Replace cvcudaReformatCreate /
+ * cvcudaReformatSubmit (reference: src/cvcuda/OpReformat.cpp:28-55, declared in src/cvcuda/include/cvcuda/OpReformat.h). */
+B200PP_PUBLIC NVCVStatus cvcudaReformatCreate(NVCVOperatorHandle *handle);
+B200PP_PUBLIC NVCVStatus cvcudaReformatSubmit(NVCVOperatorHandle handle, cudaStream_t stream, NVCVTensorHandle in,
+                                              NVCVTensorHandle out);
+
 /* Additions (no counterpart in the reference): the whole fused pass -- per-channel normalisation, float16 output,
  * per-sample regions of interest and flip codes, letterbox placement -- on tensor / image-batch handles. `op` is the
  * B200ppResizeOp of preproc.h; its roi / flipCode pointers are device memory. The operator handle is the one

@@ -231,6 +231,13 @@ typedef struct B200ppNormalizeOp
 B200PP_PUBLIC int b200ppNormalize(const B200ppImageSet *src, const B200ppImageSet *dst, const B200ppNormalizeOp *op,
                                   cudaStream_t stream);
 
+/* Stand-alone Reformat: dst(n, y, x, c) = src(n, y, x, c) for numSamples images; each side is a B200ppDest-style view
+ * (base, element type, channels, width, height and the four byte strides), which expresses NHWC / HWC and NCHW / CHW
+ * alike. Element type, channel count and image size must agree. Replaces cvcuda::priv::Reformat::operator()
+ * (src/cvcuda/priv/OpReformat.cpp:36-60, kernels src/cvcuda/priv/legacy/reformat.cu), minus the handle unpacking; the
+ * reference's golden is the same element-wise copy (tests/cvcuda/system/TestOpReformat.cpp:51-69). */
+B200PP_PUBLIC int b200ppReformat(const B200ppDest *src, const B200ppDest *dst, int32_t numSamples, cudaStream_t stream);
+
 /* Message of the last failed call on this thread ("" if none). Mirrors nvcvPeekAtLastStatusMessage
  * (src/nvcv/src/include/nvcv/Status.h). */
 B200PP_PUBLIC const char *b200ppGetLastErrorMessage(void);

@@ -130,6 +130,10 @@ def bind_operators(lib_path: str):
         f = getattr(L, name)
         f.restype = C.c_int
         f.argtypes = [H, C.c_void_p, H, H, C.c_int]
+    L.cvcudaReformatCreate.restype = C.c_int
+    L.cvcudaReformatCreate.argtypes = [C.POINTER(H)]
+    L.cvcudaReformatSubmit.restype = C.c_int
+    L.cvcudaReformatSubmit.argtypes = [H, C.c_void_p, H, H]
     L.cvcudaNormalizeCreate.restype = C.c_int
     L.cvcudaNormalizeCreate.argtypes = [C.POINTER(H)]
     for name in ("cvcudaNormalizeSubmit", "cvcudaNormalizeVarShapeSubmit"):
