@@ -15,6 +15,8 @@ from .ops import (  # noqa: F401
     Interp,
     NORMALIZE_SCALE_IS_STDDEV,
     RectI,
+    convertto,
+    convertto_into,
     crop_flip_normalize_reformat,
     crop_flip_normalize_reformat_into,
     fused_preprocess_into,

@@ -106,7 +106,8 @@ enum OpKind
     OP_CROP_FLIP_NORMALIZE_REFORMAT = 2,
     OP_RESIZE                       = 3,
     OP_NORMALIZE                    = 4,
-    OP_REFORMAT                     = 5
+    OP_REFORMAT                     = 5,
+    OP_CONVERT_TO                   = 6
 };
 
 // The handle is the object pointer itself, as in the reference (src/cvcuda/priv/IOperator.hpp:37-40). Operators hold
@@ -614,9 +615,55 @@ NVCVStatus reformat_tensor(NVCVOperatorHandle handle, cudaStream_t stream, NVCVT
     return forward(b200ppReformat(&s, &d, i.samples, stream));
 }
 
+// ---------------------------------------------------------------------------------------------- stand-alone ConvertTo
+
+NVCVStatus convert_tensor(NVCVOperatorHandle handle, cudaStream_t stream, NVCVTensorHandle in, NVCVTensorHandle out,
+                          double alpha, double beta)
+{
+    if (NVCVStatus st = check_handle(handle, OP_CONVERT_TO))
+        return st;
+    if (!nvcv().ok)
+        return report(B200PP_ERROR_INTERNAL, "libnvcv_types is not loaded in this process");
+    NVCVStatus st = B200PP_SUCCESS;
+    ImageView  i, o;
+    if (!export_tensor(in, i, "Input", st) || !export_tensor(out, o, "Output", st))
+        return st;
+    // src/cvcuda/priv/legacy/convert_to.cu:140-160: both sides (N)HWC
+    if (!layout_is(i, "NHWC", "HWC") || !layout_is(o, "NHWC", "HWC") || !i.valid || !o.valid)
+        return report(B200PP_ERROR_INVALID_ARGUMENT, "Invalid DataFormat: input and output must be kNHWC or kHWC");
+    B200ppImageSet s, d;
+    std::memset(&s, 0, sizeof(s));
+    std::memset(&d, 0, sizeof(d));
+    const ImageView *views[2] = {&i, &o};
+    B200ppImageSet  *sets[2]  = {&s, &d};
+    for (int k = 0; k < 2; ++k)
+    {
+        sets[k]->base         = views[k]->base;
+        sets[k]->dtype        = views[k]->dtype;
+        sets[k]->channels     = views[k]->channels * views[k]->elemChannels;
+        sets[k]->numSamples   = views[k]->samples;
+        sets[k]->width        = views[k]->cols;
+        sets[k]->height       = views[k]->rows;
+        sets[k]->rowStride    = views[k]->rowStride;
+        sets[k]->sampleStride = views[k]->sampleStride;
+    }
+    return forward(b200ppConvertTo(&s, &d, alpha, beta, stream));
+}
+
 } // namespace
 
 // ================================================================================================ exported symbols
+
+extern "C" NVCVStatus cvcudaConvertToCreate(NVCVOperatorHandle *handle)
+{
+    return create(handle, OP_CONVERT_TO);
+}
+
+extern "C" NVCVStatus cvcudaConvertToSubmit(NVCVOperatorHandle handle, cudaStream_t stream, NVCVTensorHandle in,
+                                            NVCVTensorHandle out, const double alpha, const double beta)
+{
+    return convert_tensor(handle, stream, in, out, alpha, beta);
+}
 
 extern "C" NVCVStatus cvcudaReformatCreate(NVCVOperatorHandle *handle)
 {

@@ -1,5 +1,6 @@
 // Host side of the plain-C launch layer: argument validation, kernel selection and launch.
 // The single translation unit that contains all device code of the library.
+#include "convert_kernels.cuh"
 #include "normalize_kernels.cuh"
 #include "plain_resize_kernels.cuh"
 #include "reformat_kernels.cuh"
@@ -766,6 +767,58 @@ extern "C" int b200ppReformat(const B200ppDest *src, const B200ppDest *dst, int3
         break;
     }
     return check_launch("Reformat");
+}
+
+// ================================================================================================ stand-alone ConvertTo
+
+extern "C" int b200ppConvertTo(const B200ppImageSet *src, const B200ppImageSet *dst, double alpha, double beta,
+                               cudaStream_t stream)
+{
+    if (!src || !dst)
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "Null argument");
+    // checks of src/cvcuda/priv/legacy/convert_to.cu:140-188
+    if (src->imageList || dst->imageList)
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "ConvertTo works on tensors");
+    auto known = [](int t) {
+        return t == B200PP_U8 || t == B200PP_S8 || t == B200PP_U16 || t == B200PP_S16 || t == B200PP_S32 || t == B200PP_F32;
+    };
+    if (!known(src->dtype))
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "Invalid input DataType");
+    if (!known(dst->dtype))
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "Invalid output DataType");
+    if (src->numSamples != dst->numSamples || src->width != dst->width || src->height != dst->height
+        || src->channels != dst->channels)
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "Invalid input/output shape: the shapes must be equal");
+    if (src->channels < 1 || src->channels > 4)
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "Invalid channel number %d", src->channels);
+    if (src->numSamples < 0 || src->width < 0 || src->height < 0)
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "Invalid shape");
+    if (src->numSamples == 0 || src->width == 0 || src->height == 0)
+        return B200PP_SUCCESS;
+    if (!src->base || !dst->base)
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "Input and output must be cuda-accessible, pitch-linear memory");
+    ConvertKParams kp{};
+    kp.src        = static_cast<const uint8_t *>(src->base);
+    kp.dst        = static_cast<uint8_t *>(dst->base);
+    kp.sSample    = src->sampleStride;
+    kp.sRow       = src->rowStride;
+    kp.dSample    = dst->sampleStride;
+    kp.dRow       = dst->rowStride;
+    kp.numSamples = src->numSamples;
+    kp.rowElems   = src->width * src->channels;
+    kp.height     = src->height;
+    kp.srcType    = src->dtype;
+    kp.dstType    = dst->dtype;
+    kp.srcElem    = elem_size(src->dtype);
+    kp.dstElem    = elem_size(dst->dtype);
+    kp.alpha      = alpha;
+    kp.beta       = beta;
+    dim3 block(32, 8);
+    dim3 grid((kp.rowElems + 127) / 128, (kp.height + 15) / 16, std::min(src->numSamples, 65535));
+    if (grid.y > 65535u)
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "Input or output tensors are too large");
+    convert_kernel<<<grid, block, 0, stream>>>(kp);
+    return check_launch("ConvertTo");
 }
 
 extern "C" const char *b200ppGetLastErrorMessage(void)

@@ -172,6 +172,8 @@ def lib() -> C.CDLL:
         L.b200ppNormalize.argtypes = [C.POINTER(_ImageSet), C.POINTER(_ImageSet), C.POINTER(_NormalizeOp), C.c_void_p]
         L.b200ppReformat.restype = C.c_int
         L.b200ppReformat.argtypes = [C.POINTER(_Dest), C.POINTER(_Dest), C.c_int32, C.c_void_p]
+        L.b200ppConvertTo.restype = C.c_int
+        L.b200ppConvertTo.argtypes = [C.POINTER(_ImageSet), C.POINTER(_ImageSet), C.c_double, C.c_double, C.c_void_p]
         L.b200ppSetKernelPath.argtypes = [C.c_int]
         L.b200ppGetLaunchCount.restype = C.c_uint64
         L.b200ppReadDeviceError.restype = C.c_int
@@ -663,3 +665,25 @@ def reformat(src: torch.Tensor, dst_layout: str, *, src_layout: str = "", stream
     dev = src.device if src.is_cuda else torch.device("cuda", torch.cuda.current_device())
     out = torch.empty(tuple(dims[k] for k in dst_layout), dtype=src.dtype, device=dev)
     return reformat_into(out, src, src_layout=src_layout, dst_layout=dst_layout, stream=stream)
+
+
+# ------------------------------------------------------------------------------------------------ stand-alone ConvertTo
+
+def convertto_into(dst: torch.Tensor, src: torch.Tensor, scale: float = 1.0, offset: float = 0.0, *, stream=None):
+    """cvcuda.convertto_into (python/mod_cvcuda/OpConvertTo.cpp): dst = SaturateCast(scale * src + offset), (N)HWC tensors of
+    equal shape, the element type of ``dst`` decides the conversion."""
+    if isinstance(src, ImageBatchVarShape) or isinstance(dst, ImageBatchVarShape):
+        raise Error(Status.ERROR_INVALID_ARGUMENT, "ConvertTo works on tensors")
+    if src.dim() != dst.dim():
+        raise Error(Status.ERROR_INVALID_ARGUMENT, "Invalid DataFormat between input and output")
+    s, keep_s = _image_set(src, "Input")
+    d, keep_d = _image_set(dst, "Output")
+    _check(lib().b200ppConvertTo(C.byref(s), C.byref(d), float(scale), float(offset), _stream_handle(stream)))
+    return dst
+
+
+def convertto(src: torch.Tensor, dtype: torch.dtype, scale: float = 1.0, offset: float = 0.0, *, stream=None):
+    """cvcuda.convertto: allocates an output of the input's shape with element type ``dtype``."""
+    dev = src.device if src.is_cuda else torch.device("cuda", torch.cuda.current_device())
+    out = torch.empty(tuple(src.shape), dtype=dtype, device=dev)
+    return convertto_into(out, src, scale, offset, stream=stream)

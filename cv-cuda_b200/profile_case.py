@@ -24,7 +24,7 @@ INV_STD = tuple(float(np.float32(1.0) / np.float32(s)) for s in (58.395, 57.12, 
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--case", default="classify", choices=("classify", "classify-nhwc-u8", "classify-nhwc-f32", "classify-nhwc-u8-nearest", "4k", "4k-nearest", "letterbox", "cfnr", "varshape", "resize-rgba", "resize-rgba-nearest", "resize-rgb", "normalize-rgba", "normalize-rgb-f32", "reformat-u8", "reformat-f32"))
+    ap.add_argument("--case", default="classify", choices=("classify", "classify-nhwc-u8", "classify-nhwc-f32", "classify-nhwc-u8-nearest", "4k", "4k-nearest", "letterbox", "cfnr", "varshape", "resize-rgba", "resize-rgba-nearest", "resize-rgb", "normalize-rgba", "normalize-rgb-f32", "reformat-u8", "reformat-f32", "convertto-u8-f32", "convertto-f32-u8"))
     ap.add_argument("--images", type=int, default=32)
     ap.add_argument("--path", type=int, default=0)
     ap.add_argument("--launches", type=int, default=5)
@@ -108,6 +108,16 @@ def main():
 
         def run():
             pkg.reformat_into(out, src, src_layout="NHWC", dst_layout="NCHW")
+    elif a.case.startswith("convertto-"):
+        # stand-alone ConvertTo on 1080x1920 RGB: uint8 -> float32 (x 1/255) or float32 -> uint8 (x 255)
+        to_f32 = a.case.endswith("u8-f32")
+        src = torch.randint(0, 256, (n, 1080, 1920, 3), dtype=torch.uint8, device="cuda", generator=g)
+        src = src if to_f32 else src.float() / 255.0
+        out = torch.empty((n, 1080, 1920, 3), dtype=torch.float32 if to_f32 else torch.uint8, device="cuda")
+        print(f"convertto: {(src.numel() * src.element_size() + out.numel() * out.element_size()) / 1e6:.1f} MB in + out")
+
+        def run():
+            pkg.convertto_into(out, src, 1.0 / 255.0 if to_f32 else 255.0, 0.0)
     elif a.case == "cfnr":
         # CropFlipNormalizeReformat on the reference benchmark's image size (bench/BenchCropFlipNormalizeReformat.cpp:
         # 1080x1920, crop = full image, flip both axes), here 3-channel uint8 -> float32 NCHW with per-channel constants

@@ -175,6 +175,12 @@ B200PP_PUBLIC NVCVStatus cvcudaReformatCreate(NVCVOperatorHandle *handle);
 B200PP_PUBLIC NVCVStatus cvcudaReformatSubmit(NVCVOperatorHandle handle, cudaStream_t stream, NVCVTensorHandle in,
                                               NVCVTensorHandle out);
 
+/* Stand-alone ConvertTo: out = SaturateCast(alpha * in + beta). Replace cvcudaConvertToCreate / cvcudaConvertToSubmit
+ * (reference: src/cvcuda/OpConvertTo.cpp:28-55, declared in src/cvcuda/include/cvcuda/OpConvertTo.h). */
+B200PP_PUBLIC NVCVStatus cvcudaConvertToCreate(NVCVOperatorHandle *handle);
+B200PP_PUBLIC NVCVStatus cvcudaConvertToSubmit(NVCVOperatorHandle handle, cudaStream_t stream, NVCVTensorHandle in,
+                                               NVCVTensorHandle out, const double alpha, const double beta);
+
 /* Additions (no counterpart in the reference): the whole fused pass -- per-channel normalisation, float16 output,
  * per-sample regions of interest and flip codes, letterbox placement -- on tensor / image-batch handles. `op` is the
  * B200ppResizeOp of preproc.h; its roi / flipCode pointers are device memory. The operator handle is the one

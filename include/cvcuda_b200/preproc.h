@@ -238,6 +238,14 @@ B200PP_PUBLIC int b200ppNormalize(const B200ppImageSet *src, const B200ppImageSe
  * reference's golden is the same element-wise copy (tests/cvcuda/system/TestOpReformat.cpp:51-69). */
 B200PP_PUBLIC int b200ppReformat(const B200ppDest *src, const B200ppDest *dst, int32_t numSamples, cudaStream_t stream);
 
+/* Stand-alone ConvertTo: dst = SaturateCast(alpha * src + beta) element by element on dense (N)HWC tensors of equal
+ * shape; element types uint8, int8, uint16, int16, int32, float32 on either side. Replaces
+ * cvcuda::priv::ConvertTo::operator() (src/cvcuda/priv/OpConvertTo.cpp, kernel src/cvcuda/priv/legacy/convert_to.cu:36-58),
+ * minus the handle unpacking; arithmetic in double precision as the reference's test expects
+ * (tests/cvcuda/system/TestOpConvertTo.cpp:118-133). */
+B200PP_PUBLIC int b200ppConvertTo(const B200ppImageSet *src, const B200ppImageSet *dst, double alpha, double beta,
+                                  cudaStream_t stream);
+
 /* Message of the last failed call on this thread ("" if none). Mirrors nvcvPeekAtLastStatusMessage
  * (src/nvcv/src/include/nvcv/Status.h). */
 B200PP_PUBLIC const char *b200ppGetLastErrorMessage(void);

@@ -368,3 +368,18 @@ def ref_normalize(image: np.ndarray, base: np.ndarray, scale: np.ndarray, gscale
                          scale.ctypes.data, int(scale.size > 1), gscale, shift, epsilon, flags)
     assert rc == 0
     return out
+
+
+# ------------------------------------------------------------------------------------------------ stand-alone ConvertTo
+
+def convert_to(src: np.ndarray, out_dtype, alpha: float, beta: float) -> np.ndarray:
+    """The reference test's expectation for ConvertTo, value by value (tests/cvcuda/system/TestOpConvertTo.cpp:118-133):
+    ``SaturateCast<DstT>(alpha * val + beta)`` with double alpha / beta, i.e. product and sum in double precision, then
+    round half to even and clamp for the integer types (cuda_tools/detail/SaturateCastImpl.hpp, host path) or a plain
+    narrowing for float32."""
+    v = np.float64(alpha) * src.astype(np.float64) + np.float64(beta)
+    od = np.dtype(out_dtype)
+    if od.kind == "f":
+        return v.astype(od)
+    info = np.iinfo(od)
+    return np.clip(np.rint(v), info.min, info.max).astype(od)

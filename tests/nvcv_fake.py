@@ -130,6 +130,10 @@ def bind_operators(lib_path: str):
         f = getattr(L, name)
         f.restype = C.c_int
         f.argtypes = [H, C.c_void_p, H, H, C.c_int]
+    L.cvcudaConvertToCreate.restype = C.c_int
+    L.cvcudaConvertToCreate.argtypes = [C.POINTER(H)]
+    L.cvcudaConvertToSubmit.restype = C.c_int
+    L.cvcudaConvertToSubmit.argtypes = [H, C.c_void_p, H, H, C.c_double, C.c_double]
     L.cvcudaReformatCreate.restype = C.c_int
     L.cvcudaReformatCreate.argtypes = [C.POINTER(H)]
     L.cvcudaReformatSubmit.restype = C.c_int
