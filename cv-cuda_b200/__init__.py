@@ -17,6 +17,10 @@ from .ops import (  # noqa: F401
     RectI,
     convertto,
     convertto_into,
+    copymakeborder,
+    copymakeborder_into,
+    copymakeborderstack,
+    copymakeborderstack_into,
     crop_flip_normalize_reformat,
     crop_flip_normalize_reformat_into,
     fused_preprocess_into,

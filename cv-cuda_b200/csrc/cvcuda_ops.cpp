@@ -107,7 +107,8 @@ enum OpKind
     OP_RESIZE                       = 3,
     OP_NORMALIZE                    = 4,
     OP_REFORMAT                     = 5,
-    OP_CONVERT_TO                   = 6
+    OP_CONVERT_TO                   = 6,
+    OP_COPY_MAKE_BORDER             = 7
 };
 
 // The handle is the object pointer itself, as in the reference (src/cvcuda/priv/IOperator.hpp:37-40). Operators hold
@@ -652,7 +653,173 @@ NVCVStatus convert_tensor(NVCVOperatorHandle handle, cudaStream_t stream, NVCVTe
 
 } // namespace
 
+// ---------------------------------------------------------------------------------------------- stand-alone CopyMakeBorder
+
+void image_set_from_view(const ImageView &v, B200ppImageSet &s)
+{
+    std::memset(&s, 0, sizeof(s));
+    s.base         = v.base;
+    s.dtype        = v.dtype;
+    s.channels     = v.channels * v.elemChannels;
+    s.numSamples   = v.samples;
+    s.width        = v.cols;
+    s.height       = v.rows;
+    s.rowStride    = v.rowStride;
+    s.sampleStride = v.sampleStride;
+}
+
+bool image_set_from_batch(NVCVImageBatchHandle h, cudaStream_t stream, const char *what, B200ppImageSet &s, NVCVStatus &status)
+{
+    NVCVImageBatchData b;
+    std::memset(&b, 0, sizeof(b));
+    if (h == nullptr || nvcv().imageBatchExportData(h, stream, &b) != B200PP_SUCCESS || b.bufferType != 1)
+    {
+        status = report(B200PP_ERROR_INVALID_ARGUMENT, "%s must be varshape image batch", what);
+        return false;
+    }
+    if (b.varShapeStrided.uniqueFormat == 0)
+    {
+        status = report(B200PP_ERROR_INVALID_ARGUMENT, "Images in the %s batch must all have the same format", what);
+        return false;
+    }
+    int channels = 0, planes = 0, kind = -1, bits[4] = {0, 0, 0, 0};
+    nvcv().imageFormatGetNumChannels(b.varShapeStrided.uniqueFormat, &channels);
+    nvcv().imageFormatGetNumPlanes(b.varShapeStrided.uniqueFormat, &planes);
+    nvcv().imageFormatGetDataKind(b.varShapeStrided.uniqueFormat, &kind);
+    nvcv().imageFormatGetBitsPerChannel(b.varShapeStrided.uniqueFormat, bits);
+    if (planes > 1)
+    {
+        status = report(B200PP_ERROR_INVALID_ARGUMENT, "%s batch must hold interleaved (single-plane) images", what);
+        return false;
+    }
+    std::memset(&s, 0, sizeof(s));
+    s.dtype      = element_type(kind, bits[0]);
+    s.channels   = channels;
+    s.numSamples = b.numImages;
+    s.imageList  = b.varShapeStrided.imageList;
+    s.maxWidth   = b.varShapeStrided.maxWidth;
+    s.maxHeight  = b.varShapeStrided.maxHeight;
+    return true;
+}
+
+// top / left of the variable-shape forms: int32 (N)HWC tensors with one value per image along the width
+// (src/cvcuda/priv/legacy/copy_make_border_var_shape.cu:195-219 and the kernel's ptr(0, 0, image) at :41-42).
+bool offset_tensor(NVCVTensorHandle h, const char *what, int samples, const int32_t *&ptr, NVCVStatus &status)
+{
+    ImageView v;
+    if (!export_tensor(h, v, what, status))
+        return false;
+    if (v.dtype != B200PP_S32)
+    {
+        status = report(B200PP_ERROR_INVALID_ARGUMENT, "Invalid %s DataType", what);
+        return false;
+    }
+    if (!v.valid || !layout_is(v, "HWC", "NHWC"))
+    {
+        status = report(B200PP_ERROR_INVALID_ARGUMENT, "Invalid %s DataFormat", what);
+        return false;
+    }
+    if (v.cols < samples || (v.cols > 1 && v.colStride != 4))
+    {
+        status = report(B200PP_ERROR_INVALID_ARGUMENT, "%s must hold one packed int32 per image along its width", what);
+        return false;
+    }
+    ptr = reinterpret_cast<const int32_t *>(v.base);
+    return true;
+}
+
+NVCVStatus border_tensor(NVCVOperatorHandle handle, cudaStream_t stream, NVCVTensorHandle in, NVCVTensorHandle out, int top,
+                         int left, int borderMode, const float4 &value)
+{
+    if (NVCVStatus st = check_handle(handle, OP_COPY_MAKE_BORDER))
+        return st;
+    if (!nvcv().ok)
+        return report(B200PP_ERROR_INTERNAL, "libnvcv_types is not loaded in this process");
+    NVCVStatus st = B200PP_SUCCESS;
+    ImageView  i, o;
+    if (!export_tensor(in, i, "Input", st) || !export_tensor(out, o, "Output", st))
+        return st;
+    // order of src/cvcuda/priv/legacy/copy_make_border.cu:102-122
+    if (std::strcmp(i.layout, o.layout) != 0)
+        return report(B200PP_ERROR_INVALID_ARGUMENT, "Invalid DataFormat between input (%s) and output (%s)", i.layout, o.layout);
+    if (!layout_is(i, "HWC", "NHWC") || !i.valid || !o.valid)
+        return report(B200PP_ERROR_INVALID_ARGUMENT, "Invalid input DataFormat %s, the valid DataFormats are: \"NHWC\", \"HWC\"",
+                      i.layout);
+    if (i.dtype != o.dtype || i.elemChannels != o.elemChannels)
+        return report(B200PP_ERROR_INVALID_ARGUMENT, "Invalid DataType between input and output");
+    B200ppImageSet s, d;
+    image_set_from_view(i, s);
+    image_set_from_view(o, d);
+    const float v[4] = {value.x, value.y, value.z, value.w};
+    return forward(b200ppCopyMakeBorder(&s, &d, top, left, nullptr, nullptr, borderMode, v, stream));
+}
+
+// Variable-shape input; the output is a variable-shape batch (outBatch) or a tensor (outTensor: the "stack" form).
+NVCVStatus border_varshape(NVCVOperatorHandle handle, cudaStream_t stream, NVCVImageBatchHandle in,
+                           NVCVImageBatchHandle outBatch, NVCVTensorHandle outTensor, NVCVTensorHandle top,
+                           NVCVTensorHandle left, int borderMode, const float4 &value)
+{
+    if (NVCVStatus st = check_handle(handle, OP_COPY_MAKE_BORDER))
+        return st;
+    if (!nvcv().ok)
+        return report(B200PP_ERROR_INTERNAL, "libnvcv_types is not loaded in this process");
+    NVCVStatus     st = B200PP_SUCCESS;
+    B200ppImageSet s, d;
+    if (!image_set_from_batch(in, stream, "Input", s, st))
+        return st;
+    if (outBatch)
+    {
+        if (!image_set_from_batch(outBatch, stream, "Output", d, st))
+            return st;
+    }
+    else
+    {
+        ImageView o;
+        if (!export_tensor(outTensor, o, "Output", st))
+            return st;
+        if (!o.valid || !layout_is(o, "HWC", "NHWC"))
+            return report(B200PP_ERROR_INVALID_ARGUMENT,
+                          "Invalid input DataFormat %s, the valid DataFormats are: \"NHWC\", \"HWC\"", o.layout);
+        image_set_from_view(o, d);
+    }
+    const int32_t *topPtr = nullptr, *leftPtr = nullptr;
+    if (!offset_tensor(left, "Left", s.numSamples, leftPtr, st) || !offset_tensor(top, "Top", s.numSamples, topPtr, st))
+        return st;
+    const float v[4] = {value.x, value.y, value.z, value.w};
+    return forward(b200ppCopyMakeBorder(&s, &d, 0, 0, topPtr, leftPtr, borderMode, v, stream));
+}
+
 // ================================================================================================ exported symbols
+
+extern "C" NVCVStatus cvcudaCopyMakeBorderCreate(NVCVOperatorHandle *handle)
+{
+    return create(handle, OP_COPY_MAKE_BORDER);
+}
+
+extern "C" NVCVStatus cvcudaCopyMakeBorderSubmit(NVCVOperatorHandle handle, cudaStream_t stream, NVCVTensorHandle in,
+                                                 NVCVTensorHandle out, int32_t top, int32_t left, NVCVBorderType borderMode,
+                                                 const float4 borderValue)
+{
+    return border_tensor(handle, stream, in, out, top, left, static_cast<int>(borderMode), borderValue);
+}
+
+extern "C" NVCVStatus cvcudaCopyMakeBorderVarShapeSubmit(NVCVOperatorHandle handle, cudaStream_t stream,
+                                                         NVCVImageBatchHandle in, NVCVImageBatchHandle out,
+                                                         NVCVTensorHandle top, NVCVTensorHandle left,
+                                                         NVCVBorderType borderMode, const float4 borderValue)
+{
+    if (out == nullptr)
+        return report(B200PP_ERROR_INVALID_ARGUMENT, "Output must be varshape image batch");
+    return border_varshape(handle, stream, in, out, nullptr, top, left, static_cast<int>(borderMode), borderValue);
+}
+
+extern "C" NVCVStatus cvcudaCopyMakeBorderVarShapeStackSubmit(NVCVOperatorHandle handle, cudaStream_t stream,
+                                                              NVCVImageBatchHandle in, NVCVTensorHandle out,
+                                                              NVCVTensorHandle top, NVCVTensorHandle left,
+                                                              NVCVBorderType borderMode, const float4 borderValue)
+{
+    return border_varshape(handle, stream, in, nullptr, out, top, left, static_cast<int>(borderMode), borderValue);
+}
 
 extern "C" NVCVStatus cvcudaConvertToCreate(NVCVOperatorHandle *handle)
 {

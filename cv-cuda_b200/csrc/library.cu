@@ -1,5 +1,6 @@
 // Host side of the plain-C launch layer: argument validation, kernel selection and launch.
 // The single translation unit that contains all device code of the library.
+#include "border_kernels.cuh"
 #include "convert_kernels.cuh"
 #include "normalize_kernels.cuh"
 #include "plain_resize_kernels.cuh"
@@ -819,6 +820,151 @@ extern "C" int b200ppConvertTo(const B200ppImageSet *src, const B200ppImageSet *
         return fail(B200PP_ERROR_INVALID_ARGUMENT, "Input or output tensors are too large");
     convert_kernel<<<grid, block, 0, stream>>>(kp);
     return check_launch("ConvertTo");
+}
+
+// ================================================================================================ stand-alone CopyMakeBorder
+
+namespace b200pp {
+
+// One pixel's bytes for the constant border: each channel value converted from float to the element type the way a C++
+// static_cast does inside the type's range (toward zero), clamped to the range outside it.
+static void border_fill_bytes(int dtype, int channels, const float value[4], unsigned (&fill)[4])
+{
+    uint8_t   bytes[16] = {};
+    const int es        = elem_size(dtype);
+    for (int c = 0; c < channels; ++c)
+    {
+        const float v = value ? value[c] : 0.f;
+        if (dtype == B200PP_F32)
+        {
+            std::memcpy(bytes + c * es, &v, 4);
+            continue;
+        }
+        double lo = 0, hi = 255;
+        switch (dtype)
+        {
+        case B200PP_S8:
+            lo = -128, hi = 127;
+            break;
+        case B200PP_U16:
+            hi = 65535;
+            break;
+        case B200PP_S16:
+            lo = -32768, hi = 32767;
+            break;
+        case B200PP_S32:
+            lo = -2147483648.0, hi = 2147483647.0;
+            break;
+        default:
+            break;
+        }
+        double d = v != v ? 0.0 : std::trunc(static_cast<double>(v));
+        d        = d < lo ? lo : (d > hi ? hi : d);
+        const long long i = static_cast<long long>(d);
+        std::memcpy(bytes + c * es, &i, es); // little-endian: the low bytes are the two's-complement element
+    }
+    std::memcpy(fill, bytes, 16);
+}
+
+template<int PB>
+static void launch_border(dim3 grid, dim3 block, cudaStream_t stream, const BorderKParams &kp)
+{
+    copy_make_border_kernel<PB><<<grid, block, 0, stream>>>(kp);
+}
+
+} // namespace b200pp
+
+extern "C" int b200ppCopyMakeBorder(const B200ppImageSet *src, const B200ppImageSet *dst, int32_t top, int32_t left,
+                                    const int32_t *topList, const int32_t *leftList, int32_t borderMode,
+                                    const float borderValue[4], cudaStream_t stream)
+{
+    if (!src || !dst)
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "Null argument");
+    // Checks and order of the reference operator (src/cvcuda/priv/legacy/copy_make_border.cu:98-166 for tensors,
+    // copy_make_border_var_shape.cu:150-222 for variable-shape batches).
+    if (src->dtype != dst->dtype)
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "Invalid DataType between input and output");
+    if (src->channels != dst->channels)
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "Input and output channels are different");
+    if (src->channels > 4 || src->channels < 1)
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "Invalid channel number %d", src->channels);
+    if (!(src->dtype == B200PP_U8 || src->dtype == B200PP_U16 || src->dtype == B200PP_S16 || src->dtype == B200PP_F32
+          || src->dtype == B200PP_S8 || src->dtype == B200PP_S32))
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "Invalid DataType %d", src->dtype);
+    if (borderMode < B200PP_BORDER_CONSTANT || borderMode > B200PP_BORDER_REFLECT101)
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "Invalid borderType %d", borderMode);
+    if (src->numSamples != dst->numSamples)
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "Input and output samples are different");
+    if ((topList == nullptr) != (leftList == nullptr))
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "Top and left must both be lists or both be single values");
+    if (!dst->imageList && src->imageList && !topList)
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "Variable-shape input needs per-sample top and left");
+    if (!src->imageList && !dst->imageList && !topList
+        && !(top >= 0 && dst->height >= top + src->height && left >= 0 && dst->width >= left + src->width))
+        return fail(B200PP_ERROR_INVALID_ARGUMENT,
+                    "Invalid border %d %d %d %d, top >= 0 && bottom >= 0 && left >= 0 && right >= 0, in resolution: %dx%d, "
+                    "out resolution: %dx%d",
+                    top, dst->height - top - src->height, left, dst->width - left - src->width, src->height, src->width,
+                    dst->height, dst->width);
+    if (src->numSamples < 0)
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "Negative batch size");
+    if (src->numSamples == 0)
+        return B200PP_SUCCESS;
+    if ((!src->base && !src->imageList) || (!dst->base && !dst->imageList))
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "Input and output must be cuda-accessible, pitch-linear memory");
+    const int gw = dst->imageList ? dst->maxWidth : dst->width, gh = dst->imageList ? dst->maxHeight : dst->height;
+    if (gw < 0 || gh < 0 || (!src->imageList && (src->width < 0 || src->height < 0)))
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "Invalid image size");
+    if (gw == 0 || gh == 0)
+        return B200PP_SUCCESS;
+
+    BorderKParams kp{};
+    kp.src        = plain_side(src);
+    kp.dst        = plain_side(dst);
+    kp.numSamples = src->numSamples;
+    kp.top        = top;
+    kp.left       = left;
+    kp.topList    = topList;
+    kp.leftList   = leftList;
+    kp.border     = borderMode;
+    border_fill_bytes(src->dtype, src->channels, borderValue, kp.fill);
+    const int       pixBytes = elem_size(src->dtype) * src->channels;
+    const long long rowBytes = static_cast<long long>(gw) * pixBytes;
+    if (rowBytes > 0x7fffffffll)
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "Input or output size exceeds 2147483647. Tensor is too large.");
+    dim3 block(64, 4);
+    dim3 grid(static_cast<unsigned>((rowBytes + 255) / 256), (gh + 4 * kBorderRows - 1) / (4 * kBorderRows),
+              std::min(src->numSamples, 65535));
+    if (grid.y > 65535u)
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "Input or output tensors are too large");
+    switch (pixBytes)
+    {
+    case 1:
+        launch_border<1>(grid, block, stream, kp);
+        break;
+    case 2:
+        launch_border<2>(grid, block, stream, kp);
+        break;
+    case 3:
+        launch_border<3>(grid, block, stream, kp);
+        break;
+    case 4:
+        launch_border<4>(grid, block, stream, kp);
+        break;
+    case 6:
+        launch_border<6>(grid, block, stream, kp);
+        break;
+    case 8:
+        launch_border<8>(grid, block, stream, kp);
+        break;
+    case 12:
+        launch_border<12>(grid, block, stream, kp);
+        break;
+    default:
+        launch_border<16>(grid, block, stream, kp);
+        break;
+    }
+    return check_launch("CopyMakeBorder");
 }
 
 extern "C" const char *b200ppGetLastErrorMessage(void)

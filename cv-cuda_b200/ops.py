@@ -172,6 +172,9 @@ def lib() -> C.CDLL:
         L.b200ppNormalize.argtypes = [C.POINTER(_ImageSet), C.POINTER(_ImageSet), C.POINTER(_NormalizeOp), C.c_void_p]
         L.b200ppReformat.restype = C.c_int
         L.b200ppReformat.argtypes = [C.POINTER(_Dest), C.POINTER(_Dest), C.c_int32, C.c_void_p]
+        L.b200ppCopyMakeBorder.restype = C.c_int
+        L.b200ppCopyMakeBorder.argtypes = [C.POINTER(_ImageSet), C.POINTER(_ImageSet), C.c_int32, C.c_int32, C.c_void_p,
+                                           C.c_void_p, C.c_int32, C.POINTER(C.c_float), C.c_void_p]
         L.b200ppConvertTo.restype = C.c_int
         L.b200ppConvertTo.argtypes = [C.POINTER(_ImageSet), C.POINTER(_ImageSet), C.c_double, C.c_double, C.c_void_p]
         L.b200ppSetKernelPath.argtypes = [C.c_int]
@@ -687,3 +690,80 @@ def convertto(src: torch.Tensor, dtype: torch.dtype, scale: float = 1.0, offset:
     dev = src.device if src.is_cuda else torch.device("cuda", torch.cuda.current_device())
     out = torch.empty(tuple(src.shape), dtype=dtype, device=dev)
     return convertto_into(out, src, scale, offset, stream=stream)
+
+
+# ------------------------------------------------------------------------------------------------ stand-alone CopyMakeBorder
+
+def _border_value(border_value) -> "C.Array":
+    vals = [float(v) for v in (border_value or [])]
+    if len(vals) > 4:
+        raise Error(Status.ERROR_INVALID_ARGUMENT, "Channels of borderValue should <= 4.")
+    return (C.c_float * 4)(*(vals + [0.0] * (4 - len(vals))))
+
+
+def _offset_list(t: torch.Tensor, what: str, count: int):
+    """top / left of the variable-shape forms: an int32 CUDA tensor with one packed value per image."""
+    if not isinstance(t, torch.Tensor) or not t.is_cuda or t.dtype != torch.int32:
+        raise Error(Status.ERROR_INVALID_ARGUMENT, f"Invalid {what} DataType")
+    if t.numel() < count or not t.is_contiguous():
+        raise Error(Status.ERROR_INVALID_ARGUMENT, f"{what} must hold one packed int32 per image")
+    return t
+
+
+def copymakeborder_into(dst, src, border_mode: Border = Border.CONSTANT, border_value: Sequence[float] = (), *, top, left,
+                        stream=None):
+    """cvcuda.copymakeborder_into (python/mod_cvcuda/OpCopyMakeBorder.cpp:234-262 for tensors, :358-386 for image
+    batches) and cvcuda.copymakeborderstack_into (:295-325: image batch -> tensor). ``top`` / ``left`` are ints for
+    tensors, int32 CUDA tensors with one value per image for image batches."""
+    value = _border_value(border_value)
+    s, keep_s = _image_set(src, "Input")
+    d, keep_d = _image_set(dst, "Output")
+    if isinstance(src, ImageBatchVarShape):
+        tl, ll = _offset_list(top, "Top", len(src)), _offset_list(left, "Left", len(src))
+        _check(lib().b200ppCopyMakeBorder(C.byref(s), C.byref(d), 0, 0, tl.data_ptr(), ll.data_ptr(), int(border_mode), value,
+                                          _stream_handle(stream)))
+        return dst
+    if isinstance(dst, ImageBatchVarShape):
+        raise Error(Status.ERROR_INVALID_ARGUMENT, "Input must be varshape image batch")
+    if src.dim() != dst.dim():
+        raise Error(Status.ERROR_INVALID_ARGUMENT, "Invalid DataFormat between input and output")
+    _check(lib().b200ppCopyMakeBorder(C.byref(s), C.byref(d), int(top), int(left), None, None, int(border_mode), value,
+                                      _stream_handle(stream)))
+    return dst
+
+
+def copymakeborder(src, border_mode: Border = Border.CONSTANT, border_value: Sequence[float] = (), *, top, left, bottom=None,
+                   right=None, out_heights=None, out_widths=None, stream=None):
+    """cvcuda.copymakeborder: allocates the output. Tensors take top / bottom / left / right
+    (python/mod_cvcuda/OpCopyMakeBorder.cpp:81-99); image batches take top / left tensors and out_heights / out_widths
+    lists (:161-192)."""
+    if isinstance(src, ImageBatchVarShape):
+        if out_heights is None or out_widths is None or len(out_heights) != len(src) or len(out_widths) != len(src):
+            raise Error(Status.ERROR_INVALID_ARGUMENT, "out_heights / out_widths must have one entry per input image")
+        out = ImageBatchVarShape([torch.empty((int(h), int(w), src.channels), dtype=src.dtype, device=src.device)
+                                  for h, w in zip(out_heights, out_widths)])
+        return copymakeborder_into(out, src, border_mode, border_value, top=top, left=left, stream=stream)
+    if bottom is None or right is None:
+        raise Error(Status.ERROR_INVALID_ARGUMENT, "Tensor inputs need top, bottom, left and right")
+    shape = list(src.shape)
+    shape[-3] += int(top) + int(bottom)
+    shape[-2] += int(left) + int(right)
+    dev = src.device if src.is_cuda else torch.device("cuda", torch.cuda.current_device())
+    out = torch.empty(tuple(shape), dtype=src.dtype, device=dev)
+    return copymakeborder_into(out, src, border_mode, border_value, top=top, left=left, stream=stream)
+
+
+def copymakeborderstack_into(dst: torch.Tensor, src: ImageBatchVarShape, border_mode: Border = Border.CONSTANT,
+                             border_value: Sequence[float] = (), *, top, left, stream=None):
+    """cvcuda.copymakeborderstack_into (python/mod_cvcuda/OpCopyMakeBorder.cpp:101-127): every image of the batch lands in
+    one sample of the (N)HWC tensor ``dst``."""
+    if not isinstance(src, ImageBatchVarShape) or isinstance(dst, ImageBatchVarShape):
+        raise Error(Status.ERROR_INVALID_ARGUMENT, "Input must be varshape image batch, output a tensor")
+    return copymakeborder_into(dst, src, border_mode, border_value, top=top, left=left, stream=stream)
+
+
+def copymakeborderstack(src: ImageBatchVarShape, border_mode: Border = Border.CONSTANT, border_value: Sequence[float] = (), *,
+                        top, left, out_height: int, out_width: int, stream=None):
+    """cvcuda.copymakeborderstack (python/mod_cvcuda/OpCopyMakeBorder.cpp:129-141): allocates the NHWC output."""
+    out = torch.empty((len(src), int(out_height), int(out_width), src.channels), dtype=src.dtype, device=src.device)
+    return copymakeborderstack_into(out, src, border_mode, border_value, top=top, left=left, stream=stream)

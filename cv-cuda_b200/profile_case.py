@@ -24,7 +24,7 @@ INV_STD = tuple(float(np.float32(1.0) / np.float32(s)) for s in (58.395, 57.12, 
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--case", default="classify", choices=("classify", "classify-nhwc-u8", "classify-nhwc-f32", "classify-nhwc-u8-nearest", "4k", "4k-nearest", "letterbox", "cfnr", "varshape", "resize-rgba", "resize-rgba-nearest", "resize-rgb", "normalize-rgba", "normalize-rgb-f32", "reformat-u8", "reformat-f32", "convertto-u8-f32", "convertto-f32-u8"))
+    ap.add_argument("--case", default="classify", choices=("classify", "classify-nhwc-u8", "classify-nhwc-f32", "classify-nhwc-u8-nearest", "4k", "4k-nearest", "letterbox", "cfnr", "varshape", "resize-rgba", "resize-rgba-nearest", "resize-rgb", "normalize-rgba", "normalize-rgb-f32", "reformat-u8", "reformat-f32", "convertto-u8-f32", "convertto-f32-u8", "border-rgb", "border-rgb-reflect", "border-rgba-f32"))
     ap.add_argument("--images", type=int, default=32)
     ap.add_argument("--path", type=int, default=0)
     ap.add_argument("--launches", type=int, default=5)
@@ -118,6 +118,19 @@ def main():
 
         def run():
             pkg.convertto_into(out, src, 1.0 / 255.0 if to_f32 else 255.0, 0.0)
+    elif a.case.startswith("border-"):
+        # stand-alone CopyMakeBorder: 1080x1920 images into 1144x1984 (32 pixels on every side; the letterbox / padding
+        # step of a detection pipeline), constant or reflect-101 border
+        f32 = a.case.endswith("f32")
+        ch = 4 if "rgba" in a.case else 3
+        src = torch.randint(0, 256, (n, 1080, 1920, ch), dtype=torch.uint8, device="cuda", generator=g)
+        src = src.float() if f32 else src
+        out = torch.empty((n, 1144, 1984, ch), dtype=src.dtype, device="cuda")
+        mode = pkg.Border.REFLECT101 if a.case.endswith("reflect") else pkg.Border.CONSTANT
+        print(f"copymakeborder: {(src.numel() * src.element_size() + out.numel() * out.element_size()) / 1e6:.1f} MB in + out")
+
+        def run():
+            pkg.copymakeborder_into(out, src, mode, (114.0, 114.0, 114.0, 0.0), top=32, left=32)
     elif a.case == "cfnr":
         # CropFlipNormalizeReformat on the reference benchmark's image size (bench/BenchCropFlipNormalizeReformat.cpp:
         # 1080x1920, crop = full image, flip both axes), here 3-channel uint8 -> float32 NCHW with per-channel constants

@@ -46,6 +46,10 @@ typedef struct __attribute__((aligned(8))) int2 /* CUDA vector type */
 {
     int x, y;
 } int2;
+typedef struct __attribute__((aligned(16))) float4 /* CUDA vector type */
+{
+    float x, y, z, w;
+} float4;
 #    endif
 
 typedef int      NVCVInterpolationType; /* cvcuda/Types.h:39-51 */
@@ -180,6 +184,24 @@ B200PP_PUBLIC NVCVStatus cvcudaReformatSubmit(NVCVOperatorHandle handle, cudaStr
 B200PP_PUBLIC NVCVStatus cvcudaConvertToCreate(NVCVOperatorHandle *handle);
 B200PP_PUBLIC NVCVStatus cvcudaConvertToSubmit(NVCVOperatorHandle handle, cudaStream_t stream, NVCVTensorHandle in,
                                                NVCVTensorHandle out, const double alpha, const double beta);
+
+/* Stand-alone CopyMakeBorder: tensor -> tensor with one (top, left); variable-shape batch -> variable-shape batch, and
+ * variable-shape batch -> tensor ("stack"), with int32 top / left tensors holding one value per image along the width.
+ * Replace cvcudaCopyMakeBorderCreate / cvcudaCopyMakeBorderSubmit / cvcudaCopyMakeBorderVarShapeSubmit /
+ * cvcudaCopyMakeBorderVarShapeStackSubmit (reference: src/cvcuda/OpCopyMakeBorder.cpp:29-82, declared in
+ * src/cvcuda/include/cvcuda/OpCopyMakeBorder.h:53-140). */
+B200PP_PUBLIC NVCVStatus cvcudaCopyMakeBorderCreate(NVCVOperatorHandle *handle);
+B200PP_PUBLIC NVCVStatus cvcudaCopyMakeBorderSubmit(NVCVOperatorHandle handle, cudaStream_t stream, NVCVTensorHandle in,
+                                                    NVCVTensorHandle out, int32_t top, int32_t left,
+                                                    NVCVBorderType borderMode, const float4 borderValue);
+B200PP_PUBLIC NVCVStatus cvcudaCopyMakeBorderVarShapeSubmit(NVCVOperatorHandle handle, cudaStream_t stream,
+                                                            NVCVImageBatchHandle in, NVCVImageBatchHandle out,
+                                                            NVCVTensorHandle top, NVCVTensorHandle left,
+                                                            NVCVBorderType borderMode, const float4 borderValue);
+B200PP_PUBLIC NVCVStatus cvcudaCopyMakeBorderVarShapeStackSubmit(NVCVOperatorHandle handle, cudaStream_t stream,
+                                                                 NVCVImageBatchHandle in, NVCVTensorHandle out,
+                                                                 NVCVTensorHandle top, NVCVTensorHandle left,
+                                                                 NVCVBorderType borderMode, const float4 borderValue);
 
 /* Additions (no counterpart in the reference): the whole fused pass -- per-channel normalisation, float16 output,
  * per-sample regions of interest and flip codes, letterbox placement -- on tensor / image-batch handles. `op` is the

@@ -246,6 +246,18 @@ B200PP_PUBLIC int b200ppReformat(const B200ppDest *src, const B200ppDest *dst, i
 B200PP_PUBLIC int b200ppConvertTo(const B200ppImageSet *src, const B200ppImageSet *dst, double alpha, double beta,
                                   cudaStream_t stream);
 
+/* Stand-alone CopyMakeBorder: dst[i] = src[i] placed at (left, top) inside dst[i], every other destination pixel taken
+ * by the border rule (B200PP_BORDER_*; the constant rule writes borderValue[c] converted to the element type). Dense
+ * tensors or image lists on either side; top / left apply to all samples unless topList and leftList (device arrays, one
+ * packed int32 per sample) are given, as the reference's variable-shape forms require. 1 to 4 interleaved channels of
+ * uint8, int8, uint16, int16, int32 or float32. Replaces cvcuda::priv::CopyMakeBorder::operator() in its three forms
+ * (src/cvcuda/priv/OpCopyMakeBorder.cpp:42-124; kernels src/cvcuda/priv/legacy/copy_make_border.cu and
+ * copy_make_border_var_shape.cu), minus the handle unpacking; results follow the reference's CPU golden
+ * (tests/cvcuda/system/TestOpCopyMakeBorder.cpp:40-97) bit for bit. */
+B200PP_PUBLIC int b200ppCopyMakeBorder(const B200ppImageSet *src, const B200ppImageSet *dst, int32_t top, int32_t left,
+                                       const int32_t *topList, const int32_t *leftList, int32_t borderMode,
+                                       const float borderValue[4], cudaStream_t stream);
+
 /* Message of the last failed call on this thread ("" if none). Mirrors nvcvPeekAtLastStatusMessage
  * (src/nvcv/src/include/nvcv/Status.h). */
 B200PP_PUBLIC const char *b200ppGetLastErrorMessage(void);

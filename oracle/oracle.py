@@ -79,6 +79,9 @@ def lib() -> C.CDLL:
         L.oracle_normalize.restype = C.c_int
         L.oracle_normalize.argtypes = [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p,
                                        C.c_void_p, C.c_void_p, C.c_void_p, C.c_float, C.c_float, C.c_float, C.c_uint32]
+        L.oracle_copy_make_border.restype = C.c_int
+        L.oracle_copy_make_border.argtypes = [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p,
+                                              C.c_int32, C.c_int32, C.c_void_p]
         L.oracle_sat_u8.restype = C.c_uint8
         L.oracle_sat_u8.argtypes = [C.c_float]
         L.oracle_sat_s16.restype = C.c_int16
@@ -114,6 +117,9 @@ def ref() -> Optional[C.CDLL]:
             R.ref_normalize.restype = C.c_int
             R.ref_normalize.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_void_p,
                                         C.c_int, C.c_float, C.c_float, C.c_float, C.c_uint32]
+        if hasattr(R, "ref_copy_make_border"):
+            R.ref_copy_make_border.restype = C.c_int
+            R.ref_copy_make_border.argtypes = [C.c_void_p, C.c_void_p] + [C.c_int] * 10 + [C.c_void_p]
         for name, rt in (("ref_sat_u8_f32", C.c_uint8), ("ref_sat_s32_f32", C.c_int32), ("ref_sat_s16_f32", C.c_int16)):
             f = getattr(R, name)
             f.restype = rt
@@ -383,3 +389,60 @@ def convert_to(src: np.ndarray, out_dtype, alpha: float, beta: float) -> np.ndar
         return v.astype(od)
     info = np.iinfo(od)
     return np.clip(np.rint(v), info.min, info.max).astype(od)
+
+
+# ------------------------------------------------------------------------------------------------ stand-alone CopyMakeBorder
+
+def border_fill(value, dtype, channels: int) -> np.ndarray:
+    """The per-channel constant border value converted to the element type the way the golden does
+    (static_cast<T>(float), tests/cvcuda/system/TestOpCopyMakeBorder.cpp:69), as the low bytes of four 32-bit words."""
+    v = np.zeros(4, np.float32)
+    v[:len(value)] = np.asarray(value, np.float32)[:4]
+    words = np.zeros(4, np.uint32)
+    dt = np.dtype(dtype)
+    for c in range(4):
+        if dt.kind in "iu":  # inside the type's range a static_cast drops the fraction; outside it (undefined there): clamp
+            info = np.iinfo(dt)
+            elem = np.array([min(max(np.trunc(np.float64(v[c])), info.min), info.max)]).astype(dt)
+        else:
+            elem = np.array([v[c]]).astype(dt)
+        words[c] = np.frombuffer(elem.tobytes().ljust(4, b"\0"), np.uint32)[0]
+    return words
+
+
+def copy_make_border(images: Sequence[np.ndarray], out_sizes: Sequence[tuple], top, left, border: int, value=(0, 0, 0, 0)) -> list:
+    """Stand-alone CopyMakeBorder restatement on packed HxWxC images; out_sizes are (w, h) per image; top / left one
+    int each, or one per image."""
+    imgs = [np.ascontiguousarray(im) for im in images]
+    n = len(imgs)
+    dt, ch = imgs[0].dtype, imgs[0].shape[2]
+    outs = [np.empty((h, w, ch), dtype=dt) for (w, h) in out_sizes]
+    S = (_PlainImage * n)()
+    D = (_PlainImage * n)()
+    for i in range(n):
+        h, w, _ = imgs[i].shape
+        S[i] = _PlainImage(imgs[i].ctypes.data, w, h, imgs[i].strides[0])
+        D[i] = _PlainImage(outs[i].ctypes.data, out_sizes[i][0], out_sizes[i][1], outs[i].strides[0])
+    per = not np.isscalar(top)
+    t = np.ascontiguousarray(np.atleast_1d(top), np.int32)
+    l = np.ascontiguousarray(np.atleast_1d(left), np.int32)
+    fill = border_fill(value, dt, ch)
+    rc = lib().oracle_copy_make_border(S, D, n, dt.itemsize, ch, t.ctypes.data, l.ctypes.data, int(per), border, fill.ctypes.data)
+    assert rc == 0
+    return outs
+
+
+def ref_copy_make_border(batch: np.ndarray, out_size: tuple, top: int, left: int, border: int, value=(0, 0, 0, 0)) -> np.ndarray:
+    """The reference's own CopyMakeBorder golden (tensor form) on a packed [N, H, W, C] batch."""
+    R = ref()
+    assert R is not None and hasattr(R, "ref_copy_make_border")
+    batch = np.ascontiguousarray(batch)
+    n, h, w, ch = batch.shape
+    ow, oh = out_size
+    out = np.empty((n, oh, ow, ch), dtype=batch.dtype)
+    v = np.zeros(4, np.float32)
+    v[:len(value)] = np.asarray(value, np.float32)[:4]
+    rc = R.ref_copy_make_border(out.ctypes.data, batch.ctypes.data, n, ow, oh, w, h, ch, DTYPE_CODE[batch.dtype], top, left,
+                                border, v.ctypes.data)
+    assert rc == 0
+    return out

@@ -511,3 +511,43 @@ int64_t oracle_resize_source_bytes(int32_t srcW, int32_t srcH, int64_t rowStride
     free(bm);
     return cnt * 32;
 }
+
+/* ---------------------------------------------------------------- stand-alone CopyMakeBorder */
+
+#include "resize_oracle.h"
+
+/* tests/cvcuda/system/TestOpCopyMakeBorder.cpp:40-97 (tensor form) and :99-175 (variable-shape forms): each destination
+ * pixel takes the source pixel at (x - left, y - top), or -- outside the source -- the per-channel constant converted
+ * with static_cast<T>, or the source pixel the border rule maps to. elemSize 1, 2 or 4; `fill` holds the constants
+ * already converted to the element type (low bytes of each 32-bit word). */
+int oracle_copy_make_border(const OraclePlainImage *src, const OraclePlainImage *dst, int32_t n, int32_t elemSize,
+                            int32_t channels, const int32_t *top, const int32_t *left, int32_t perSample, int32_t border,
+                            const uint32_t *fill)
+{
+    if (channels < 1 || channels > 4 || border < 0 || border > 4 || !(elemSize == 1 || elemSize == 2 || elemSize == 4))
+        return -1;
+    for (int32_t i = 0; i < n; ++i)
+    {
+        const int t = top[perSample ? i : 0], l = left[perSample ? i : 0];
+        for (int y = 0; y < dst[i].height; ++y)
+            for (int x = 0; x < dst[i].width; ++x)
+            {
+                int       sx = x - l, sy = y - t;
+                uint8_t  *d  = (uint8_t *)dst[i].base + y * dst[i].rowStride + (int64_t)x * channels * elemSize;
+                const int in = sx >= 0 && sx < src[i].width && sy >= 0 && sy < src[i].height;
+                if (!in && border == ORC_BORDER_CONSTANT)
+                {
+                    for (int c = 0; c < channels; ++c) memcpy(d + c * elemSize, &fill[c], (size_t)elemSize);
+                    continue;
+                }
+                if (!in)
+                {
+                    border_index(&sx, src[i].width, border);
+                    border_index(&sy, src[i].height, border);
+                }
+                memcpy(d, (const uint8_t *)src[i].base + sy * src[i].rowStride + (int64_t)sx * channels * elemSize,
+                       (size_t)channels * elemSize);
+            }
+    }
+    return 0;
+}

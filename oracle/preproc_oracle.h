@@ -117,6 +117,13 @@ int16_t  oracle_sat_s16(float v);
 int32_t  oracle_sat_s32(float v);
 uint16_t oracle_f32_to_f16_bits(float v);
 
+/* Stand-alone CopyMakeBorder golden (tests/cvcuda/system/TestOpCopyMakeBorder.cpp:40-175); images are the
+ * OraclePlainImage of resize_oracle.h. top / left hold one value, or one per sample when perSample != 0. */
+struct OraclePlainImage;
+int oracle_copy_make_border(const struct OraclePlainImage *src, const struct OraclePlainImage *dst, int32_t n,
+                            int32_t elemSize, int32_t channels, const int32_t *top, const int32_t *left, int32_t perSample,
+                            int32_t border, const uint32_t *fill);
+
 #ifdef __cplusplus
 }
 #endif

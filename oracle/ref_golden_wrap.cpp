@@ -253,6 +253,88 @@ int16_t ref_sat_s16_f32(float v)
 }
 }
 
+// tests/cvcuda/system/TestOpCopyMakeBorder.cpp:40-97  CopyMakeBorder<T> (tensor form), cut by signature. It asks the
+// destination's data-access object for its extents and strides: a stand-in answers.
+namespace nvcv {
+struct TensorDataAccessStridedImagePlanar
+{
+    int  samples, rows, cols, channels;
+    long rowBytes, sampleBytes;
+
+    int numSamples() const
+    {
+        return samples;
+    }
+
+    int numRows() const
+    {
+        return rows;
+    }
+
+    int numCols() const
+    {
+        return cols;
+    }
+
+    int numChannels() const
+    {
+        return channels;
+    }
+
+    long rowStride() const
+    {
+        return rowBytes;
+    }
+
+    long sampleStride() const
+    {
+        return sampleBytes;
+    }
+};
+} // namespace nvcv
+
+#include REF_GOLDEN_BORDER_INC
+
+namespace {
+template<typename T>
+void ref_border_t(void *dst, const void *src, int n, int dw, int dh, int sw, int sh, int ch, int top, int left, int border,
+                  const float *value)
+{
+    std::vector<T> hSrc(static_cast<const T *>(src), static_cast<const T *>(src) + static_cast<size_t>(n) * sh * sw * ch);
+    std::vector<T> hDst(static_cast<size_t>(n) * dh * dw * ch);
+    nvcv::TensorDataAccessStridedImagePlanar acc{n, dh, dw, ch, static_cast<long>(dw) * ch * static_cast<long>(sizeof(T)),
+                                                 static_cast<long>(dh) * dw * ch * static_cast<long>(sizeof(T))};
+    CopyMakeBorder<T>(hDst, hSrc, acc, sw, sh, sw * ch, ch, sh * sw * ch, top, left, static_cast<NVCVBorderType>(border),
+                      float4{value[0], value[1], value[2], value[3]});
+    std::memcpy(dst, hDst.data(), hDst.size() * sizeof(T));
+}
+} // namespace
+
+// Packed [n, h, w, ch] tensors; dtype: 0 uint8, 2 uint16, 3 int16, 5 int32, 6 float32.
+extern "C" int ref_copy_make_border(void *dst, const void *src, int n, int dw, int dh, int sw, int sh, int ch, int dtype,
+                                    int top, int left, int border, const float *value)
+{
+    switch (dtype)
+    {
+    case 0:
+        ref_border_t<uint8_t>(dst, src, n, dw, dh, sw, sh, ch, top, left, border, value);
+        return 0;
+    case 2:
+        ref_border_t<uint16_t>(dst, src, n, dw, dh, sw, sh, ch, top, left, border, value);
+        return 0;
+    case 3:
+        ref_border_t<int16_t>(dst, src, n, dw, dh, sw, sh, ch, top, left, border, value);
+        return 0;
+    case 5:
+        ref_border_t<int32_t>(dst, src, n, dw, dh, sw, sh, ch, top, left, border, value);
+        return 0;
+    case 6:
+        ref_border_t<float>(dst, src, n, dw, dh, sw, sh, ch, top, left, border, value);
+        return 0;
+    }
+    return -1;
+}
+
 // tests/cvcuda/system/TestOpNormalize.cpp:34-77  Normalize (uint8 images, float32 base / scale), cut by signature
 #include REF_GOLDEN_NORMALIZE_INC
 

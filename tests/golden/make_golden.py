@@ -104,10 +104,37 @@ def normalize_cases():
     return out
 
 
+def border_cases():
+    """Stand-alone CopyMakeBorder golden (tensor form) on small versions of the reference's table rows plus every
+    border rule on each element type."""
+    out, k = {}, 0
+    rng = np.random.default_rng(77)
+    rows = [(12, 13, 2, 12, 16, 0, 3, 0, (12, 100, 245, 0), np.uint8, 3), (21, 11, 1, 0, 11, 5, 0, 0, (13, 5, 4, 0), np.uint8, 3),
+            (23, 13, 2, 44, 55, 33, 22, 1, (0, 0, 0, 0), np.uint8, 3), (23, 13, 2, 33, 20, 41, 42, 2, (0, 0, 0, 0), np.uint8, 4),
+            (23, 13, 2, 100, 85, 53, 62, 3, (0, 0, 0, 0), np.float32, 3), (24, 12, 2, 56, 123, 77, 98, 4, (0, 0, 0, 0), np.float32, 4)]
+    for dt in (np.uint16, np.int16, np.int32):
+        for border in range(5):
+            rows.append((7, 5, 1, 6, 9, 11, 3, border, (1000, 20000, 300, 7), dt, 1 + border % 4))
+    for (w, h, n, top, bottom, left, right, border, value, dt, ch) in rows:
+        if dt == np.float32:
+            src = (rng.integers(0, 256, (n, h, w, ch)) / 255.0).astype(np.float32)
+        else:
+            info = np.iinfo(dt)
+            src = rng.integers(info.min, int(info.max) + 1, (n, h, w, ch)).astype(dt)
+        out[f"border{k}_src"] = src
+        out[f"border{k}_par"] = np.array([top, bottom, left, right, border], np.int32)
+        out[f"border{k}_val"] = np.array(value, np.float32)
+        out[f"border{k}_ref"] = O.ref_copy_make_border(src, (w + left + right, h + top + bottom), top, left, border, value)
+        k += 1
+    out["border_count"] = np.array(k)
+    return out
+
+
 if __name__ == "__main__":
     assert build_oracle.build_ref() is not None, "reference tree not available"
     np.savez_compressed(os.path.join(HERE, "rccr_golden.npz"), **rccr_cases())
     np.savez_compressed(os.path.join(HERE, "cfnr_golden.npz"), **cfnr_cases())
     np.savez_compressed(os.path.join(HERE, "resize_golden.npz"), **resize_cases())
     np.savez_compressed(os.path.join(HERE, "normalize_golden.npz"), **normalize_cases())
+    np.savez_compressed(os.path.join(HERE, "border_golden.npz"), **border_cases())
     print("written", [f for f in os.listdir(HERE) if f.endswith(".npz")])

@@ -47,6 +47,10 @@ assert C.sizeof(TensorData) == 288 and C.sizeof(ImageBatchData) == 48
 _fake = None
 
 
+class Float4(C.Structure):
+    _fields_ = [("x", C.c_float), ("y", C.c_float), ("z", C.c_float), ("w", C.c_float)]
+
+
 def fake():
     global _fake
     if _fake is None:
@@ -134,6 +138,14 @@ def bind_operators(lib_path: str):
     L.cvcudaConvertToCreate.argtypes = [C.POINTER(H)]
     L.cvcudaConvertToSubmit.restype = C.c_int
     L.cvcudaConvertToSubmit.argtypes = [H, C.c_void_p, H, H, C.c_double, C.c_double]
+    L.cvcudaCopyMakeBorderCreate.restype = C.c_int
+    L.cvcudaCopyMakeBorderCreate.argtypes = [C.POINTER(H)]
+    L.cvcudaCopyMakeBorderSubmit.restype = C.c_int
+    L.cvcudaCopyMakeBorderSubmit.argtypes = [H, C.c_void_p, H, H, C.c_int32, C.c_int32, C.c_int, Float4]
+    for name in ("cvcudaCopyMakeBorderVarShapeSubmit", "cvcudaCopyMakeBorderVarShapeStackSubmit"):
+        f = getattr(L, name)
+        f.restype = C.c_int
+        f.argtypes = [H, C.c_void_p, H, H, H, H, C.c_int, Float4]
     L.cvcudaReformatCreate.restype = C.c_int
     L.cvcudaReformatCreate.argtypes = [C.POINTER(H)]
     L.cvcudaReformatSubmit.restype = C.c_int
