@@ -932,8 +932,8 @@ extern "C" int b200ppCopyMakeBorder(const B200ppImageSet *src, const B200ppImage
     const long long rowBytes = static_cast<long long>(gw) * pixBytes;
     if (rowBytes > 0x7fffffffll)
         return fail(B200PP_ERROR_INVALID_ARGUMENT, "Input or output size exceeds 2147483647. Tensor is too large.");
-    dim3 block(64, 4);
-    dim3 grid(static_cast<unsigned>((rowBytes + 255) / 256), (gh + 4 * kBorderRows - 1) / (4 * kBorderRows),
+    dim3 block(32, 8);
+    dim3 grid(static_cast<unsigned>((rowBytes + 511) / 512), (gh + 8 * kBorderRows - 1) / (8 * kBorderRows),
               std::min(src->numSamples, 65535));
     if (grid.y > 65535u)
         return fail(B200PP_ERROR_INVALID_ARGUMENT, "Input or output tensors are too large");
