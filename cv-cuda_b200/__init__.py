@@ -33,7 +33,11 @@ from .ops import (  # noqa: F401
     read_device_error,
     reformat,
     reformat_into,
+    random_crop_rects,
+    random_resized_crop,
+    random_resized_crop_into,
     resize,
+    resized_crop_into,
     resize_into,
     resize_crop_convert_reformat,
     resize_crop_convert_reformat_into,

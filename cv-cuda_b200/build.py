@@ -16,7 +16,7 @@ CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libcvcuda_b200.so")
 
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
-SOURCES = ["library.cu", "cvcuda_ops.cpp"]
+SOURCES = ["library.cu", "cvcuda_ops.cpp", "random_crop.cpp"]
 
 
 def _stale() -> bool:

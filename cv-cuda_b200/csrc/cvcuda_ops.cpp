@@ -39,6 +39,10 @@ struct NvcvApi
     NVCVStatus (*imageFormatGetNumChannels)(NVCVImageFormat, int32_t *)                     = nullptr;
     NVCVStatus (*imageFormatGetNumPlanes)(NVCVImageFormat, int32_t *)                       = nullptr;
     void (*setThreadStatus)(NVCVStatus, const char *, ...)                                  = nullptr;
+    // per-image sizes of a variable-shape batch on the host (RandomResizedCrop draws its rectangles from them)
+    NVCVStatus (*imageBatchVarShapeGetImages)(NVCVImageBatchHandle, int32_t, NVCVImageHandle *, int32_t) = nullptr;
+    NVCVStatus (*imageGetSize)(NVCVImageHandle, int32_t *, int32_t *)                       = nullptr;
+    NVCVStatus (*imageDecRef)(NVCVImageHandle, int *)                                       = nullptr;
     bool ok                                                                                 = false;
 };
 
@@ -67,6 +71,9 @@ const NvcvApi &nvcv()
         B200_BIND(imageFormatGetNumChannels, "nvcvImageFormatGetNumChannels");
         B200_BIND(imageFormatGetNumPlanes, "nvcvImageFormatGetNumPlanes");
         B200_BIND(setThreadStatus, "nvcvSetThreadStatus");
+        B200_BIND(imageBatchVarShapeGetImages, "nvcvImageBatchVarShapeGetImages");
+        B200_BIND(imageGetSize, "nvcvImageGetSize");
+        B200_BIND(imageDecRef, "nvcvImageDecRef");
 #undef B200_BIND
         api.ok = api.tensorExportData && api.imageBatchExportData && api.dataTypeGetDataKind
               && api.dataTypeGetBitsPerChannel && api.imageFormatGetDataKind && api.imageFormatGetBitsPerChannel
@@ -108,7 +115,8 @@ enum OpKind
     OP_NORMALIZE                    = 4,
     OP_REFORMAT                     = 5,
     OP_CONVERT_TO                   = 6,
-    OP_COPY_MAKE_BORDER             = 7
+    OP_COPY_MAKE_BORDER             = 7,
+    OP_RANDOM_RESIZED_CROP          = 8
 };
 
 // The handle is the object pointer itself, as in the reference (src/cvcuda/priv/IOperator.hpp:37-40). Operators hold
@@ -117,6 +125,12 @@ struct Operator
 {
     uint64_t magic;
     int      kind;
+    // RandomResizedCrop only (the one operator with state: its generator advances with every call, as in the
+    // reference; calls on one such handle must not overlap)
+    B200ppRandomCrop *generator   = nullptr;
+    int32_t          *rectsDevice = nullptr;
+    int32_t          *rectsHost   = nullptr;
+    int               maxBatch    = 0;
 };
 
 NVCVStatus create(NVCVOperatorHandle *handle, int kind)
@@ -789,7 +803,150 @@ NVCVStatus border_varshape(NVCVOperatorHandle handle, cudaStream_t stream, NVCVI
     return forward(b200ppCopyMakeBorder(&s, &d, 0, 0, topPtr, leftPtr, borderMode, v, stream));
 }
 
+// ---------------------------------------------------------------------------------------------- RandomResizedCrop
+
+NVCVStatus random_crop_create(NVCVOperatorHandle *handle, double minScale, double maxScale, double minRatio, double maxRatio,
+                              int32_t maxBatch, uint32_t seed)
+{
+    if (handle == nullptr)
+        return report(B200PP_ERROR_INVALID_ARGUMENT, "Pointer to NVCVOperator handle must not be NULL");
+    // src/cvcuda/priv/legacy/random_resized_crop.cu:300-304
+    if (minScale > maxScale || minRatio > maxRatio)
+        return report(B200PP_ERROR_INVALID_ARGUMENT, "Invalid Parameter: scale and ratio should be of kind (min, max)");
+    Operator *op = new (std::nothrow) Operator{kMagic, OP_RANDOM_RESIZED_CROP};
+    if (!op)
+        return report(7 /* NVCV_ERROR_OUT_OF_MEMORY */, "Not enough memory to create the operator");
+    op->maxBatch = maxBatch > 0 ? maxBatch : 0;
+    int st       = b200ppRandomCropCreate(&op->generator, minScale, maxScale, minRatio, maxRatio, seed);
+    if (st == B200PP_SUCCESS && op->maxBatch > 0)
+    {
+        op->rectsHost = new (std::nothrow) int32_t[4 * static_cast<size_t>(op->maxBatch)];
+        st            = op->rectsHost ? b200ppParamBufferCreate(reinterpret_cast<void **>(&op->rectsDevice),
+                                                                16 * static_cast<size_t>(op->maxBatch))
+                                      : B200PP_ERROR_INTERNAL;
+    }
+    if (st != B200PP_SUCCESS)
+    {
+        nvcvOperatorDestroy(reinterpret_cast<NVCVOperatorHandle>(op));
+        return report(st, "Cannot create the RandomResizedCrop operator: %s", b200ppGetLastErrorMessage());
+    }
+    *handle = reinterpret_cast<NVCVOperatorHandle>(op);
+    return B200PP_SUCCESS;
+}
+
+// Checks shared by both forms, in the reference's order (random_resized_crop.cu:410-436): channel count, element
+// type, equal types, interpolation.
+NVCVStatus random_crop_checks(const B200ppImageSet &s, const B200ppImageSet &d, int interp)
+{
+    if (s.channels > 4)
+        return report(B200PP_ERROR_INVALID_ARGUMENT, "Invalid channel number %d", s.channels);
+    if (!(s.dtype == B200PP_U8 || s.dtype == B200PP_U16 || s.dtype == B200PP_S16 || s.dtype == B200PP_F32))
+        return report(B200PP_ERROR_INVALID_ARGUMENT, "Invalid DataType");
+    if (s.dtype != d.dtype)
+        return report(B200PP_ERROR_INVALID_ARGUMENT, "DataType of input and output must be equal");
+    if (interp == 2 /* NVCV_INTERP_CUBIC */)
+        return report(B200PP_ERROR_NOT_IMPLEMENTED, "Interpolation not implemented: NVCV_INTERP_CUBIC");
+    if (interp != B200PP_INTERP_NEAREST && interp != B200PP_INTERP_LINEAR)
+        return report(B200PP_ERROR_INVALID_ARGUMENT, "Invalid interpolation %d", interp);
+    return B200PP_SUCCESS;
+}
+
+NVCVStatus random_crop_launch(Operator *op, cudaStream_t stream, const B200ppImageSet &s, const B200ppImageSet &d, int interp)
+{
+    if (int st = b200ppParamBufferUpload(op->rectsDevice, op->rectsHost, 16 * static_cast<size_t>(s.numSamples), stream))
+        return forward(st);
+    return forward(b200ppResizedCrop(&s, &d, op->rectsDevice, interp, stream));
+}
+
+NVCVStatus random_crop_tensor(NVCVOperatorHandle handle, cudaStream_t stream, NVCVTensorHandle in, NVCVTensorHandle out,
+                              int interp)
+{
+    if (NVCVStatus st = check_handle(handle, OP_RANDOM_RESIZED_CROP))
+        return st;
+    if (!nvcv().ok)
+        return report(B200PP_ERROR_INTERNAL, "libnvcv_types is not loaded in this process");
+    Operator  *op = reinterpret_cast<Operator *>(handle);
+    NVCVStatus st = B200PP_SUCCESS;
+    ImageView  i, o;
+    if (!export_tensor(in, i, "Input", st) || !export_tensor(out, o, "Output", st))
+        return st;
+    // random_resized_crop.cu:395-408
+    if (std::strcmp(i.layout, o.layout) != 0)
+        return report(B200PP_ERROR_INVALID_ARGUMENT, "Invalid DataFormat between input (%s) and output (%s)", i.layout, o.layout);
+    if (!layout_is(i, "HWC", "NHWC") || !i.valid || !o.valid)
+        return report(B200PP_ERROR_INVALID_ARGUMENT, "Invalid input DataFormat %s, the valid DataFormats are: \"NHWC\", \"HWC\"",
+                      i.layout);
+    B200ppImageSet s, d;
+    image_set_from_view(i, s);
+    image_set_from_view(o, d);
+    if ((st = random_crop_checks(s, d, interp)))
+        return st;
+    if (s.numSamples > op->maxBatch)
+        return report(B200PP_ERROR_INVALID_ARGUMENT, "Batch of %d images exceeds the operator's maxBatchSize %d", s.numSamples,
+                      op->maxBatch);
+    for (int k = 0; k < s.numSamples; ++k)
+        if (b200ppRandomCropNext(op->generator, s.height, s.width, op->rectsHost + 4 * k) != B200PP_SUCCESS)
+            return report(B200PP_ERROR_INVALID_ARGUMENT, "Invalid input size %dx%d", s.width, s.height);
+    return random_crop_launch(op, stream, s, d, interp);
+}
+
+NVCVStatus random_crop_varshape(NVCVOperatorHandle handle, cudaStream_t stream, NVCVImageBatchHandle in,
+                                NVCVImageBatchHandle out, int interp)
+{
+    if (NVCVStatus st = check_handle(handle, OP_RANDOM_RESIZED_CROP))
+        return st;
+    if (!nvcv().ok)
+        return report(B200PP_ERROR_INTERNAL, "libnvcv_types is not loaded in this process");
+    if (!nvcv().imageBatchVarShapeGetImages || !nvcv().imageGetSize)
+        return report(B200PP_ERROR_INTERNAL, "libnvcv_types lacks nvcvImageBatchVarShapeGetImages / nvcvImageGetSize");
+    Operator      *op = reinterpret_cast<Operator *>(handle);
+    NVCVStatus     st = B200PP_SUCCESS;
+    B200ppImageSet s, d;
+    if (!image_set_from_batch(in, stream, "Input", s, st) || !image_set_from_batch(out, stream, "Output", d, st))
+        return st;
+    if ((st = random_crop_checks(s, d, interp)))
+        return st;
+    if (s.numSamples != d.numSamples)
+        return report(B200PP_ERROR_INVALID_ARGUMENT, "Input and output samples are different");
+    if (s.numSamples > op->maxBatch)
+        return report(B200PP_ERROR_INVALID_ARGUMENT, "Batch of %d images exceeds the operator's maxBatchSize %d", s.numSamples,
+                      op->maxBatch);
+    // one rectangle per image from that image's own size (random_resized_crop_var_shape.cu:366-380)
+    for (int k = 0; k < s.numSamples; ++k)
+    {
+        NVCVImageHandle image = nullptr;
+        int32_t         w = 0, h = 0;
+        if (nvcv().imageBatchVarShapeGetImages(in, k, &image, 1) != B200PP_SUCCESS || image == nullptr)
+            return report(B200PP_ERROR_INVALID_ARGUMENT, "Cannot access image %d of the input batch", k);
+        const NVCVStatus sizeStatus = nvcv().imageGetSize(image, &w, &h);
+        if (nvcv().imageDecRef)
+            nvcv().imageDecRef(image, nullptr);
+        if (sizeStatus != B200PP_SUCCESS || b200ppRandomCropNext(op->generator, h, w, op->rectsHost + 4 * k) != B200PP_SUCCESS)
+            return report(B200PP_ERROR_INVALID_ARGUMENT, "Invalid size of input image %d", k);
+    }
+    return random_crop_launch(op, stream, s, d, interp);
+}
+
 // ================================================================================================ exported symbols
+
+extern "C" NVCVStatus cvcudaRandomResizedCropCreate(NVCVOperatorHandle *handle, double minScale, double maxScale,
+                                                    double minRatio, double maxRatio, int32_t maxBatchSize, uint32_t seed)
+{
+    return random_crop_create(handle, minScale, maxScale, minRatio, maxRatio, maxBatchSize, seed);
+}
+
+extern "C" NVCVStatus cvcudaRandomResizedCropSubmit(NVCVOperatorHandle handle, cudaStream_t stream, NVCVTensorHandle in,
+                                                    NVCVTensorHandle out, const NVCVInterpolationType interpolation)
+{
+    return random_crop_tensor(handle, stream, in, out, static_cast<int>(interpolation));
+}
+
+extern "C" NVCVStatus cvcudaRandomResizedCropVarShapeSubmit(NVCVOperatorHandle handle, cudaStream_t stream,
+                                                            NVCVImageBatchHandle in, NVCVImageBatchHandle out,
+                                                            const NVCVInterpolationType interpolation)
+{
+    return random_crop_varshape(handle, stream, in, out, static_cast<int>(interpolation));
+}
 
 extern "C" NVCVStatus cvcudaCopyMakeBorderCreate(NVCVOperatorHandle *handle)
 {
@@ -895,6 +1052,9 @@ extern "C" void nvcvOperatorDestroy(NVCVOperatorHandle handle)
     if (op && op->magic == kMagic)
     {
         op->magic = 0;
+        b200ppRandomCropDestroy(op->generator);
+        b200ppParamBufferDestroy(op->rectsDevice);
+        delete[] op->rectsHost;
         delete op;
     }
 }

@@ -588,10 +588,13 @@ static PlainSide plain_side(const B200ppImageSet *s)
 
 } // namespace b200pp
 
-extern "C" int b200ppResize(const B200ppImageSet *src, const B200ppImageSet *dst, int32_t interp, cudaStream_t stream)
+static int resize_common(const B200ppImageSet *src, const B200ppImageSet *dst, int32_t interp, const int32_t *cropRects,
+                         cudaStream_t stream)
 {
     if (!src || !dst)
         return fail(B200PP_ERROR_INVALID_ARGUMENT, "Null argument");
+    if (reinterpret_cast<uintptr_t>(cropRects) & 15)
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "Crop rectangles must be packed int32 x 4 on a 16-byte boundary");
     // Checks, order and status codes of the reference operator (src/cvcuda/priv/OpResize.cu:501-555, :455-486).
     if (src->dtype != dst->dtype)
         return fail(B200PP_ERROR_INVALID_ARGUMENT, "Input and output data type are different");
@@ -623,6 +626,7 @@ extern "C" int b200ppResize(const B200ppImageSet *src, const B200ppImageSet *dst
     kp.src        = plain_side(src);
     kp.dst        = plain_side(dst);
     kp.numSamples = src->numSamples;
+    kp.cropRects  = cropRects;
     const int gw = dst->imageList ? dst->maxWidth : dst->width, gh = dst->imageList ? dst->maxHeight : dst->height;
     if (gw < 1 || gh < 1)
         return fail(B200PP_ERROR_INVALID_ARGUMENT, "Output image list needs its maximum width and height");
@@ -647,6 +651,19 @@ extern "C" int b200ppResize(const B200ppImageSet *src, const B200ppImageSet *dst
         break;
     }
     return check_launch("Resize");
+}
+
+extern "C" int b200ppResize(const B200ppImageSet *src, const B200ppImageSet *dst, int32_t interp, cudaStream_t stream)
+{
+    return resize_common(src, dst, interp, nullptr, stream);
+}
+
+extern "C" int b200ppResizedCrop(const B200ppImageSet *src, const B200ppImageSet *dst, const int32_t *cropRects,
+                                 int32_t interp, cudaStream_t stream)
+{
+    if (!cropRects)
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "Null crop rectangles");
+    return resize_common(src, dst, interp, cropRects, stream);
 }
 
 // ================================================================================================ stand-alone Normalize
@@ -965,6 +982,42 @@ extern "C" int b200ppCopyMakeBorder(const B200ppImageSet *src, const B200ppImage
         break;
     }
     return check_launch("CopyMakeBorder");
+}
+
+// Device parameter buffers of operator objects that draw per-sample parameters on the host (RandomResizedCrop): the
+// handle layer (cvcuda_ops.cpp) does not include the CUDA runtime, so allocation and upload live here.
+extern "C" int b200ppParamBufferCreate(void **dev, size_t bytes)
+{
+    if (!dev)
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "Null argument");
+    *dev = nullptr;
+    if (bytes == 0)
+        return B200PP_SUCCESS;
+    if (cudaMalloc(dev, bytes) != cudaSuccess)
+    {
+        cudaGetLastError();
+        return fail(B200PP_ERROR_INTERNAL, "Cannot allocate %zu bytes of device memory for operator parameters", bytes);
+    }
+    return B200PP_SUCCESS;
+}
+
+extern "C" void b200ppParamBufferDestroy(void *dev)
+{
+    if (dev)
+        cudaFree(dev);
+}
+
+// Copy from pageable host memory: the runtime stages it before returning, so the caller may reuse `host` at once.
+extern "C" int b200ppParamBufferUpload(void *dev, const void *host, size_t bytes, cudaStream_t stream)
+{
+    if (bytes == 0)
+        return B200PP_SUCCESS;
+    if (!dev || !host)
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "Null argument");
+    const cudaError_t e = cudaMemcpyAsync(dev, host, bytes, cudaMemcpyHostToDevice, stream);
+    if (e != cudaSuccess)
+        return fail(B200PP_ERROR_INTERNAL, "Parameter upload failed: %s", cudaGetErrorString(e));
+    return B200PP_SUCCESS;
 }
 
 extern "C" const char *b200ppGetLastErrorMessage(void)

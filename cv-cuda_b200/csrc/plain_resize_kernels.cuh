@@ -30,8 +30,9 @@ struct PlainSide
 
 struct PlainResizeKParams
 {
-    PlainSide src, dst;
-    int       numSamples;
+    PlainSide  src, dst;
+    int        numSamples;
+    const int *cropRects; // device, (left, top, width, height) per sample: the golden's crop arguments; null = whole images
 };
 
 struct PlainView
@@ -188,9 +189,10 @@ __device__ __forceinline__ T blend_exact(T p00, T p10, T p01, T p11, double wy0,
 
 // The golden's linear tap along one axis (ResizeUtils.cpp:224-234): first tap index (clamped), second tap index, and
 // the weight of the second tap, in double precision.
-__device__ __forceinline__ void linear_tap_exact(float scale, int d, int size, int &s0, int &s1, double &w1)
+__device__ __forceinline__ void linear_tap_exact(float scale, int d, int size, int origin, int &s0, int &s1, double &w1)
 {
-    double f = __dsub_rn(__dmul_rn(static_cast<double>(scale), __dadd_rn(static_cast<double>(d), 0.5)), 0.5);
+    double f = __dadd_rn(__dsub_rn(__dmul_rn(static_cast<double>(scale), __dadd_rn(static_cast<double>(d), 0.5)), 0.5),
+                         static_cast<double>(origin));
     int    s = __double2int_rd(f);
     w1       = (s < 0) ? 0.0 : ((s > size - 2) ? 1.0 : __dsub_rn(f, static_cast<double>(s)));
     s0       = max(0, min(s, size - 2));
@@ -212,8 +214,15 @@ __global__ void __launch_bounds__(256, INTERP == B200PP_INTERP_LINEAR && sizeof(
         if (dx0 >= D.w || dy0 >= D.h || S.w < 1 || S.h < 1)
             continue;
         // float scale factors, as the golden computes them (ResizeUtils.cpp:193-194)
-        const float scaleW = __fdiv_rn(static_cast<float>(S.w), static_cast<float>(D.w));
-        const float scaleH = __fdiv_rn(static_cast<float>(S.h), static_cast<float>(D.h));
+        // over the crop rectangle when there is one (:190-194); taps clamp at the image's edges either way
+        int left = 0, top = 0, cropW = S.w, cropH = S.h;
+        if (p.cropRects)
+        {
+            const int4 r = *reinterpret_cast<const int4 *>(p.cropRects + 4 * n);
+            left = r.x, top = r.y, cropW = r.z, cropH = r.w;
+        }
+        const float scaleW = __fdiv_rn(static_cast<float>(cropW), static_cast<float>(D.w));
+        const float scaleH = __fdiv_rn(static_cast<float>(cropH), static_cast<float>(D.h));
         // whole-pixel vector accesses when every address involved is a multiple of the pixel size
         const bool vector = C != 3
                          && ((reinterpret_cast<unsigned long long>(S.base) | reinterpret_cast<unsigned long long>(D.base)
@@ -233,13 +242,14 @@ __global__ void __launch_bounds__(256, INTERP == B200PP_INTERP_LINEAR && sizeof(
             if constexpr (INTERP == B200PP_INTERP_NEAREST)
             {
                 // :204-220, float arithmetic
-                off0[k] = max(min(__float2int_rd(__fmul_rn(scaleW, __fadd_rn(static_cast<float>(dx), 0.5f))), S.w - 1), 0) * kPix;
+                const float fx = __fadd_rn(__fmul_rn(scaleW, __fadd_rn(static_cast<float>(dx), 0.5f)), static_cast<float>(left));
+                off0[k]        = max(min(__float2int_rd(fx), S.w - 1), 0) * kPix;
             }
             else
             {
                 int    s0, s1;
                 double w1;
-                linear_tap_exact(scaleW, dx, S.w, s0, s1, w1);
+                linear_tap_exact(scaleW, dx, S.w, left, s0, s1, w1);
                 off0[k] = s0 * kPix;
                 off1[k] = s1 * kPix;
                 if constexpr (kFast)
@@ -263,7 +273,8 @@ __global__ void __launch_bounds__(256, INTERP == B200PP_INTERP_LINEAR && sizeof(
             uint8_t *drow = D.base + dy * D.pitch;
             if constexpr (INTERP == B200PP_INTERP_NEAREST)
             {
-                const int sy = max(min(__float2int_rd(__fmul_rn(scaleH, __fadd_rn(static_cast<float>(dy), 0.5f))), S.h - 1), 0);
+                const float fy = __fadd_rn(__fmul_rn(scaleH, __fadd_rn(static_cast<float>(dy), 0.5f)), static_cast<float>(top));
+                const int   sy = max(min(__float2int_rd(fy), S.h - 1), 0);
                 const uint8_t   *srow = S.base + sy * S.pitch;
                 PlainPixel<T, C> px[kPlainCols];
 #pragma unroll
@@ -278,7 +289,7 @@ __global__ void __launch_bounds__(256, INTERP == B200PP_INTERP_LINEAR && sizeof(
                 // :222-241: products and sum in double precision, left to right
                 int    sy, sy1;
                 double fy;
-                linear_tap_exact(scaleH, dy, S.h, sy, sy1, fy);
+                linear_tap_exact(scaleH, dy, S.h, top, sy, sy1, fy);
                 const double   wy0 = __dsub_rn(1.0, fy);
                 const uint8_t *r0 = S.base + sy * S.pitch, *r1 = S.base + sy1 * S.pitch;
 
@@ -325,7 +336,7 @@ __global__ void __launch_bounds__(256, INTERP == B200PP_INTERP_LINEAR && sizeof(
                                 asm volatile("" ::: "memory");
                                 int    s0, s1;
                                 double w1;
-                                linear_tap_exact(scaleW, min(dx0 + 32 * k, D.w - 1), S.w, s0, s1, w1);
+                                linear_tap_exact(scaleW, min(dx0 + 32 * k, D.w - 1), S.w, left, s0, s1, w1);
                                 u[c] = blend_exact<uint8_t>((q00[k] >> (8 * c)) & 0xffu, (q10[k] >> (8 * c)) & 0xffu,
                                                             (q01[k] >> (8 * c)) & 0xffu, (q11[k] >> (8 * c)) & 0xffu, wy0, fy,
                                                             __dsub_rn(1.0, w1), w1);

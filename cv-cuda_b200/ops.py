@@ -11,7 +11,7 @@ from __future__ import annotations
 import ctypes as C
 import enum
 import os
-from typing import NamedTuple, Optional, Sequence, Tuple, Union
+from typing import List, NamedTuple, Optional, Sequence, Tuple, Union
 
 import numpy as np
 import torch
@@ -172,6 +172,14 @@ def lib() -> C.CDLL:
         L.b200ppNormalize.argtypes = [C.POINTER(_ImageSet), C.POINTER(_ImageSet), C.POINTER(_NormalizeOp), C.c_void_p]
         L.b200ppReformat.restype = C.c_int
         L.b200ppReformat.argtypes = [C.POINTER(_Dest), C.POINTER(_Dest), C.c_int32, C.c_void_p]
+        L.b200ppRandomCropCreate.restype = C.c_int
+        L.b200ppRandomCropCreate.argtypes = [C.POINTER(C.c_void_p), C.c_double, C.c_double, C.c_double, C.c_double, C.c_uint32]
+        L.b200ppRandomCropDestroy.restype = None
+        L.b200ppRandomCropDestroy.argtypes = [C.c_void_p]
+        L.b200ppRandomCropNext.restype = C.c_int
+        L.b200ppRandomCropNext.argtypes = [C.c_void_p, C.c_int32, C.c_int32, C.POINTER(C.c_int32)]
+        L.b200ppResizedCrop.restype = C.c_int
+        L.b200ppResizedCrop.argtypes = [C.POINTER(_ImageSet), C.POINTER(_ImageSet), C.c_void_p, C.c_int32, C.c_void_p]
         L.b200ppCopyMakeBorder.restype = C.c_int
         L.b200ppCopyMakeBorder.argtypes = [C.POINTER(_ImageSet), C.POINTER(_ImageSet), C.c_int32, C.c_int32, C.c_void_p,
                                            C.c_void_p, C.c_int32, C.POINTER(C.c_float), C.c_void_p]
@@ -566,6 +574,84 @@ def _image_set(x: Union[torch.Tensor, ImageBatchVarShape], what: str):
     s.rowStride = x.stride(-3) * es
     s.sampleStride = x.stride(0) * es if x.dim() == 4 else 0
     return s, x
+
+
+def resized_crop_into(dst: Union[torch.Tensor, ImageBatchVarShape], src: Union[torch.Tensor, ImageBatchVarShape],
+                      rects: torch.Tensor, interp: Interp = Interp.LINEAR, *, stream=None):
+    """Every image of ``src`` cropped to its rectangle and resized to the size of the corresponding image of ``dst``:
+    ``rects`` is an int32 CUDA tensor [N, 4] of (left, top, width, height). The resampling step of
+    cvcuda.random_resized_crop with caller-chosen rectangles (the reference draws them inside the operator,
+    src/cvcuda/priv/legacy/random_resized_crop.cu:459-467)."""
+    if isinstance(src, ImageBatchVarShape) != isinstance(dst, ImageBatchVarShape):
+        raise Error(Status.ERROR_INVALID_ARGUMENT, "Input and output must both be tensors or both be image batches")
+    if not isinstance(src, ImageBatchVarShape) and src.dim() != dst.dim():
+        raise Error(Status.ERROR_INVALID_ARGUMENT, "Input and output data layout are different")
+    s, keep_s = _image_set(src, "Input")
+    d, keep_d = _image_set(dst, "Output")
+    if not isinstance(rects, torch.Tensor) or not rects.is_cuda or rects.dtype != torch.int32 or not rects.is_contiguous() \
+            or rects.numel() != 4 * s.numSamples:
+        raise Error(Status.ERROR_INVALID_ARGUMENT, "rects must be a contiguous int32 CUDA tensor [N, 4]")
+    if s.numSamples == 0:
+        return dst
+    _check(lib().b200ppResizedCrop(C.byref(s), C.byref(d), rects.data_ptr(), int(interp), _stream_handle(stream)))
+    return dst
+
+
+def random_crop_rects(sizes: Sequence[Tuple[int, int]], min_scale: float = 0.08, max_scale: float = 1.0,
+                      min_ratio: float = 0.75, max_ratio: float = 1.3333333333333333, seed: int = 0) -> List[Tuple[int, int, int, int]]:
+    """The crop rectangles (left, top, width, height) the reference's RandomResizedCrop operator draws for images of the
+    given (width, height) sizes, in order, from a fresh generator (src/cvcuda/priv/legacy/random_resized_crop.cu:336-390;
+    seed 0 = a random seed, as there)."""
+    gen = C.c_void_p()
+    status = lib().b200ppRandomCropCreate(C.byref(gen), float(min_scale), float(max_scale), float(min_ratio),
+                                          float(max_ratio), int(seed) & 0xFFFFFFFF)
+    if status != 0:
+        raise Error(Status(status), "Invalid Parameter: scale and ratio should be of kind (min, max)")
+    try:
+        out, rect = [], (C.c_int32 * 4)()
+        for (w, h) in sizes:
+            if lib().b200ppRandomCropNext(gen, int(h), int(w), rect) != 0:
+                raise Error(Status.ERROR_INVALID_ARGUMENT, f"Invalid image size {w}x{h}")
+            out.append(tuple(rect))
+        return out
+    finally:
+        lib().b200ppRandomCropDestroy(gen)
+
+
+def random_resized_crop_into(dst, src, min_scale: float = 0.08, max_scale: float = 1.0, min_ratio: float = 0.75,
+                             max_ratio: float = 1.3333333333333333, interp: Interp = Interp.LINEAR, seed: int = 0, *,
+                             stream=None):
+    """cvcuda.random_resized_crop_into for tensors and image batches (python/mod_cvcuda/OpRandomResizedCrop.cpp:29-52,
+    :65-88): like the reference, every call builds a fresh generator from ``seed`` and draws one rectangle per image."""
+    if int(interp) == 2:
+        raise Error(Status.ERROR_NOT_IMPLEMENTED, "Interpolation not implemented: NVCV_INTERP_CUBIC")
+    if int(interp) not in (0, 1):
+        raise Error(Status.ERROR_INVALID_ARGUMENT, f"Invalid interpolation {int(interp)}")
+    if isinstance(src, ImageBatchVarShape):
+        sizes = [(im.shape[1], im.shape[0]) for im in src._images]
+    else:
+        if src.dim() not in (3, 4):
+            raise Error(Status.ERROR_INVALID_ARGUMENT, "Input must have (N)HWC layout")
+        sizes = [(src.shape[-2], src.shape[-3])] * (src.shape[0] if src.dim() == 4 else 1)
+    rects = random_crop_rects(sizes, min_scale, max_scale, min_ratio, max_ratio, seed)
+    dev = src.device if isinstance(src, ImageBatchVarShape) or src.is_cuda else torch.device("cuda", torch.cuda.current_device())
+    table = torch.tensor(rects, dtype=torch.int32).reshape(-1, 4).to(dev)
+    return resized_crop_into(dst, src, table, interp, stream=stream)
+
+
+def random_resized_crop(src, shape_or_sizes, min_scale: float = 0.08, max_scale: float = 1.0, min_ratio: float = 0.75,
+                        max_ratio: float = 1.3333333333333333, interp: Interp = Interp.LINEAR, seed: int = 0, *, stream=None):
+    """cvcuda.random_resized_crop: allocates the output ((N)HWC shape for a tensor, (width, height) per image for a batch)."""
+    if isinstance(src, ImageBatchVarShape):
+        sizes = list(shape_or_sizes)
+        if len(sizes) != len(src):
+            raise Error(Status.ERROR_INVALID_ARGUMENT, "Invalid outputs sizes, must be equal to input batch size")
+        out = ImageBatchVarShape([torch.empty((int(h), int(w), src.channels), dtype=src.dtype, device=src.device)
+                                  for (w, h) in sizes])
+    else:
+        dev = src.device if src.is_cuda else torch.device("cuda", torch.cuda.current_device())
+        out = torch.empty(tuple(int(v) for v in shape_or_sizes), dtype=src.dtype, device=dev)
+    return random_resized_crop_into(out, src, min_scale, max_scale, min_ratio, max_ratio, interp, seed, stream=stream)
 
 
 def resize_into(dst: Union[torch.Tensor, ImageBatchVarShape], src: Union[torch.Tensor, ImageBatchVarShape],

@@ -24,7 +24,7 @@ INV_STD = tuple(float(np.float32(1.0) / np.float32(s)) for s in (58.395, 57.12, 
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--case", default="classify", choices=("classify", "classify-nhwc-u8", "classify-nhwc-f32", "classify-nhwc-u8-nearest", "4k", "4k-nearest", "letterbox", "cfnr", "varshape", "resize-rgba", "resize-rgba-nearest", "resize-rgb", "normalize-rgba", "normalize-rgb-f32", "reformat-u8", "reformat-f32", "convertto-u8-f32", "convertto-f32-u8", "border-rgb", "border-rgb-reflect", "border-rgba-f32"))
+    ap.add_argument("--case", default="classify", choices=("classify", "classify-nhwc-u8", "classify-nhwc-f32", "classify-nhwc-u8-nearest", "4k", "4k-nearest", "letterbox", "cfnr", "varshape", "resize-rgba", "resize-rgba-nearest", "resize-rgb", "normalize-rgba", "normalize-rgb-f32", "reformat-u8", "reformat-f32", "convertto-u8-f32", "convertto-f32-u8", "border-rgb", "border-rgb-reflect", "border-rgba-f32", "rrc-rgb", "rrc-rgb-nearest"))
     ap.add_argument("--images", type=int, default=32)
     ap.add_argument("--path", type=int, default=0)
     ap.add_argument("--launches", type=int, default=5)
@@ -131,6 +131,20 @@ def main():
 
         def run():
             pkg.copymakeborder_into(out, src, mode, (114.0, 114.0, 114.0, 0.0), top=32, left=32)
+    elif a.case.startswith("rrc-"):
+        # RandomResizedCrop with the reference's default limits (scale 0.08..1, ratio 3/4..4/3), seed 1: 1080x1920 RGB
+        # -> 224x224; the rectangles are drawn once, the timed call is the resized-crop launch the operator makes
+        src = torch.randint(0, 256, (n, 1080, 1920, 3), dtype=torch.uint8, device="cuda", generator=g)
+        out = torch.empty((n, 224, 224, 3), dtype=torch.uint8, device="cuda")
+        rects = pkg.random_crop_rects([(1920, 1080)] * n, seed=1)
+        table = torch.tensor(rects, dtype=torch.int32, device="cuda")
+        interp = 0 if a.case.endswith("nearest") else 1
+        tapped = sum((min(h, 224) * (2 - (interp == 0))) * w * 3 for (_, _, w, h) in rects)
+        print(f"random_resized_crop: crop area {sum(w * h for (_, _, w, h) in rects) * 3 / 1e6:.1f} MB, "
+              f"rows tapped about {tapped / 1e6:.1f} MB, output {out.numel() / 1e6:.1f} MB")
+
+        def run():
+            pkg.resized_crop_into(out, src, table, interp)
     elif a.case == "cfnr":
         # CropFlipNormalizeReformat on the reference benchmark's image size (bench/BenchCropFlipNormalizeReformat.cpp:
         # 1080x1920, crop = full image, flip both axes), here 3-channel uint8 -> float32 NCHW with per-channel constants

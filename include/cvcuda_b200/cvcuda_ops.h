@@ -35,6 +35,7 @@ typedef int NVCVStatus; /* values: B200PP_* of preproc.h = NVCVStatus of nvcv/St
 typedef struct NVCVOperator   *NVCVOperatorHandle;   /* cvcuda/Operator.h:34 */
 typedef struct NVCVTensor     *NVCVTensorHandle;     /* nvcv/Tensor.h:43 */
 typedef struct NVCVImageBatch *NVCVImageBatchHandle; /* nvcv/ImageBatch.h:54 */
+typedef struct NVCVImage      *NVCVImageHandle;      /* nvcv/Image.h */
 
 typedef struct NVCVSize2D /* nvcv/Size.h:33-36 */
 {
@@ -202,6 +203,23 @@ B200PP_PUBLIC NVCVStatus cvcudaCopyMakeBorderVarShapeStackSubmit(NVCVOperatorHan
                                                                  NVCVImageBatchHandle in, NVCVTensorHandle out,
                                                                  NVCVTensorHandle top, NVCVTensorHandle left,
                                                                  NVCVBorderType borderMode, const float4 borderValue);
+
+/* RandomResizedCrop: one random crop rectangle per image (area fraction in [minScale, maxScale], aspect ratio
+ * log-uniform in [minRatio, maxRatio], drawn from a std::mt19937 seeded with `seed`, 0 = random seed) resized to the
+ * output's size, nearest or linear (cubic: NVCV_ERROR_NOT_IMPLEMENTED). The handle owns the generator and a device
+ * parameter buffer for maxBatchSize images; calls on one handle must not overlap. Replace cvcudaRandomResizedCropCreate /
+ * cvcudaRandomResizedCropSubmit / cvcudaRandomResizedCropVarShapeSubmit (reference: src/cvcuda/OpRandomResizedCrop.cpp:29-70,
+ * declared in src/cvcuda/include/cvcuda/OpRandomResizedCrop.h). The variable-shape form asks the object-model library for
+ * each input image's size (nvcvImageBatchVarShapeGetImages, nvcvImageGetSize), as the reference does through
+ * ImageBatchVarShape::operator[]. */
+B200PP_PUBLIC NVCVStatus cvcudaRandomResizedCropCreate(NVCVOperatorHandle *handle, double minScale, double maxScale,
+                                                       double minRatio, double maxRatio, int32_t maxBatchSize,
+                                                       uint32_t seed);
+B200PP_PUBLIC NVCVStatus cvcudaRandomResizedCropSubmit(NVCVOperatorHandle handle, cudaStream_t stream, NVCVTensorHandle in,
+                                                       NVCVTensorHandle out, const NVCVInterpolationType interpolation);
+B200PP_PUBLIC NVCVStatus cvcudaRandomResizedCropVarShapeSubmit(NVCVOperatorHandle handle, cudaStream_t stream,
+                                                               NVCVImageBatchHandle in, NVCVImageBatchHandle out,
+                                                               const NVCVInterpolationType interpolation);
 
 /* Additions (no counterpart in the reference): the whole fused pass -- per-channel normalisation, float16 output,
  * per-sample regions of interest and flip codes, letterbox placement -- on tensor / image-batch handles. `op` is the

@@ -13,6 +13,7 @@
 #ifndef CVCUDA_B200_PREPROC_H
 #define CVCUDA_B200_PREPROC_H
 
+#include <stddef.h>
 #include <stdint.h>
 
 #if defined(__cplusplus)
@@ -210,6 +211,32 @@ B200PP_PUBLIC int b200ppCropFlipNormalizeReformat(const B200ppSource *src, const
  * reference's CPU golden (tests/cvcuda/system/ResizeUtils.cpp:189-241) bit for bit for the integer element types.
  * Cubic and area interpolation are not implemented (B200PP_ERROR_NOT_IMPLEMENTED). */
 B200PP_PUBLIC int b200ppResize(const B200ppImageSet *src, const B200ppImageSet *dst, int32_t interp, cudaStream_t stream);
+
+/* Resize of one crop rectangle per image: dst[i] = the rectangle cropRects[i] = (left, top, width, height; device, packed
+ * int32 x 4 on a 16-byte boundary) of src[i], resized to the size of dst[i]. The resampling step of the reference's
+ * RandomResizedCrop (kernels src/cvcuda/priv/legacy/random_resized_crop.cu:92-154, which take top / left / scale per
+ * sample), with the arithmetic of the reference's CPU golden for it (test::ResizedCrop,
+ * tests/cvcuda/system/ResizeUtils.cpp:189-241 with its crop arguments): sample positions are scaled by crop / output
+ * size and shifted by (left, top); taps clamp at the image's edges, not the rectangle's. Nearest and linear. */
+B200PP_PUBLIC int b200ppResizedCrop(const B200ppImageSet *src, const B200ppImageSet *dst, const int32_t *cropRects,
+                                    int32_t interp, cudaStream_t stream);
+
+/* The crop-rectangle generator of the reference's RandomResizedCrop
+ * (src/cvcuda/priv/legacy/random_resized_crop.cu:288-390): a std::mt19937 seeded with `seed` (0 = from the system's
+ * random device) and the reference's draw sequence, so equal seeds give the reference's rectangles. Host only, not
+ * thread-safe per generator. Next() writes (left, top, width, height) of the next crop of a rows x cols image. */
+typedef struct B200ppRandomCrop B200ppRandomCrop;
+B200PP_PUBLIC int  b200ppRandomCropCreate(B200ppRandomCrop **gen, double minScale, double maxScale, double minRatio,
+                                          double maxRatio, uint32_t seed);
+B200PP_PUBLIC void b200ppRandomCropDestroy(B200ppRandomCrop *gen);
+B200PP_PUBLIC int  b200ppRandomCropNext(B200ppRandomCrop *gen, int32_t rows, int32_t cols, int32_t rect[4]);
+
+/* Device buffers for per-sample parameters drawn on the host (what an operator object such as RandomResizedCrop owns,
+ * src/cvcuda/priv/legacy/random_resized_crop.cu:305-313,459-475): allocate once, upload from pageable host memory on the
+ * stream of the launch that reads them. */
+B200PP_PUBLIC int  b200ppParamBufferCreate(void **dev, size_t bytes);
+B200PP_PUBLIC void b200ppParamBufferDestroy(void *dev);
+B200PP_PUBLIC int  b200ppParamBufferUpload(void *dev, const void *host, size_t bytes, cudaStream_t stream);
 
 /* Parameters of the stand-alone Normalize. base and scale are float32 device tensors addressed as
  * ptr + n*stride[0] + y*stride[1] + x*stride[2] + c*stride[3] (bytes); a stride of 0 broadcasts along that dimension. */

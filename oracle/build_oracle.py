@@ -69,9 +69,10 @@ def build_ref(ref_root: str = DEFAULT_REF_ROOT, force: bool = False) -> str | No
     resize_tu = os.path.join(ref_root, "tests/cvcuda/system/ResizeUtils.cpp")
     norm_tu = os.path.join(ref_root, "tests/cvcuda/system/TestOpNormalize.cpp")
     border_tu = os.path.join(ref_root, "tests/cvcuda/system/TestOpCopyMakeBorder.cpp")
-    if not all(os.path.exists(f) for f in (rccr_tu, cfnr_tu, resize_tu, norm_tu, border_tu)):
+    crop_tu = os.path.join(ref_root, "tests/cvcuda/system/TestOpRandomResizedCrop.cpp")
+    if not all(os.path.exists(f) for f in (rccr_tu, cfnr_tu, resize_tu, norm_tu, border_tu, crop_tu)):
         return REF_SO if os.path.exists(REF_SO) else None
-    if not (force or _stale(REF_SO, REF_WRAP, rccr_tu, cfnr_tu, resize_tu, norm_tu, border_tu)):
+    if not (force or _stale(REF_SO, REF_WRAP, rccr_tu, cfnr_tu, resize_tu, norm_tu, border_tu, crop_tu)):
         return REF_SO
     os.makedirs(REF_DIR, exist_ok=True)
     scratch = tempfile.mkdtemp(prefix="refgold_")
@@ -86,6 +87,8 @@ def build_ref(ref_root: str = DEFAULT_REF_ROOT, force: bool = False) -> str | No
             f.write(_cut_function(norm_tu, "static void Normalize(std::vector<uint8_t> &hDst", start_at_template=False))
         with open(os.path.join(scratch, "border.inc"), "w") as f:
             f.write(_cut_function(border_tu, "static void CopyMakeBorder(std::vector<T> &hDst, const std::vector<T> &hSrc,"))
+        with open(os.path.join(scratch, "random_crop.inc"), "w") as f:
+            f.write(_cut_function(crop_tu, "static void GetCropParams(std::mt19937 &generator", start_at_template=False))
         inc = [
             "-I" + os.path.join(ref_root, "tests"),
             "-I" + os.path.join(ref_root, "src/cvcuda/include"),
@@ -96,7 +99,7 @@ def build_ref(ref_root: str = DEFAULT_REF_ROOT, force: bool = False) -> str | No
         cmd = [
             "g++", "-std=c++17", *CFLAGS, "-w",
             '-DREF_GOLDEN_RCCR_INC="rccr.inc"', '-DREF_GOLDEN_CFNR_INC="cfnr.inc"', '-DREF_GOLDEN_RESIZE_INC="resize.inc"',
-            '-DREF_GOLDEN_NORMALIZE_INC="normalize.inc"', '-DREF_GOLDEN_BORDER_INC="border.inc"',
+            '-DREF_GOLDEN_NORMALIZE_INC="normalize.inc"', '-DREF_GOLDEN_BORDER_INC="border.inc"', '-DREF_GOLDEN_RANDOM_CROP_INC="random_crop.inc"',
             *inc, "-o", REF_SO, REF_WRAP,
         ]
         subprocess.check_call(cmd)

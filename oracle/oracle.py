@@ -74,6 +74,9 @@ def lib() -> C.CDLL:
         L.oracle_resize_source_bytes.restype = C.c_int64
         L.oracle_resize_source_bytes.argtypes = [C.c_int32, C.c_int32, C.c_int64, C.c_void_p,
                                                  C.POINTER(_ResizeParams)]
+        L.oracle_resized_crop.restype = C.c_int
+        L.oracle_resized_crop.argtypes = [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
+                                          C.c_void_p]
         L.oracle_resize_plain.restype = C.c_int
         L.oracle_resize_plain.argtypes = [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32]
         L.oracle_normalize.restype = C.c_int
@@ -109,6 +112,10 @@ def ref() -> Optional[C.CDLL]:
         R.ref_cfnr.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int,
                                C.c_int, C.c_int, C.c_int, C.c_float, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
                                C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_float, C.c_float, C.c_float, C.c_uint32]
+        if hasattr(R, "ref_resized_crop"):
+            R.ref_resized_crop.restype = C.c_int
+            R.ref_resized_crop.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int,
+                                           C.c_int, C.c_int, C.c_void_p]
         if hasattr(R, "ref_resize"):
             R.ref_resize.restype = C.c_int
             R.ref_resize.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int,
@@ -296,9 +303,10 @@ class _PlainImage(C.Structure):
 
 
 def resize_plain(images: Sequence[np.ndarray], out_sizes: Sequence[tuple], interp: int,
-                 golden_float: bool = False) -> list:
+                 golden_float: bool = False, rects=None) -> list:
     """Stand-alone Resize restatement (resize_oracle.h) on packed HxWxC images (C = 1..4; uint8, uint16, int16 or
-    float32); out_sizes are (w, h) per image. Returns the resized images."""
+    float32); out_sizes are (w, h) per image; rects, if given, one (left, top, width, height) crop rectangle per image
+    (the golden's crop arguments). Returns the resized images."""
     imgs = [np.ascontiguousarray(im) for im in images]
     n = len(imgs)
     dt = imgs[0].dtype
@@ -310,15 +318,28 @@ def resize_plain(images: Sequence[np.ndarray], out_sizes: Sequence[tuple], inter
         h, w, _ = imgs[i].shape
         S[i] = _PlainImage(imgs[i].ctypes.data, w, h, imgs[i].strides[0])
         D[i] = _PlainImage(outs[i].ctypes.data, out_sizes[i][0], out_sizes[i][1], outs[i].strides[0])
-    rc = lib().oracle_resize_plain(S, D, n, DTYPE_CODE[np.dtype(dt)], ch, interp, int(golden_float))
+    r = None if rects is None else np.ascontiguousarray(np.asarray(rects, np.int32).reshape(n, 4))
+    rc = lib().oracle_resized_crop(S, D, n, DTYPE_CODE[np.dtype(dt)], ch, interp, int(golden_float),
+                                   None if r is None else r.ctypes.data)
     assert rc == 0
     return outs
 
 
-def ref_resize(image: np.ndarray, out_size: tuple, interp: int) -> np.ndarray:
-    """The reference's own Resize golden (test::resizedCrop as test::Resize calls it) on one packed HxWxC image."""
+def ref_resize(image: np.ndarray, out_size: tuple, interp: int, rect=None) -> np.ndarray:
+    """The reference's own Resize golden (test::resizedCrop as test::Resize calls it, or with a (left, top, width,
+    height) crop rectangle as test::ResizedCrop calls it) on one packed HxWxC image."""
     R = ref()
     assert R is not None and hasattr(R, "ref_resize")
+    if rect is not None:
+        image = np.ascontiguousarray(image)
+        h, w, ch = image.shape
+        ow, oh = out_size
+        out = np.empty((oh, ow, ch), dtype=image.dtype)
+        r = np.ascontiguousarray(np.asarray(rect, np.int32))
+        rc = R.ref_resized_crop(out.ctypes.data, ow * ch, ow, oh, image.ctypes.data, w * ch, w, h, ch, DTYPE_CODE[image.dtype],
+                                interp, r.ctypes.data)
+        assert rc == 0
+        return out
     image = np.ascontiguousarray(image)
     h, w, ch = image.shape
     ow, oh = out_size
@@ -445,4 +466,19 @@ def ref_copy_make_border(batch: np.ndarray, out_size: tuple, top: int, left: int
     rc = R.ref_copy_make_border(out.ctypes.data, batch.ctypes.data, n, ow, oh, w, h, ch, DTYPE_CODE[batch.dtype], top, left,
                                 border, v.ctypes.data)
     assert rc == 0
+    return out
+
+
+# ------------------------------------------------------------------------------------------------ RandomResizedCrop
+
+def ref_random_crop_rects(seed: int, sizes, min_scale=0.08, max_scale=1.0, min_ratio=0.75, max_ratio=4.0 / 3.0) -> np.ndarray:
+    """Rectangles (left, top, width, height) from the reference test's own GetCropParams for images of the given
+    (width, height) sizes, one generator seeded with `seed` for the whole sequence."""
+    R = ref()
+    assert R is not None and hasattr(R, "ref_random_crop_rects")
+    rc = np.ascontiguousarray(np.array([(h, w) for (w, h) in sizes], np.int32))
+    out = np.empty((len(sizes), 4), np.int32)
+    R.ref_random_crop_rects.restype = C.c_int
+    R.ref_random_crop_rects.argtypes = [C.c_uint, C.c_double, C.c_double, C.c_double, C.c_double, C.c_void_p, C.c_int, C.c_void_p]
+    assert R.ref_random_crop_rects(seed, min_scale, max_scale, min_ratio, max_ratio, rc.ctypes.data, len(sizes), out.ctypes.data) == 0
     return out

@@ -358,8 +358,16 @@ extern "C" int ref_normalize(uint8_t *dst, const uint8_t *src, int w, int h, int
 namespace {
 template<typename T>
 void ref_resize_t(void *dst, int dstStepElems, int dstW, int dstH, const void *src, int srcStepElems, int srcW, int srcH,
-                  int channels, int interp)
+                  int channels, int interp, const int *rect = nullptr)
 {
+    if (rect) // the call test::ResizedCrop makes (ResizeUtils.cpp:360-369): left, top, crop_cols, crop_rows
+    {
+        nvcv::test::resizedCrop<T>(static_cast<T *>(dst), dstStepElems, nvcv::Size2D{dstW, dstH}, static_cast<const T *>(src),
+                                   srcStepElems, nvcv::Size2D{srcW, srcH}, rect[1], rect[0], rect[3], rect[2],
+                                   nvcv::ImageFormat{channels, 1}, static_cast<NVCVInterpolationType>(interp),
+                                   std::numeric_limits<T>::min(), std::numeric_limits<T>::max());
+        return;
+    }
     // the call test::Resize makes for nearest / linear / cubic (ResizeUtils.cpp:320-323)
     nvcv::test::resizedCrop<T>(static_cast<T *>(dst), dstStepElems, nvcv::Size2D{dstW, dstH}, static_cast<const T *>(src),
                                srcStepElems, nvcv::Size2D{srcW, srcH}, 0, 0, srcH, srcW, nvcv::ImageFormat{channels, 1},
@@ -388,4 +396,48 @@ extern "C" int ref_resize(void *dst, int dstStepElems, int dstW, int dstH, const
         return 0;
     }
     return -1;
+}
+
+extern "C" int ref_resized_crop(void *dst, int dstStepElems, int dstW, int dstH, const void *src, int srcStepElems, int srcW,
+                                int srcH, int channels, int dtype, int interp, const int *rect)
+{
+    switch (dtype)
+    {
+    case 0:
+        ref_resize_t<uint8_t>(dst, dstStepElems, dstW, dstH, src, srcStepElems, srcW, srcH, channels, interp, rect);
+        return 0;
+    case 2:
+        ref_resize_t<uint16_t>(dst, dstStepElems, dstW, dstH, src, srcStepElems, srcW, srcH, channels, interp, rect);
+        return 0;
+    case 3:
+        ref_resize_t<int16_t>(dst, dstStepElems, dstW, dstH, src, srcStepElems, srcW, srcH, channels, interp, rect);
+        return 0;
+    case 6:
+        ref_resize_t<float>(dst, dstStepElems, dstW, dstH, src, srcStepElems, srcW, srcH, channels, interp, rect);
+        return 0;
+    }
+    return -1;
+}
+
+// tests/cvcuda/system/TestOpRandomResizedCrop.cpp:39-93  GetCropParams (the test's copy of the operator's rectangle
+// generator), cut by signature.
+#include <random>
+#include REF_GOLDEN_RANDOM_CROP_INC
+
+// The first n rectangles (left, top, width, height) a generator seeded with `seed` yields for rows x cols images.
+extern "C" int ref_random_crop_rects(unsigned seed, double minScale, double maxScale, double minRatio, double maxRatio,
+                                     const int *rowsCols, int n, int *rects)
+{
+    std::mt19937 generator(seed);
+    for (int i = 0; i < n; ++i)
+    {
+        int top = 0, left = 0, cropRows = 0, cropCols = 0;
+        GetCropParams(generator, minScale, maxScale, minRatio, maxRatio, rowsCols[2 * i], rowsCols[2 * i + 1], &top, &left,
+                      &cropRows, &cropCols);
+        rects[4 * i + 0] = left;
+        rects[4 * i + 1] = top;
+        rects[4 * i + 2] = cropCols;
+        rects[4 * i + 3] = cropRows;
+    }
+    return 0;
 }

@@ -54,6 +54,12 @@ static void copy_elem(void *d, const void *s, int es)
 int oracle_resize_plain(const OraclePlainImage *src, const OraclePlainImage *dst, int32_t n, int32_t dtype,
                         int32_t channels, int32_t interp, int32_t goldenFloat)
 {
+    return oracle_resized_crop(src, dst, n, dtype, channels, interp, goldenFloat, 0);
+}
+
+int oracle_resized_crop(const OraclePlainImage *src, const OraclePlainImage *dst, int32_t n, int32_t dtype,
+                        int32_t channels, int32_t interp, int32_t goldenFloat, const int32_t *rects)
+{
     if (!(dtype == 0 || dtype == 2 || dtype == 3 || dtype == 6) || channels < 1 || channels > 4 || (interp != 0 && interp != 1))
         return -1;
     const int es = elem_size(dtype);
@@ -61,8 +67,10 @@ int oracle_resize_plain(const OraclePlainImage *src, const OraclePlainImage *dst
     {
         const OraclePlainImage *S = &src[i], *D = &dst[i];
         /* ResizeUtils.cpp:193-194: float scale factors */
-        const float scaleH = (float)S->height / D->height;
-        const float scaleW = (float)S->width / D->width;
+        const int   left = rects ? rects[4 * i + 0] : 0, top = rects ? rects[4 * i + 1] : 0;
+        const int   cropW = rects ? rects[4 * i + 2] : S->width, cropH = rects ? rects[4 * i + 3] : S->height;
+        const float scaleH = (float)cropH / D->height;
+        const float scaleW = (float)cropW / D->width;
         for (int dy = 0; dy < D->height; ++dy)
         {
             for (int dx = 0; dx < D->width; ++dx)
@@ -71,8 +79,8 @@ int oracle_resize_plain(const OraclePlainImage *src, const OraclePlainImage *dst
                 if (interp == 0)
                 {
                     /* :204-220: float arithmetic */
-                    const float fy = scaleH * (dy + 0.5f) + 0;
-                    const float fx = scaleW * (dx + 0.5f) + 0;
+                    const float fy = scaleH * (dy + 0.5f) + top;
+                    const float fx = scaleW * (dx + 0.5f) + left;
                     int         sy = (int)floorf(fy);
                     int         sx = (int)floorf(fx);
                     sy             = sy < S->height - 1 ? sy : S->height - 1;
@@ -83,8 +91,8 @@ int oracle_resize_plain(const OraclePlainImage *src, const OraclePlainImage *dst
                 else
                 {
                     /* :222-241: the float scale is promoted, everything else is double */
-                    double fy = scaleH * (dy + 0.5) - 0.5 + 0;
-                    double fx = scaleW * (dx + 0.5) - 0.5 + 0;
+                    double fy = scaleH * (dy + 0.5) - 0.5 + top;
+                    double fx = scaleW * (dx + 0.5) - 0.5 + left;
                     int    sy = (int)floor(fy);
                     int    sx = (int)floor(fx);
                     fy        = (sy < 0) ? 0 : ((sy > S->height - 2) ? 1 : fy - sy);

@@ -36,6 +36,12 @@ typedef struct OraclePlainImage
 int oracle_resize_plain(const OraclePlainImage *src, const OraclePlainImage *dst, int32_t n, int32_t dtype,
                         int32_t channels, int32_t interp, int32_t goldenFloat);
 
+/* The same golden with its crop arguments (ResizeUtils.cpp:190-194: top, left, crop_rows, crop_cols), as the
+ * RandomResizedCrop test calls it (tests/cvcuda/system/TestOpRandomResizedCrop.cpp:206-208): rects holds
+ * (left, top, crop_cols, crop_rows) per image, NULL = whole images. Taps clamp at the image's edges, not the rectangle's. */
+int oracle_resized_crop(const OraclePlainImage *src, const OraclePlainImage *dst, int32_t n, int32_t dtype,
+                        int32_t channels, int32_t interp, int32_t goldenFloat, const int32_t *rects);
+
 /* Stand-alone Normalize golden (tests/cvcuda/system/TestOpNormalize.cpp:34-77), element types as in preproc_oracle.h
  * (source: U8, S8, U16, S16, S32, F32; destination the same set). base / scale: float32, addressed as
  * ptr + n*stride[0] + y*stride[1] + x*stride[2] + c*stride[3] (bytes; 0 broadcasts). flags bit 0: scale holds standard

@@ -27,14 +27,63 @@ FAKE_API void fakeTensorDestroy(NVCVTensorHandle h)
     delete reinterpret_cast<NVCVTensorData *>(h);
 }
 
+namespace {
+// The exported struct first, so a batch handle reads as one; then the host-side image sizes (width, height pairs)
+// that the real library keeps in its image objects.
+struct FakeBatch
+{
+    NVCVImageBatchData data;
+    int32_t           *sizes;
+};
+} // namespace
+
 FAKE_API NVCVImageBatchHandle fakeImageBatchCreate(const NVCVImageBatchData *d)
 {
-    return reinterpret_cast<NVCVImageBatchHandle>(new NVCVImageBatchData(*d));
+    return reinterpret_cast<NVCVImageBatchHandle>(new FakeBatch{*d, nullptr});
+}
+
+FAKE_API NVCVImageBatchHandle fakeImageBatchCreateSized(const NVCVImageBatchData *d, const int32_t *widthHeight)
+{
+    FakeBatch *b = new FakeBatch{*d, new int32_t[2 * (d->numImages > 0 ? d->numImages : 1)]};
+    std::memcpy(b->sizes, widthHeight, sizeof(int32_t) * 2 * d->numImages);
+    return reinterpret_cast<NVCVImageBatchHandle>(b);
 }
 
 FAKE_API void fakeImageBatchDestroy(NVCVImageBatchHandle h)
 {
-    delete reinterpret_cast<NVCVImageBatchData *>(h);
+    FakeBatch *b = reinterpret_cast<FakeBatch *>(h);
+    if (b)
+        delete[] b->sizes;
+    delete b;
+}
+
+// Image handles of this double are pointers to a batch's (width, height) pair; they carry no reference count.
+FAKE_API NVCVStatus nvcvImageBatchVarShapeGetImages(NVCVImageBatchHandle h, int32_t begIndex, NVCVImageHandle *outImages,
+                                                    int32_t numImages)
+{
+    FakeBatch *b = reinterpret_cast<FakeBatch *>(h);
+    if (!b || !outImages || !b->sizes)
+        return 2;
+    if (begIndex < 0 || begIndex + numImages > b->data.numImages)
+        return 10;
+    for (int i = 0; i < numImages; ++i) outImages[i] = reinterpret_cast<NVCVImageHandle>(b->sizes + 2 * (begIndex + i));
+    return 0;
+}
+
+FAKE_API NVCVStatus nvcvImageGetSize(NVCVImageHandle h, int32_t *width, int32_t *height)
+{
+    if (!h || !width || !height)
+        return 2;
+    *width  = reinterpret_cast<const int32_t *>(h)[0];
+    *height = reinterpret_cast<const int32_t *>(h)[1];
+    return 0;
+}
+
+FAKE_API NVCVStatus nvcvImageDecRef(NVCVImageHandle, int *newRefCount)
+{
+    if (newRefCount)
+        *newRefCount = 1;
+    return 0;
 }
 
 FAKE_API NVCVStatus fakeLastStatus()

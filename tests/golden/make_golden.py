@@ -130,6 +130,22 @@ def border_cases():
     return out
 
 
+def random_crop_cases():
+    """Rectangle sequences of the reference test's GetCropParams (TestOpRandomResizedCrop.cpp:39-93): several seeds and
+    parameter sets, image sizes of its table, including a set no random try can satisfy (the central-crop fallback)."""
+    out, k = {}, 0
+    sizes = [(42, 48), (113, 12), (421, 148), (313, 212), (42, 40), (21, 21), (420, 420), (210, 210), (1920, 1080), (5, 400)] * 4
+    for seed in (1, 2, 77, 12345, 4000000000):
+        for par in ((0.08, 1.0, 0.75, 4.0 / 3.0), (0.5, 0.9, 0.5, 2.0), (1.0, 1.0, 3.0, 4.0), (0.2, 1.0, 0.8, 1.3)):
+            out[f"seq{k}_seed"] = np.array(seed, np.int64)
+            out[f"seq{k}_par"] = np.array(par, np.float64)
+            out[f"seq{k}_sizes"] = np.array(sizes, np.int32)
+            out[f"seq{k}_rects"] = O.ref_random_crop_rects(seed, sizes, *par)
+            k += 1
+    out["count"] = np.array(k)
+    return out
+
+
 if __name__ == "__main__":
     assert build_oracle.build_ref() is not None, "reference tree not available"
     np.savez_compressed(os.path.join(HERE, "rccr_golden.npz"), **rccr_cases())
@@ -137,4 +153,5 @@ if __name__ == "__main__":
     np.savez_compressed(os.path.join(HERE, "resize_golden.npz"), **resize_cases())
     np.savez_compressed(os.path.join(HERE, "normalize_golden.npz"), **normalize_cases())
     np.savez_compressed(os.path.join(HERE, "border_golden.npz"), **border_cases())
+    np.savez_compressed(os.path.join(HERE, "random_crop_golden.npz"), **random_crop_cases())
     print("written", [f for f in os.listdir(HERE) if f.endswith(".npz")])

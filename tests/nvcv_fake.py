@@ -63,6 +63,8 @@ def fake():
         F.fakeTensorDestroy.argtypes = [C.c_void_p]
         F.fakeImageBatchCreate.restype = C.c_void_p
         F.fakeImageBatchCreate.argtypes = [C.POINTER(ImageBatchData)]
+        F.fakeImageBatchCreateSized.restype = C.c_void_p
+        F.fakeImageBatchCreateSized.argtypes = [C.POINTER(ImageBatchData), C.POINTER(C.c_int32)]
         F.fakeImageBatchDestroy.argtypes = [C.c_void_p]
         F.fakeLastStatus.restype = C.c_int
         F.fakeLastMessage.restype = C.c_char_p
@@ -110,7 +112,9 @@ def image_batch_handle(batch, kind="u", bits=8):
     d.varShapeStrided.uniqueFormat = format_code(kind, bits, batch.channels, planes)
     d.varShapeStrided.maxWidth, d.varShapeStrided.maxHeight = batch.max_size
     d.varShapeStrided.imageList = batch.descriptor_table().data_ptr()
-    return fake().fakeImageBatchCreate(C.byref(d))
+    wh = [(im.shape[2], im.shape[1]) if batch.planar else (im.shape[1], im.shape[0]) for im in batch._images]
+    sizes = (C.c_int32 * (2 * max(1, len(batch))))(*[v for pair in wh for v in pair])
+    return fake().fakeImageBatchCreateSized(C.byref(d), sizes)
 
 
 def bind_operators(lib_path: str):
@@ -146,6 +150,12 @@ def bind_operators(lib_path: str):
         f = getattr(L, name)
         f.restype = C.c_int
         f.argtypes = [H, C.c_void_p, H, H, H, H, C.c_int, Float4]
+    L.cvcudaRandomResizedCropCreate.restype = C.c_int
+    L.cvcudaRandomResizedCropCreate.argtypes = [C.POINTER(H), C.c_double, C.c_double, C.c_double, C.c_double, C.c_int32, C.c_uint32]
+    for name in ("cvcudaRandomResizedCropSubmit", "cvcudaRandomResizedCropVarShapeSubmit"):
+        f = getattr(L, name)
+        f.restype = C.c_int
+        f.argtypes = [H, C.c_void_p, H, H, C.c_int]
     L.cvcudaReformatCreate.restype = C.c_int
     L.cvcudaReformatCreate.argtypes = [C.POINTER(H)]
     L.cvcudaReformatSubmit.restype = C.c_int
