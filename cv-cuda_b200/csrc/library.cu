@@ -835,6 +835,22 @@ extern "C" int b200ppConvertTo(const B200ppImageSet *src, const B200ppImageSet *
     dim3 grid((kp.rowElems + 127) / 128, (kp.height + 15) / 16, std::min(src->numSamples, 65535));
     if (grid.y > 65535u)
         return fail(B200PP_ERROR_INVALID_ARGUMENT, "Input or output tensors are too large");
+    // 8-bit sources go through a 256-entry table of results when the rows allow word loads and vector stores
+    const uintptr_t srcBits = reinterpret_cast<uintptr_t>(kp.src) | static_cast<uintptr_t>(kp.sRow)
+                            | static_cast<uintptr_t>(kp.sSample);
+    const uintptr_t dstBits = reinterpret_cast<uintptr_t>(kp.dst) | static_cast<uintptr_t>(kp.dRow)
+                            | static_cast<uintptr_t>(kp.dSample);
+    if (kp.srcElem == 1 && (srcBits & 3) == 0 && (dstBits & (4 * kp.dstElem - 1)) == 0 && g_kernelPath.load() != 1)
+    {
+        dim3 lutGrid(((kp.rowElems + 3) / 4 + 127) / 128, grid.y, grid.z);
+        if (kp.dstElem == 4)
+            convert_lut_kernel<4><<<lutGrid, block, 0, stream>>>(kp);
+        else if (kp.dstElem == 2)
+            convert_lut_kernel<2><<<lutGrid, block, 0, stream>>>(kp);
+        else
+            convert_lut_kernel<1><<<lutGrid, block, 0, stream>>>(kp);
+        return check_launch("ConvertTo");
+    }
     convert_kernel<<<grid, block, 0, stream>>>(kp);
     return check_launch("ConvertTo");
 }
