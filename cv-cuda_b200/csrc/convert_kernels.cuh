@@ -106,10 +106,10 @@ __global__ void __launch_bounds__(256) convert_kernel(const ConvertKParams p)
 
 // 8-bit sources: the 256 possible results are computed once per CTA with the arithmetic above and kept in shared
 // memory; an element then costs one shared-memory lookup. A thread handles four 4-byte words of source, 32 words apart
-// (a warp reads 128 contiguous bytes and writes 128 x DE), in each of two rows. DE = destination element bytes. Needs
+// (a warp reads 128 contiguous bytes and writes 128 x DE), in each of two or four rows per pass. DE = destination element bytes. Needs
 // source rows on 4-byte and destination rows on 4 x DE-byte boundaries (the caller checks).
 template<int DE>
-__global__ void __launch_bounds__(256) convert_lut_kernel(const ConvertKParams p)
+__global__ void __launch_bounds__(256, 5) convert_lut_kernel(const ConvertKParams p)
 {
     __shared__ unsigned lut[256];
     {
@@ -120,56 +120,65 @@ __global__ void __launch_bounds__(256) convert_lut_kernel(const ConvertKParams p
         lut[t] = bits;
     }
     __syncthreads();
-    const int w0       = blockIdx.x * (blockDim.x * 4) + threadIdx.x;
-    const int y0       = (blockIdx.y * blockDim.y + threadIdx.y) * 2;
-    const int rowWords = (p.rowElems + 3) >> 2;
+    constexpr int RPT      = DE == 4 ? 2 : 4; // rows per thread and pass: keeps 32 to 64 bytes of loads in flight per thread
+    const int     w0       = blockIdx.x * (blockDim.x * 4) + threadIdx.x;
+    const int     rowWords = (p.rowElems + 3) >> 2;
     if (w0 >= rowWords)
         return;
     for (int n = blockIdx.z; n < p.numSamples; n += gridDim.z)
     {
-#pragma unroll
-        for (int r = 0; r < 2; ++r)
+        // the grid's y extent may be smaller than the image: CTAs walk down in steps, so the table is built less often
+        for (int yb = blockIdx.y; yb * (blockDim.y * RPT) < p.height; yb += gridDim.y)
         {
-            const int y = y0 + r;
-            if (y >= p.height)
-                break;
-            const unsigned *s = reinterpret_cast<const unsigned *>(p.src + n * p.sSample + y * p.sRow);
-            uint8_t        *d = p.dst + n * p.dSample + y * p.dRow;
-            unsigned        q[4];
+            const int y0 = (yb * blockDim.y + threadIdx.y) * RPT;
+            unsigned  q[RPT][4];
             // the row's last word may reach up to three bytes past its last element: still inside the aligned word
             // that holds that element, so the load cannot leave the allocation's pages
 #pragma unroll
-            for (int k = 0; k < 4; ++k) q[k] = __ldg(s + min(w0 + 32 * k, rowWords - 1));
-#pragma unroll
-            for (int k = 0; k < 4; ++k)
+            for (int r = 0; r < RPT; ++r)
             {
-                const int w = w0 + 32 * k;
-                if (w >= rowWords)
+                const unsigned *s = reinterpret_cast<const unsigned *>(p.src + n * p.sSample + min(y0 + r, p.height - 1) * p.sRow);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) q[r][k] = __ldg(s + min(w0 + 32 * k, rowWords - 1));
+            }
+#pragma unroll
+            for (int r = 0; r < RPT; ++r)
+            {
+                const int y = y0 + r;
+                if (y >= p.height)
                     break;
-                const unsigned o0 = lut[q[k] & 255u], o1 = lut[(q[k] >> 8) & 255u], o2 = lut[(q[k] >> 16) & 255u],
-                               o3 = lut[q[k] >> 24];
-                const int      count = min(4, p.rowElems - 4 * w);
-                uint8_t       *out   = d + static_cast<long long>(w) * (4 * DE);
-                if (count == 4)
+                uint8_t *d = p.dst + n * p.dSample + y * p.dRow;
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
                 {
-                    if constexpr (DE == 4)
-                        *reinterpret_cast<uint4 *>(out) = make_uint4(o0, o1, o2, o3);
-                    else if constexpr (DE == 2)
-                        *reinterpret_cast<uint2 *>(out) = make_uint2(o0 | (o1 << 16), o2 | (o3 << 16));
-                    else
-                        *reinterpret_cast<unsigned *>(out) = o0 | (o1 << 8) | (o2 << 16) | (o3 << 24);
-                }
-                else
-                {
-                    const unsigned o[3] = {o0, o1, o2};
-                    for (int j = 0; j < count; ++j)
+                    const int w = w0 + 32 * k;
+                    if (w >= rowWords)
+                        break;
+                    const unsigned v  = q[r][k];
+                    const unsigned o0 = lut[v & 255u], o1 = lut[(v >> 8) & 255u], o2 = lut[(v >> 16) & 255u], o3 = lut[v >> 24];
+                    const int      count = min(4, p.rowElems - 4 * w);
+                    uint8_t       *out   = d + static_cast<long long>(w) * (4 * DE);
+                    if (count == 4)
                     {
                         if constexpr (DE == 4)
-                            reinterpret_cast<unsigned *>(out)[j] = o[j];
+                            *reinterpret_cast<uint4 *>(out) = make_uint4(o0, o1, o2, o3);
                         else if constexpr (DE == 2)
-                            reinterpret_cast<unsigned short *>(out)[j] = static_cast<unsigned short>(o[j]);
+                            *reinterpret_cast<uint2 *>(out) = make_uint2(o0 | (o1 << 16), o2 | (o3 << 16));
                         else
-                            out[j] = static_cast<uint8_t>(o[j]);
+                            *reinterpret_cast<unsigned *>(out) = o0 | (o1 << 8) | (o2 << 16) | (o3 << 24);
+                    }
+                    else
+                    {
+                        const unsigned o[3] = {o0, o1, o2};
+                        for (int j = 0; j < count; ++j)
+                        {
+                            if constexpr (DE == 4)
+                                reinterpret_cast<unsigned *>(out)[j] = o[j];
+                            else if constexpr (DE == 2)
+                                reinterpret_cast<unsigned short *>(out)[j] = static_cast<unsigned short>(o[j]);
+                            else
+                                out[j] = static_cast<uint8_t>(o[j]);
+                        }
                     }
                 }
             }

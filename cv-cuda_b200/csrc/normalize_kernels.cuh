@@ -142,6 +142,119 @@ __global__ void __launch_bounds__(256) normalize_kernel(const NormalizeKParams p
     }
 }
 
+// uint8 sources with base and scale that vary by channel only (the usual mean / standard-deviation case): the 256
+// possible results per channel are computed once per CTA with the arithmetic above and kept in shared memory; an element
+// then costs one shared-memory lookup. A thread handles four 4-byte words of a source row, 32 words apart (a warp reads 128
+// contiguous bytes and writes 128 x DE), in each of two or four rows per pass; DE = destination element bytes. Images whose rows are not
+// on word (source) or 4 x DE-byte (destination) boundaries go byte by byte / element by element.
+template<int DE>
+__global__ void __launch_bounds__(256, 5) normalize_lut_kernel(const NormalizeKParams p)
+{
+    __shared__ unsigned lut[4 * 256];
+    {
+        const int   t = threadIdx.y * blockDim.x + threadIdx.x; // 256 threads
+        const float v = static_cast<float>(t);
+        for (int c = 0; c < p.channels; ++c)
+        {
+            const float b = *reinterpret_cast<const float *>(reinterpret_cast<const char *>(p.base) + c * p.baseStride[3]);
+            const float m = normalize_mul(p, *reinterpret_cast<const float *>(reinterpret_cast<const char *>(p.scale) + c * p.scaleStride[3]));
+            const float o = __fadd_rn(__fmul_rn(__fmul_rn(__fsub_rn(v, b), m), p.gscale), p.shift);
+            unsigned    bits = 0;
+            store_any(reinterpret_cast<uint8_t *>(&bits), p.dstType, o);
+            lut[c * 256 + t] = bits;
+        }
+    }
+    __syncthreads();
+    constexpr int RPT = DE == 4 ? 2 : 4; // rows per thread and pass: keeps 32 to 64 bytes of loads in flight per thread
+    const int     w0  = blockIdx.x * (blockDim.x * 4) + threadIdx.x;
+    for (int n = blockIdx.z; n < p.numSamples; n += gridDim.z)
+    {
+        const PlainView S = plain_view(p.src, n), D = plain_view(p.dst, n);
+        const int       rowElems = min(S.w, D.w) * p.channels, h = min(S.h, D.h);
+        const int       rowWords = (rowElems + 3) >> 2;
+        if (w0 >= rowWords)
+            continue;
+        const bool alignedS = ((reinterpret_cast<uintptr_t>(S.base) | static_cast<uintptr_t>(S.pitch)) & 3) == 0;
+        const bool alignedD = ((reinterpret_cast<uintptr_t>(D.base) | static_cast<uintptr_t>(D.pitch)) & (4 * DE - 1)) == 0;
+        // the grid's y extent may be smaller than the image: CTAs walk down in steps, so the table is built less often
+        for (int yb = blockIdx.y; yb * (blockDim.y * RPT) < h; yb += gridDim.y)
+        {
+            const int y0 = (yb * blockDim.y + threadIdx.y) * RPT;
+            unsigned  q[RPT][4];
+#pragma unroll
+            for (int r = 0; r < RPT; ++r)
+            {
+                const uint8_t *s = S.base + min(y0 + r, h - 1) * S.pitch;
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+                {
+                    const int w = min(w0 + 32 * k, rowWords - 1);
+                    if (alignedS)
+                    {
+                        // the row's last word may reach up to three bytes past its last element: still inside the
+                        // aligned word that holds that element, so the load cannot leave the allocation's pages
+                        q[r][k] = __ldg(reinterpret_cast<const unsigned *>(s) + w);
+                    }
+                    else
+                    {
+                        q[r][k] = 0;
+                        for (int j = 0; j < 4 && 4 * w + j < rowElems; ++j)
+                            q[r][k] |= static_cast<unsigned>(__ldg(s + 4 * w + j)) << (8 * j);
+                    }
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < RPT; ++r)
+            {
+                const int y = y0 + r;
+                if (y >= h)
+                    break;
+                uint8_t *d = D.base + y * D.pitch;
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+                {
+                    const int w = w0 + 32 * k;
+                    if (w >= rowWords)
+                        break;
+                    unsigned o[4];
+                    int      c = (4 * w) % p.channels;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                    {
+                        o[j] = lut[c * 256 + ((q[r][k] >> (8 * j)) & 255u)];
+                        c    = c + 1 == p.channels ? 0 : c + 1;
+                    }
+                    const int count = min(4, rowElems - 4 * w);
+                    uint8_t  *out   = d + static_cast<long long>(w) * (4 * DE);
+                    if (count == 4 && alignedD)
+                    {
+                        if constexpr (DE == 4)
+                            *reinterpret_cast<uint4 *>(out) = make_uint4(o[0], o[1], o[2], o[3]);
+                        else if constexpr (DE == 2)
+                            *reinterpret_cast<uint2 *>(out) = make_uint2(o[0] | (o[1] << 16), o[2] | (o[3] << 16));
+                        else
+                            *reinterpret_cast<unsigned *>(out) = o[0] | (o[1] << 8) | (o[2] << 16) | (o[3] << 24);
+                    }
+                    else
+                    {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            if (j < count)
+                            {
+                                if constexpr (DE == 4)
+                                    reinterpret_cast<unsigned *>(out)[j] = o[j];
+                                else if constexpr (DE == 2)
+                                    reinterpret_cast<unsigned short *>(out)[j] = static_cast<unsigned short>(o[j]);
+                                else
+                                    out[j] = static_cast<uint8_t>(o[j]);
+                            }
+                    }
+                }
+            }
+        }
+    }
+}
+
 } // namespace b200pp
 
 #endif

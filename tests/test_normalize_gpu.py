@@ -9,7 +9,7 @@ import torch
 
 import nvcv_fake as NF
 import ref_tables as T
-from gpu_util import _TORCH_DTYPE, padded_images, to_dev
+from gpu_util import kernel_path, _TORCH_DTYPE, padded_images, to_dev
 
 pytestmark = pytest.mark.gpu
 
@@ -71,6 +71,30 @@ def test_normalize_types_channels_broadcast(pkg, oracle, src_dt, dst_dt, ch):
             pkg.normalize_into(dst, to_dev(np.stack(images)), to_dev(base), to_dev(scale), flags, 1.5, -2.0, eps)
             torch.cuda.synchronize()
             _same(dst.cpu().numpy(), want, f"base {bshape} scale {sshape} flags {flags}")
+
+
+@pytest.mark.parametrize("dst_dt", [np.uint8, np.int8, np.uint16, np.int16, np.int32, np.float32], ids=lambda d: np.dtype(d).name)
+@pytest.mark.parametrize("ch", [1, 2, 3, 4])
+def test_normalize_uint8_per_channel_both_kernels(pkg, oracle, dst_dt, ch):
+    """uint8 sources with per-channel base / scale take the table kernel; kernel path 1 keeps the arithmetic kernel on the
+    same inputs. Row lengths that are no multiple of four elements, aligned and unaligned rows, every destination type."""
+    rng = np.random.default_rng(40 + ch)
+    images = [rng.integers(0, 256, (9, 21, ch), dtype=np.uint8), rng.integers(0, 256, (14, 5, ch), dtype=np.uint8),
+              rng.integers(0, 256, (3, 1, ch), dtype=np.uint8)]
+    base = rng.uniform(0, 255, (1, 1, 1, ch)).astype(np.float32)
+    scale = rng.uniform(0.2, 3.0, (1, 1, 1, ch)).astype(np.float32)
+    for flags, eps, gs, sh in ((0, 0.0, 1.0, 0.0), (1, 0.25, 40.0, 100.0)):
+        want = oracle.normalize(images, base, scale, dst_dt, gs, sh, eps, flags)
+        for pad, off in ((32, 0), (1, 1)):
+            for path in (0, 1):
+                src = pkg.ImageBatchVarShape(padded_images(images, pad_to=pad, offset=off))
+                dst = pkg.ImageBatchVarShape([torch.zeros(im.shape, dtype=_TORCH_DTYPE[np.dtype(dst_dt)], device="cuda")
+                                              for im in images])
+                with kernel_path(pkg, path):
+                    pkg.normalize_into(dst, src, to_dev(base), to_dev(scale), flags, gs, sh, eps)
+                torch.cuda.synchronize()
+                for i in range(len(images)):
+                    _same(dst[i].cpu().numpy(), want[i], f"image {i}, pad {pad}, path {path}, flags {flags}")
 
 
 def test_normalize_strided_views_and_errors(pkg, oracle):
