@@ -76,6 +76,99 @@ __global__ void __launch_bounds__(256) reformat_kernel(const ReformatKParams p)
     }
 }
 
+// Three 8-bit channels, packed interleaved on one side (pixel stride 3, channel stride 1) and planar on the other
+// (pixel stride 1), every row and plane on a 16-byte boundary: the common RGB8 NHWC <-> NCHW case. A thread moves 16
+// pixels of two rows: three 16-byte vectors on the interleaved side, one 16-byte vector per plane on the other, shuffled
+// in registers with byte permutes (six per four pixels). TO_PLANAR: interleaved source. The ragged end of a row (width
+// not a multiple of 16) goes byte by byte.
+template<bool TO_PLANAR>
+__global__ void __launch_bounds__(256) reformat_u8x3_kernel(const ReformatKParams p)
+{
+    const int x  = (blockIdx.x * blockDim.x + threadIdx.x) * 16;
+    const int y0 = (blockIdx.y * blockDim.y + threadIdx.y) * 2;
+    if (x >= p.width)
+        return;
+    const long long iSample = TO_PLANAR ? p.sSample : p.dSample, iRow = TO_PLANAR ? p.sRow : p.dRow;
+    const long long pSample = TO_PLANAR ? p.dSample : p.sSample, pRow = TO_PLANAR ? p.dRow : p.sRow;
+    const long long pChan   = TO_PLANAR ? p.dChan : p.sChan;
+    for (int n = blockIdx.z; n < p.numSamples; n += gridDim.z)
+    {
+        if (x + 16 > p.width)
+        {
+            for (int r = 0; r < 2 && y0 + r < p.height; ++r)
+                for (int k = x; k < p.width; ++k)
+                    for (int c = 0; c < 3; ++c)
+                        p.dst[n * p.dSample + (y0 + r) * p.dRow + k * p.dPix + c * p.dChan]
+                            = p.src[n * p.sSample + (y0 + r) * p.sRow + k * p.sPix + c * p.sChan];
+            continue;
+        }
+        unsigned in[2][12];
+#pragma unroll
+        for (int r = 0; r < 2; ++r)
+        {
+            const int y = min(y0 + r, p.height - 1);
+            if constexpr (TO_PLANAR)
+            {
+                const uint4 *s = reinterpret_cast<const uint4 *>(p.src + n * iSample + y * iRow + x * 3);
+#pragma unroll
+                for (int v = 0; v < 3; ++v)
+                {
+                    const uint4 q = __ldg(s + v);
+                    in[r][4 * v + 0] = q.x, in[r][4 * v + 1] = q.y, in[r][4 * v + 2] = q.z, in[r][4 * v + 3] = q.w;
+                }
+            }
+            else
+            {
+#pragma unroll
+                for (int c = 0; c < 3; ++c)
+                {
+                    const uint4 q = __ldg(reinterpret_cast<const uint4 *>(p.src + n * pSample + c * pChan + y * pRow + x));
+                    in[r][4 * c + 0] = q.x, in[r][4 * c + 1] = q.y, in[r][4 * c + 2] = q.z, in[r][4 * c + 3] = q.w;
+                }
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < 2; ++r)
+        {
+            const int y = y0 + r;
+            if (y >= p.height)
+                break;
+            unsigned out[12];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) // four pixels = twelve bytes = words a, b, c interleaved / one word per plane
+            {
+                if constexpr (TO_PLANAR)
+                {
+                    const unsigned a = in[r][3 * j], b = in[r][3 * j + 1], c = in[r][3 * j + 2];
+                    out[0 + j] = __byte_perm(__byte_perm(a, b, 0x0630), c, 0x5210); // bytes 0, 3, 6, 9
+                    out[4 + j] = __byte_perm(__byte_perm(a, b, 0x0741), c, 0x6210); // bytes 1, 4, 7, 10
+                    out[8 + j] = __byte_perm(__byte_perm(a, b, 0x0052), c, 0x7410); // bytes 2, 5, 8, 11
+                }
+                else
+                {
+                    const unsigned c0 = in[r][j], c1 = in[r][4 + j], c2 = in[r][8 + j];
+                    out[3 * j + 0] = __byte_perm(__byte_perm(c0, c1, 0x1040), c2, 0x3410); // r0 g0 b0 r1
+                    out[3 * j + 1] = __byte_perm(__byte_perm(c0, c1, 0x6205), c2, 0x3250); // g1 b1 r2 g2
+                    out[3 * j + 2] = __byte_perm(__byte_perm(c0, c1, 0x0730), c2, 0x7216); // b2 r3 g3 b3
+                }
+            }
+            if constexpr (TO_PLANAR)
+            {
+#pragma unroll
+                for (int c = 0; c < 3; ++c)
+                    *reinterpret_cast<uint4 *>(p.dst + n * pSample + c * pChan + y * pRow + x)
+                        = make_uint4(out[4 * c], out[4 * c + 1], out[4 * c + 2], out[4 * c + 3]);
+            }
+            else
+            {
+                uint4 *d = reinterpret_cast<uint4 *>(p.dst + n * iSample + y * iRow + x * 3);
+#pragma unroll
+                for (int v = 0; v < 3; ++v) d[v] = make_uint4(out[4 * v], out[4 * v + 1], out[4 * v + 2], out[4 * v + 3]);
+            }
+        }
+    }
+}
+
 } // namespace b200pp
 
 #endif
