@@ -186,6 +186,91 @@ __global__ void __launch_bounds__(256, 5) convert_lut_kernel(const ConvertKParam
     }
 }
 
+// float32 sources: a thread converts two groups of four adjacent elements (one 16-byte load each, 32 groups apart) in
+// each of two rows and stores each group's results as one word / 8 bytes / 16 bytes, with the arithmetic of
+// convert_kernel. DE = destination element bytes. Needs source rows on 16-byte and destination rows on 4 x DE-byte
+// boundaries (the caller checks); the ragged end of a row goes element by element.
+template<int DE>
+__global__ void __launch_bounds__(256) convert_f32_kernel(const ConvertKParams p)
+{
+    const int g0        = blockIdx.x * (blockDim.x * 2) + threadIdx.x;
+    const int y0        = (blockIdx.y * blockDim.y + threadIdx.y) * 2;
+    const int rowGroups = (p.rowElems + 3) >> 2;
+    if (g0 >= rowGroups)
+        return;
+    for (int n = blockIdx.z; n < p.numSamples; n += gridDim.z)
+    {
+        float4 v[2][2];
+#pragma unroll
+        for (int r = 0; r < 2; ++r)
+        {
+            const uint8_t *s = p.src + n * p.sSample + min(y0 + r, p.height - 1) * p.sRow;
+#pragma unroll
+            for (int k = 0; k < 2; ++k)
+            {
+                const int g = min(g0 + 32 * k, rowGroups - 1);
+                if (4 * g + 4 <= p.rowElems)
+                    v[r][k] = __ldg(reinterpret_cast<const float4 *>(s) + g);
+                else
+                {
+                    const float *f = reinterpret_cast<const float *>(s) + 4 * g;
+                    const int    c = p.rowElems - 4 * g;
+                    v[r][k]        = make_float4(f[0], c > 1 ? f[1] : 0.f, c > 2 ? f[2] : 0.f, 0.f);
+                }
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < 2; ++r)
+        {
+            const int y = y0 + r;
+            if (y >= p.height)
+                break;
+            uint8_t *d = p.dst + n * p.dSample + y * p.dRow;
+#pragma unroll
+            for (int k = 0; k < 2; ++k)
+            {
+                const int g = g0 + 32 * k;
+                if (g >= rowGroups)
+                    break;
+                const float in[4] = {v[r][k].x, v[r][k].y, v[r][k].z, v[r][k].w};
+                unsigned    o[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                {
+                    o[j] = 0;
+                    store_saturated(reinterpret_cast<uint8_t *>(&o[j]), p.dstType,
+                                    __dadd_rn(__dmul_rn(p.alpha, static_cast<double>(in[j])), p.beta));
+                }
+                const int count = min(4, p.rowElems - 4 * g);
+                uint8_t  *out   = d + static_cast<long long>(g) * (4 * DE);
+                if (count == 4)
+                {
+                    if constexpr (DE == 4)
+                        *reinterpret_cast<uint4 *>(out) = make_uint4(o[0], o[1], o[2], o[3]);
+                    else if constexpr (DE == 2)
+                        *reinterpret_cast<uint2 *>(out) = make_uint2(o[0] | (o[1] << 16), o[2] | (o[3] << 16));
+                    else
+                        *reinterpret_cast<unsigned *>(out) = o[0] | (o[1] << 8) | (o[2] << 16) | (o[3] << 24);
+                }
+                else
+                {
+#pragma unroll
+                    for (int j = 0; j < 3; ++j)
+                        if (j < count)
+                        {
+                            if constexpr (DE == 4)
+                                reinterpret_cast<unsigned *>(out)[j] = o[j];
+                            else if constexpr (DE == 2)
+                                reinterpret_cast<unsigned short *>(out)[j] = static_cast<unsigned short>(o[j]);
+                            else
+                                out[j] = static_cast<uint8_t>(o[j]);
+                        }
+                }
+            }
+        }
+    }
+}
+
 } // namespace b200pp
 
 #endif

@@ -899,6 +899,17 @@ extern "C" int b200ppConvertTo(const B200ppImageSet *src, const B200ppImageSet *
             convert_lut_kernel<1><<<lutGrid, block, 0, stream>>>(kp);
         return check_launch("ConvertTo");
     }
+    if (kp.srcType == B200PP_F32 && (srcBits & 15) == 0 && (dstBits & (4 * kp.dstElem - 1)) == 0 && g_kernelPath.load() != 1)
+    {
+        dim3 vecGrid(((kp.rowElems + 3) / 4 + 63) / 64, grid.y, grid.z);
+        if (kp.dstElem == 4)
+            convert_f32_kernel<4><<<vecGrid, block, 0, stream>>>(kp);
+        else if (kp.dstElem == 2)
+            convert_f32_kernel<2><<<vecGrid, block, 0, stream>>>(kp);
+        else
+            convert_f32_kernel<1><<<vecGrid, block, 0, stream>>>(kp);
+        return check_launch("ConvertTo");
+    }
     convert_kernel<<<grid, block, 0, stream>>>(kp);
     return check_launch("ConvertTo");
 }

@@ -81,6 +81,35 @@ def test_strided_views_rank3_and_errors(pkg, oracle):
     assert pkg.convertto(torch.empty((0, 4, 4, 3), dtype=torch.uint8, device="cuda"), torch.float32).shape == (0, 4, 4, 3)
 
 
+@pytest.mark.parametrize("st", [np.uint8, np.int8, np.float32], ids=lambda d: np.dtype(d).name)
+@pytest.mark.parametrize("dt", TYPES, ids=lambda d: np.dtype(d).name)
+def test_vector_and_table_kernels_against_the_plain_one(pkg, oracle, st, dt):
+    """8-bit sources take the table kernel and float32 sources the vector kernel when rows sit on word / vector
+    boundaries; kernel path 1 keeps the element-by-element kernel. Views of wider storage give aligned rows with ragged
+    ends (1, 2, 3 elements past the last full group)."""
+    from gpu_util import kernel_path
+    rng = np.random.default_rng(23)
+    for w in (37, 38, 39, 40, 1):
+        if st == np.float32:
+            full = rng.uniform(-400, 400, (2, 13, 48, 3)).astype(np.float32)
+            full.flat[:8] = [0.5, 1.5, 2.5, -0.5, -1.5, 254.5, 255.5, 1e10]
+        else:
+            info = np.iinfo(st)
+            full = rng.integers(info.min, int(info.max) + 1, (2, 13, 48, 3)).astype(st)
+        src = to_dev(full)[:, :, :w]
+        for alpha, beta in ((1.0, 0.0), (0.7, 3.5), (-2.1, 100.25)):
+            want = oracle.convert_to(full[:, :, :w], dt, alpha, beta)
+            for path in (0, 1):
+                store = torch.zeros((2, 13, 48, 3), dtype=_TORCH_DTYPE[np.dtype(dt)], device="cuda")
+                with kernel_path(pkg, path):
+                    pkg.convertto_into(store[:, :, :w], src, alpha, beta)
+                torch.cuda.synchronize()
+                out = store.cpu().numpy()
+                _same(np.ascontiguousarray(out[:, :, :w]), want, f"w {w} alpha {alpha} path {path}")
+                out[:, :, :w] = 0
+                assert not out.view(np.uint8).any(), "wrote outside the destination view"
+
+
 def test_convertto_through_operator_symbols(pkg, oracle):
     ops = NF.bind_operators(pkg.lib_path())
     stream = torch.cuda.current_stream().cuda_stream
