@@ -121,6 +121,46 @@ def main():
     emit("4: 64 x 1080p -> 640x360 linear in a 640^2 canvas, pad 114, BGR, x/255, f32 NCHW", n, t_new, t_ref,
          "resized 640x360 region only: the reference needs CopyMakeBorder for the canvas",
          cpu_images_per_s(host, spec, np.float32, threads, a.cpu_seconds), f"{k} of 64 images per pass")
+    # ---- configs 2 and 4 as chains of this library's own stand-alone operators (the shape of the reference's unfused
+    # pipelines: Resize -> [CopyMakeBorder] -> Normalize / ConvertTo -> Reformat), against the fused call above. The
+    # chains round to uint8 after the resize, so their values differ from the fused result; this is a timing line.
+    def chain_line(name, images, stages, fused_us):
+        times = {k: round(gpu_us(fn, a.launches), 1) for k, fn in stages}
+        line = {"config": name, "images": images, "stage_us": times, "chain_us_per_launch": round(sum(times.values()), 1),
+                "fused_us_per_launch": round(fused_us, 1), "launches_in_chain": len(stages)}
+        line["fused_speedup"] = round(line["chain_us_per_launch"] / fused_us, 2)
+        print(json.dumps(line), flush=True)
+
+    n2 = 256
+    small = torch.empty((n2, 256, 256, 3), dtype=torch.uint8, device="cuda")
+    normed = torch.empty((n2, 224, 224, 3), dtype=torch.float32, device="cuda")
+    planar = torch.empty((n2, 3, 224, 224), dtype=torch.float32, device="cuda")
+    mean_t = torch.tensor(MEAN, dtype=torch.float32, device="cuda").reshape(1, 1, 1, 3)
+    mul_t = torch.tensor(INV_STD, dtype=torch.float32, device="cuda").reshape(1, 1, 1, 3)
+    fused2 = gpu_us(lambda: pkg.fused_preprocess_into(planar, src, resize_dim=(256, 256), interp=1, crop_pos=(16, 16),
+                                                      layout="NCHW", base=MEAN, mul=INV_STD, srcCast=False), a.launches)
+    chain_line("2 as a chain: Resize 256^2 u8 -> (crop view) Normalize -> f32 -> Reformat NCHW", n2,
+               [("resize", lambda: pkg.resize_into(small, src, 1)),
+                ("normalize", lambda: pkg.normalize_into(normed, small[:, 16:240, 16:240], mean_t, mul_t)),
+                ("reformat", lambda: pkg.reformat_into(planar, normed, src_layout="NHWC", dst_layout="NCHW"))], fused2)
+    del small, normed, planar
+
+    n4 = 64
+    s4 = src[:n4]
+    r4 = torch.empty((n4, 360, 640, 3), dtype=torch.uint8, device="cuda")
+    b4 = torch.empty((n4, 640, 640, 3), dtype=torch.uint8, device="cuda")
+    f4 = torch.empty((n4, 640, 640, 3), dtype=torch.float32, device="cuda")
+    p4 = torch.empty((n4, 3, 640, 640), dtype=torch.float32, device="cuda")
+    fused4 = gpu_us(lambda: pkg.fused_preprocess_into(p4, s4, resize_dim=(640, 360), interp=1, layout="NCHW", manip=1,
+                                                      scale=1 / 255.0, srcCast=True, dst_pos=(0, 140), region_size=(640, 360),
+                                                      pad_value=114.0), a.launches)
+    chain_line("4 as a chain: Resize 640x360 u8 -> CopyMakeBorder 640^2 (114) -> ConvertTo f32 x1/255 -> Reformat NCHW "
+               "(no channel swap in the chain)", n4,
+               [("resize", lambda: pkg.resize_into(r4, s4, 1)),
+                ("copymakeborder", lambda: pkg.copymakeborder_into(b4, r4, 0, (114.0, 114.0, 114.0), top=140, left=0)),
+                ("convertto", lambda: pkg.convertto_into(f4, b4, 1 / 255.0, 0.0)),
+                ("reformat", lambda: pkg.reformat_into(p4, f4, src_layout="NHWC", dst_layout="NCHW"))], fused4)
+    del r4, b4, f4, p4
     del src, out, ref, ref4, s4
 
     # ---- config 5: 4K, linear and nearest
