@@ -815,6 +815,27 @@ extern "C" int b200ppReformat(const B200ppDest *src, const B200ppDest *dst, int3
             return check_launch("Reformat");
         }
     }
+    // the same for 32-bit elements (float32 / int32 RGB)
+    if (elem_size(src->dtype) == 4 && kp.channels == 3 && g_kernelPath.load(std::memory_order_relaxed) != 1)
+    {
+        const bool toPlanar   = kp.sPix == 12 && kp.sChan == 4 && kp.dPix == 4;
+        const bool fromPlanar = kp.dPix == 12 && kp.dChan == 4 && kp.sPix == 4;
+        const uintptr_t bits  = reinterpret_cast<uintptr_t>(kp.src) | reinterpret_cast<uintptr_t>(kp.dst)
+                             | static_cast<uintptr_t>(kp.sSample) | static_cast<uintptr_t>(kp.sRow)
+                             | static_cast<uintptr_t>(kp.dSample) | static_cast<uintptr_t>(kp.dRow)
+                             | static_cast<uintptr_t>(toPlanar ? kp.dChan : kp.sChan);
+        if ((toPlanar || fromPlanar) && (bits & 15) == 0)
+        {
+            dim3 vgrid((kp.width + 127) / 128, (kp.height + 15) / 16, std::min(numSamples, 65535));
+            if (vgrid.y > 65535u)
+                return fail(B200PP_ERROR_INVALID_ARGUMENT, "Input or output tensors are too large");
+            if (toPlanar)
+                reformat_w32x3_kernel<true><<<vgrid, block, 0, stream>>>(kp);
+            else
+                reformat_w32x3_kernel<false><<<vgrid, block, 0, stream>>>(kp);
+            return check_launch("Reformat");
+        }
+    }
     const int perThread = 4 / std::min(4, elem_size(src->dtype)); // pixels per thread: one 32-bit word per channel
     dim3      grid((kp.width + 32 * perThread - 1) / (32 * perThread), (kp.height + 31) / 32, std::min(numSamples, 65535));
     if (grid.y > 65535u)

@@ -169,6 +169,68 @@ __global__ void __launch_bounds__(256) reformat_u8x3_kernel(const ReformatKParam
     }
 }
 
+// Three 32-bit channels, packed interleaved on one side (pixel stride 12, channel stride 4) and planar on the other
+// (pixel stride 4), every row and plane on a 16-byte boundary: float32 / int32 RGB NHWC <-> NCHW. A thread moves four
+// pixels of each of two rows: three 16-byte vectors on the interleaved side, one per plane on the other; the shuffle is
+// a renaming of registers. The ragged end of a row goes element by element.
+template<bool TO_PLANAR>
+__global__ void __launch_bounds__(256) reformat_w32x3_kernel(const ReformatKParams p)
+{
+    const int x  = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    const int y0 = (blockIdx.y * blockDim.y + threadIdx.y) * 2;
+    if (x >= p.width)
+        return;
+    const long long iSample = TO_PLANAR ? p.sSample : p.dSample, iRow = TO_PLANAR ? p.sRow : p.dRow;
+    const long long pSample = TO_PLANAR ? p.dSample : p.sSample, pRow = TO_PLANAR ? p.dRow : p.sRow;
+    const long long pChan   = TO_PLANAR ? p.dChan : p.sChan;
+    for (int n = blockIdx.z; n < p.numSamples; n += gridDim.z)
+    {
+        if (x + 4 > p.width)
+        {
+            for (int r = 0; r < 2 && y0 + r < p.height; ++r)
+                for (int k = x; k < p.width; ++k)
+                    for (int c = 0; c < 3; ++c)
+                        *reinterpret_cast<unsigned *>(p.dst + n * p.dSample + (y0 + r) * p.dRow + k * p.dPix + c * p.dChan)
+                            = *reinterpret_cast<const unsigned *>(p.src + n * p.sSample + (y0 + r) * p.sRow + k * p.sPix + c * p.sChan);
+            continue;
+        }
+        uint4 in[2][3];
+#pragma unroll
+        for (int r = 0; r < 2; ++r)
+        {
+            const int y = min(y0 + r, p.height - 1);
+#pragma unroll
+            for (int v = 0; v < 3; ++v)
+                in[r][v] = TO_PLANAR ? __ldg(reinterpret_cast<const uint4 *>(p.src + n * iSample + y * iRow + x * 12ll) + v)
+                                     : __ldg(reinterpret_cast<const uint4 *>(p.src + n * pSample + v * pChan + y * pRow + x * 4ll));
+        }
+#pragma unroll
+        for (int r = 0; r < 2; ++r)
+        {
+            const int y = y0 + r;
+            if (y >= p.height)
+                break;
+            const uint4 a = in[r][0], b = in[r][1], c = in[r][2];
+            if constexpr (TO_PLANAR)
+            {
+                // a = r0 g0 b0 r1, b = g1 b1 r2 g2, c = b2 r3 g3 b3
+                uint8_t *d = p.dst + n * pSample + y * pRow + x * 4ll;
+                *reinterpret_cast<uint4 *>(d)             = make_uint4(a.x, a.w, b.z, c.y);
+                *reinterpret_cast<uint4 *>(d + pChan)     = make_uint4(a.y, b.x, b.w, c.z);
+                *reinterpret_cast<uint4 *>(d + 2 * pChan) = make_uint4(a.z, b.y, c.x, c.w);
+            }
+            else
+            {
+                // a = r0..r3, b = g0..g3, c = b0..b3
+                uint4 *d = reinterpret_cast<uint4 *>(p.dst + n * iSample + y * iRow + x * 12ll);
+                d[0]     = make_uint4(a.x, b.x, c.x, a.y);
+                d[1]     = make_uint4(b.y, c.y, a.z, b.z);
+                d[2]     = make_uint4(c.z, a.w, b.w, c.w);
+            }
+        }
+    }
+}
+
 } // namespace b200pp
 
 #endif

@@ -64,27 +64,29 @@ def test_reformat_types_rank3_and_views(pkg, dt):
     assert not out.view(np.uint8).any(), "wrote outside the destination view"
 
 
+@pytest.mark.parametrize("dt", [np.uint8, np.float32, np.int32], ids=lambda d: np.dtype(d).name)
 @pytest.mark.parametrize("to_planar", [True, False], ids=["to-planar", "to-interleaved"])
-def test_reformat_rgb8_vector_kernel(pkg, to_planar):
-    """RGB8 between packed interleaved and planar with every row on a 16-byte boundary takes the vector kernel (16 pixels
-    per thread, byte permutes); kernel path 1 keeps the word-per-channel kernel on the same data. Widths with and without
-    a ragged end (views of wider storage keep the rows aligned), heights that end inside a thread's pair of rows."""
+def test_reformat_rgb_vector_kernels(pkg, to_planar, dt):
+    """Three channels of 8 or 32 bits between packed interleaved and planar with every row on a 16-byte boundary take the
+    vector kernels (16 or 4 pixels per thread); kernel path 1 keeps the word-per-channel kernel on the same data. Widths
+    with and without a ragged end (views of wider storage keep the rows aligned), heights that end inside a thread's pair of rows."""
     from gpu_util import kernel_path
     rng = np.random.default_rng(11)
+    TD = _TORCH_DTYPE[np.dtype(dt)]
     for (n, h, w, W) in ((2, 37, 528, 528), (3, 5, 16, 16), (2, 9, 45, 64), (1, 1, 7, 16), (2, 18, 1000, 1008)):
-        data = _data(rng, (n, h, w, 3), np.uint8)  # logical NHWC content
+        data = _data(rng, (n, h, w, 3), dt)  # logical NHWC content
         if to_planar:
-            src = torch.zeros((n, h, W, 3), dtype=torch.uint8, device="cuda")
+            src = torch.zeros((n, h, W, 3), dtype=TD, device="cuda")
             src[:, :, :w] = to_dev(data)
             src_view, sl, dl = src[:, :, :w], "NHWC", "NCHW"
-            store = torch.zeros((n, 3, h, W), dtype=torch.uint8, device="cuda")
+            store = torch.zeros((n, 3, h, W), dtype=TD, device="cuda")
             dst_view = store[:, :, :, :w]
             want = np.transpose(data, (0, 3, 1, 2))
         else:
-            src = torch.zeros((n, 3, h, W), dtype=torch.uint8, device="cuda")
+            src = torch.zeros((n, 3, h, W), dtype=TD, device="cuda")
             src[:, :, :, :w] = to_dev(np.ascontiguousarray(np.transpose(data, (0, 3, 1, 2))))
             src_view, sl, dl = src[:, :, :, :w], "NCHW", "NHWC"
-            store = torch.zeros((n, h, W, 3), dtype=torch.uint8, device="cuda")
+            store = torch.zeros((n, h, W, 3), dtype=TD, device="cuda")
             dst_view = store[:, :, :w]
             want = data
         for path in (0, 1):
@@ -92,7 +94,7 @@ def test_reformat_rgb8_vector_kernel(pkg, to_planar):
             with kernel_path(pkg, path):
                 pkg.reformat_into(dst_view, src_view, src_layout=sl, dst_layout=dl)
             torch.cuda.synchronize()
-            assert np.array_equal(dst_view.cpu().numpy(), want), (n, h, w, W, path)
+            assert np.array_equal(dst_view.cpu().numpy().view(np.uint8), np.ascontiguousarray(want).view(np.uint8)), (n, h, w, W, path)
             rest = store.clone()
             if to_planar:
                 rest[:, :, :, :w] = 0
