@@ -143,6 +143,16 @@ __device__ __forceinline__ unsigned load_packed(const uint8_t *p, bool vector)
 {
     if (C == 4 && vector)
         return *reinterpret_cast<const unsigned *>(p);
+    if (C == 3 && vector)
+    {
+        // rows on word boundaries: the aligned word that holds the pixel's first byte and, only when the pixel runs past
+        // it, the next one (which then holds the pixel's last byte, so it lies inside the image); byte 3 is not used
+        const unsigned  shift = static_cast<unsigned>(reinterpret_cast<unsigned long long>(p) & 3ull);
+        const unsigned *w     = reinterpret_cast<const unsigned *>(p - shift);
+        const unsigned  lo    = w[0];
+        const unsigned  hi    = shift >= 2 ? w[1] : 0u;
+        return __funnelshift_r(lo, hi, shift * 8);
+    }
     unsigned w = p[0];
     if (C > 1)
         w |= static_cast<unsigned>(p[1]) << 8 | static_cast<unsigned>(p[2]) << 16;
@@ -224,11 +234,12 @@ __global__ void __launch_bounds__(256, INTERP == B200PP_INTERP_LINEAR && sizeof(
         const float scaleW = __fdiv_rn(static_cast<float>(cropW), static_cast<float>(D.w));
         const float scaleH = __fdiv_rn(static_cast<float>(cropH), static_cast<float>(D.h));
         // whole-pixel vector accesses when every address involved is a multiple of the pixel size
-        const bool vector = C != 3
-                         && ((reinterpret_cast<unsigned long long>(S.base) | reinterpret_cast<unsigned long long>(D.base)
-                              | static_cast<unsigned long long>(S.pitch) | static_cast<unsigned long long>(D.pitch))
-                             & (kPix - 1))
-                                == 0;
+        // (three uint8 channels: word loads need the source rows on 4-byte boundaries; stores stay byte by byte)
+        const bool vectorFlag = C != 3 ? ((reinterpret_cast<unsigned long long>(S.base) | reinterpret_cast<unsigned long long>(D.base)
+                                           | static_cast<unsigned long long>(S.pitch) | static_cast<unsigned long long>(D.pitch))
+                                          & (kPix - 1))
+                                             == 0
+                                       : (kFast && ((reinterpret_cast<unsigned long long>(S.base) | static_cast<unsigned long long>(S.pitch)) & 3ull) == 0);
 
         // ---- columns: source byte offsets and weights, once per thread and sample
         int    off0[kPlainCols], off1[kPlainCols];
@@ -263,7 +274,10 @@ __global__ void __launch_bounds__(256, INTERP == B200PP_INTERP_LINEAR && sizeof(
             }
         }
 
-        // ---- rows
+        // ---- rows. The body is compiled twice, with the vector-access decision as a constant: as a run-time flag both
+        // forms of every load and store were issued under predicates, a quarter of all issue slots.
+        auto rows = [&](auto vectorTag) {
+            constexpr bool vector = decltype(vectorTag)::value;
 #pragma unroll 1
         for (int j = 0; j < kPlainRows; ++j)
         {
@@ -381,6 +395,11 @@ __global__ void __launch_bounds__(256, INTERP == B200PP_INTERP_LINEAR && sizeof(
                 }
             }
         }
+        };
+        if (vectorFlag)
+            rows(std::true_type{});
+        else
+            rows(std::false_type{});
     }
 }
 
