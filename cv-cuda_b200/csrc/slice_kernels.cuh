@@ -190,7 +190,7 @@ __device__ __forceinline__ void store_four(uint8_t *d, float a, float b, float c
 }
 
 template<int DK>
-__global__ void __launch_bounds__(256, 5) slice_u8x3_kernel(const SliceKParams p, const int dstType, const int vecStore)
+__global__ void __launch_bounds__(256, 4) slice_u8x3_kernel(const SliceKParams p, const int dstType, const int vecStore)
 {
     const int j0 = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
     const int iBase = blockIdx.y * (blockDim.y * kSliceRowsPerThread) + threadIdx.y;
@@ -210,37 +210,58 @@ __global__ void __launch_bounds__(256, 5) slice_u8x3_kernel(const SliceKParams p
         const bool colsFast = cols == 4 && j0 + 3 < s.cw && xlo >= 0 && xlo + 3 < s.w;
         const bool rowAligned = (reinterpret_cast<unsigned long long>(s.img) & 3ull) == 0 && (s.pitch & 3ll) == 0;
 
-#pragma unroll 1
+        // Pass 1: the aligned source words of all of the thread's rows are requested before any arithmetic, so that
+        // sixteen loads are in flight per thread instead of four. mode: 0 no such row, 1 words loaded, 2 fast but
+        // unaligned (bytes, pass 2), 3 edge / border (slice_pixel, pass 2).
+        unsigned tw[kSliceRowsPerThread][4];
+        int      mode[kSliceRowsPerThread];
+        unsigned shiftBits = 0;
+#pragma unroll
         for (int r = 0; r < kSliceRowsPerThread; ++r)
         {
             const int i = iBase + r * blockDim.y;
-            if (i >= p.dstH)
-                break;
             const int y = flipY ? s.ch - 1 - i + s.cy : i + s.cy;
-            if (!(colsFast && i < s.ch && y >= 0 && y < s.h))
+            mode[r]     = i >= p.dstH ? 0 : ((colsFast && i < s.ch && y >= 0 && y < s.h) ? 2 : 3);
+            tw[r][0] = tw[r][1] = tw[r][2] = tw[r][3] = 0;
+            if (mode[r] == 2)
+            {
+                const uint8_t           *rowPtr = s.img + y * s.pitch;
+                const unsigned long long addr   = reinterpret_cast<unsigned long long>(rowPtr + 3ll * xlo);
+                if (rowAligned && (addr & ~3ull) + 16 <= reinterpret_cast<unsigned long long>(rowPtr) + static_cast<unsigned long long>(s.pitch))
+                {
+                    // aligned window of four words inside the row's pitch
+                    const unsigned *wp = reinterpret_cast<const unsigned *>(addr & ~3ull);
+                    shiftBits          = static_cast<unsigned>(addr & 3ull) * 8; // the same for every row: pitch % 4 == 0
+                    tw[r][0] = __ldg(wp), tw[r][1] = __ldg(wp + 1), tw[r][2] = __ldg(wp + 2), tw[r][3] = __ldg(wp + 3);
+                    mode[r] = 1;
+                }
+            }
+        }
+
+#pragma unroll
+        for (int r = 0; r < kSliceRowsPerThread; ++r)
+        {
+            const int i = iBase + r * blockDim.y;
+            if (mode[r] == 0)
+                break;
+            if (mode[r] == 3)
             {
                 for (int q = 0; q < cols; ++q) slice_pixel<3>(p, s, n, i, j0 + q, B200PP_U8, dstType, 1, base, mul);
                 continue;
             }
-
             // twelve source bytes as three words, byte 3q+c = channel c of source pixel xlo+q
-            const uint8_t           *rowPtr = s.img + y * s.pitch;
-            const uint8_t           *a      = rowPtr + 3ll * xlo;
-            const unsigned long long addr   = reinterpret_cast<unsigned long long>(a);
-            unsigned                 w0, w1, w2;
-            if (rowAligned && (addr & ~3ull) + 16 <= reinterpret_cast<unsigned long long>(rowPtr) + static_cast<unsigned long long>(s.pitch))
+            unsigned w0, w1, w2;
+            if (mode[r] == 1)
             {
-                // aligned window of four words inside the row's pitch; shift the twelve bytes into place
-                const unsigned *wp = reinterpret_cast<const unsigned *>(addr & ~3ull);
-                const unsigned  sh = static_cast<unsigned>(addr & 3ull) * 8;
-                const unsigned  t0 = __ldg(wp), t1 = __ldg(wp + 1), t2 = __ldg(wp + 2), t3 = __ldg(wp + 3);
-                w0 = __funnelshift_r(t0, t1, sh);
-                w1 = __funnelshift_r(t1, t2, sh);
-                w2 = __funnelshift_r(t2, t3, sh);
+                w0 = __funnelshift_r(tw[r][0], tw[r][1], shiftBits);
+                w1 = __funnelshift_r(tw[r][1], tw[r][2], shiftBits);
+                w2 = __funnelshift_r(tw[r][2], tw[r][3], shiftBits);
             }
             else
             {
-                unsigned b[12];
+                const int      y = flipY ? s.ch - 1 - i + s.cy : i + s.cy;
+                const uint8_t *a = s.img + y * s.pitch + 3ll * xlo;
+                unsigned       b[12];
 #pragma unroll
                 for (int k = 0; k < 12; ++k) b[k] = a[k];
                 w0 = b[0] | b[1] << 8 | b[2] << 16 | b[3] << 24;
