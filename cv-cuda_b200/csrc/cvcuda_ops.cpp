@@ -180,6 +180,7 @@ struct ImageView
     uint8_t *base = nullptr;
     int      dtype = -1;
     int      elemChannels = 1; // channels carried by the element type itself (3U8 -> 3)
+    int64_t  elements = 0;     // product of the shape, whatever the layout
     char     layout[NVCV_TENSOR_MAX_RANK + 1] = "";
 };
 
@@ -200,6 +201,8 @@ bool export_tensor(NVCVTensorHandle h, ImageView &v, const char *what, NVCVStatu
     v.base  = d.strided.basePtr;
     std::memcpy(v.layout, d.layout.data, sizeof(v.layout));
     v.layout[NVCV_TENSOR_MAX_RANK] = 0;
+    v.elements = d.rank >= 1 ? 1 : 0;
+    for (int i = 0; i < d.rank; ++i) v.elements *= d.shape[i];
 
     int iN = -1, iC = -1, iH = -1, iW = -1;
     for (int i = 0; i < d.rank; ++i)
@@ -478,9 +481,11 @@ NVCVStatus plain_resize_varshape(NVCVOperatorHandle handle, cudaStream_t stream,
 
 // ---------------------------------------------------------------------------------------------- stand-alone Normalize
 
-// base / scale tensor -> pointer and the four broadcast strides (a dimension of extent 1 gets stride 0).
-bool param_tensor(NVCVTensorHandle h, const char *what, int samples, int channels, const float *&ptr, int64_t (&stride)[4],
-                  NVCVStatus &status)
+// base / scale tensor -> pointer and the four broadcast strides (a dimension of extent 1 gets stride 0). Every extent must
+// be 1 or the input's (src/cvcuda/priv/legacy/normalize.cu:300-306, checkParamShape); rows / cols < 0 stands for a
+// variable-shape input, whose images have no common size, so only extent 1 fits there.
+bool param_tensor(NVCVTensorHandle h, const char *what, int samples, int rows, int cols, int channels, const float *&ptr,
+                  int64_t (&stride)[4], NVCVStatus &status)
 {
     ImageView v;
     char      msg[96];
@@ -492,9 +497,12 @@ bool param_tensor(NVCVTensorHandle h, const char *what, int samples, int channel
         status = report(B200PP_ERROR_INVALID_ARGUMENT, "Input %s must be a float32 (N)HWC tensor", what);
         return false;
     }
-    if (!(v.samples == 1 || v.samples >= samples) || !(v.channels == 1 || v.channels >= channels))
+    if (!(v.samples == 1 || v.samples == samples) || !(v.channels == 1 || v.channels == channels)
+        || !(v.rows == 1 || v.rows == rows) || !(v.cols == 1 || v.cols == cols))
     {
-        status = report(B200PP_ERROR_INVALID_ARGUMENT, "Input %s cannot be broadcast to the input's samples / channels", what);
+        status = report(B200PP_ERROR_INVALID_ARGUMENT,
+                        "Input %s has shape [%d,%d,%d,%d]: every extent must be 1 or equal to the input's", what, v.samples,
+                        v.rows, v.cols, v.channels);
         return false;
     }
     ptr       = reinterpret_cast<const float *>(v.base);
@@ -513,8 +521,9 @@ NVCVStatus normalize_common(NVCVOperatorHandle handle, cudaStream_t stream, cons
     NVCVStatus        st = B200PP_SUCCESS;
     B200ppNormalizeOp op;
     std::memset(&op, 0, sizeof(op));
-    if (!param_tensor(base, "base", s.numSamples, s.channels, op.base, op.baseStride, st)
-        || !param_tensor(scale, "scale", s.numSamples, s.channels, op.scale, op.scaleStride, st))
+    const int rows = s.imageList ? -1 : s.height, cols = s.imageList ? -1 : s.width;
+    if (!param_tensor(base, "base", s.numSamples, rows, cols, s.channels, op.base, op.baseStride, st)
+        || !param_tensor(scale, "scale", s.numSamples, rows, cols, s.channels, op.scale, op.scaleStride, st))
         return st;
     op.gscale  = gscale;
     op.shift   = shift;
@@ -1125,6 +1134,21 @@ extern "C" NVCVStatus cvcudaCropFlipNormalizeReformatSubmit(NVCVOperatorHandle h
     if (!o.valid || !bs.valid || !sc.valid || !cr.valid)
         return report(B200PP_ERROR_INVALID_ARGUMENT, "Output, base, scale and cropRect must be image-like tensors");
 
+    // The reference reads these tensors through typed accessors without looking at their element types or extents
+    // (OpCropFlipNormalizeReformat.cu:208-215); here a mismatch is refused before any pointer is reinterpreted.
+    if (fc.dtype != B200PP_S32 || cr.dtype != B200PP_S32)
+        return report(B200PP_ERROR_INVALID_ARGUMENT, "flipCode and cropRect must be int32 tensors");
+    if (bs.dtype != B200PP_F32 || sc.dtype != B200PP_F32)
+        return report(B200PP_ERROR_INVALID_ARGUMENT, "base and scale must be float32 tensors");
+    if (fc.elements < b.numImages)
+        return report(B200PP_ERROR_INVALID_ARGUMENT, "flipCode must hold one code per input image: %lld for %d images",
+                      static_cast<long long>(fc.elements), b.numImages);
+    if (cr.samples < b.numImages || cr.elements < int64_t(4) * cr.samples)
+        return report(B200PP_ERROR_INVALID_ARGUMENT,
+                      "cropRect must hold four int32 values per input image: shape [N,1,1,4] with N >= %d", b.numImages);
+    if (b.varShapeStrided.uniqueFormat == 0)
+        return report(B200PP_ERROR_INVALID_ARGUMENT, "All images of the input batch must have the same format");
+
     int channels = 0, planes = 0, kind = -1, bits[4] = {0, 0, 0, 0};
     nvcv().imageFormatGetNumChannels(b.varShapeStrided.uniqueFormat, &channels);
     nvcv().imageFormatGetNumPlanes(b.varShapeStrided.uniqueFormat, &planes);
@@ -1141,6 +1165,12 @@ extern "C" NVCVStatus cvcudaCropFlipNormalizeReformatSubmit(NVCVOperatorHandle h
         return report(B200PP_ERROR_INVALID_ARGUMENT, "Unsupported output data type");
     if (!layout_is(o, "NHWC", "NCHW"))
         return report(B200PP_ERROR_INVALID_ARGUMENT, "Invalid tensor layout in output");
+    // The kernel writes numImages samples of the input's channel count (OpCropFlipNormalizeReformat.cu:264-267 sizes its
+    // grid by the input batch): a smaller output would be overrun.
+    if (o.samples < b.numImages || o.channels < channels)
+        return report(B200PP_ERROR_INVALID_ARGUMENT,
+                      "Output must have at least the input's samples and channels: %d x %d provided for %d x %d",
+                      o.samples, o.channels, b.numImages, channels);
 
     B200ppSource s;
     std::memset(&s, 0, sizeof(s));

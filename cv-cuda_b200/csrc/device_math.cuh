@@ -190,10 +190,15 @@ __device__ __forceinline__ Geom load_geom(const ResizeKParams &p, int n)
     g.image = g.base;
     if (p.roi)
     {
-        const int *r = reinterpret_cast<const int *>(reinterpret_cast<const char *>(p.roi) + n * p.roiStride);
-        g.base += static_cast<long long>(r[1]) * g.pitch + 3LL * r[0];
-        g.w = r[2];
-        g.h = r[3];
+        // The rectangle is intersected with the image before anything is addressed through it; a rectangle that misses the
+        // image, or has no area, shrinks to the nearest single pixel. For rectangles inside the image (the contract)
+        // nothing changes.
+        const int *r  = reinterpret_cast<const int *>(reinterpret_cast<const char *>(p.roi) + n * p.roiStride);
+        const int  x0 = min(max(r[0], 0), max(g.w - 1, 0)), y0 = min(max(r[1], 0), max(g.h - 1, 0));
+        const int  x1 = min(max(r[0] + max(r[2], 1), x0 + 1), max(g.w, 1)), y1 = min(max(r[1] + max(r[3], 1), y0 + 1), max(g.h, 1));
+        g.base += static_cast<long long>(y0) * g.pitch + 3LL * x0;
+        g.w = x1 - x0;
+        g.h = y1 - y0;
     }
     g.flip = p.flip ? p.flip[n] : 2;
     if (p.list || p.roi)

@@ -99,8 +99,11 @@ __device__ __forceinline__ void store_plain(uint8_t *p, const PlainPixel<T, C> &
     }
 }
 
-// rint(|sum|) clamped to the element type's range (ResizeUtils.cpp:226-234); float32 elements keep the blend as it is,
-// like the reference's CUDA operator.
+// The blend rounded half to even and clamped to the element type's range (ResizeUtils.cpp:226-234). The golden rounds
+// |sum|; for unsigned types that is the same thing, and for int16 the sign is kept, as the reference's CUDA operators
+// do (src/cvcuda/priv/OpResize.cu:228-262 saturate-cast the signed blend) -- the golden's fabs would turn a negative
+// blend positive, which its own tests never reach (int16 rows are nearest only). float32 elements keep the blend as it
+// is, like the reference's CUDA operator.
 template<typename T>
 __device__ __forceinline__ T finish_linear(double sum)
 {
@@ -108,7 +111,7 @@ __device__ __forceinline__ T finish_linear(double sum)
         return static_cast<float>(sum);
     else
     {
-        const double r  = rint(fabs(sum));
+        const double r  = rint(T(-1) < T(0) ? sum : fabs(sum));
         const double lo = T(-1) < T(0) ? -32768.0 : 0.0;
         const double hi = sizeof(T) == 1 ? 255.0 : (T(-1) < T(0) ? 32767.0 : 65535.0);
         return static_cast<T>(r < lo ? lo : (r > hi ? hi : r));

@@ -112,7 +112,8 @@ __device__ __forceinline__ void slice_pixel(const SliceKParams &p, const SliceSa
     int y = (s.flip == 0 || s.flip == -1) ? s.ch - 1 - i + s.cy : i + s.cy;
 
     bool inside = (x >= 0 && x < s.w && y >= 0 && y < s.h);
-    if (!inside && p.border != B200PP_BORDER_CONSTANT)
+    // an empty image has no pixel to replicate, wrap or reflect: every rule then answers with the constant
+    if (!inside && p.border != B200PP_BORDER_CONSTANT && s.w >= 1 && s.h >= 1)
     {
         x      = border_index(x, s.w, p.border);
         y      = border_index(y, s.h, p.border);

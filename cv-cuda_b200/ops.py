@@ -322,7 +322,9 @@ class ImageBatchVarShape:
                     arr[i].numPlanes = 1
                     arr[i].planes[0] = _ImagePlane(w, h, im.stride(0) * es, im.data_ptr())
             host = torch.frombuffer(bytearray(bytes(arr)), dtype=torch.uint8).pin_memory()
-            self._table = host.to(self.device, non_blocking=True)
+            # a blocking copy: the table is complete before this returns, so a kernel launched on any stream sees it
+            # (the launch stream is the caller's choice and need not be torch's current stream)
+            self._table = host.to(self.device, non_blocking=False)
         return self._table
 
 
@@ -635,7 +637,11 @@ def random_resized_crop_into(dst, src, min_scale: float = 0.08, max_scale: float
         sizes = [(src.shape[-2], src.shape[-3])] * (src.shape[0] if src.dim() == 4 else 1)
     rects = random_crop_rects(sizes, min_scale, max_scale, min_ratio, max_ratio, seed)
     dev = src.device if isinstance(src, ImageBatchVarShape) or src.is_cuda else torch.device("cuda", torch.cuda.current_device())
+    # a blocking upload from pageable memory: complete before the launch, whatever stream that is on
     table = torch.tensor(rects, dtype=torch.int32).reshape(-1, 4).to(dev)
+    if stream is not None:
+        # the table goes back to torch's caching allocator when this function returns; tell it which stream still reads it
+        table.record_stream(stream if isinstance(stream, torch.cuda.Stream) else torch.cuda.ExternalStream(int(stream)))
     return resized_crop_into(dst, src, table, interp, stream=stream)
 
 
@@ -685,13 +691,18 @@ def resize(src: Union[torch.Tensor, ImageBatchVarShape], shape_or_sizes, interp:
 
 # ------------------------------------------------------------------------------------------------ stand-alone Normalize
 
-def _broadcast_param(t: torch.Tensor, what: str):
+def _broadcast_param(t: torch.Tensor, what: str, extents):
     """Pointer and the four byte strides (sample, row, column, channel; 0 where the extent is 1) of a float32 CUDA
-    parameter tensor of rank 1 to 4, aligned to the right ((N)HWC)."""
+    parameter tensor of rank 1 to 4, aligned to the right ((N)HWC). ``extents`` = the input's (N, H, W, C), H and W being
+    None for an image batch: every extent of the parameter must be 1 or the input's
+    (src/cvcuda/priv/legacy/normalize.cu:300-306)."""
     if not t.is_cuda or t.dtype != torch.float32 or t.dim() < 1 or t.dim() > 4:
         raise Error(Status.ERROR_INVALID_ARGUMENT, f"Input {what} must be cuda-accessible, pitch-linear tensor")
     shape = (1,) * (4 - t.dim()) + tuple(t.shape)
     stride = (0,) * (4 - t.dim()) + tuple(t.stride())
+    if any(shape[k] != 1 and shape[k] != extents[k] for k in range(4)):
+        raise Error(Status.ERROR_INVALID_ARGUMENT,
+                    f"Input {what} has shape {shape}: every extent must be 1 or equal to the input's")
     return t.data_ptr(), (C.c_int64 * 4)(*[0 if shape[k] == 1 else stride[k] * 4 for k in range(4)])
 
 
@@ -706,8 +717,10 @@ def normalize_into(dst, src, base: torch.Tensor, scale: torch.Tensor, flags: Opt
     s, keep_s = _image_set(src, "Input")
     d, keep_d = _image_set(dst, "Output")
     op = _NormalizeOp()
-    op.base, op.baseStride = _broadcast_param(base, "base")
-    op.scale, op.scaleStride = _broadcast_param(scale, "scale")
+    extents = (s.numSamples, None, None, s.channels) if isinstance(src, ImageBatchVarShape) \
+        else (s.numSamples, s.height, s.width, s.channels)
+    op.base, op.baseStride = _broadcast_param(base, "base", extents)
+    op.scale, op.scaleStride = _broadcast_param(scale, "scale", extents)
     op.gscale, op.shift, op.epsilon, op.flags = float(globalscale), float(globalshift), float(epsilon), int(flags or 0)
     _check(lib().b200ppNormalize(C.byref(s), C.byref(d), C.byref(op), _stream_handle(stream)))
     return dst

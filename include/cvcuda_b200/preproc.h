@@ -152,7 +152,10 @@ typedef struct B200ppResizeOp
     float   padValue;
 
     /* Optional per-sample device arrays. roi: int32 (x, y, w, h) per sample, roiStride bytes apart (0 = packed): the
-     * sample's source is that sub-view of its image. flipCode: packed int32 per sample, applied to region coordinates
+     * sample's source is that sub-view of its image. Contract: the rectangle lies inside the image and has w, h >= 1; the
+     * kernels intersect it with the image before addressing through it (a rectangle that misses the image shrinks to
+     * the nearest single pixel), so a bad rectangle gives meaningless pixels but no access outside the image.
+     * flipCode: packed int32 per sample, applied to region coordinates
      * after the resize with the reference's codes (1 mirror x, 0 mirror y, -1 both, anything else none). */
     const int32_t *roi;
     int64_t        roiStride;

@@ -32,7 +32,10 @@ typedef struct OraclePlainImage
  * interpolation the reference golden rounds the blend to an integer and clamps it to [FLT_MIN, FLT_MAX]
  * (ResizeUtils.cpp:226-234 with std::numeric_limits<float>::min()); with goldenFloat == 0 the blend is stored as
  * computed, which is what the reference's CUDA operator does (src/cvcuda/priv/OpResize.cu:228-262) and what the
- * product implements. Returns 0, or -1 for arguments it does not cover. */
+ * product implements. The same flag covers the golden's other quirk: it rounds fabs(blend) (ResizeUtils.cpp:226), so a
+ * negative int16 blend comes out positive; with goldenFloat == 0 the signed blend is rounded and clamped, as the
+ * reference's CUDA operators do (their tests run int16 with nearest only, so the golden's sign flip is never
+ * exercised). Returns 0, or -1 for arguments it does not cover. */
 int oracle_resize_plain(const OraclePlainImage *src, const OraclePlainImage *dst, int32_t n, int32_t dtype,
                         int32_t channels, int32_t interp, int32_t goldenFloat);
 

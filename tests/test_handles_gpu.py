@@ -95,3 +95,41 @@ def test_cfnr_submit(pkg, ops, oracle, idx):
     torch.cuda.synchronize()
     assert_parity(tdst.cpu().numpy(), want, what=f"row {idx}")
     ops.nvcvOperatorDestroy(h_op)
+
+
+def test_cfnr_submit_refuses_tensors_it_would_overrun_or_misread(pkg, ops):
+    """An output with fewer samples or channels than the batch, flipCode / cropRect that are not int32 or hold too few
+    entries, base / scale that are not float32: INVALID_ARGUMENT before anything is launched. (The reference's typed
+    accessors would read or write past the tensors, src/cvcuda/priv/OpCropFlipNormalizeReformat.cu:208-215,264-267.)"""
+    rng = np.random.default_rng(3)
+    images = [rng.integers(0, 256, (20, 24, 3), dtype=np.uint8) for _ in range(3)]
+    batch = pkg.ImageBatchVarShape(padded_images(images))
+    good = dict(out=torch.zeros((3, 3, 16, 16), dtype=torch.float32, device="cuda"),
+                rect=to_dev(np.tile(np.asarray([0, 0, 16, 16], np.int32), (3, 1)).reshape(3, 1, 1, 4)),
+                flip=to_dev(np.zeros(3, np.int32)), base=to_dev(np.zeros((1, 1, 1, 3), np.float32)),
+                scale=to_dev(np.ones((1, 1, 1, 3), np.float32)))
+    h_op = C.c_void_p()
+    assert ops.cvcudaCropFlipNormalizeReformatCreate(C.byref(h_op)) == 0
+
+    def submit(**over):
+        a = dict(good, **over)
+        st = ops.cvcudaCropFlipNormalizeReformatSubmit(
+            h_op, _stream(), NF.image_batch_handle(batch, "u", 8), NF.tensor_handle(a["out"], "NCHW"),
+            NF.tensor_handle(a["rect"], "NHWC"), 0, 0.0, NF.tensor_handle(a["flip"], "N"), NF.tensor_handle(a["base"], "NHWC"),
+            NF.tensor_handle(a["scale"], "NHWC"), 1.0, 0.0, 0.0, 0)
+        torch.cuda.synchronize()
+        return st
+
+    assert submit() == 0, NF.fake().fakeLastMessage()
+    bad = [dict(out=torch.zeros((2, 3, 16, 16), dtype=torch.float32, device="cuda")),
+           dict(out=torch.zeros((3, 2, 16, 16), dtype=torch.float32, device="cuda")),
+           dict(flip=to_dev(np.zeros(2, np.int32))),
+           dict(flip=to_dev(np.zeros(3, np.float32))),
+           dict(rect=to_dev(np.zeros((2, 1, 1, 4), np.int32))),
+           dict(rect=to_dev(np.zeros((3, 1, 1, 2), np.int32))),
+           dict(rect=to_dev(np.zeros((3, 1, 1, 4), np.float32))),
+           dict(base=to_dev(np.zeros((1, 1, 1, 3), np.int32))),
+           dict(scale=to_dev(np.zeros((1, 1, 1, 3), np.uint8)))]
+    for over in bad:
+        assert submit(**over) == 2, f"accepted {list(over)}"
+    ops.nvcvOperatorDestroy(h_op)

@@ -127,6 +127,41 @@ def test_normalize_strided_views_and_errors(pkg, oracle):
     assert pkg.normalize(torch.empty((0, 4, 4, 3), dtype=torch.uint8, device="cuda"), b, s).shape == (0, 4, 4, 3)
 
 
+def test_normalize_refuses_base_and_scale_shapes_that_do_not_broadcast(pkg):
+    """Every extent of base / scale must be 1 or the input's (src/cvcuda/priv/legacy/normalize.cu:300-306); for an image
+    batch, whose images have no common size, rows and columns must be 1. Checked through the Python mirror and through
+    the operator symbols."""
+    INVALID = pkg.ops.Status.ERROR_INVALID_ARGUMENT
+    src = torch.zeros((2, 8, 6, 3), dtype=torch.uint8, device="cuda")
+    dst = torch.zeros_like(src)
+    one = torch.ones((1, 1, 1, 3), dtype=torch.float32, device="cuda")
+    shapes = [(1, 2, 1, 3), (1, 1, 5, 3), (3, 1, 1, 3), (1, 1, 1, 4), (1, 1, 1, 2), (1, 16, 1, 3)]
+    batch = pkg.ImageBatchVarShape([torch.zeros((8, 6, 3), dtype=torch.uint8, device="cuda") for _ in range(2)])
+    bout = pkg.ImageBatchVarShape([torch.zeros((8, 6, 3), dtype=torch.uint8, device="cuda") for _ in range(2)])
+    ops = NF.bind_operators(pkg.lib_path())
+    stream = torch.cuda.current_stream().cuda_stream
+    h_op = C.c_void_p()
+    assert ops.cvcudaNormalizeCreate(C.byref(h_op)) == 0
+    for shape in shapes + [(1, 8, 6, 3)]:
+        p = torch.ones(shape, dtype=torch.float32, device="cuda")
+        full = shape == (1, 8, 6, 3)  # fits the tensor, not the image batch
+        for args in ((dst, src, p, one), (dst, src, one, p), (bout, batch, p, one)):
+            if full and args[0] is dst:
+                pkg.normalize_into(*args)
+                continue
+            with pytest.raises(pkg.ops.Error) as e:
+                pkg.normalize_into(*args)
+            assert e.value.status == INVALID
+        st = ops.cvcudaNormalizeSubmit(h_op, stream, NF.tensor_handle(src, "NHWC"), NF.tensor_handle(p, "NHWC"),
+                                       NF.tensor_handle(one, "NHWC"), NF.tensor_handle(dst, "NHWC"), 1.0, 0.0, 0.0, 0)
+        assert st == (0 if full else 2), shape
+        st = ops.cvcudaNormalizeVarShapeSubmit(h_op, stream, NF.image_batch_handle(batch), NF.tensor_handle(one, "NHWC"),
+                                               NF.tensor_handle(p, "NHWC"), NF.image_batch_handle(bout), 1.0, 0.0, 0.0, 0)
+        assert st == 2, shape
+    torch.cuda.synchronize()
+    ops.nvcvOperatorDestroy(h_op)
+
+
 def test_normalize_through_operator_symbols(pkg, oracle):
     ops = NF.bind_operators(pkg.lib_path())
     stream = torch.cuda.current_stream().cuda_stream

@@ -51,3 +51,15 @@ def test_float_linear_without_the_golden_rounding(oracle):
     tiny = np.finfo(np.float32).tiny  # the golden clamps to [numeric_limits<float>::min(), max()]: zero becomes FLT_MIN
     assert np.all((a == np.rint(a)) | (a == tiny)) and np.abs(a - b).max() <= 0.5
     assert not np.array_equal(a, b)
+
+
+def test_int16_linear_keeps_the_sign_unlike_the_golden(oracle):
+    """The golden rounds |blend| (ResizeUtils.cpp:226); the product follows the reference's CUDA operators, which keep the
+    sign of an int16 blend. On non-negative data the two forms agree."""
+    neg = np.full((6, 7, 3), -100, np.int16)
+    assert np.all(oracle.resize_plain([neg], [(13, 9)], 1, golden_float=False)[0] == -100)
+    assert np.all(oracle.resize_plain([neg], [(13, 9)], 1, golden_float=True)[0] == 100)
+    rng = np.random.default_rng(4)
+    pos = rng.integers(0, 32768, (9, 11, 3)).astype(np.int16)
+    assert np.array_equal(oracle.resize_plain([pos], [(20, 17)], 1, golden_float=False)[0],
+                          oracle.resize_plain([pos], [(20, 17)], 1, golden_float=True)[0])

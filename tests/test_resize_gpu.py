@@ -85,6 +85,35 @@ def test_resize_types_channels_strides(pkg, oracle, dt, ch, interp):
         assert not frame.any(), "wrote outside the destination view"
 
 
+def test_resize_negative_int16_keeps_its_sign(pkg, oracle):
+    """Linear interpolation of negative int16 data gives negative results, as the reference's CUDA operators do
+    (src/cvcuda/priv/OpResize.cu:228-262 saturate-cast the signed blend). The reference's CPU golden rounds |blend|
+    (tests/cvcuda/system/ResizeUtils.cpp:226) and would answer +100 for an image of -100; its tests never run int16 with
+    linear interpolation. Tensor and variable-shape forms, Resize and the resized crop of RandomResizedCrop."""
+    rng = np.random.default_rng(17)
+    flat = np.full((2, 20, 24, 3), -100, np.int16)
+    got = pkg.resize(to_dev(flat), (2, 31, 45, 3), 1).cpu().numpy()
+    assert np.all(got == -100)
+    images = [rng.integers(-32768, 0, (h, w, 3)).astype(np.int16) for (w, h) in ((33, 21), (18, 40))]
+    sizes = [(50, 30), (11, 17)]
+    want = oracle.resize_plain(images, sizes, 1)
+    assert all((w < 0).all() for w in want)
+    got = pkg.resize(pkg.ImageBatchVarShape(padded_images(images, pad_to=32)), sizes, 1)
+    torch.cuda.synchronize()
+    for i in range(2):
+        _same(got[i].cpu().numpy(), want[i], f"var-shape image {i}")
+    same = [rng.integers(-32768, 0, (26, 35, 3)).astype(np.int16) for _ in range(2)]
+    _same(pkg.resize(to_dev(np.stack(same)), (2, 40, 29, 3), 1).cpu().numpy(),
+          np.stack(oracle.resize_plain(same, [(29, 40)] * 2, 1)), "tensor")
+    rects = [(3, 2, 20, 15), (0, 5, 35, 11)]
+    want = oracle.resize_plain(same, [(16, 12)] * 2, 1, rects=rects)
+    assert all((w < 0).all() for w in want)
+    out = torch.empty((2, 12, 16, 3), dtype=torch.int16, device="cuda")
+    pkg.resized_crop_into(out, to_dev(np.stack(same)), to_dev(np.asarray(rects, np.int32)), 1)
+    torch.cuda.synchronize()
+    _same(out.cpu().numpy(), np.stack(want), "resized crop")
+
+
 def test_resize_degenerate_sizes(pkg, oracle):
     """1x1 sources and destinations; identity; sources one pixel wide or high with linear interpolation, where the
     reference golden itself would read outside the image: the result must be the replicated pixel row / column."""
