@@ -666,6 +666,78 @@ extern "C" int b200ppResizedCrop(const B200ppImageSet *src, const B200ppImageSet
     return resize_common(src, dst, interp, cropRects, stream);
 }
 
+// ------------------------------------------------------------------------------------------------------------------------
+// b200ppResizedCropNoAlloc: the resized crop for callers that must not allocate device memory.
+//
+// A crop-and-resize launch reads one rectangle per image from a device table. b200ppResizedCrop leaves that table to the
+// caller, who normally gets it from cudaMalloc (or from b200ppParamBufferCreate, which calls cudaMalloc). Some callers
+// cannot do that: a plug-in that runs inside an inference server's request path where every byte of device memory was
+// handed out at start-up, a process that shares its GPU with a model sized to fill it, code between two points of a
+// pipeline where a cudaMalloc would stall every stream of the device. For them the table lives in the library image
+// itself, in the fixed array below, and the rectangles arrive as an ordinary host array.
+//
+// The price: the array has a fixed capacity (B200PP_NO_ALLOC_MAX_RECTS rectangles = 64 KiB, held by every GPU that loads
+// the library until the process exits), and there is only one per GPU, so two such calls whose GPU work overlaps (on
+// two streams, or from two threads) overwrite each other's rectangles. Calls on one stream are ordered and safe.
+// Nothing in the table has to start at zero: a call overwrites the entries it uses before its kernel reads them and
+// never reads further; whatever an earlier call left beyond them is ignored.
+static __device__ __align__(256) int32_t g_noAllocRects[B200PP_NO_ALLOC_MAX_RECTS * 4];
+
+namespace {
+// In host code `g_noAllocRects` names a host-side shadow, not device memory: the device address has to be asked for,
+// once per device with that device current. Cached here per device ordinal.
+constexpr int kNoAllocMaxDevices = 64;
+std::mutex    g_noAllocMutex;
+int32_t      *g_noAllocRectsDev[kNoAllocMaxDevices] = {};
+} // namespace
+
+extern "C" int b200ppResizedCropNoAlloc(const B200ppImageSet *src, const B200ppImageSet *dst, const int32_t *hostRects,
+                                        int32_t interp, cudaStream_t stream)
+{
+    if (!src || !dst || !hostRects)
+        return fail(B200PP_ERROR_INVALID_ARGUMENT, "Null argument");
+    if (src->numSamples > B200PP_NO_ALLOC_MAX_RECTS)
+        return fail(B200PP_ERROR_INVALID_ARGUMENT,
+                    "b200ppResizedCropNoAlloc takes at most %d images per call (%d given): split the batch, or use "
+                    "b200ppResizedCrop with a rectangle table of your own",
+                    B200PP_NO_ALLOC_MAX_RECTS, src->numSamples);
+    if (src->numSamples <= 0) // nothing to upload; the common checks decide between "empty batch" and "negative size"
+        return b200ppResize(src, dst, interp, stream);
+    int device = -1;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kNoAllocMaxDevices)
+    {
+        cudaGetLastError();
+        return fail(B200PP_ERROR_INTERNAL, "No current CUDA device (or its ordinal is above %d)", kNoAllocMaxDevices - 1);
+    }
+    int32_t *table = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_noAllocMutex);
+        if (!g_noAllocRectsDev[device])
+        {
+            // first call on this device: look the array's device address up
+            void             *addr = nullptr;
+            const cudaError_t e    = cudaGetSymbolAddress(&addr, g_noAllocRects);
+            if (e != cudaSuccess || !addr)
+            {
+                cudaGetLastError();
+                return fail(B200PP_ERROR_INTERNAL, "Cannot locate the built-in rectangle table on device %d: %s", device,
+                            cudaGetErrorString(e));
+            }
+            g_noAllocRectsDev[device] = static_cast<int32_t *>(addr);
+        }
+        table = g_noAllocRectsDev[device];
+    }
+    // Pageable or page-locked host memory alike; ordered on `stream` before the kernel below.
+    const cudaError_t e = cudaMemcpyAsync(table, hostRects, sizeof(int32_t) * 4 * static_cast<size_t>(src->numSamples),
+                                          cudaMemcpyHostToDevice, stream);
+    if (e != cudaSuccess)
+    {
+        cudaGetLastError();
+        return fail(B200PP_ERROR_INTERNAL, "Upload of the crop rectangles failed: %s", cudaGetErrorString(e));
+    }
+    return resize_common(src, dst, interp, table, stream);
+}
+
 // Rows of CTAs for the table kernels (Normalize, ConvertTo): one per block of rows, up to the grid limit (the kernels
 // walk down the image in steps of the grid's height beyond it). Fewer, longer-lived CTAs were slower (227 vs 193 us on
 // 32 x 1080p RGB uint8 -> float32 with sixteen CTAs per SM): the table costs little next to the tail it creates.

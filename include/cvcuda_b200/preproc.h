@@ -224,6 +224,32 @@ B200PP_PUBLIC int b200ppResize(const B200ppImageSet *src, const B200ppImageSet *
 B200PP_PUBLIC int b200ppResizedCrop(const B200ppImageSet *src, const B200ppImageSet *dst, const int32_t *cropRects,
                                     int32_t interp, cudaStream_t stream);
 
+/* b200ppResizedCrop for callers that cannot allocate device memory. No counterpart in the reference: its
+ * RandomResizedCrop operator allocates its rectangle table with cudaMalloc when the operator is created.
+ *
+ * Who needs it: code that runs where cudaMalloc is off limits -- a pre-processing plug-in inside a serving process
+ * whose device memory was all handed out at start-up, a GPU shared with a model that fills it, a latency-critical
+ * stretch of a pipeline where the device-wide stall of an allocation is not acceptable. Such a caller still owns its
+ * images (src, dst: device memory as for b200ppResizedCrop) but has nowhere to put the per-image rectangle table the
+ * kernel reads. Here the table is an array built into the library, and the rectangles are passed from the HOST:
+ * hostRects = numSamples x (left, top, width, height) int32 in ordinary or page-locked host memory, copied to the
+ * built-in table on `stream` ahead of the kernel. The call allocates nothing, on the device or through any library.
+ *
+ * Limits and rules:
+ *  - at most B200PP_NO_ALLOC_MAX_RECTS images per call; more is refused with B200PP_ERROR_INVALID_ARGUMENT (split the
+ *    batch). The table costs 64 KiB of device memory on every GPU that loads the library, until the process exits;
+ *  - one table per GPU, shared by every call: calls whose GPU work can overlap (different streams, several threads)
+ *    race on it and read each other's rectangles. Issue them on one stream, or order them with events. The table keeps
+ *    the last call's rectangles; that is harmless, because a call overwrites every entry it reads;
+ *  - the first call on each device looks up the table's device address (once, with that device current). Make that first
+ *    call outside any stream capture; later calls only enqueue one copy and one kernel;
+ *  - hostRects must stay unchanged until the copy has been taken: for pageable memory that is when the call returns,
+ *    for page-locked memory when the stream reaches the copy.
+ * Results are those of b200ppResizedCrop given the same rectangles. */
+#define B200PP_NO_ALLOC_MAX_RECTS 4096
+B200PP_PUBLIC int b200ppResizedCropNoAlloc(const B200ppImageSet *src, const B200ppImageSet *dst, const int32_t *hostRects,
+                                           int32_t interp, cudaStream_t stream);
+
 /* The crop-rectangle generator of the reference's RandomResizedCrop
  * (src/cvcuda/priv/legacy/random_resized_crop.cu:288-390): a std::mt19937 seeded with `seed` (0 = from the system's
  * random device) and the reference's draw sequence, so equal seeds give the reference's rectangles. Host only, not
