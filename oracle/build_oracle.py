@@ -156,6 +156,131 @@ def build_ref_cuda(ref_root: str = DEFAULT_REF_ROOT, force: bool = False) -> str
     return REF_CUDA_SO
 
 
+# ---------------------------------------------------------------------------------------------------------------------
+# The reference's object model (libnvcv_types) and its own operators (a reduced libcvcuda), compiled from the reference
+# tree where it lies with g++ / nvcc directly. The reference's build system is not run; the two things it would generate
+# are produced here into a scratch directory: the version headers (a plain substitution of the version numbers into
+# cmake/VersionDef.h.in and cmake/VersionUtils.h.in) and the linker version scripts (the list of NVCV_DEFINE_API /
+# CVCUDA_DEFINE_API names per version node, which is all cmake/CreateExportsFile.cmake writes).
+
+REF_NVCV_SO = os.path.join(REF_DIR, "libnvcv_types.so.0")
+REF_CVCUDA_SO = os.path.join(REF_DIR, "libcvcuda_ref.so")
+REF_VERSION = (0, 15, 0, 0)
+
+# operators of the reduced reference library: the two of the hot path and the ones its un-fused chains are made of
+REF_OPS = ["ResizeCropConvertReformat", "CropFlipNormalizeReformat", "Resize", "Normalize", "ConvertTo", "Reformat",
+           "CopyMakeBorder", "RandomResizedCrop", "CustomCrop"]
+REF_LEGACY = ["CvCudaLegacyHelpers.cpp", "resize_var_shape.cu", "normalize.cu", "normalize_var_shape.cu", "convert_to.cu",
+              "reformat.cu", "copy_make_border.cu", "copy_make_border_var_shape.cu", "random_resized_crop.cu",
+              "random_resized_crop_var_shape.cu", "custom_crop.cu"]
+
+
+def _render_version_headers(ref_root: str, scratch: str) -> str:
+    import re
+    gen = os.path.join(scratch, "gen")
+    sub = {"VERSION_MAJOR": REF_VERSION[0], "VERSION_MINOR": REF_VERSION[1], "VERSION_PATCH": REF_VERSION[2],
+           "VERSION_TWEAK": REF_VERSION[3], "VERSION_SUFFIX": "", "VERSION_FULL": "%d.%d.%d" % REF_VERSION[:3],
+           "VERSION_API_CODE": REF_VERSION[0] * 100 + REF_VERSION[1], "VERSION_BUILD": "%d_%d_%d-direct" % REF_VERSION[:3],
+           "REPO_COMMIT": "unknown"}
+    for prefix, inc in (("NVCV", "nvcv"), ("CVCUDA", "cvcuda")):
+        for tmpl, out in (("VersionDef.h.in", "VersionDef.h"), ("VersionUtils.h.in", os.path.join("detail", "VersionUtils.h"))):
+            text = open(os.path.join(ref_root, "cmake", tmpl)).read()
+            text = re.sub(r"@(\w+)@", lambda m: str(dict(sub, LIBPREFIX=prefix).get(m.group(1), m.group(0))), text)
+            dst = os.path.join(gen, inc, out)
+            os.makedirs(os.path.dirname(dst), exist_ok=True)
+            with open(dst, "w") as f:
+                f.write(text)
+    return gen
+
+
+def _version_script(prefix: str, sources, out: str) -> str:
+    import collections
+    import re
+    nodes = collections.defaultdict(set)
+    for src in sources:
+        for ln in open(src):
+            m = re.match(r"^[A-Z_]+_DEFINE_API\(+([^,]+),([^,]+),[^,]+,([^,]+)", ln)
+            if m:
+                nodes[(int(m.group(1)), int(m.group(2)))].add(m.group(3).strip())
+    text, prev = "", None
+    for key in sorted(nodes):
+        text += "%s_%d.%d {\nglobal:\n" % (prefix, *key) + "".join("    %s;\n" % fn for fn in sorted(nodes[key]))
+        text += ("} %s_%d.%d;\n\n" % (prefix, *prev)) if prev else "local: *;\n};\n\n"
+        prev = key
+    with open(out, "w") as f:
+        f.write(text)
+    return out
+
+
+def _compile_all(jobs, workers: int = 8):
+    """jobs: list of argv lists; run them `workers` at a time, fail on the first error."""
+    from concurrent.futures import ThreadPoolExecutor
+    with ThreadPoolExecutor(max_workers=workers) as pool:
+        for rc, cmd in pool.map(lambda c: (subprocess.call(c), c), jobs):
+            if rc != 0:
+                raise subprocess.CalledProcessError(rc, cmd)
+
+
+def build_ref_ops(ref_root: str = DEFAULT_REF_ROOT, force: bool = False):
+    """oracle/_ref/libnvcv_types.so.0 (the reference's tensor / image / image-batch objects) and
+    oracle/_ref/libcvcuda_ref.so (the reference's own operators of REF_OPS, sm_100a). Returns the two paths, or None when
+    the reference tree is absent and no earlier build exists."""
+    import glob
+    nvcv_src = os.path.join(ref_root, "src/nvcv/src")
+    cv_src = os.path.join(ref_root, "src/cvcuda")
+    have = os.path.exists(REF_NVCV_SO) and os.path.exists(REF_CVCUDA_SO)
+    if not os.path.isdir(nvcv_src) or not os.path.isdir(cv_src):
+        return (REF_NVCV_SO, REF_CVCUDA_SO) if have else None
+    if have and not force and not _stale(REF_CVCUDA_SO, __file__):
+        return REF_NVCV_SO, REF_CVCUDA_SO
+    os.makedirs(REF_DIR, exist_ok=True)
+    nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+    scratch = tempfile.mkdtemp(prefix="refops_")
+    try:
+        gen = _render_version_headers(ref_root, scratch)
+        util = [os.path.join(ref_root, "src/nvcv/util", f) for f in ("Assert.cpp", "CheckError.cpp", "String.cpp", "Version.cpp")]
+        inc = ["-I" + os.path.join(ref_root, "src"), "-I" + os.path.join(nvcv_src, "include"), "-I" + nvcv_src, "-I" + gen,
+               "-I/usr/local/cuda/include"]
+        # --- libnvcv_types
+        api = sorted(glob.glob(os.path.join(nvcv_src, "*.cpp")))
+        srcs = api + sorted(glob.glob(os.path.join(nvcv_src, "priv", "*.cpp"))) + util
+        objs, jobs = [], []
+        for i, src in enumerate(srcs):
+            obj = os.path.join(scratch, "nvcv_%d.o" % i)
+            objs.append(obj)
+            jobs.append(["g++", "-std=c++17", "-O2", "-fPIC", "-w", "-DNVCV_EXPORTING=1", *inc, "-c", src, "-o", obj])
+        _compile_all(jobs)
+        script = _version_script("NVCV", api, os.path.join(scratch, "nvcv.ldscript"))
+        subprocess.check_call(["g++", "-shared", "-o", REF_NVCV_SO, *objs, "-Wl,--version-script=" + script,
+                               "-Wl,-soname,libnvcv_types.so.0", "-L/usr/local/cuda/lib64", "-lcudart_static", "-ldl", "-lrt",
+                               "-pthread"])
+        link = os.path.join(REF_DIR, "libnvcv_types.so")
+        if os.path.lexists(link):
+            os.remove(link)
+        os.symlink(os.path.basename(REF_NVCV_SO), link)
+        # --- the reference's operators
+        cinc = inc + ["-I" + os.path.join(cv_src, "include"), "-I" + cv_src]
+        api = [os.path.join(cv_src, "Operator.cpp")] + [os.path.join(cv_src, "Op%s.cpp" % op) for op in REF_OPS]
+        priv = [os.path.join(cv_src, "priv", "IOperator.cpp")]
+        for op in REF_OPS:
+            priv += [f for f in (os.path.join(cv_src, "priv", "Op%s.%s" % (op, ext)) for ext in ("cpp", "cu")) if os.path.exists(f)]
+        legacy = [os.path.join(cv_src, "priv", "legacy", f) for f in REF_LEGACY]
+        objs, jobs = [], []
+        for i, src in enumerate(api + priv + legacy + util):
+            obj = os.path.join(scratch, "cv_%d.o" % i)
+            objs.append(obj)
+            jobs.append([nvcc, "-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-w", "-DNDEBUG",
+                         "-DCVCUDA_EXPORTING=1", "--expt-relaxed-constexpr", "--extended-lambda", "-Xcompiler", "-fPIC", *cinc,
+                         "-c", src, "-o", obj])
+        _compile_all(jobs)
+        script = _version_script("CVCUDA", api, os.path.join(scratch, "cvcuda.ldscript"))
+        subprocess.check_call([nvcc, "-shared", "-o", REF_CVCUDA_SO, *objs, "-Xlinker", "--version-script=" + script,
+                               "-Xlinker", "-rpath,$ORIGIN", "-L" + REF_DIR, "-l:libnvcv_types.so.0"])
+    finally:
+        shutil.rmtree(scratch, ignore_errors=True)
+    return REF_NVCV_SO, REF_CVCUDA_SO
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--ref-root", default=DEFAULT_REF_ROOT)
@@ -164,6 +289,7 @@ def main() -> int:
     print("oracle:", build_oracle(a.force))
     print("reference golden:", build_ref(a.ref_root, a.force) or "reference tree absent, not built")
     print("reference CUDA kernels:", build_ref_cuda(a.ref_root, a.force) or "reference tree absent, not built")
+    print("reference object model + operators:", build_ref_ops(a.ref_root, a.force) or "reference tree absent, not built")
     return 0
 
 

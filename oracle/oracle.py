@@ -482,3 +482,47 @@ def ref_random_crop_rects(seed: int, sizes, min_scale=0.08, max_scale=1.0, min_r
     R.ref_random_crop_rects.argtypes = [C.c_uint, C.c_double, C.c_double, C.c_double, C.c_double, C.c_void_p, C.c_int, C.c_void_p]
     assert R.ref_random_crop_rects(seed, min_scale, max_scale, min_ratio, max_ratio, rc.ctypes.data, len(sizes), out.ctypes.data) == 0
     return out
+
+
+# ------------------------------------------------------------------------------------------------ composed references
+# The fused entry points do in one pass what the reference needs a chain of operators for. Each function below builds
+# the expected result of such a pass from the reference's OWN golden functions only (oracle/_ref), chained the way a user
+# of the reference would chain its operators, so that the additions to the restatement in preproc_oracle.c (per-channel
+# affine in the resize path, float16 store, region of interest + flip, letterbox) are pinned as well.
+
+def ref_resize_then_normalize(batch: np.ndarray, resize, crop, out_size, interp, base, mul, out_dtype=np.float32) -> np.ndarray:
+    """ResizeCropConvertReformat (scale 1, offset 0, float32, no rounding in between) followed by the per-channel
+    (v - base) * mul of CropFlipNormalizeReformat on the float image (whole image, no flip), NCHW; float16 = that result
+    rounded to nearest even. Goldens: tests/cvcuda/system/TestOpResizeCropConvertReformat.cpp:76-172 and
+    TestOpCropFlipNormalizeReformat.cpp:43-149 (its float32 -> float32 instance; the Normalize golden of
+    TestOpNormalize.cpp:34-77 only exists for uint8 -> uint8 images)."""
+    mid = ref_rccr(batch, resize, crop, out_size, interp, 0, 1.0, 0.0, False, np.float32, planar=False)
+    ow, oh = out_size
+    out = np.stack([ref_cfnr(im, False, (0, 0, ow, oh), 2, out_size, np.float32, True, 0, 0.0, base, mul, 1.0, 0.0, 0.0, 0)
+                    for im in mid])
+    return out if np.dtype(out_dtype) == np.float32 else out.astype(out_dtype)
+
+
+def ref_crop_resize_flip_normalize(images: Sequence[np.ndarray], rects, flips, out_size, base, mul,
+                                   out_dtype=np.float32) -> np.ndarray:
+    """Per image: the rectangle cut out as an image of its own (CustomCrop), resized by ResizeCropConvertReformat's golden
+    to uint8 (the intermediate a chain of operators has), then CropFlipNormalizeReformat's golden with the whole resized
+    image as crop, the flip code and the per-channel constants, NCHW."""
+    ow, oh = out_size
+    outs = []
+    for im, (x, y, w, h), f in zip(images, rects, flips):
+        sub = np.ascontiguousarray(im[y:y + h, x:x + w])
+        small = ref_rccr(sub[None], out_size, (0, 0), out_size, 1, 0, 1.0, 0.0, True, np.uint8, planar=False)[0]
+        outs.append(ref_cfnr(small, False, (0, 0, ow, oh), int(f), out_size, np.float32, True, 0, 0.0, base, mul, 1.0, 0.0, 0.0, 0))
+    out = np.stack(outs)
+    return out if np.dtype(out_dtype) == np.float32 else out.astype(out_dtype)
+
+
+def ref_letterbox(batch: np.ndarray, resize, canvas, dst_pos, pad_value: int, scale: float) -> np.ndarray:
+    """Resize (stand-alone Resize golden, tests/cvcuda/system/ResizeUtils.cpp:189-300) -> CopyMakeBorder golden with a
+    constant (TestOpCopyMakeBorder.cpp:40-97) -> ResizeCropConvertReformat's golden as an identity-sized nearest pass that
+    reverses the channels, multiplies by `scale` and writes float32 NCHW (the ConvertTo + channel swap + Reformat tail)."""
+    small = np.stack([ref_resize(im, resize, 1) for im in batch])
+    cw, ch = canvas
+    padded = ref_copy_make_border(small, canvas, dst_pos[1], dst_pos[0], 0, (pad_value,) * 4)
+    return ref_rccr(padded, (cw, ch), (0, 0), (cw, ch), 0, 1, scale, 0.0, False, np.float32, planar=True)

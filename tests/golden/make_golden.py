@@ -146,12 +146,53 @@ def random_crop_cases():
     return out
 
 
+MEAN = (123.675, 116.28, 103.53)
+INV_STD = tuple(float(np.float32(1.0) / np.float32(s)) for s in (58.395, 57.12, 57.375))
+
+
+def fused_cases():
+    """The fused passes of the benchmark configurations, scaled down, as CHAINS of the reference's own goldens
+    (oracle.ref_resize_then_normalize / ref_crop_resize_flip_normalize / ref_letterbox): what the one-pass entry points
+    must reproduce. Kinds: 0 = resize + crop + per-channel normalise (float32 / float16, nearest / linear),
+    1 = rectangle + resize + flip + normalise (float16), 2 = letterbox."""
+    rng = np.random.default_rng(2468)
+    out, k = {}, 0
+    for (w, h, n), rs, crop, osz, interp, dt in (((120, 68, 2), (32, 32), (2, 2), (28, 28), 1, np.float32),
+                                                 ((120, 68, 2), (48, 48), (4, 4), (40, 40), 1, np.float16),
+                                                 ((120, 68, 2), (48, 48), (4, 4), (40, 40), 0, np.float16),
+                                                 ((61, 47, 1), (90, 70), (10, 5), (64, 48), 1, np.float32)):
+        src = rng.integers(0, 256, (n, h, w, 3), dtype=np.uint8)
+        out[f"fused{k}_kind"] = np.array(0)
+        out[f"fused{k}_src"] = src
+        out[f"fused{k}_par"] = np.array([*rs, *crop, *osz, interp], np.int32)
+        out[f"fused{k}_ref"] = O.ref_resize_then_normalize(src, rs, crop, osz, interp, MEAN, INV_STD, dt)
+        k += 1
+    sizes = [(97, 71), (160, 45), (53, 120)]
+    images = [rng.integers(0, 256, (h, w, 3), dtype=np.uint8) for (w, h) in sizes]
+    rects = np.array([(5, 7, 80, 60), (0, 0, 160, 45), (20, 30, 30, 41)], np.int32)
+    flips = np.array([1, 2, 1], np.int32)
+    out[f"fused{k}_kind"] = np.array(1)
+    for i, im in enumerate(images):
+        out[f"fused{k}_src{i}"] = im
+    out[f"fused{k}_rects"], out[f"fused{k}_flips"] = rects, flips
+    out[f"fused{k}_par"] = np.array([28, 28], np.int32)
+    out[f"fused{k}_ref"] = O.ref_crop_resize_flip_normalize(images, rects, flips, (28, 28), MEAN, INV_STD, np.float16)
+    k += 1
+    src = rng.integers(0, 256, (2, 54, 96, 3), dtype=np.uint8)  # 96x54 -> 32x18 (factor 3, as 1080p -> 640x360) in 32x32
+    out[f"fused{k}_kind"] = np.array(2)
+    out[f"fused{k}_src"] = src
+    out[f"fused{k}_par"] = np.array([32, 18, 32, 32, 0, 7, 114], np.int32)
+    out[f"fused{k}_ref"] = O.ref_letterbox(src, (32, 18), (32, 32), (0, 7), 114, 1.0 / 255.0)
+    k += 1
+    out["fused_count"] = np.array(k)
+    return out
+
+
+CASES = {"rccr": rccr_cases, "cfnr": cfnr_cases, "resize": resize_cases, "normalize": normalize_cases, "border": border_cases,
+         "random_crop": random_crop_cases, "fused": fused_cases}
+
 if __name__ == "__main__":
     assert build_oracle.build_ref() is not None, "reference tree not available"
-    np.savez_compressed(os.path.join(HERE, "rccr_golden.npz"), **rccr_cases())
-    np.savez_compressed(os.path.join(HERE, "cfnr_golden.npz"), **cfnr_cases())
-    np.savez_compressed(os.path.join(HERE, "resize_golden.npz"), **resize_cases())
-    np.savez_compressed(os.path.join(HERE, "normalize_golden.npz"), **normalize_cases())
-    np.savez_compressed(os.path.join(HERE, "border_golden.npz"), **border_cases())
-    np.savez_compressed(os.path.join(HERE, "random_crop_golden.npz"), **random_crop_cases())
+    for name in (sys.argv[1:] or list(CASES)):  # python tests/golden/make_golden.py [name ...]
+        np.savez_compressed(os.path.join(HERE, f"{name}_golden.npz"), **CASES[name]())
     print("written", [f for f in os.listdir(HERE) if f.endswith(".npz")])

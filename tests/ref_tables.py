@@ -11,6 +11,8 @@ from __future__ import annotations
 
 from typing import NamedTuple
 
+import os
+
 import numpy as np
 
 NEAREST, LINEAR = 0, 1
@@ -279,3 +281,22 @@ def normalize_case(row: NormalizeRow, seed: int):
     base = rng.uniform(0.0, 255.0, bshape).astype(np.float32)
     scale = rng.uniform(0.0, 1.0, sshape).astype(np.float32)
     return images, base, scale
+
+
+# ------------------------------------------------------------------------------------------------ fused passes
+
+MEAN = (123.675, 116.28, 103.53)
+INV_STD = tuple(float(np.float32(1.0) / np.float32(s)) for s in (58.395, 57.12, 57.375))
+
+
+def fused_fixture_cases():
+    """(kind, inputs, parameters, expected) of tests/golden/fused_golden.npz: outputs of CHAINS of the reference's goldens."""
+    z = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "fused_golden.npz"))
+    for k in range(int(z["fused_count"])):
+        kind = int(z[f"fused{k}_kind"])
+        if kind == 1:
+            n = len(z[f"fused{k}_rects"])
+            yield k, kind, ([z[f"fused{k}_src{i}"] for i in range(n)], z[f"fused{k}_rects"], z[f"fused{k}_flips"]), \
+                z[f"fused{k}_par"], z[f"fused{k}_ref"]
+        else:
+            yield k, kind, z[f"fused{k}_src"], z[f"fused{k}_par"], z[f"fused{k}_ref"]

@@ -153,3 +153,67 @@ def test_algorithmic_bytes_of_the_north_star_config(oracle):
     """1080p -> 256x256 linear -> centre 224x224: 448 source rows of 5056 sector-granular bytes each."""
     spec = oracle.ResizeSpec(resize=(256, 256), crop=(16, 16), out_size=(224, 224), interp=1)
     assert oracle.resize_source_bytes(1920, 1080, 1920 * 3, spec) == 2265088
+
+
+# ------------------------------------------------------------------------------------------------ fused passes vs chains
+
+from ref_tables import INV_STD, MEAN, fused_fixture_cases  # noqa: E402
+
+
+def restated_fused(oracle, kind, inputs, par, dtype):
+    """The restatement's one-pass result for a fixture case."""
+    if kind == 0:
+        rw, rh, cx, cy, ow, oh, interp = (int(v) for v in par)
+        spec = oracle.ResizeSpec(resize=(rw, rh), crop=(cx, cy), out_size=(ow, oh), interp=interp, src_cast=False, base=MEAN,
+                                 mul=INV_STD)
+        return oracle.resize_crop(list(inputs), spec, dtype, True)
+    if kind == 1:
+        images, rects, flips = inputs
+        ow, oh = (int(v) for v in par)
+        spec = oracle.ResizeSpec(resize=(ow, oh), out_size=(ow, oh), interp=1, src_cast=True, base=MEAN, mul=INV_STD)
+        return oracle.resize_crop(images, spec, dtype, True, roi=rects, flip=flips)
+    rw, rh, cw, ch, dx, dy, pad = (int(v) for v in par)
+    spec = oracle.ResizeSpec(resize=(rw, rh), out_size=(rw, rh), interp=1, src_cast=True, manip=1, scale=1.0 / 255.0,
+                             canvas=(cw, ch), dst_pos=(dx, dy), pad_value=float(pad))
+    return oracle.resize_crop(list(inputs), spec, dtype, True)
+
+
+def test_fused_passes_equal_chains_of_the_reference_goldens_fixtures(oracle):
+    """Per-channel affine in the resize path, float16 store, rectangle + flip, letterbox: the restatement's one pass equals,
+    bit for bit, the committed outputs of chains of the reference's own golden functions."""
+    count = 0
+    for k, kind, inputs, par, ref in fused_fixture_cases():
+        got = restated_fused(oracle, kind, inputs, par, ref.dtype)
+        assert _same(got, ref), f"fixture {k} (kind {kind})"
+        count += 1
+    assert count == 6
+
+
+def test_fused_passes_equal_chains_of_the_reference_goldens_at_config_shapes(oracle):
+    """The same on the benchmark configurations' real image sizes (one or two images each), with the chains computed here
+    by the reference's compiled goldens."""
+    if oracle.ref() is None:
+        pytest.skip("reference golden not compiled on this machine")
+    rng = np.random.default_rng(1234)
+    src = rng.integers(0, 256, (1, 1080, 1920, 3), dtype=np.uint8)
+    spec = oracle.ResizeSpec(resize=(256, 256), crop=(16, 16), out_size=(224, 224), interp=1, src_cast=False, base=MEAN,
+                             mul=INV_STD)
+    assert _same(oracle.resize_crop(list(src), spec, np.float32, True, nthreads=4),
+                 oracle.ref_resize_then_normalize(src, (256, 256), (16, 16), (224, 224), 1, MEAN, INV_STD)), "config 2"
+    spec = oracle.ResizeSpec(resize=(640, 360), out_size=(640, 360), interp=1, src_cast=True, manip=1, scale=1.0 / 255.0,
+                             canvas=(640, 640), dst_pos=(0, 140), pad_value=114.0)
+    assert _same(oracle.resize_crop(list(src), spec, np.float32, True, nthreads=4),
+                 oracle.ref_letterbox(src, (640, 360), (640, 640), (0, 140), 114, 1.0 / 255.0)), "config 4"
+    big = rng.integers(0, 256, (1, 2160, 3840, 3), dtype=np.uint8)
+    for interp in (0, 1):
+        spec = oracle.ResizeSpec(resize=(512, 512), crop=(32, 32), out_size=(448, 448), interp=interp, src_cast=False,
+                                 base=MEAN, mul=INV_STD)
+        assert _same(oracle.resize_crop(list(big), spec, np.float16, True, nthreads=4),
+                     oracle.ref_resize_then_normalize(big, (512, 512), (32, 32), (448, 448), interp, MEAN, INV_STD,
+                                                      np.float16)), f"config 5 interp {interp}"
+    images = [big[0, :1500, :2900], src[0]]
+    rects = np.array([(100, 200, 1700, 1290), (480, 0, 960, 1080)], np.int32)
+    flips = np.array([1, 2], np.int32)
+    spec = oracle.ResizeSpec(resize=(224, 224), out_size=(224, 224), interp=1, src_cast=True, base=MEAN, mul=INV_STD)
+    assert _same(oracle.resize_crop(images, spec, np.float16, True, roi=rects, flip=flips, nthreads=4),
+                 oracle.ref_crop_resize_flip_normalize(images, rects, flips, (224, 224), MEAN, INV_STD, np.float16)), "config 3"
