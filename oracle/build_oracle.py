@@ -281,6 +281,37 @@ def build_ref_ops(ref_root: str = DEFAULT_REF_ROOT, force: bool = False):
     return REF_NVCV_SO, REF_CVCUDA_SO
 
 
+REF_HARNESS_SRC = os.path.join(HERE, "ref_ops_harness.cpp")
+HARNESS_B200_SO = os.path.join(REF_DIR, "libharness_b200.so")
+HARNESS_REF_SO = os.path.join(REF_DIR, "libharness_ref.so")
+
+
+def build_ref_harness(ref_root: str = DEFAULT_REF_ROOT, force: bool = False):
+    """oracle/_ref/libharness_b200.so and libharness_ref.so: ref_ops_harness.cpp (written against the reference's header-only
+    C++ API) linked once against the B200 library and once against the reference's own operators, both over the
+    reference's real libnvcv_types. Needs build_ref_ops' outputs and the B200 library."""
+    b200 = os.path.join(os.path.dirname(HERE), "cv-cuda_b200", "libcvcuda_b200.so")
+    have = os.path.exists(HARNESS_B200_SO) and os.path.exists(HARNESS_REF_SO)
+    if not os.path.isdir(os.path.join(ref_root, "src/cvcuda/include")) or not os.path.exists(REF_CVCUDA_SO) or not os.path.exists(b200):
+        return (HARNESS_B200_SO, HARNESS_REF_SO) if have else None
+    if have and not force and not _stale(HARNESS_B200_SO, REF_HARNESS_SRC, REF_CVCUDA_SO) and not _stale(HARNESS_REF_SO, REF_HARNESS_SRC):
+        return HARNESS_B200_SO, HARNESS_REF_SO
+    scratch = tempfile.mkdtemp(prefix="refharness_")
+    try:
+        gen = _render_version_headers(ref_root, scratch)
+        common = ["g++", "-std=c++17", "-O2", "-fPIC", "-shared", "-w", "-I" + os.path.join(ref_root, "src/cvcuda/include"),
+                  "-I" + os.path.join(ref_root, "src/nvcv/src/include"), "-I" + gen, "-I/usr/local/cuda/include",
+                  "-I" + os.path.join(os.path.dirname(HERE), "include"), REF_HARNESS_SRC]
+        tail = ["-L" + REF_DIR, "-l:libnvcv_types.so.0", "-L/usr/local/cuda/lib64", "-lcudart_static", "-ldl", "-lrt", "-pthread"]
+        # $ORIGIN = oracle/_ref; the B200 library sits in ../../cv-cuda_b200
+        subprocess.check_call(common + ["-DHARNESS_B200", "-o", HARNESS_B200_SO, "-L" + os.path.dirname(b200), "-l:libcvcuda_b200.so",
+                                        "-Wl,-rpath,$ORIGIN:$ORIGIN/../../cv-cuda_b200"] + tail)
+        subprocess.check_call(common + ["-o", HARNESS_REF_SO, "-l:libcvcuda_ref.so", "-Wl,-rpath,$ORIGIN"] + tail)
+    finally:
+        shutil.rmtree(scratch, ignore_errors=True)
+    return HARNESS_B200_SO, HARNESS_REF_SO
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--ref-root", default=DEFAULT_REF_ROOT)
@@ -290,6 +321,7 @@ def main() -> int:
     print("reference golden:", build_ref(a.ref_root, a.force) or "reference tree absent, not built")
     print("reference CUDA kernels:", build_ref_cuda(a.ref_root, a.force) or "reference tree absent, not built")
     print("reference object model + operators:", build_ref_ops(a.ref_root, a.force) or "reference tree absent, not built")
+    print("harness over the reference's C++ API:", build_ref_harness(a.ref_root, a.force) or "not built")
     return 0
 
 
