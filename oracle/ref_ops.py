@@ -31,7 +31,7 @@ def load(which: str) -> Optional[C.CDLL]:
         L = C.CDLL(path(which))
         L.h_last_message.restype = C.c_char_p
         L.h_which.restype = C.c_char_p
-        for name in ("h_rccr_tensor", "h_rccr_varshape", "h_cfnr", "h_time_classify", "h_time_letterbox", "h_time_varshape"):
+        for name in ("h_rccr_tensor", "h_rccr_varshape", "h_cfnr", "h_time_classify", "h_time_letterbox", "h_time_varshape", "h_time_cfnr"):
             getattr(L, name).restype = C.c_int
         _loaded[which] = L
     return _loaded[which]
@@ -123,4 +123,10 @@ def time_varshape(L, sizes, out_size, rects, flips, chain: bool, warmup: int, it
     ms, launches = C.c_float(), C.c_int()
     _check(L, L.h_time_varshape(ws, hs, n, out_size[0], out_size[1], C.c_void_p(rects.ctypes.data), C.c_void_p(flips.ctypes.data),
                                 int(chain), warmup, iters, C.byref(ms), C.byref(launches)))
+    return ms.value, launches.value
+
+
+def time_cfnr(L, n, h, w, warmup: int, iters: int):
+    ms, launches = C.c_float(), C.c_int()
+    _check(L, L.h_time_cfnr(n, h, w, warmup, iters, C.byref(ms), C.byref(launches)))
     return ms.value, launches.value

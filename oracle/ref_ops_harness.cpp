@@ -531,4 +531,40 @@ int h_time_varshape(const int *ws, const int *hs, int n, int ow, int oh, const i
         }
     });
 }
+// CropFlipNormalizeReformat alone, on the shape of the reference's own benchmark (bench/BenchCropFlipNormalizeReformat.cpp:
+// crop = the whole image, flip both axes, REFLECT101) with RGB uint8 images of w x h -> float32 NCHW.
+int h_time_cfnr(int n, int h, int w, int warmup, int iters, float *ms, int *launches)
+{
+    return guarded([&] {
+        Stream                   st;
+        std::vector<nvcv::Image> keep;
+        nvcv::ImageBatchVarShape batch(n);
+        for (int i = 0; i < n; ++i)
+        {
+            nvcv::Image img(nvcv::Size2D{w, h}, nvcv::FMT_RGB8);
+            auto        data = img.exportData<nvcv::ImageDataStridedCuda>();
+            check(cudaMemset2D(data->plane(0).basePtr, data->plane(0).rowStride, 11 + i, static_cast<size_t>(w) * 3, h),
+                  "cudaMemset2D");
+            keep.push_back(img);
+            batch.pushBack(img);
+        }
+        nvcv::Tensor out = make_tensor(n, h, w, 3, true, 6);
+        nvcv::Tensor tRect(nvcv::TensorShape({n, 1, 1, 4}, "NHWC"), nvcv::TYPE_S32);
+        nvcv::Tensor tFlip(nvcv::TensorShape({n}, "N"), nvcv::TYPE_S32);
+        nvcv::Tensor tBase(nvcv::TensorShape({1, 1, 1, 3}, "NHWC"), nvcv::TYPE_F32);
+        nvcv::Tensor tScale(nvcv::TensorShape({1, 1, 1, 3}, "NHWC"), nvcv::TYPE_F32);
+        std::vector<int32_t> rects(static_cast<size_t>(n) * 4), flips(n, -1);
+        for (int i = 0; i < n; ++i) rects[4 * i] = 0, rects[4 * i + 1] = 0, rects[4 * i + 2] = w, rects[4 * i + 3] = h;
+        copy_tensor(tRect, rects.data(), true);
+        copy_tensor(tFlip, flips.data(), true);
+        copy_tensor(tBase, const_cast<float *>(kMean), true);
+        copy_tensor(tScale, const_cast<float *>(kStd), true);
+        cvcuda::CropFlipNormalizeReformat cfnr;
+        *launches = 1;
+        *ms       = time_passes(st.s, warmup, iters, [&] {
+            cfnr(st.s, batch, out, tRect, NVCV_BORDER_REFLECT101, 0.f, tFlip, tBase, tScale, 1.f, 0.f, 0.f,
+                 CVCUDA_NORMALIZE_SCALE_IS_STDDEV);
+        });
+    });
+}
 }

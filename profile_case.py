@@ -1,6 +1,6 @@
 """A small, self-ending run of one kernel, sized for an `ncu` capture.
 
-    python cv-cuda_b200/profile_case.py [--case classify|4k|letterbox] [--images 32] [--path 0|1|2] [--launches 5]
+    python profile_case.py [--case classify|4k|letterbox] [--images 32] [--path 0|1|2] [--launches 5]
 
 `classify` is the 1080p -> 256x256 -> 224x224 float32 NCHW case of bench.py at a reduced batch: 32 images are
 199 MB of source, larger than the 126 MB L2, so DRAM counters still mean something, while the whole run holds well
@@ -14,7 +14,7 @@ import sys
 import numpy as np
 import torch
 
-ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 import __graft_entry__ as ge  # noqa: E402
 
