@@ -448,6 +448,8 @@ def run_native(args) -> int:
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     pkg = ge.load_package()  # raises when libcvcuda_b200.so is missing: there is no fallback path
+    if args.path:
+        pkg.set_kernel_path(args.path)
     cfg = Config(args.config)
     n = per_gpu_images(cfg, args, world)
     mul = inv_std()
@@ -723,6 +725,8 @@ def main() -> int:
                     help="weak: the configuration's batch on every GPU; strong: the whole job (1024 images for 5-*) split evenly")
     ap.add_argument("--images", type=int, default=0, help="images per GPU, overriding the configuration (small profiling runs)")
     ap.add_argument("--kernel-only", action="store_true", help="device-resident timing only: no end-to-end, CPU or reference legs")
+    ap.add_argument("--path", type=int, default=0, choices=(0, 1, 2, 3),
+                    help="kernel choice of the resize path for profiling runs: 0 automatic, 1 per-pixel gather, 2 staged, 3 row walk")
     ap.add_argument("--harness-leg", choices=("ref", "b200"), default=None, help=argparse.SUPPRESS)
     args = ap.parse_args()
     if args.harness_leg:

@@ -71,8 +71,9 @@ static int elem_size(int dtype)
 
 struct DeviceFacts
 {
-    int smCount      = 0;
-    int maxSmemOptin = 0;
+    int                    smCount      = 0;
+    int                    maxSmemOptin = 0;
+    volatile unsigned int *errorMirror  = nullptr; // host view of the device error word (see raise_device_error)
 };
 
 static const DeviceFacts &device_facts(int dev)
@@ -86,9 +87,42 @@ static const DeviceFacts &device_facts(int dev)
         DeviceFacts f;
         cudaDeviceGetAttribute(&f.smCount, cudaDevAttrMultiProcessorCount, dev);
         cudaDeviceGetAttribute(&f.maxSmemOptin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+        // One page-locked, device-mapped word per device, made the first time the library is used on it (the one thing this
+        // library ever allocates on its own; it lives until the process ends). Without it the error word is still there
+        // for b200ppReadDeviceError, only nothing reports it unasked.
+        unsigned int *host = nullptr, *mapped = nullptr;
+        if (cudaHostAlloc(reinterpret_cast<void **>(&host), sizeof(unsigned int), cudaHostAllocMapped | cudaHostAllocPortable) == cudaSuccess)
+        {
+            *host = 0;
+            if (cudaHostGetDevicePointer(reinterpret_cast<void **>(&mapped), host, 0) == cudaSuccess
+                && cudaMemcpyToSymbol(g_deviceErrorMirror, &mapped, sizeof(mapped)) == cudaSuccess)
+                f.errorMirror = host;
+            else
+                cudaFreeHost(host);
+        }
+        cudaGetLastError();
         it = cache.emplace(dev, f).first;
     }
     return it->second;
+}
+
+// A kernel of an earlier call on the current device gave up on one of its bounded waits: say so now (no synchronisation;
+// the word is page-locked host memory the kernel wrote through). It stays set until b200ppReadDeviceError clears it.
+static int pending_device_error()
+{
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess)
+    {
+        cudaGetLastError();
+        return B200PP_SUCCESS; // no device yet: the launch below reports that
+    }
+    const volatile unsigned int *w = device_facts(dev).errorMirror;
+    if (w && *w != 0)
+        return fail(B200PP_ERROR_INTERNAL,
+                    "An earlier launch on device %d gave up on a bounded internal wait (error word 0x%x); its output is "
+                    "incomplete. b200ppReadDeviceError reads and clears the word",
+                    dev, *w);
+    return B200PP_SUCCESS;
 }
 
 // Resident CTAs per SM of one staged-kernel instantiation for a block size and dynamic shared-memory size. The first
@@ -424,6 +458,8 @@ extern "C" int b200ppResizeCropConvertReformat(const B200ppSource *src, const B2
 
     const int dk        = dst->dtype == B200PP_U8 ? DST_U8 : (dst->dtype == B200PP_F32 ? DST_F32 : DST_F16);
     const int srcWBound = src->imageList ? (src->maxWidth > 0 ? src->maxWidth : 3840) : src->width;
+    if (const int st = pending_device_error())
+        return st;
     if (op->interp == B200PP_INTERP_NEAREST)
         return run_resize_dk<B200PP_INTERP_NEAREST>(dk, kp, srcWBound, stream);
     return run_resize_dk<B200PP_INTERP_LINEAR>(dk, kp, srcWBound, stream);
@@ -524,6 +560,8 @@ extern "C" int b200ppCropFlipNormalizeReformat(const B200ppSource *src, const B2
     const int  path     = g_kernelPath.load(std::memory_order_relaxed);
     const bool fastCase = src->dtype == B200PP_U8 && channels == 3 && !kp.srcPlanar
                        && (dst->dtype == B200PP_U8 || dst->dtype == B200PP_F32 || dst->dtype == B200PP_F16);
+    if (const int st = pending_device_error())
+        return st;
     if (fastCase && path != 1)
     {
         // four destination pixels per thread; one vector store per channel when the destination is planar and every
@@ -1207,6 +1245,9 @@ extern "C" int b200ppSelfTestWaitTimeout(uint32_t limitMs, cudaStream_t stream)
 {
     if (limitMs == 0 || limitMs > 1000)
         return fail(B200PP_ERROR_INVALID_ARGUMENT, "The wait limit of the self-test must be 1..1000 ms");
+    int dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess)
+        device_facts(dev); // sets up the host view of the error word on first use
     wait_timeout_probe_kernel<<<1, 32, 0, stream>>>(static_cast<unsigned long long>(limitMs) * 1000000ull);
     return check_launch("wait self-test");
 }
@@ -1222,6 +1263,10 @@ extern "C" int b200ppReadDeviceError(uint32_t *outError)
         cudaGetLastError();
         return fail(B200PP_ERROR_INTERNAL, "Could not read the device error word");
     }
+    int dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess)
+        if (volatile unsigned int *w = device_facts(dev).errorMirror)
+            *w = 0;
     *outError = v;
     return B200PP_SUCCESS;
 }

@@ -28,6 +28,20 @@ namespace b200pp {
 // for a free ring slot, 4 = the producer gave up draining its copies at exit, 8 = the wait self-test gave up (expected),
 // 16 = the staged kernel was launched with a shape it refuses (nothing was written).
 __device__ unsigned int g_deviceError;
+// Where the host can see the word without synchronising: a page-locked, device-mapped copy that the library sets up once per
+// device (null until then). The entry points look at it before they launch, so a kernel that gave up on a wait turns the
+// NEXT call on that device into B200PP_ERROR_INTERNAL instead of going unnoticed.
+__device__ unsigned int *g_deviceErrorMirror;
+
+__device__ __forceinline__ void raise_device_error(unsigned bits)
+{
+    atomicOr(&g_deviceError, bits);
+    if (g_deviceErrorMirror)
+    {
+        atomicOr_system(g_deviceErrorMirror, bits);
+        __threadfence_system();
+    }
+}
 
 constexpr int                kProducerThreads = 32;
 constexpr unsigned long long kWaitLimitNs     = 2000000000ull; // 2 s
@@ -386,7 +400,7 @@ __global__ void wait_timeout_probe_kernel(unsigned long long limitNs)
     }
     __syncthreads();
     if (!mbar_wait(&bar, 0, limitNs) && threadIdx.x == 0)
-        atomicOr(&g_deviceError, 8u);
+        raise_device_error(8u);
 }
 
 // Bulk asynchronous copy global -> shared, completion counted in bytes on `bar`.
@@ -896,7 +910,7 @@ __global__ void __launch_bounds__(288, INTERP == B200PP_INTERP_NEAREST ? 3 : 2) 
         || (consumerWarps / cfg.teams) % cfg.colBlocks != 0)
     {
         if (threadIdx.x == 0)
-            atomicOr(&g_deviceError, 16u);
+            raise_device_error(16u);
         return;
     }
 
@@ -959,7 +973,7 @@ __global__ void __launch_bounds__(288, INTERP == B200PP_INTERP_NEAREST ? 3 : 2) 
                 bool bad = false;
                 if (lane == 0 && kb + j >= S && !mbar_wait(&empty[s], emptyParity))
                 {
-                    atomicOr(&g_deviceError, 2u);
+                    raise_device_error(2u);
                     bad = true;
                 }
                 if (__any_sync(0xffffffffu, bad))
@@ -997,7 +1011,7 @@ __global__ void __launch_bounds__(288, INTERP == B200PP_INTERP_NEAREST ? 3 : 2) 
             for (long long j = (issued > S ? issued - S : 0); j < issued; ++j)
                 if (!mbar_wait(&full[j % S], static_cast<unsigned>((j / S) & 1)))
                 {
-                    atomicOr(&g_deviceError, 4u);
+                    raise_device_error(4u);
                     break;
                 }
         }
@@ -1035,7 +1049,7 @@ __global__ void __launch_bounds__(288, INTERP == B200PP_INTERP_NEAREST ? 3 : 2) 
     {
         if (!mbar_wait_addr(fullA + 8u * s, fullParity))
         {
-            atomicOr(&g_deviceError, 1u);
+            raise_device_error(1u);
             return;
         }
         const unsigned infoAddr = infoA + static_cast<unsigned>(s) * static_cast<unsigned>(sizeof(UnitInfo));

@@ -318,19 +318,26 @@ B200PP_PUBLIC int b200ppCopyMakeBorder(const B200ppImageSet *src, const B200ppIm
  * (src/nvcv/src/include/nvcv/Status.h). */
 B200PP_PUBLIC const char *b200ppGetLastErrorMessage(void);
 
-/* Kernel selection for tests and profiling: 0 automatic (default), 1 force the per-pixel gather kernels,
- * 2 force the staged (bulk-copy pipelined) kernel where it applies, 3 force the row-walk kernel. Process-wide. Returns
- * the previous value. */
+/* ---- Test and profiling hooks. Not part of the operator interface: process-wide state that two threads cannot set
+ * differently, kept for the tests (which run every kernel on the same inputs) and for profiling runs. The same holds for
+ * the B200PP_* environment variables (B200PP_STAGES, _UNIT_ROWS, _TEAMS, _MAX_CONSUMERS, _MAX_CTAS_PER_SM, _BLOCK_UNITS,
+ * _WALK_ROWS), which are read once per process and only reshape launches. ---- */
+
+/* Kernel selection: 0 automatic (default), 1 force the per-pixel gather kernels, 2 force the staged (bulk-copy pipelined)
+ * kernel where it applies, 3 force the row-walk kernel. Process-wide. Returns the previous value. Test hook. */
 B200PP_PUBLIC int b200ppSetKernelPath(int path);
 
 /* Number of kernels this library has launched in this process (all threads). */
 B200PP_PUBLIC uint64_t b200ppGetLaunchCount(void);
 
 /* Reads and clears the device-side error word of the current device (blocking). Non-zero means a kernel gave up
- * on a bounded wait; bit layout is documented next to the kernels. */
+ * on a bounded wait; bit layout is documented next to the kernels. A set word is also reported unasked: the kernel writes
+ * it through to a page-locked word the host can see, and the next b200ppResizeCropConvertReformat /
+ * b200ppCropFlipNormalizeReformat call on that device (hence the next cvcuda...Submit) returns B200PP_ERROR_INTERNAL
+ * without launching, until this function has cleared it. No synchronisation is added to any call for this. */
 B200PP_PUBLIC int b200ppReadDeviceError(uint32_t *outError);
 
-/* Self-test of the kernels' bounded waits: launches one warp that waits, for at most limitMs (1..1000) milliseconds, on a
+/* Test hook. Self-test of the kernels' bounded waits: launches one warp that waits, for at most limitMs (1..1000) milliseconds, on a
  * barrier nothing completes. The kernel then returns normally and bit 8 of the device error word is set; the context
  * stays usable. No counterpart in the reference. */
 B200PP_PUBLIC int b200ppSelfTestWaitTimeout(uint32_t limitMs, cudaStream_t stream);

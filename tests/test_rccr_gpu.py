@@ -296,9 +296,17 @@ def test_bounded_wait_gives_up_and_reports(pkg, oracle):
     torch.cuda.synchronize()
     elapsed = time.perf_counter() - t0
     assert 0.015 < elapsed < 1.0
+    # the word reaches the host by itself: the next call on this device is refused as an internal error, unasked and
+    # without a synchronisation of its own, until the word has been read
+    src = np.random.default_rng(1).integers(0, 256, (1, 40, 60, 3), dtype=np.uint8)
+    before = pkg.launch_count()
+    for _ in range(2):
+        with pytest.raises(pkg.ops.Error) as e:
+            pkg.resize_crop_convert_reformat(to_dev(src), (48, 32), 1, (0, 0, 48, 32), layout="NCHW", data_type=torch.float32)
+        assert e.value.status == pkg.ops.Status.ERROR_INTERNAL and "bounded internal wait" in e.value.message
+    assert pkg.launch_count() == before
     assert pkg.read_device_error() == 8
     assert pkg.read_device_error() == 0  # reading clears the word
-    src = np.random.default_rng(1).integers(0, 256, (1, 40, 60, 3), dtype=np.uint8)
     spec = oracle.ResizeSpec(resize=(48, 32), out_size=(48, 32), interp=1, src_cast=False)
     out = pkg.resize_crop_convert_reformat(to_dev(src), (48, 32), 1, (0, 0, 48, 32), layout="NCHW", data_type=torch.float32,
                                            srcCast=False)
