@@ -7,6 +7,7 @@ Everything computes in ``libcvcuda_b200.so`` (hand-written sm_100a kernels); the
 importing the operator functions fails loudly when the library has not been built.
 """
 from . import ops as _ops
+from . import cvcuda  # noqa: F401  (the reference-style object surface: cvcuda = nvcv = cvcuda_b200.cvcuda)
 from . import sharding  # noqa: F401
 from .ops import (  # noqa: F401
     Border,
