@@ -357,6 +357,35 @@ static int run_resize_dk(int dk, const ResizeKParams &kp, int srcWBound, cudaStr
 
 } // namespace b200pp
 
+namespace b200pp {
+
+template<typename S, typename D>
+static void launch_slice_typed_sd(int channels, dim3 grid, dim3 block, cudaStream_t stream, const SliceKParams &kp, int srcType,
+                                  int dstType)
+{
+    if (channels == 1)
+        slice_typed_kernel<S, D, 1><<<grid, block, 0, stream>>>(kp, srcType, dstType);
+    else if (channels == 3)
+        slice_typed_kernel<S, D, 3><<<grid, block, 0, stream>>>(kp, srcType, dstType);
+    else
+        slice_typed_kernel<S, D, 4><<<grid, block, 0, stream>>>(kp, srcType, dstType);
+}
+
+static void launch_slice_typed(bool srcFloat, bool dstFloat, int channels, dim3 grid, dim3 block, cudaStream_t stream,
+                               const SliceKParams &kp, int srcType, int dstType)
+{
+    if (srcFloat && dstFloat)
+        launch_slice_typed_sd<float, float>(channels, grid, block, stream, kp, srcType, dstType);
+    else if (srcFloat)
+        launch_slice_typed_sd<float, uint8_t>(channels, grid, block, stream, kp, srcType, dstType);
+    else if (dstFloat)
+        launch_slice_typed_sd<uint8_t, float>(channels, grid, block, stream, kp, srcType, dstType);
+    else
+        launch_slice_typed_sd<uint8_t, uint8_t>(channels, grid, block, stream, kp, srcType, dstType);
+}
+
+} // namespace b200pp
+
 using namespace b200pp;
 
 // ================================================================================================ C entry points
@@ -581,6 +610,34 @@ extern "C" int b200ppCropFlipNormalizeReformat(const B200ppSource *src, const B2
         else
             slice_u8x3_kernel<DST_U8><<<grid, block, 0, stream>>>(kp, dst->dtype, vecStore);
         return check_launch("CropFlipNormalizeReformat (uint8 x 3)");
+    }
+    // uint8 / float32 on both sides, 1, 3 or 4 channels: the typed kernel (element types and channel count compiled in)
+    const bool typedCase = (src->dtype == B200PP_U8 || src->dtype == B200PP_F32) && (dst->dtype == B200PP_U8 || dst->dtype == B200PP_F32)
+                        && (channels == 1 || channels == 3 || channels == 4);
+    // ... and among those the single-plane cases: one channel, or planar source to planar destination
+    const bool planeCase = typedCase && (channels == 1 || (kp.srcPlanar && kp.dPix == elem_size(dst->dtype)));
+    if (planeCase && path != 1)
+    {
+        const bool sf = src->dtype == B200PP_F32, df = dst->dtype == B200PP_F32;
+        const int  pix = sf ? 4 : 16, rowsPerBlock = 8 * (sf ? 4 : 2) * kSlicePlaneIters;
+        dim3       grid((kp.dstW + 32 * pix - 1) / (32 * pix), (kp.dstH + rowsPerBlock - 1) / rowsPerBlock,
+                        static_cast<unsigned>(std::min<long long>(static_cast<long long>(kp.numSamples) * channels, 32768)));
+        if (sf && df)
+            slice_plane_kernel<float, float><<<grid, block, 0, stream>>>(kp, src->dtype, dst->dtype, channels);
+        else if (sf)
+            slice_plane_kernel<float, uint8_t><<<grid, block, 0, stream>>>(kp, src->dtype, dst->dtype, channels);
+        else if (df)
+            slice_plane_kernel<uint8_t, float><<<grid, block, 0, stream>>>(kp, src->dtype, dst->dtype, channels);
+        else
+            slice_plane_kernel<uint8_t, uint8_t><<<grid, block, 0, stream>>>(kp, src->dtype, dst->dtype, channels);
+        return check_launch("CropFlipNormalizeReformat (planes)");
+    }
+    if (typedCase && path != 1)
+    {
+        const int rowsPerBlock = 8 * slice_typed_rows(channels);
+        dim3      grid((kp.dstW + 127) / 128, (kp.dstH + rowsPerBlock - 1) / rowsPerBlock, std::min(kp.numSamples, 32768));
+        launch_slice_typed(src->dtype == B200PP_F32, dst->dtype == B200PP_F32, channels, grid, block, stream, kp, src->dtype, dst->dtype);
+        return check_launch("CropFlipNormalizeReformat (typed)");
     }
     dim3 grid((kp.dstW + 31) / 32, (kp.dstH + 7) / 8, std::min(kp.numSamples, 32768));
     slice_gather_kernel<4><<<grid, block, 0, stream>>>(kp, src->dtype, dst->dtype, elem_size(src->dtype));

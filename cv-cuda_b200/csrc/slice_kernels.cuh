@@ -307,6 +307,390 @@ __global__ void __launch_bounds__(256, 4) slice_u8x3_kernel(const SliceKParams p
     }
 }
 
+// Typed kernel for the common element types other than interleaved RGB uint8: uint8 or float32 sources of 1, 3 or 4
+// channels, planar or interleaved, to uint8 or float32. Same shape of work as slice_u8x3_kernel -- a thread produces four
+// adjacent destination pixels in each of kSliceRowsPerThread rows, all loads of all rows requested before the arithmetic
+// -- with the element types and the channel count as template arguments, so that no choice is made per element. Four
+// pixels that lie inside the crop with their source pixels inside the image take the fast path; crop edges, borders and
+// ragged row ends go through slice_pixel. S, D: float or uint8_t.
+template<typename S>
+__device__ __forceinline__ float slice_load(const uint8_t *p)
+{
+    if constexpr (sizeof(S) == 4)
+        return __ldg(reinterpret_cast<const float *>(p));
+    else // float(byte) through the mantissa of 2^23: no conversion instruction
+        return __fsub_rn(__uint_as_float(0x4B000000u | __ldg(p)), 8388608.0f);
+}
+
+// Four finished values as four uint8 in one word: round half to even and clamp without a conversion instruction (clamp,
+// then add 1.5 * 2^23: the rounded value is the low byte of the sum's bit pattern; NaN clamps to 0 like cvt.sat), two byte
+// permutes to gather.
+__device__ __forceinline__ unsigned pack_sat_u8x4(float a, float b, float c, float e)
+{
+    const unsigned ua = __float_as_uint(__fadd_rn(fminf(fmaxf(a, 0.0f), 255.0f), 12582912.0f));
+    const unsigned ub = __float_as_uint(__fadd_rn(fminf(fmaxf(b, 0.0f), 255.0f), 12582912.0f));
+    const unsigned uc = __float_as_uint(__fadd_rn(fminf(fmaxf(c, 0.0f), 255.0f), 12582912.0f));
+    const unsigned ue = __float_as_uint(__fadd_rn(fminf(fmaxf(e, 0.0f), 255.0f), 12582912.0f));
+    return __byte_perm(__byte_perm(ua, ub, 0x0040), __byte_perm(uc, ue, 0x0040), 0x5410);
+}
+
+// Four finished values to four consecutive elements; `vec`: the address is a multiple of the four elements' size.
+template<typename D>
+__device__ __forceinline__ void slice_store4(uint8_t *d, float a, float b, float c, float e, bool vec)
+{
+    if constexpr (sizeof(D) == 4)
+    {
+        if (vec)
+            *reinterpret_cast<float4 *>(d) = make_float4(a, b, c, e);
+        else
+        {
+            float *f = reinterpret_cast<float *>(d);
+            f[0] = a, f[1] = b, f[2] = c, f[3] = e;
+        }
+    }
+    else
+    {
+        const unsigned w = pack_sat_u8x4(a, b, c, e);
+        if (vec)
+            *reinterpret_cast<unsigned *>(d) = w;
+        else
+            d[0] = static_cast<uint8_t>(w), d[1] = static_cast<uint8_t>(w >> 8), d[2] = static_cast<uint8_t>(w >> 16),
+            d[3] = static_cast<uint8_t>(w >> 24);
+    }
+}
+
+// Rows per thread: four for one channel, two for three or four (the loaded values of all rows live in registers).
+__host__ __device__ constexpr int slice_typed_rows(int channels)
+{
+    return channels == 1 ? 4 : 2;
+}
+
+template<typename S, typename D, int C>
+__global__ void __launch_bounds__(256, C == 1 ? 4 : 3) slice_typed_kernel(const SliceKParams p, const int srcType, const int dstType)
+{
+    constexpr int kRows = slice_typed_rows(C);
+    const int     j0    = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    const int     iBase = blockIdx.y * (blockDim.y * kRows) + threadIdx.y;
+    if (j0 >= p.dstW || iBase >= p.dstH)
+        return;
+    float base[C], mul[C];
+    load_constants<C>(p, base, mul);
+    const int  cols     = min(4, p.dstW - j0);
+    const bool dstPacked = p.dPix == C * static_cast<long long>(sizeof(D)) && p.dChan == static_cast<long long>(sizeof(D)); // interleaved
+    const bool dstPlanes = p.dPix == static_cast<long long>(sizeof(D));                                                   // planar
+
+    for (int n = blockIdx.z; n < p.numSamples; n += gridDim.z)
+    {
+        const SliceSample s     = load_slice_sample(p, n);
+        const bool        flipX = (s.flip == 1 || s.flip == -1);
+        const bool        flipY = (s.flip == 0 || s.flip == -1);
+        const int         xlo   = flipX ? s.cw - 1 - (j0 + 3) + s.cx : j0 + s.cx; // leftmost of the four source pixels
+        const bool        colsFast = cols == 4 && j0 + 3 < s.cw && xlo >= 0 && xlo + 3 < s.w;
+
+        float v[kRows][4 * C]; // [row][source pixel q * C + channel]
+        int   mode[kRows];     // 0 no such row, 1 loaded, 3 edge / border
+#pragma unroll
+        for (int r = 0; r < kRows; ++r)
+        {
+            const int i = iBase + r * blockDim.y;
+            const int y = flipY ? s.ch - 1 - i + s.cy : i + s.cy;
+            mode[r]     = i >= p.dstH ? 0 : ((colsFast && i < s.ch && y >= 0 && y < s.h) ? 1 : 3);
+            if (mode[r] == 1)
+            {
+                if (p.srcPlanar)
+                {
+#pragma unroll
+                    for (int k = 0; k < C; ++k)
+                    {
+                        const uint8_t  *plane = p.list ? p.list[n].planes[k].basePtr : s.img + k * s.planeStride;
+                        const long long pp    = p.list ? p.list[n].planes[k].rowStride : s.pitch;
+                        const uint8_t  *a     = plane + y * pp + static_cast<long long>(xlo) * sizeof(S);
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) v[r][q * C + k] = slice_load<S>(a + q * sizeof(S));
+                    }
+                }
+                else
+                {
+                    const uint8_t *a = s.img + y * s.pitch + static_cast<long long>(xlo) * (C * sizeof(S));
+                    if (sizeof(S) == 1 && C == 4 && (reinterpret_cast<unsigned long long>(a) & 3ull) == 0)
+                    {
+                        // four-byte pixels on word boundaries: one load per pixel, the bytes picked out with permutes
+#pragma unroll
+                        for (int q = 0; q < 4; ++q)
+                        {
+                            const unsigned word = __ldg(reinterpret_cast<const unsigned *>(a) + q);
+#pragma unroll
+                            for (int k = 0; k < C; ++k) v[r][q * C + k] = byte_as_float(word, 0x7540u + (k & 3));
+                        }
+                    }
+                    else
+                    {
+#pragma unroll
+                        for (int e = 0; e < 4 * C; ++e) v[r][e] = slice_load<S>(a + e * sizeof(S));
+                    }
+                }
+            }
+        }
+
+#pragma unroll
+        for (int r = 0; r < kRows; ++r)
+        {
+            const int i = iBase + r * blockDim.y;
+            if (mode[r] == 0)
+                break;
+            if (mode[r] == 3)
+            {
+                for (int q = 0; q < cols; ++q) slice_pixel<C>(p, s, n, i, j0 + q, srcType, dstType, sizeof(S), base, mul);
+                continue;
+            }
+            float o[4][C]; // [destination column][channel]
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+#pragma unroll
+                for (int k = 0; k < C; ++k)
+                    o[flipX ? 3 - q : q][k]
+                        = __fadd_rn(__fmul_rn(__fmul_rn(__fsub_rn(v[r][q * C + k], base[k]), mul[k]), p.gscale), p.shift);
+
+            uint8_t *dst = p.dst + n * p.dSample + i * p.dRow + j0 * p.dPix;
+            if (dstPlanes)
+            {
+#pragma unroll
+                for (int k = 0; k < C; ++k)
+                {
+                    uint8_t *d = dst + k * p.dChan;
+                    slice_store4<D>(d, o[0][k], o[1][k], o[2][k], o[3][k], (reinterpret_cast<unsigned long long>(d) & (4 * sizeof(D) - 1)) == 0);
+                }
+            }
+            else if (dstPacked)
+            {
+                const bool vec = (reinterpret_cast<unsigned long long>(dst) & (4 * sizeof(D) - 1)) == 0;
+                float      f[4 * C];
+#pragma unroll
+                for (int q = 0; q < 4; ++q)
+#pragma unroll
+                    for (int k = 0; k < C; ++k) f[q * C + k] = o[q][k];
+#pragma unroll
+                for (int g = 0; g < C; ++g)
+                    slice_store4<D>(dst + 4 * g * sizeof(D), f[4 * g], f[4 * g + 1], f[4 * g + 2], f[4 * g + 3], vec);
+            }
+            else
+            {
+#pragma unroll
+                for (int q = 0; q < 4; ++q)
+#pragma unroll
+                    for (int k = 0; k < C; ++k)
+                    {
+                        uint8_t *d = dst + q * p.dPix + k * p.dChan;
+                        if constexpr (sizeof(D) == 4)
+                            *reinterpret_cast<float *>(d) = o[q][k];
+                        else
+                            *d = static_cast<uint8_t>(sat_u8(o[q][k]));
+                    }
+            }
+        }
+    }
+}
+
+// Single-plane kernel: one-channel images, and planar sources written to planar destinations (every channel is then an
+// independent one-channel problem: blockIdx.z runs over sample x channel). A thread produces kPix adjacent destination
+// pixels -- sixteen uint8 or four float32 sources, i.e. sixteen source bytes, fetched as aligned words -- in each of kRows
+// rows, all rows' loads first. With four one-byte loads per thread, as the typed kernel would issue, a thread has far too
+// few bytes in flight to cover the memory latency (measured 125 us for 32 one-channel 1080p uint8 images).
+constexpr int kSlicePlaneIters = 4;
+
+template<typename S, typename D>
+__global__ void __launch_bounds__(256, 4) slice_plane_kernel(const SliceKParams p, const int srcType, const int dstType,
+                                                             const int planes)
+{
+    constexpr int kPix  = 16 / static_cast<int>(sizeof(S));
+    constexpr int kRows = sizeof(S) == 1 ? 2 : 4;
+    const int     j0    = (blockIdx.x * blockDim.x + threadIdx.x) * kPix;
+    const int     iFirst = blockIdx.y * (blockDim.y * kRows * kSlicePlaneIters) + threadIdx.y;
+    if (j0 >= p.dstW || iFirst >= p.dstH)
+        return;
+    const int cols = min(kPix, p.dstW - j0);
+
+    for (int z = blockIdx.z; z < p.numSamples * planes; z += gridDim.z)
+    {
+        const int         n = z / planes, k = z - n * planes;
+        const SliceSample s = load_slice_sample(p, n);
+        const uint8_t    *img;
+        long long         pitch;
+        if (planes > 1)
+        {
+            img   = p.list ? p.list[n].planes[k].basePtr : s.img + k * s.planeStride;
+            pitch = p.list ? p.list[n].planes[k].rowStride : s.pitch;
+        }
+        else
+        {
+            img   = s.img;
+            pitch = s.pitch;
+        }
+        // per-channel constants of this plane (load_constants for one channel)
+        const int   bk   = p.baseCh == 1 ? 0 : k, sk = p.scaleCh == 1 ? 0 : k;
+        const float base = *reinterpret_cast<const float *>(reinterpret_cast<const char *>(p.base) + bk * p.baseChanStride);
+        const float sc   = *reinterpret_cast<const float *>(reinterpret_cast<const char *>(p.scale) + sk * p.scaleChanStride);
+        const float mul  = p.stddev ? __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fmul_rn(sc, sc), p.epsilon))) : sc;
+
+        const bool flipX = (s.flip == 1 || s.flip == -1);
+        const bool flipY = (s.flip == 0 || s.flip == -1);
+        const int  xlo   = flipX ? s.cw - 1 - (j0 + kPix - 1) + s.cx : j0 + s.cx; // leftmost of the source pixels
+        const bool colsFast = cols == kPix && j0 + kPix - 1 < s.cw && xlo >= 0 && xlo + kPix - 1 < s.w;
+        const bool rowAligned = (reinterpret_cast<unsigned long long>(img) & 3ull) == 0 && (pitch & 3ll) == 0;
+
+        // A CTA walks down kSlicePlaneIters blocks of rows: what a thread has to find out about its sample (three dependent
+        // loads) is then paid once per 64 or more rows, not once per 16.
+        for (int it = 0; it < kSlicePlaneIters; ++it)
+        {
+        const int iBase = iFirst + it * (blockDim.y * kRows);
+        if (iBase >= p.dstH)
+            break;
+        unsigned w[kRows][5];
+        int      mode[kRows]; // 0 no such row, 1 words loaded, 3 anything else (per pixel)
+        unsigned shiftBits = 0;
+#pragma unroll
+        for (int r = 0; r < kRows; ++r)
+        {
+            const int i = iBase + r * blockDim.y;
+            const int y = flipY ? s.ch - 1 - i + s.cy : i + s.cy;
+            mode[r]     = i >= p.dstH ? 0 : 3;
+            if (mode[r] == 3 && colsFast && rowAligned && i < s.ch && y >= 0 && y < s.h)
+            {
+                const uint8_t           *rowPtr = img + y * pitch;
+                const unsigned long long addr   = reinterpret_cast<unsigned long long>(rowPtr + static_cast<long long>(xlo) * sizeof(S));
+                const bool               extra  = (addr & 3ull) != 0; // only uint8 rows can start inside a word
+                if ((addr & ~3ull) + (extra ? 20 : 16) <= reinterpret_cast<unsigned long long>(rowPtr) + static_cast<unsigned long long>(pitch))
+                {
+                    const unsigned *wp = reinterpret_cast<const unsigned *>(addr & ~3ull);
+                    shiftBits          = static_cast<unsigned>(addr & 3ull) * 8;
+                    if ((addr & 15ull) == 0)
+                    {
+                        const uint4 q = __ldg(reinterpret_cast<const uint4 *>(wp));
+                        w[r][0] = q.x, w[r][1] = q.y, w[r][2] = q.z, w[r][3] = q.w, w[r][4] = 0;
+                    }
+                    else
+                    {
+                        w[r][0] = __ldg(wp), w[r][1] = __ldg(wp + 1), w[r][2] = __ldg(wp + 2), w[r][3] = __ldg(wp + 3);
+                        w[r][4] = extra ? __ldg(wp + 4) : 0u;
+                    }
+                    mode[r] = 1;
+                }
+            }
+        }
+
+#pragma unroll
+        for (int r = 0; r < kRows; ++r)
+        {
+            const int i = iBase + r * blockDim.y;
+            if (mode[r] == 0)
+                break;
+            uint8_t *dst = p.dst + n * p.dSample + k * p.dChan + i * p.dRow + j0 * p.dPix;
+            if (mode[r] == 3)
+            {
+                // per pixel, with the crop, border and flip rules of slice_pixel, for this plane only
+                for (int q = 0; q < cols; ++q)
+                {
+                    const int j = j0 + q;
+                    float     o = 0.f;
+                    if (i < s.ch && j < s.cw)
+                    {
+                        int  x = flipX ? s.cw - 1 - j + s.cx : j + s.cx;
+                        int  y = flipY ? s.ch - 1 - i + s.cy : i + s.cy;
+                        bool inside = (x >= 0 && x < s.w && y >= 0 && y < s.h);
+                        if (!inside && p.border != B200PP_BORDER_CONSTANT && s.w >= 1 && s.h >= 1)
+                        {
+                            x      = border_index(x, s.w, p.border);
+                            y      = border_index(y, s.h, p.border);
+                            inside = true;
+                        }
+                        const float v = inside ? load_any(img + y * pitch + static_cast<long long>(x) * sizeof(S), srcType) : p.borderAsSrc;
+                        o             = __fadd_rn(__fmul_rn(__fmul_rn(__fsub_rn(v, base), mul), p.gscale), p.shift);
+                    }
+                    store_any(dst + q * p.dPix, dstType, o);
+                }
+                continue;
+            }
+            float t[kPix]; // by source pixel
+            if constexpr (sizeof(S) == 4)
+            {
+#pragma unroll
+                for (int q = 0; q < kPix; ++q) t[q] = __uint_as_float(w[r][q]);
+            }
+            else
+            {
+#pragma unroll
+                for (int g = 0; g < kPix / 4; ++g)
+                {
+                    const unsigned word = __funnelshift_r(w[r][g], w[r][g + 1], shiftBits);
+#pragma unroll
+                    for (int b = 0; b < 4; ++b) t[4 * g + b] = byte_as_float(word, 0x7540u + b);
+                }
+            }
+#pragma unroll
+            for (int q = 0; q < kPix; ++q) t[q] = __fadd_rn(__fmul_rn(__fmul_rn(__fsub_rn(t[q], base), mul), p.gscale), p.shift);
+            float o[kPix]; // by destination column: the reversal is a renaming of registers under a uniform branch
+            if (flipX)
+            {
+#pragma unroll
+                for (int q = 0; q < kPix; ++q) o[q] = t[kPix - 1 - q];
+            }
+            else
+            {
+#pragma unroll
+                for (int q = 0; q < kPix; ++q) o[q] = t[q];
+            }
+            if (p.dPix == static_cast<long long>(sizeof(D)))
+            {
+                const unsigned long long da = reinterpret_cast<unsigned long long>(dst);
+                if constexpr (sizeof(D) == 4)
+                {
+#pragma unroll
+                    for (int g = 0; g < kPix / 4; ++g)
+                        slice_store4<D>(dst + 16 * g, o[4 * g], o[4 * g + 1], o[4 * g + 2], o[4 * g + 3], (da & 15ull) == 0);
+                }
+                else
+                {
+                    unsigned pk[kPix / 4];
+#pragma unroll
+                    for (int g = 0; g < kPix / 4; ++g)
+                        pk[g] = pack_sat_u8x4(o[4 * g], o[4 * g + 1], o[4 * g + 2], o[4 * g + 3]);
+                    if constexpr (kPix == 16)
+                    {
+                        if ((da & 15ull) == 0)
+                        {
+                            *reinterpret_cast<uint4 *>(dst) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                            continue;
+                        }
+                    }
+#pragma unroll
+                    for (int g = 0; g < kPix / 4; ++g)
+                    {
+                        if ((da & 3ull) == 0)
+                            reinterpret_cast<unsigned *>(dst)[g] = pk[g];
+                        else
+                        {
+#pragma unroll
+                            for (int b = 0; b < 4; ++b) dst[4 * g + b] = static_cast<uint8_t>(pk[g] >> (8 * b));
+                        }
+                    }
+                }
+            }
+            else
+            {
+#pragma unroll
+                for (int q = 0; q < kPix; ++q)
+                {
+                    if constexpr (sizeof(D) == 4)
+                        *reinterpret_cast<float *>(dst + q * p.dPix) = o[q];
+                    else
+                        dst[q * p.dPix] = static_cast<uint8_t>(sat_u8(o[q]));
+                }
+            }
+        }
+        }
+    }
+}
+
 } // namespace b200pp
 
 #endif

@@ -24,7 +24,7 @@ INV_STD = tuple(float(np.float32(1.0) / np.float32(s)) for s in (58.395, 57.12, 
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--case", default="classify", choices=("classify", "classify-nhwc-u8", "classify-nhwc-f32", "classify-nhwc-u8-nearest", "4k", "4k-nearest", "letterbox", "cfnr", "varshape", "resize-rgba", "resize-rgba-nearest", "resize-rgb", "normalize-rgba", "normalize-rgb-f32", "reformat-u8", "reformat-f32", "convertto-u8-f32", "convertto-f32-u8", "border-rgb", "border-rgb-reflect", "border-rgba-f32", "rrc-rgb", "rrc-rgb-nearest"))
+    ap.add_argument("--case", default="classify", choices=("classify", "classify-nhwc-u8", "classify-nhwc-f32", "classify-nhwc-u8-nearest", "4k", "4k-nearest", "letterbox", "cfnr", "cfnr-u8c1", "cfnr-f32c1", "cfnr-rgba8-f32", "cfnr-rgb8p-f32", "cfnr-rgbf32", "varshape", "resize-rgba", "resize-rgba-nearest", "resize-rgb", "normalize-rgba", "normalize-rgb-f32", "reformat-u8", "reformat-f32", "convertto-u8-f32", "convertto-f32-u8", "border-rgb", "border-rgb-reflect", "border-rgba-f32", "rrc-rgb", "rrc-rgb-nearest"))
     ap.add_argument("--images", type=int, default=32)
     ap.add_argument("--path", type=int, default=0)
     ap.add_argument("--launches", type=int, default=5)
@@ -158,6 +158,31 @@ def main():
 
         def run():
             pkg.crop_flip_normalize_reformat_into(out, batch, rect, flip, base, scale, layout="NCHW",
+                                                  border=pkg.Border.REFLECT101)
+    elif a.case.startswith("cfnr-"):
+        # the other element types of CropFlipNormalizeReformat, same image size, crop and flip. u8c1 / f32c1 are the
+        # reference benchmark's own cases: one channel, output of the input's type, interleaved
+        kind = a.case[5:]
+        sdt, ch, planar, ddt, lay = {"u8c1": (torch.uint8, 1, False, torch.uint8, "NHWC"), "f32c1": (torch.float32, 1, False, torch.float32, "NHWC"),
+                                     "rgba8-f32": (torch.uint8, 4, False, torch.float32, "NCHW"),
+                                     "rgb8p-f32": (torch.uint8, 3, True, torch.float32, "NCHW"),
+                                     "rgbf32": (torch.float32, 3, False, torch.float32, "NHWC")}[kind]
+        shape = (ch, 1080, 1920) if planar else (1080, 1920, ch)
+        if sdt == torch.uint8:
+            imgs = [torch.randint(0, 256, shape, dtype=torch.uint8, device="cuda", generator=g) for _ in range(n)]
+        else:
+            imgs = [torch.rand(shape, dtype=torch.float32, device="cuda", generator=g) * 255 for _ in range(n)]
+        batch = pkg.ImageBatchVarShape(imgs, planar=planar)
+        out = torch.empty((n, ch, 1080, 1920) if lay == "NCHW" else (n, 1080, 1920, ch), dtype=ddt, device="cuda")
+        rect = torch.tensor([[0, 0, 1920, 1080]] * n, dtype=torch.int32, device="cuda").reshape(n, 1, 1, 4)
+        flip = torch.full((n,), -1, dtype=torch.int32, device="cuda")
+        base = torch.tensor((MEAN + (10.0,))[:ch], dtype=torch.float32, device="cuda").reshape(1, 1, 1, ch)
+        scale = torch.tensor((INV_STD + (0.02,))[:ch], dtype=torch.float32, device="cuda").reshape(1, 1, 1, ch)
+        moved = n * 1080 * 1920 * ch * (imgs[0].element_size() + out.element_size())
+        print(f"bytes per launch {moved}")
+
+        def run():
+            pkg.crop_flip_normalize_reformat_into(out, batch, rect, flip, base, scale, 1.234, 2.345, 12.34, 0, layout=lay,
                                                   border=pkg.Border.REFLECT101)
     else:
         def run():
