@@ -922,6 +922,8 @@ extern "C" int b200ppNormalize(const B200ppImageSet *src, const B200ppImageSet *
         normalize_kernel<B200PP_U8, B200PP_U8><<<grid, block, 0, stream>>>(kp);
     else if (src->dtype == B200PP_U8 && dst->dtype == B200PP_F32)
         normalize_kernel<B200PP_U8, B200PP_F32><<<grid, block, 0, stream>>>(kp);
+    else if (src->dtype == B200PP_F32 && dst->dtype == B200PP_F32 && g_kernelPath.load(std::memory_order_relaxed) != 1)
+        normalize_kernel<B200PP_F32, B200PP_F32><<<grid, block, 0, stream>>>(kp);
     else
         normalize_kernel<-1, -1><<<grid, block, 0, stream>>>(kp);
     return check_launch("Normalize");

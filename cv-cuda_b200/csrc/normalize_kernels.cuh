@@ -38,8 +38,9 @@ __device__ __forceinline__ float normalize_mul(const NormalizeKParams &p, float 
 constexpr int kNormRows = 4;
 constexpr int kNormCols = 2;
 
-// SRC / DST: the element type when it is one of the common ones (B200PP_U8 source; B200PP_U8 or B200PP_F32
-// destination), which removes the run-time type dispatch and the conversion instructions from the element loop; -1: any.
+// SRC / DST: the element type when it is one of the common ones (B200PP_U8 source with B200PP_U8 or B200PP_F32
+// destination; B200PP_F32 to B200PP_F32, the normalisation step after a float32 resize), which removes the run-time type
+// dispatch and the conversion instructions from the element loop; -1: any.
 template<int SRC, int DST>
 __global__ void __launch_bounds__(256) normalize_kernel(const NormalizeKParams p)
 {
@@ -116,6 +117,8 @@ __global__ void __launch_bounds__(256) normalize_kernel(const NormalizeKParams p
                     if constexpr (SRC == B200PP_U8)
                         // float(byte) without a conversion instruction: the byte becomes the low mantissa bits of 2^23
                         v = __fsub_rn(__uint_as_float(0x4B000000u | ((packed[r][k] >> (8 * c)) & 0xffu)), 8388608.0f);
+                    else if constexpr (SRC == B200PP_F32)
+                        v = __ldg(reinterpret_cast<const float *>(sp) + c);
                     else
                         v = load_any(sp + c * p.srcElem, p.srcType);
                     const float b = perChannel ? cb[c] : *reinterpret_cast<const float *>(bp + c * p.baseStride[3]);
