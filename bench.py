@@ -398,6 +398,14 @@ def run_harness_leg(args) -> int:
             res[name] = {"ms_per_step": ms, "value": n / (ms / 1000.0), "launches_per_step": launches}
         except R.HarnessError as e:
             res[name] = {"unavailable": str(e)[:300]}
+    if args.harness_leg == "b200" and cfg.key in ("2", "5-linear", "5-nearest"):
+        # end to end through the handle API: nvcv tensors that wrap page-locked host memory, at most 2 GiB of source per call
+        try:
+            m = min(n, (2 ** 31 - 1) // (cfg.h * cfg.w * 3))
+            ms = R.time_classify_e2e_host(L, m, cfg.h, cfg.w, cfg.resize, cfg.crop, cfg.out, cfg.interp, 2, max(3, min(args.steps, 10)))
+            res["e2e_host_tensors"] = {"ms_per_step": ms, "value": m / (ms / 1000.0), "images": m, "output": "float32 NCHW"}
+        except R.HarnessError as e:
+            res["e2e_host_tensors"] = {"unavailable": str(e)[:300]}
     print("HARNESS " + json.dumps(res))
     return 0
 
@@ -468,15 +476,35 @@ def run_native(args) -> int:
     gen.manual_seed(SEED + rank)
     out = torch.empty(cfg.out_shape(n), dtype=tdt, device=dev)
     sizes = rects = flips = None
+    def image_arena(sizes_wh):
+        """One allocation holding every image of a variable-shape batch (rows padded to 32 bytes, images on 256-byte
+        boundaries, as the reference's allocator lays images out), filled with seeded bytes; returns (arena, views, offsets)."""
+        offs, total = [], 0
+        for (w, h) in sizes_wh:
+            offs.append(total)
+            total += ((w * 3 + 31) // 32 * 32 * h + 255) // 256 * 256
+        arena = torch.empty((total,), dtype=torch.uint8, device=dev)
+        for i in range(0, total, 1 << 27):
+            arena[i:i + (1 << 27)] = torch.randint(0, 256, (min(1 << 27, total - i),), dtype=torch.uint8, device=dev, generator=gen)
+        return arena, image_views(arena, sizes_wh, offs), offs
+
+    def image_views(arena, sizes_wh, offs):
+        views = []
+        for (w, h), o in zip(sizes_wh, offs):
+            pitch = (w * 3 + 31) // 32 * 32
+            views.append(arena[o:o + pitch * h].view(h, pitch)[:, : w * 3].unflatten(1, (w, 3)))
+        return views
+
+    arena = arena_offsets = None
     if cfg.varshape:
         sizes, rects, flips = cfg.varshape_inputs(n, rank)
-        images = [torch.randint(0, 256, (h, (w * 3 + 31) // 32 * 32), dtype=torch.uint8, device=dev, generator=gen)[:, : w * 3]
-                  .unflatten(1, (w, 3)) for (w, h) in sizes]
+        arena, images, arena_offsets = image_arena(sizes)
         src = pkg.ImageBatchVarShape(images)
         t_rects, t_flips = torch.from_numpy(rects).to(dev), torch.from_numpy(flips).to(dev)
         src_bytes = sum(w * h * 3 for (w, h) in sizes)
     elif cfg.key == "cfnr":
-        images = [torch.randint(0, 256, (cfg.h, cfg.w, 3), dtype=torch.uint8, device=dev, generator=gen) for _ in range(n)]
+        sizes = [(cfg.w, cfg.h)] * n
+        arena, images, arena_offsets = image_arena(sizes)
         src = pkg.ImageBatchVarShape(images)
         t_rects = torch.tensor([[0, 0, cfg.w, cfg.h]] * n, dtype=torch.int32, device=dev).reshape(n, 1, 1, 4)
         t_flips = torch.full((n,), -1, dtype=torch.int32, device=dev)
@@ -560,13 +588,16 @@ def run_native(args) -> int:
 
     # ---- end to end from page-locked host memory to a page-locked host result. Large batches go through a bounded
     # page-locked staging batch (at most 2 GiB of source), passed as many times as the batch needs.
+    host_batch = None
     if cfg.varshape or cfg.key == "cfnr":
+        # the whole batch lives in one page-locked arena with the device arena's layout: one copy call moves it
         m = n
-        host_images = [torch.empty(tuple(im.shape), dtype=torch.uint8).pin_memory() for im in images]
-        for h_im, im in zip(host_images, images):
-            h_im.copy_(im)
-        dev_images, dev_src, host_src = images, src, None
-        h2d_full = src_bytes
+        host_arena = torch.empty((arena.numel(),), dtype=torch.uint8).pin_memory()
+        host_arena.copy_(arena)
+        host_images = image_views(host_arena, sizes, arena_offsets)
+        host_batch = pkg.ImageBatchVarShape(host_images)
+        dev_src, host_src = src, None
+        h2d_full = host_arena.numel()
     else:
         m = min(n, max(1, (2 ** 31) // (cfg.h * cfg.w * 3)))
         host_src = torch.empty((m, cfg.h, cfg.w, 3), dtype=torch.uint8).pin_memory()
@@ -582,8 +613,7 @@ def run_native(args) -> int:
         # whole batch host -> device, fused kernel, result device -> host
         for _ in range(passes):
             if host_src is None:
-                for d_im, h_im in zip(dev_images, host_images):
-                    d_im.copy_(h_im, non_blocking=True)
+                arena.copy_(host_arena, non_blocking=True)
             else:
                 dev_src.copy_(host_src, non_blocking=True)
             step(dev_out, dev_src)
@@ -608,6 +638,28 @@ def run_native(args) -> int:
 
         e2e_modes["kernel reads pinned host rows directly + d2h"] = (e2e_direct_step, tapped)
         e2e_modes["kernel reads pinned host rows and writes the pinned host result"] = (e2e_zero_copy_step, tapped)
+    if cfg.varshape:
+        # per-sample geometry from host memory: the staged kernel's bulk copies fetch exactly the tapped row segments over
+        # PCIe (the row-walk kernel's byte loads would cross the link one sector at a time)
+        tapped = int((alg - cfg.out_bytes_per_image()) * n)
+
+        def e2e_varshape_direct():
+            prev = pkg.set_kernel_path(2)
+            try:
+                step(dev_out, host_batch)
+            finally:
+                pkg.set_kernel_path(prev)
+            host_out.copy_(dev_out, non_blocking=True)
+
+        def e2e_varshape_zero_copy():
+            prev = pkg.set_kernel_path(2)
+            try:
+                step(host_out, host_batch)
+            finally:
+                pkg.set_kernel_path(prev)
+
+        e2e_modes["kernel reads pinned host rows directly + d2h"] = (e2e_varshape_direct, tapped)
+        e2e_modes["kernel reads pinned host rows and writes the pinned host result"] = (e2e_varshape_zero_copy, tapped)
     e2e_results = {}
     for name, (fn, h2d_bytes) in e2e_modes.items():
         for _ in range(2):
@@ -698,7 +750,8 @@ def run_native(args) -> int:
                     "chain": HARNESS_NOTES[cfg.key], "unit": UNIT + " on one GPU", **ref_leg}
         handle_api = {"kind": "this library through the same wrappers and real nvcv handles: `one_pass` = the extended entry "
                               "point (cvcudaB200FusedPreprocess[VarShape]Submit), `chain` = the same operator chain as the "
-                              "reference's", "unit": UNIT + " on one GPU", **own_leg}
+                              "reference's, `e2e_host_tensors` = one_pass on nvcv tensors that wrap page-locked host memory "
+                              "(source rows pulled over PCIe, result written to the host)", "unit": UNIT + " on one GPU", **own_leg}
         line.update({
             "e2e": {"value": e2e_results[best]["value"], "unit": UNIT, "mode": best,
                     "h2d_bytes_per_step": e2e_results[best]["h2d_bytes_per_step"], "d2h_bytes_per_step": d2h_bytes,

@@ -63,6 +63,7 @@ struct StagedCfg
     int       chunksPerRow;
     long long totalUnits;   // numSamples * ceil(dstH / unitRows) * chunksPerRow
     long long blockUnits;   // consecutive units dealt to a CTA at a time
+    int       probe;        // test hook: consumers skip the taps and the arithmetic and store the pad value (memory-only run)
 };
 
 // Arguments of the crop/flip/normalise kernel.

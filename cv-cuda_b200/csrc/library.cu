@@ -164,7 +164,9 @@ static int staged_occupancy(K kernel, int dev, int kernelId, int block, int smem
 // B200PP_STAGES (ring depth), B200PP_MAX_CTAS_PER_SM (cap on resident CTAs per SM of the staged kernel) and
 // B200PP_BLOCK_UNITS (consecutive units dealt to a CTA at a time), B200PP_MAX_CONSUMERS (consumer threads per CTA),
 // B200PP_UNIT_ROWS (destination rows per work unit of the staged kernel), B200PP_WALK_ROWS (rows per CTA of the
-// row-walk kernel).
+// row-walk kernel), B200PP_PROBE (1: the staged kernel's consumers skip the taps and the arithmetic and store the pad
+// value -- the launch then moves exactly the real launch's bytes and nothing else, which measures the floor of its copy and
+// store pattern; results are meaningless).
 struct Tuning
 {
     int stages       = 0;
@@ -174,6 +176,8 @@ struct Tuning
     int unitRows     = 0;
     int walkRows     = 0;
     int teams        = 0;
+    int probe        = 0;
+    int chunkCols    = 0;
 };
 
 static const Tuning &tuning()
@@ -196,6 +200,10 @@ static const Tuning &tuning()
             v.walkRows = atoi(w);
         if (const char *t = getenv("B200PP_TEAMS"))
             v.teams = atoi(t);
+        if (const char *pr = getenv("B200PP_PROBE"))
+            v.probe = atoi(pr);
+        if (const char *cc = getenv("B200PP_CHUNK_COLS"))
+            v.chunkCols = atoi(cc);
         return v;
     }();
     return t;
@@ -253,6 +261,8 @@ static int launch_resize_staged(const ResizeKParams &kp, int srcWBound, cudaStre
     };
     const int kMaxSeg = 32 * 1024;
     cfg.chunkCols     = kp.dstW;
+    if (tuning().chunkCols >= 32)
+        cfg.chunkCols = std::min(kp.dstW, (tuning().chunkCols + 3) / 4 * 4);
     // a consumer warp covers 128 columns (four per lane) and a CTA has at most eight consumer warps
     while (cfg.chunkCols > 32 && (cfg.chunkCols > 1024 || seg_for(cfg.chunkCols) > kMaxSeg))
         cfg.chunkCols = ((cfg.chunkCols + 1) / 2 + 3) / 4 * 4;
@@ -266,7 +276,11 @@ static int launch_resize_staged(const ResizeKParams &kp, int srcWBound, cudaStre
     const int  elemBytes  = DK == DST_F32 ? 4 : (DK == DST_F16 ? 2 : 1);
     const bool planarF32  = DK == DST_F32 && kp.dPix == elemBytes && cfg.chunkCols <= 256;
     const int  rowBytes   = cfg.segBytes * cfg.rowsPerStage;
-    const int  unitTarget = (planarF32 ? 40 : 24) * 1024;
+    // Rows wider than 512 destination columns with linear interpolation (the letterbox case: 640 columns, five consumer warps
+    // side by side, one row at a time): measured best with three rows per unit and three slots, 92.3 us against 96.6 us for
+    // 64 1080p images into 640x640 (two rows, two slots); chunking such rows was slower at every size tried (109-184 us).
+    const bool wideLinear = INTERP == B200PP_INTERP_LINEAR && cfg.chunkCols > 512;
+    const int  unitTarget = (planarF32 ? 40 : (wideLinear ? 36 : 24)) * 1024;
     cfg.unitRows          = std::max(1, std::min({kMaxUnitRows, (unitTarget + rowBytes / 2) / rowBytes, kp.dstH}));
     if (tuning().unitRows > 0)
         cfg.unitRows = std::max(1, std::min({kMaxUnitRows, tuning().unitRows, kp.dstH}));
@@ -274,7 +288,7 @@ static int launch_resize_staged(const ResizeKParams &kp, int srcWBound, cudaStre
 
     const int stageBytes = rowBytes * cfg.unitRows;
     // About 30-40 KB of copies in flight per CTA (four CTAs per SM): measured best on B200; deeper rings were slower.
-    cfg.stages           = std::max(2, std::min(8, (32 * 1024) / stageBytes));
+    cfg.stages           = std::max(wideLinear ? 3 : 2, std::min(8, (32 * 1024) / stageBytes));
     if (tuning().stages > 0)
         cfg.stages = std::max(2, std::min(16, tuning().stages));
     const int smemBytes  = cfg.stages * stageBytes + cfg.stages * (int)sizeof(UnitInfo) + cfg.stages * 16
@@ -312,6 +326,7 @@ static int launch_resize_staged(const ResizeKParams &kp, int srcWBound, cudaStre
     cfg.blockUnits       = perSample ? (cfg.totalUnits + grid - 1) / grid : 1;
     if (tuning().blockUnits > 0)
         cfg.blockUnits = tuning().blockUnits;
+    cfg.probe = tuning().probe != 0;
     kernel<<<static_cast<unsigned>(grid), block, smemBytes, stream>>>(kp, cfg);
     *status = check_launch("ResizeCropConvertReformat (staged)");
     return 1;

@@ -1094,7 +1094,15 @@ __global__ void __launch_bounds__(288, INTERP == B200PP_INTERP_NEAREST ? 3 : 2) 
             {
                 const SmemRow r0{slotA + ra.y};
                 const SmemRow r1{r0.a + ((ra.x & 0x100u) ? segStep : 0u)};
-                quad_values<INTERP>(p, pv, quad, r0, r1, wy0s, wy1s, v);
+                if (cfg.probe) // memory-only run: every copy and every store of the real launch, no taps, no arithmetic
+                {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+#pragma unroll
+                        for (int c = 0; c < 3; ++c) v[i][c] = pv.v[c];
+                }
+                else
+                    quad_values<INTERP>(p, pv, quad, r0, r1, wy0s, wy1s, v);
             }
             else
             {
@@ -1135,7 +1143,7 @@ struct alignas(16) WalkRow
 };
 
 template<int INTERP, int DK, bool IL>
-__global__ void __launch_bounds__(256) resize_rowwalk_kernel(const ResizeKParams p, const int rowsPerCta, const int chunksPerRow)
+__global__ void __launch_bounds__(256, 6) resize_rowwalk_kernel(const ResizeKParams p, const int rowsPerCta, const int chunksPerRow)
 {
     __shared__ WalkRow rows[kWalkRowsMax];
 

@@ -321,7 +321,8 @@ B200PP_PUBLIC const char *b200ppGetLastErrorMessage(void);
 /* ---- Test and profiling hooks. Not part of the operator interface: process-wide state that two threads cannot set
  * differently, kept for the tests (which run every kernel on the same inputs) and for profiling runs. The same holds for
  * the B200PP_* environment variables (B200PP_STAGES, _UNIT_ROWS, _TEAMS, _MAX_CONSUMERS, _MAX_CTAS_PER_SM, _BLOCK_UNITS,
- * _WALK_ROWS), which are read once per process and only reshape launches. ---- */
+ * _WALK_ROWS, and B200PP_PROBE, which makes the staged kernel move its bytes without computing anything), which are read once
+ * per process and, PROBE apart, only reshape launches. ---- */
 
 /* Kernel selection: 0 automatic (default), 1 force the per-pixel gather kernels, 2 force the staged (bulk-copy pipelined)
  * kernel where it applies, 3 force the row-walk kernel. Process-wide. Returns the previous value. Test hook. */

@@ -1,7 +1,7 @@
 """ctypes front-end of the reference project's own CUDA kernels (oracle/_ref/libref_cuda_kernels.so).
 
-TEST / BASELINE INFRASTRUCTURE ONLY: used by GPU tests as a cross-check and by tests/reference_cuda_timing.py to time the
-reference kernels on the same GPU. The product package never imports this module.
+TEST / BASELINE INFRASTRUCTURE ONLY: used by GPU tests as a cross-check of single kernels (the timed baseline is the
+reference's whole operators, oracle/ref_ops.py). The product package never imports this module.
 """
 from __future__ import annotations
 

@@ -31,7 +31,7 @@ def load(which: str) -> Optional[C.CDLL]:
         L = C.CDLL(path(which))
         L.h_last_message.restype = C.c_char_p
         L.h_which.restype = C.c_char_p
-        for name in ("h_rccr_tensor", "h_rccr_varshape", "h_cfnr", "h_time_classify", "h_time_letterbox", "h_time_varshape", "h_time_cfnr"):
+        for name in ("h_rccr_tensor", "h_rccr_varshape", "h_cfnr", "h_time_classify", "h_time_letterbox", "h_time_varshape", "h_time_cfnr", "h_time_classify_e2e_host"):
             getattr(L, name).restype = C.c_int
         _loaded[which] = L
     return _loaded[which]
@@ -130,3 +130,11 @@ def time_cfnr(L, n, h, w, warmup: int, iters: int):
     ms, launches = C.c_float(), C.c_int()
     _check(L, L.h_time_cfnr(n, h, w, warmup, iters, C.byref(ms), C.byref(launches)))
     return ms.value, launches.value
+
+
+def time_classify_e2e_host(L, n, h, w, resize, crop, out_size, interp, warmup: int, iters: int):
+    """ms per pass of the one-pass entry point on nvcv tensors that wrap page-locked host memory (B200 build only)."""
+    ms = C.c_float()
+    _check(L, L.h_time_classify_e2e_host(n, h, w, resize[0], resize[1], crop[0], crop[1], out_size[0], out_size[1], int(interp),
+                                         warmup, iters, C.byref(ms)))
+    return ms.value

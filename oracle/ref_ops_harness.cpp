@@ -567,4 +567,52 @@ int h_time_cfnr(int n, int h, int w, int warmup, int iters, float *ms, int *laun
         });
     });
 }
+// End to end through the handle API: page-locked HOST memory wrapped as nvcv tensors (nvcv::TensorWrapData; the kernels take
+// any device-accessible address), one extended-entry-point call per pass reading the tapped source rows over PCIe and writing
+// the result rows into the page-locked result. n images of h x w -> resize (rw, rh) -> crop -> per-channel normalise -> float32
+// NCHW. B200 build only.
+int h_time_classify_e2e_host(int n, int h, int w, int rw, int rh, int cx, int cy, int ow, int oh, int interp, int warmup,
+                             int iters, float *ms)
+{
+    return guarded([&] {
+#ifdef HARNESS_B200
+        Stream       st;
+        const size_t srcBytes = static_cast<size_t>(n) * h * w * 3, dstBytes = static_cast<size_t>(n) * 3 * oh * ow * sizeof(float);
+        uint8_t     *hsrc     = nullptr;
+        float       *hdst     = nullptr;
+        check(cudaHostAlloc(reinterpret_cast<void **>(&hsrc), srcBytes, cudaHostAllocDefault), "cudaHostAlloc");
+        check(cudaHostAlloc(reinterpret_cast<void **>(&hdst), dstBytes, cudaHostAllocDefault), "cudaHostAlloc");
+        unsigned x = 2463534242u;
+        for (size_t i = 0; i < srcBytes; i += 4)
+        {
+            x ^= x << 13, x ^= x >> 17, x ^= x << 5;
+            std::memcpy(hsrc + i, &x, std::min<size_t>(4, srcBytes - i));
+        }
+        {
+            nvcv::TensorDataStridedCuda::Buffer bi{}, bo{};
+            bi.strides[3] = 1, bi.strides[2] = 3, bi.strides[1] = static_cast<int64_t>(w) * 3, bi.strides[0] = static_cast<int64_t>(h) * w * 3;
+            bi.basePtr    = reinterpret_cast<NVCVByte *>(hsrc);
+            bo.strides[3] = 4, bo.strides[2] = static_cast<int64_t>(ow) * 4, bo.strides[1] = static_cast<int64_t>(oh) * ow * 4;
+            bo.strides[0] = 3 * bo.strides[1];
+            bo.basePtr    = reinterpret_cast<NVCVByte *>(hdst);
+            nvcv::Tensor in  = nvcv::TensorWrapData(nvcv::TensorDataStridedCuda(nvcv::TensorShape({n, h, w, 3}, "NHWC"), nvcv::TYPE_U8, bi));
+            nvcv::Tensor out = nvcv::TensorWrapData(nvcv::TensorDataStridedCuda(nvcv::TensorShape({n, 3, oh, ow}, "NCHW"), nvcv::TYPE_F32, bo));
+            cvcuda::ResizeCropConvertReformat rccr;
+            B200ppResizeOp                    op;
+            std::memset(&op, 0, sizeof(op));
+            op.resizeW = rw, op.resizeH = rh, op.cropX = cx, op.cropY = cy, op.interp = interp, op.srcCast = 0;
+            op.perChannel = 1, op.gscale = 1.f, op.shift = 0.f, op.scale = 1.f;
+            for (int c = 0; c < 3; ++c) op.base[c] = kMean[c], op.mul[c] = 1.0f / kStd[c];
+            *ms = time_passes(st.s, warmup, iters, [&] {
+                nvcv::detail::CheckThrow(cvcudaB200FusedPreprocessSubmit(rccr.handle(), st.s, in.handle(), out.handle(), &op));
+            });
+        }
+        cudaFreeHost(hsrc);
+        cudaFreeHost(hdst);
+#else
+        (void)n, (void)h, (void)w, (void)rw, (void)rh, (void)cx, (void)cy, (void)ow, (void)oh, (void)interp, (void)warmup, (void)iters, (void)ms;
+        throw std::runtime_error("the one-pass entry point exists in the B200 library only");
+#endif
+    });
+}
 }
