@@ -398,6 +398,25 @@ def run_harness_leg(args) -> int:
             res[name] = {"ms_per_step": ms, "value": n / (ms / 1000.0), "launches_per_step": launches}
         except R.HarnessError as e:
             res[name] = {"unavailable": str(e)[:300]}
+    # the operators of the chain one at a time (same tensors, the others not run inside the timed region)
+    stage_names = {"2": ["ResizeCropConvertReformat f32 NHWC", "Normalize f32", "Reformat NHWC->NCHW"],
+                   "4": ["Resize u8", "CopyMakeBorder u8", "ConvertTo u8->f32", "Reformat NHWC->NCHW"]}.get(cfg.key)
+    if stage_names and "ms_per_step" in res.get("chain", {}):
+        stages = {}
+        try:
+            for i, name in enumerate(stage_names):
+                R.select_stage(L, i)
+                if cfg.key == "2":
+                    ms, _ = R.time_classify(L, n, cfg.h, cfg.w, cfg.resize, cfg.crop, cfg.out, cfg.interp, True,
+                                            (2 ** 31 - 1) // (cfg.h * cfg.w * 3), wu, it)
+                else:
+                    ms, _ = R.time_letterbox(L, n, cfg.h, cfg.w, cfg.resize, cfg.canvas, cfg.top, True, wu, it)
+                stages[name] = ms
+        except R.HarnessError as e:
+            stages["unavailable"] = str(e)[:200]
+        finally:
+            R.select_stage(L, -1)
+        res["chain"]["stage_ms"] = stages
     if args.harness_leg == "b200" and cfg.key in ("2", "5-linear", "5-nearest"):
         # end to end through the handle API: nvcv tensors that wrap page-locked host memory, at most 2 GiB of source per call
         try:

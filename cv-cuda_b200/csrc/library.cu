@@ -664,24 +664,26 @@ extern "C" int b200ppCropFlipNormalizeReformat(const B200ppSource *src, const B2
 namespace b200pp {
 
 template<typename T, int C>
-static void launch_plain(int interp, dim3 grid, dim3 block, cudaStream_t stream, const PlainResizeKParams &kp)
+static void launch_plain(int interp, bool singleTap, dim3 grid, dim3 block, cudaStream_t stream, const PlainResizeKParams &kp)
 {
     if (interp == B200PP_INTERP_NEAREST)
         resize_plain_kernel<T, C, B200PP_INTERP_NEAREST><<<grid, block, 0, stream>>>(kp);
+    else if (sizeof(T) == 1 && singleTap)
+        resize_plain_kernel<T, C, B200PP_INTERP_LINEAR, true><<<grid, block, 0, stream>>>(kp);
     else
         resize_plain_kernel<T, C, B200PP_INTERP_LINEAR><<<grid, block, 0, stream>>>(kp);
 }
 
 template<typename T>
-static void launch_plain_channels(int channels, int interp, dim3 grid, dim3 block, cudaStream_t stream,
+static void launch_plain_channels(int channels, int interp, bool singleTap, dim3 grid, dim3 block, cudaStream_t stream,
                                   const PlainResizeKParams &kp)
 {
     if (channels == 1)
-        launch_plain<T, 1>(interp, grid, block, stream, kp);
+        launch_plain<T, 1>(interp, singleTap, grid, block, stream, kp);
     else if (channels == 3)
-        launch_plain<T, 3>(interp, grid, block, stream, kp);
+        launch_plain<T, 3>(interp, singleTap, grid, block, stream, kp);
     else
-        launch_plain<T, 4>(interp, grid, block, stream, kp);
+        launch_plain<T, 4>(interp, singleTap, grid, block, stream, kp);
 }
 
 static PlainSide plain_side(const B200ppImageSet *s)
@@ -745,19 +747,24 @@ static int resize_common(const B200ppImageSet *src, const B200ppImageSet *dst, i
               std::min(src->numSamples, 65535));
     if (grid.y > 65535u)
         return fail(B200PP_ERROR_INVALID_ARGUMENT, "Input or output tensors are too large");
+    // Odd whole-number scale factors on both axes (1080p -> 640x360 is 3 x 3) put every sample position on a source pixel:
+    // all second taps weigh exactly zero and the uint8 kernel may take its single-tap shortcut.
+    auto oddMultiple = [](int s, int d) { return d > 0 && s % d == 0 && ((s / d) & 1) == 1; };
+    const bool singleTap = !src->imageList && !dst->imageList && !cropRects && oddMultiple(src->width, dst->width)
+                        && oddMultiple(src->height, dst->height);
     switch (src->dtype)
     {
     case B200PP_U8:
-        launch_plain_channels<uint8_t>(src->channels, interp, grid, block, stream, kp);
+        launch_plain_channels<uint8_t>(src->channels, interp, singleTap, grid, block, stream, kp);
         break;
     case B200PP_U16:
-        launch_plain_channels<uint16_t>(src->channels, interp, grid, block, stream, kp);
+        launch_plain_channels<uint16_t>(src->channels, interp, singleTap, grid, block, stream, kp);
         break;
     case B200PP_S16:
-        launch_plain_channels<int16_t>(src->channels, interp, grid, block, stream, kp);
+        launch_plain_channels<int16_t>(src->channels, interp, singleTap, grid, block, stream, kp);
         break;
     default:
-        launch_plain_channels<float>(src->channels, interp, grid, block, stream, kp);
+        launch_plain_channels<float>(src->channels, interp, singleTap, grid, block, stream, kp);
         break;
     }
     return check_launch("Resize");
@@ -932,6 +939,21 @@ extern "C" int b200ppNormalize(const B200ppImageSet *src, const B200ppImageSet *
         else
             normalize_lut_kernel<1><<<lutGrid, block, 0, stream>>>(kp);
         return check_launch("Normalize");
+    }
+    if (src->dtype == B200PP_F32 && dst->dtype == B200PP_F32 && perChannel && src->channels != 2
+        && g_kernelPath.load(std::memory_order_relaxed) != 1)
+    {
+        // four pixels x two rows per thread
+        dim3 fgrid((gw + 127) / 128, (gh + 15) / 16, grid.z);
+        if (fgrid.y > 65535u)
+            return fail(B200PP_ERROR_INVALID_ARGUMENT, "Input or output tensors are too large");
+        if (src->channels == 1)
+            normalize_f32_kernel<1><<<fgrid, block, 0, stream>>>(kp);
+        else if (src->channels == 3)
+            normalize_f32_kernel<3><<<fgrid, block, 0, stream>>>(kp);
+        else
+            normalize_f32_kernel<4><<<fgrid, block, 0, stream>>>(kp);
+        return check_launch("Normalize (float32)");
     }
     if (src->dtype == B200PP_U8 && dst->dtype == B200PP_U8)
         normalize_kernel<B200PP_U8, B200PP_U8><<<grid, block, 0, stream>>>(kp);

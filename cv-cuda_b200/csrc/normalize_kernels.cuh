@@ -145,6 +145,81 @@ __global__ void __launch_bounds__(256) normalize_kernel(const NormalizeKParams p
     }
 }
 
+// float32 -> float32 with base and scale that vary by channel only (the normalisation step after a float32 resize): a
+// copy with four floating-point operations per element, so it is written like one. A thread handles four adjacent pixels
+// = C 16-byte vectors in each of two rows, all loads first; which channel an element of a vector belongs to is known at
+// compile time (for three channels the pattern repeats every three vectors). Rows that do not start on 16-byte boundaries
+// go element by element.
+template<int C>
+__global__ void __launch_bounds__(256, 4) normalize_f32_kernel(const NormalizeKParams p)
+{
+    constexpr int kRows = 2;
+    const int     g  = blockIdx.x * blockDim.x + threadIdx.x; // group of four pixels
+    const int     y0 = blockIdx.y * (blockDim.y * kRows) + threadIdx.y;
+    float         cb[C], cm[C];
+#pragma unroll
+    for (int c = 0; c < C; ++c)
+    {
+        cb[c] = *reinterpret_cast<const float *>(reinterpret_cast<const char *>(p.base) + c * p.baseStride[3]);
+        cm[c] = normalize_mul(p, *reinterpret_cast<const float *>(reinterpret_cast<const char *>(p.scale) + c * p.scaleStride[3]));
+    }
+    for (int n = blockIdx.z; n < p.numSamples; n += gridDim.z)
+    {
+        const PlainView S = plain_view(p.src, n), D = plain_view(p.dst, n);
+        const int       w = min(S.w, D.w), h = min(S.h, D.h);
+        if (4 * g >= w)
+            continue;
+        const bool vec = 4 * g + 3 < w
+                      && ((reinterpret_cast<unsigned long long>(S.base) | reinterpret_cast<unsigned long long>(D.base)
+                           | static_cast<unsigned long long>(S.pitch) | static_cast<unsigned long long>(D.pitch)) & 15ull) == 0;
+        float4 v[kRows][C];
+        if (vec)
+        {
+#pragma unroll
+            for (int r = 0; r < kRows; ++r)
+            {
+                const int y = min(y0 + r * blockDim.y, h - 1);
+                const float4 *sp = reinterpret_cast<const float4 *>(S.base + y * S.pitch) + static_cast<long long>(g) * C;
+#pragma unroll
+                for (int k = 0; k < C; ++k) v[r][k] = __ldg(sp + k);
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < kRows; ++r)
+        {
+            const int y = y0 + r * blockDim.y;
+            if (y >= h)
+                break;
+            if (vec)
+            {
+                float4 *dp = reinterpret_cast<float4 *>(D.base + y * D.pitch) + static_cast<long long>(g) * C;
+#pragma unroll
+                for (int k = 0; k < C; ++k)
+                {
+                    float e[4] = {v[r][k].x, v[r][k].y, v[r][k].z, v[r][k].w};
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                    {
+                        constexpr int kDummy = 0;
+                        const int     c      = (4 * k + i) % C + kDummy; // compile-time after unrolling
+                        e[i] = __fadd_rn(__fmul_rn(__fmul_rn(__fsub_rn(e[i], cb[c]), cm[c]), p.gscale), p.shift);
+                    }
+                    dp[k] = make_float4(e[0], e[1], e[2], e[3]);
+                }
+            }
+            else
+            {
+                const float *sp = reinterpret_cast<const float *>(S.base + y * S.pitch);
+                float       *dp = reinterpret_cast<float *>(D.base + y * D.pitch);
+                for (int x = 4 * g; x < min(4 * g + 4, w); ++x)
+#pragma unroll
+                    for (int c = 0; c < C; ++c)
+                        dp[x * C + c] = __fadd_rn(__fmul_rn(__fmul_rn(__fsub_rn(sp[x * C + c], cb[c]), cm[c]), p.gscale), p.shift);
+            }
+        }
+    }
+}
+
 // uint8 sources with base and scale that vary by channel only (the usual mean / standard-deviation case): the 256
 // possible results per channel are computed once per CTA with the arithmetic above and kept in shared memory; an element
 // then costs one shared-memory lookup. A thread handles four 4-byte words of a source row, 32 words apart (a warp reads 128

@@ -213,7 +213,10 @@ __device__ __forceinline__ void linear_tap_exact(float scale, int d, int size, i
     s1       = min(s0 + 1, size - 1);
 }
 
-template<typename T, int C, int INTERP>
+// SINGLE: compiled with the single-tap shortcut for rows and columns whose second taps all weigh exactly zero (launched when
+// the host sees odd whole-number scale factors; the shortcut still checks the weights, so a wrong guess only costs time).
+// The shortcut is kept out of the general instantiation, where its extra live ranges cost 8-17 % (spills at 80 registers).
+template<typename T, int C, int INTERP, bool SINGLE = false>
 __global__ void __launch_bounds__(256, INTERP == B200PP_INTERP_LINEAR && sizeof(T) == 1 ? 3 : 1) resize_plain_kernel(const PlainResizeKParams p)
 {
     const int     dx0  = blockIdx.x * (32 * kPlainCols) + threadIdx.x;
@@ -249,6 +252,7 @@ __global__ void __launch_bounds__(256, INTERP == B200PP_INTERP_LINEAR && sizeof(
         float  wx1f[kPlainCols];                    // uint8 fast path
         double wx1d[kPlainCols];                    // other element types
         unsigned exactCols = 0; // bit k: column k's weights are multiples of 2^-8
+        unsigned zeroCols  = 0; // bit k: column k's second tap has weight exactly zero (it is then not even read)
 #pragma unroll
         for (int k = 0; k < kPlainCols; ++k)
         {
@@ -271,6 +275,9 @@ __global__ void __launch_bounds__(256, INTERP == B200PP_INTERP_LINEAR && sizeof(
                     wx1f[k] = static_cast<float>(w1);
                     if (is_multiple_of_2_to_minus_8(w1))
                         exactCols |= 1u << k;
+                    if constexpr (SINGLE)
+                        if (w1 == 0.0)
+                            zeroCols |= 1u << k;
                 }
                 else
                     wx1d[k] = w1;
@@ -320,6 +327,20 @@ __global__ void __launch_bounds__(256, INTERP == B200PP_INTERP_LINEAR && sizeof(
                     // exact tie). Adding 1.5 * 2^23 rounds half-to-even and leaves the integer in the low mantissa
                     // bits: no conversion instruction anywhere.
                     unsigned q00[kPlainCols], q10[kPlainCols], q01[kPlainCols], q11[kPlainCols];
+                    // All second taps of weight exactly zero (whole-number scale factors: 1080p -> 640x360): the blend of
+                    // every pixel is its first tap, exactly, in float32 and in double precision alike, so the row is a
+                    // gather of single pixels -- one tap of four read, one source row of two. Decided per thread (the
+                    // same for all threads when the scale factor is a whole number); anything else takes all four taps.
+                    if (SINGLE && fy == 0.0 && zeroCols == (1u << kPlainCols) - 1u)
+                    {
+#pragma unroll
+                        for (int k = 0; k < kPlainCols; ++k) q00[k] = load_packed<C>(r0 + off0[k], vector);
+#pragma unroll
+                        for (int k = 0; k < kPlainCols; ++k)
+                            if (dx0 + 32 * k < D.w)
+                                store_packed<C>(drow + static_cast<long long>(dx0 + 32 * k) * kPix, q00[k], vector);
+                        continue;
+                    }
 #pragma unroll
                     for (int k = 0; k < kPlainCols; ++k)
                     {

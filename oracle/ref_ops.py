@@ -138,3 +138,8 @@ def time_classify_e2e_host(L, n, h, w, resize, crop, out_size, interp, warmup: i
     _check(L, L.h_time_classify_e2e_host(n, h, w, resize[0], resize[1], crop[0], crop[1], out_size[0], out_size[1], int(interp),
                                          warmup, iters, C.byref(ms)))
     return ms.value
+
+
+def select_stage(L, stage: int) -> None:
+    """Chain legs time the whole chain (stage < 0, the default) or only operator number `stage` of it."""
+    L.h_select_stage(int(stage))

@@ -253,11 +253,20 @@ static float time_passes(cudaStream_t s, int warmup, int iters, F &&pass)
     return ms / static_cast<float>(iters);
 }
 
+// Chain legs time the whole chain (stage < 0) or one of its operators alone (stage = 0, 1, ...: the others are not run inside
+// the timed region; every intermediate was produced once by the warm-up passes of the whole chain).
+static int g_stage = -1;
+
 static const float kMean[3] = {123.675f, 116.28f, 103.53f};
 static const float kStd[3]  = {58.395f, 57.12f, 57.375f};
 
 extern "C"
 {
+void h_select_stage(int stage)
+{
+    g_stage = stage;
+}
+
 const char *h_last_message()
 {
     return t_message.c_str();
@@ -384,16 +393,21 @@ int h_time_classify(int n, int h, int w, int rw, int rh, int cx, int cy, int ow,
         cvcuda::Reformat                  reformat;
         if (chain)
         {
-            *launches = 3 * groups;
-            *ms       = time_passes(st.s, warmup, iters, [&] {
+            auto pass = [&](int stage) {
                 for (int g = 0; g < groups; ++g)
                 {
-                    rccr(st.s, in[g], mid[g], NVCVSize2D{rw, rh}, static_cast<NVCVInterpolationType>(interp), int2{cx, cy},
-                         NVCV_CHANNEL_NO_OP, 1.f, 0.f, false);
-                    normalize(st.s, mid[g], tBase, tScale, norm[g], 1.f, 0.f, 0.f, CVCUDA_NORMALIZE_SCALE_IS_STDDEV);
-                    reformat(st.s, norm[g], out[g]);
+                    if (stage < 0 || stage == 0)
+                        rccr(st.s, in[g], mid[g], NVCVSize2D{rw, rh}, static_cast<NVCVInterpolationType>(interp), int2{cx, cy},
+                             NVCV_CHANNEL_NO_OP, 1.f, 0.f, false);
+                    if (stage < 0 || stage == 1)
+                        normalize(st.s, mid[g], tBase, tScale, norm[g], 1.f, 0.f, 0.f, CVCUDA_NORMALIZE_SCALE_IS_STDDEV);
+                    if (stage < 0 || stage == 2)
+                        reformat(st.s, norm[g], out[g]);
                 }
-            });
+            };
+            pass(-1);
+            *launches = (g_stage < 0 ? 3 : 1) * groups;
+            *ms       = time_passes(st.s, warmup, iters, [&] { pass(g_stage); });
         }
         else
         {
@@ -434,13 +448,19 @@ int h_time_letterbox(int n, int h, int w, int rw, int rh, int cw, int ch, int to
             cvcuda::CopyMakeBorder  border;
             cvcuda::ConvertTo       convert;
             cvcuda::Reformat        reformat;
-            *launches = 4;
-            *ms       = time_passes(st.s, warmup, iters, [&] {
-                resize(st.s, in, small, NVCV_INTERP_LINEAR);
-                border(st.s, small, padded, top, 0, NVCV_BORDER_CONSTANT, float4{114.f, 114.f, 114.f, 0.f});
-                convert(st.s, padded, asFloat, 1.0 / 255.0, 0.0);
-                reformat(st.s, asFloat, out);
-            });
+            auto pass = [&](int stage) {
+                if (stage < 0 || stage == 0)
+                    resize(st.s, in, small, NVCV_INTERP_LINEAR);
+                if (stage < 0 || stage == 1)
+                    border(st.s, small, padded, top, 0, NVCV_BORDER_CONSTANT, float4{114.f, 114.f, 114.f, 0.f});
+                if (stage < 0 || stage == 2)
+                    convert(st.s, padded, asFloat, 1.0 / 255.0, 0.0);
+                if (stage < 0 || stage == 3)
+                    reformat(st.s, asFloat, out);
+            };
+            pass(-1);
+            *launches = g_stage < 0 ? 4 : 1;
+            *ms       = time_passes(st.s, warmup, iters, [&] { pass(g_stage); });
         }
         else
         {

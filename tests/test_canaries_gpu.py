@@ -106,7 +106,8 @@ def test_crop_flip_normalize_writes_only_its_output(pkg, dtype, planar):
                 g.check(f"channels {ch} width {w} path {path}")
 
 
-@pytest.mark.parametrize("dtype,ch", [(np.uint8, 1), (np.uint8, 3), (np.uint8, 4), (np.int16, 3), (np.float32, 4)],
+@pytest.mark.parametrize("dtype,ch", [(np.uint8, 1), (np.uint8, 3), (np.uint8, 4), (np.int16, 3), (np.float32, 4), (np.float32, 3),
+                                      (np.float32, 1)],
                          ids=lambda v: str(np.dtype(v).name) if not isinstance(v, int) else str(v))
 def test_standalone_operators_write_only_their_output(pkg, dtype, ch):
     rng = np.random.default_rng(3)
@@ -126,10 +127,10 @@ def test_standalone_operators_write_only_their_output(pkg, dtype, ch):
             g.check(f"resize width {w} interp {interp}")
         same = to_dev(data((2, 6, w, ch)))
         # Normalize (uint8 sources take the table kernel unless path 1 forces the arithmetic one), to the same type and to float32
-        if dtype != np.float32:
+        if True:
             b = to_dev(rng.uniform(0, 100, (1, 1, 1, ch)).astype(np.float32))
             s = to_dev(rng.uniform(0.5, 1.5, (1, 1, 1, ch)).astype(np.float32))
-            for out_dt in (dtype, np.float32):
+            for out_dt in ((dtype, np.float32) if dtype != np.float32 else (np.float32,)):  # float32 -> float32: the vector kernel
                 for path in (0, 1):
                     g = _nhwc(2, 6, w, ch, out_dt)
                     with kernel_path(pkg, path):

@@ -73,6 +73,25 @@ def test_normalize_types_channels_broadcast(pkg, oracle, src_dt, dst_dt, ch):
             _same(dst.cpu().numpy(), want, f"base {bshape} scale {sshape} flags {flags}")
 
 
+@pytest.mark.parametrize("ch", [1, 3, 4])
+def test_normalize_float32_per_channel_both_kernels(pkg, oracle, ch):
+    """float32 -> float32 with per-channel constants takes the vector kernel (rows on 16-byte boundaries) or its element
+    path (any other row); both, and the arithmetic kernel (path 1), must equal the golden bit for bit at every width."""
+    rng = np.random.default_rng(40 + ch)
+    base = rng.uniform(-50, 50, (1, 1, 1, ch)).astype(np.float32)
+    scale = rng.uniform(0.1, 2.0, (1, 1, 1, ch)).astype(np.float32)
+    for w in list(range(1, 41)) + [224]:
+        images = [rng.uniform(-300, 300, (7, w, ch)).astype(np.float32) for _ in range(2)]
+        for flags, eps in ((0, 0.0), (1, 0.5)):
+            want = np.stack(oracle.normalize(images, base, scale, np.float32, 1.5, -2.0, eps, flags))
+            for path in (0, 1):
+                dst = torch.empty((2, 7, w, ch), dtype=torch.float32, device="cuda")
+                with kernel_path(pkg, path):
+                    pkg.normalize_into(dst, to_dev(np.stack(images)), to_dev(base), to_dev(scale), flags, 1.5, -2.0, eps)
+                torch.cuda.synchronize()
+                _same(dst.cpu().numpy(), want, f"width {w} flags {flags} path {path}")
+
+
 @pytest.mark.parametrize("dst_dt", [np.uint8, np.int8, np.uint16, np.int16, np.int32, np.float32], ids=lambda d: np.dtype(d).name)
 @pytest.mark.parametrize("ch", [1, 2, 3, 4])
 def test_normalize_uint8_per_channel_both_kernels(pkg, oracle, dst_dt, ch):
