@@ -31,7 +31,7 @@ def load(which: str) -> Optional[C.CDLL]:
         L = C.CDLL(path(which))
         L.h_last_message.restype = C.c_char_p
         L.h_which.restype = C.c_char_p
-        for name in ("h_rccr_tensor", "h_rccr_varshape", "h_cfnr", "h_time_classify", "h_time_letterbox", "h_time_varshape", "h_time_cfnr", "h_time_classify_e2e_host"):
+        for name in ("h_rccr_tensor", "h_rccr_varshape", "h_cfnr", "h_time_classify", "h_time_letterbox", "h_time_varshape", "h_time_cfnr", "h_time_classify_e2e_host", "h_time_single_op"):
             getattr(L, name).restype = C.c_int
         _loaded[which] = L
     return _loaded[which]
@@ -143,3 +143,13 @@ def time_classify_e2e_host(L, n, h, w, resize, crop, out_size, interp, warmup: i
 def select_stage(L, stage: int) -> None:
     """Chain legs time the whole chain (stage < 0, the default) or only operator number `stage` of it."""
     L.h_select_stage(int(stage))
+
+
+SINGLE_OPS = {"resize": 0, "normalize_u8_f32": 1, "convertto_u8_f32": 2, "reformat_f32": 3, "copymakeborder": 4}
+
+
+def time_single_op(L, op: str, n, h, w, out_size=(0, 0), interp=1, warmup: int = 3, iters: int = 20):
+    """ms per call of one stand-alone operator on a dense RGB batch (see h_time_single_op)."""
+    ms = C.c_float()
+    _check(L, L.h_time_single_op(SINGLE_OPS[op], n, h, w, out_size[0], out_size[1], int(interp), warmup, iters, C.byref(ms)))
+    return ms.value

@@ -635,4 +635,51 @@ int h_time_classify_e2e_host(int n, int h, int w, int rw, int rh, int cx, int cy
 #endif
     });
 }
+// Stand-alone operators alone, on dense RGB uint8 / float32 tensors of n x h x w: op 0 = Resize to rw x rh (interp), 1 = Normalize
+// uint8 -> float32 with per-channel mean / std, 2 = ConvertTo uint8 -> float32 (x 1/255), 3 = Reformat float32 NHWC -> NCHW,
+// 4 = CopyMakeBorder (32 pixels on every side, constant).
+int h_time_single_op(int op, int n, int h, int w, int rw, int rh, int interp, int warmup, int iters, float *ms)
+{
+    return guarded([&] {
+        Stream       st;
+        nvcv::Tensor in = make_tensor(n, h, w, 3, false, op == 3 ? 6 : 0);
+        fill_bytes(in, 99u);
+        nvcv::Tensor tBase(nvcv::TensorShape({1, 1, 1, 3}, "NHWC"), nvcv::TYPE_F32);
+        nvcv::Tensor tScale(nvcv::TensorShape({1, 1, 1, 3}, "NHWC"), nvcv::TYPE_F32);
+        copy_tensor(tBase, const_cast<float *>(kMean), true);
+        copy_tensor(tScale, const_cast<float *>(kStd), true);
+        if (op == 0)
+        {
+            nvcv::Tensor   out = make_tensor(n, rh, rw, 3, false, 0);
+            cvcuda::Resize resize;
+            *ms = time_passes(st.s, warmup, iters, [&] { resize(st.s, in, out, static_cast<NVCVInterpolationType>(interp)); });
+        }
+        else if (op == 1)
+        {
+            nvcv::Tensor      out = make_tensor(n, h, w, 3, false, 6);
+            cvcuda::Normalize normalize;
+            *ms = time_passes(st.s, warmup, iters,
+                              [&] { normalize(st.s, in, tBase, tScale, out, 1.f, 0.f, 0.f, CVCUDA_NORMALIZE_SCALE_IS_STDDEV); });
+        }
+        else if (op == 2)
+        {
+            nvcv::Tensor      out = make_tensor(n, h, w, 3, false, 6);
+            cvcuda::ConvertTo convert;
+            *ms = time_passes(st.s, warmup, iters, [&] { convert(st.s, in, out, 1.0 / 255.0, 0.0); });
+        }
+        else if (op == 3)
+        {
+            nvcv::Tensor     out = make_tensor(n, h, w, 3, true, 6);
+            cvcuda::Reformat reformat;
+            *ms = time_passes(st.s, warmup, iters, [&] { reformat(st.s, in, out); });
+        }
+        else
+        {
+            nvcv::Tensor           out = make_tensor(n, h + 64, w + 64, 3, false, 0);
+            cvcuda::CopyMakeBorder border;
+            *ms = time_passes(st.s, warmup, iters,
+                              [&] { border(st.s, in, out, 32, 32, NVCV_BORDER_CONSTANT, float4{1.f, 2.f, 3.f, 0.f}); });
+        }
+    });
+}
 }
