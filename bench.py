@@ -17,7 +17,9 @@ evenly over the GPUs); cfnr = CropFlipNormalizeReformat alone on 32 1080p images
 
 One JSON line is printed by rank 0. `value` = images/s with inputs resident in HBM, device-timed with CUDA events on the
 launching stream, max over ranks; with fewer than 200 steps the timed window of exactly `steps` passes is repeated
-(`repeats`) and the median window is reported with the spread. `e2e` = the same metric from page-locked HOST buffers to a
+(`repeats`) and the median window is reported with the spread. The timed steps are issued twice: one library call per
+step from Python (`eager_ms_per_step`) and the same launches replayed from one CUDA graph (`launch_mode`; `value` and
+`ms_per_step` are the replay's, `--no-graph` keeps the first). `e2e` = the same metric from page-locked HOST buffers to a
 page-locked HOST result through the library's C entry point, transfers inside the timed region, with the measured
 concurrent host<->device copy bandwidth of the same buffers beside it. `roofline` relates the kernel's algorithmic bytes
 to the measured HBM copy bandwidth. `cpu_baseline` times the CPU implementation on a bounded sample on the host cores.
@@ -560,17 +562,44 @@ def run_native(args) -> int:
         step(out, src)
     repeats = 1 if args.steps >= 200 else max(1, min(9, math.ceil(200 / args.steps)))
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    windows, launches = [], 0
-    for _ in range(repeats):
-        barrier()
-        launches0 = pkg.launch_count()
-        e0.record()
+
+    def timed_windows(run_window):
+        got = []
+        for _ in range(repeats):
+            barrier()
+            e0.record()
+            run_window()
+            e1.record()
+            barrier()
+            got.append(max_over_ranks(e0.elapsed_time(e1)))
+        return got
+
+    def eager_window():
         for _ in range(args.steps):
             step(out, src)
-        e1.record()
-        barrier()
-        launches = pkg.launch_count() - launches0
-        windows.append(max_over_ranks(e0.elapsed_time(e1)))
+
+    launches0 = pkg.launch_count()
+    eager_window()
+    launches = pkg.launch_count() - launches0  # kernels of one window, counted by the library at launch time
+    eager = timed_windows(eager_window)
+    # The same `steps` launches replayed from one CUDA graph: no host work between the kernels, which is how a serving loop
+    # that cares about the last microseconds issues them (the host side of a call is 20 us of Python here). Every rank must
+    # take the same branch: the windows hold barriers.
+    windows, launch_mode = eager, "one library call per step from Python"
+    if not args.no_graph:
+        try:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+                eager_window()
+            graph.replay()
+            torch.cuda.synchronize()
+            captured = 1
+        except Exception as exc:  # noqa: BLE001 - the eager figure stands
+            captured = 0
+            if rank == 0:
+                print(f"bench: CUDA graph capture failed ({exc}); reporting the eager loop", file=sys.stderr)
+        if int(max_over_ranks(float(1 - captured))) == 0:
+            windows, launch_mode = timed_windows(graph.replay), "CUDA graph replay of the timed steps"
     ms_total = statistics.median(windows)
     ms_per_step = ms_total / args.steps
     value = world * n * args.steps / (ms_total / 1000.0)
@@ -596,6 +625,7 @@ def run_native(args) -> int:
         "repeats": repeats, "window_ms_per_step": {"median": ms_per_step, "min": min(windows) / args.steps,
                                                    "max": max(windows) / args.steps},
         "gb_per_s_algorithmic_per_gpu": achieved, "roofline": roofline, "gpu_launches": int(launches),
+        "launch_mode": launch_mode, "eager_ms_per_step": statistics.median(eager) / args.steps,
     }
     if args.kernel_only:
         if rank == 0:
@@ -796,6 +826,8 @@ def main() -> int:
     ap.add_argument("--scaling", default="weak", choices=("weak", "strong"),
                     help="weak: the configuration's batch on every GPU; strong: the whole job (1024 images for 5-*) split evenly")
     ap.add_argument("--images", type=int, default=0, help="images per GPU, overriding the configuration (small profiling runs)")
+    ap.add_argument("--no-graph", action="store_true", help="time one library call per step from Python only (default: also replay "
+                    "the timed steps from a CUDA graph and report that)")
     ap.add_argument("--kernel-only", action="store_true", help="device-resident timing only: no end-to-end, CPU or reference legs")
     ap.add_argument("--path", type=int, default=0, choices=(0, 1, 2, 3),
                     help="kernel choice of the resize path for profiling runs: 0 automatic, 1 per-pixel gather, 2 staged, 3 row walk")

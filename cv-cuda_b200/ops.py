@@ -247,6 +247,7 @@ class ImageBatchVarShape:
         self.planar = planar
         self._images = []
         self._table = None
+        self._max_size = None
         self.pushback(images)
 
     def pushback(self, images: Union[torch.Tensor, Sequence[torch.Tensor]]) -> None:
@@ -262,6 +263,7 @@ class ImageBatchVarShape:
                             "All input images in a batch must have the same format (including number of channels)")
             self._images.append(im)
         self._table = None
+        self._max_size = None
 
     def popback(self, count: int = 1) -> None:
         """Removes the last `count` images (nvcv.ImageBatchVarShape.popback)."""
@@ -270,10 +272,12 @@ class ImageBatchVarShape:
         if count:
             del self._images[-count:]
             self._table = None
+            self._max_size = None
 
     def clear(self) -> None:
         self._images = []
         self._table = None
+        self._max_size = None
 
     def _channels(self, im: torch.Tensor) -> int:
         return im.shape[0] if self.planar else im.shape[2]
@@ -303,8 +307,12 @@ class ImageBatchVarShape:
 
     @property
     def max_size(self) -> Tuple[int, int]:
-        sizes = [self.size(i) for i in range(len(self))]
-        return max(s[0] for s in sizes), max(s[1] for s in sizes)
+        # kept with the batch like the reference keeps its maxSize (src/nvcv/src/priv/ImageBatchVarShape.cpp:215-254): an
+        # operator call must not walk the images
+        if self._max_size is None:
+            sizes = [self.size(i) for i in range(len(self))]
+            self._max_size = (max(s[0] for s in sizes), max(s[1] for s in sizes))
+        return self._max_size
 
     def descriptor_table(self) -> torch.Tensor:
         """uint8 CUDA tensor holding ``NVCVImageBufferStrided[len(self)]``."""

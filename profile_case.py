@@ -24,10 +24,12 @@ INV_STD = tuple(float(np.float32(1.0) / np.float32(s)) for s in (58.395, 57.12, 
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--case", default="classify", choices=("classify", "classify-nhwc-u8", "classify-nhwc-f32", "classify-nhwc-u8-nearest", "4k", "4k-nearest", "letterbox", "cfnr", "cfnr-u8c1", "cfnr-f32c1", "cfnr-rgba8-f32", "cfnr-rgb8p-f32", "cfnr-rgbf32", "varshape", "resize-rgba", "resize-rgba-nearest", "resize-rgb", "normalize-rgba", "normalize-rgb-f32", "reformat-u8", "reformat-f32", "convertto-u8-f32", "convertto-f32-u8", "border-rgb", "border-rgb-reflect", "border-rgba-f32", "rrc-rgb", "rrc-rgb-nearest"))
+    ap.add_argument("--case", default="classify", choices=("classify", "classify-nhwc-u8", "classify-nhwc-f32", "classify-nhwc-u8-nearest", "4k", "4k-nearest", "letterbox", "cfnr", "cfnr-u8c1", "cfnr-f32c1", "cfnr-rgba8-f32", "cfnr-rgb8p-f32", "cfnr-rgbf32", "varshape", "varshape-narrow", "varshape-1080p", "varshape-mixed", "resize-rgba", "resize-rgba-nearest", "resize-rgb", "normalize-rgba", "normalize-rgb-f32", "reformat-u8", "reformat-f32", "convertto-u8-f32", "convertto-f32-u8", "border-rgb", "border-rgb-reflect", "border-rgba-f32", "rrc-rgb", "rrc-rgb-nearest"))
     ap.add_argument("--images", type=int, default=32)
     ap.add_argument("--path", type=int, default=0)
     ap.add_argument("--launches", type=int, default=5)
+    ap.add_argument("--graph", action="store_true", help="replay the launches from a CUDA graph: device time with no host "
+                    "work between launches (small batches otherwise measure the Python call, not the kernel)")
     a = ap.parse_args()
     pkg = ge.load_package()
     pkg.set_kernel_path(a.path)
@@ -49,11 +51,12 @@ def main():
         out = torch.empty((n, 3, 448, 448), dtype=torch.float16, device="cuda")
         kw = dict(resize_dim=(512, 512), interp=int(a.case == "4k"), crop_pos=(32, 32), layout="NCHW", base=MEAN,
                   mul=INV_STD, srcCast=False)
-    elif a.case == "varshape":
+    elif a.case in ("varshape", "varshape-narrow"):
         # config 3: variable-shape RGB batch, one random rectangle per image -> 224x224 linear, horizontal flip p=0.5,
         # mean/std, float16 NCHW
         rng = np.random.default_rng(1234)
-        sizes = [(int(rng.integers(480, 3841)), int(rng.integers(360, 2161))) for _ in range(n)]
+        wmax, hmax = (3840, 2160) if a.case == "varshape" else (1300, 975)  # narrow: every row segment fits a small ring slot
+        sizes = [(int(rng.integers(480, wmax + 1)), int(rng.integers(360, hmax + 1))) for _ in range(n)]
         imgs = [torch.randint(0, 256, (h, (w * 3 + 31) // 32 * 32), dtype=torch.uint8, device="cuda", generator=g)
                 [:, : w * 3].unflatten(1, (w, 3)) for w, h in sizes]
         src = pkg.ImageBatchVarShape(imgs)
@@ -70,6 +73,19 @@ def main():
                   flip_code=flip)
         src_bytes = sum(r[2] * r[3] * 3 for r in rects)
         print(f"varshape: crop rectangles hold {src_bytes / 1e6:.1f} MB, output {out.numel() * 2 / 1e6:.1f} MB")
+    elif a.case in ("varshape-1080p", "varshape-mixed"):
+        # ResizeCropConvertReformat on an image list, the reference operator's own variable-shape form (no rectangles, no
+        # flip, scalar constants): every image 1080x1920, or sizes from 0.5x to 1x of that
+        rng = np.random.default_rng(7)
+        if a.case == "varshape-1080p":
+            sizes = [(1920, 1080)] * n
+        else:
+            sizes = [(int(1920 * f), int(1080 * f)) for f in rng.uniform(0.5, 1.0, n)]
+        imgs = [torch.randint(0, 256, (h, (w * 3 + 31) // 32 * 32), dtype=torch.uint8, device="cuda", generator=g)
+                [:, : w * 3].unflatten(1, (w, 3)) for w, h in sizes]
+        src = pkg.ImageBatchVarShape(imgs)
+        out = torch.empty((n, 3, 224, 224), dtype=torch.float32, device="cuda")
+        kw = dict(resize_dim=(256, 256), interp=1, crop_pos=(16, 16), layout="NCHW", scale=1 / 255.0, srcCast=False)
     elif a.case == "letterbox":
         src = torch.randint(0, 256, (n, 1080, 1920, 3), dtype=torch.uint8, device="cuda", generator=g)
         out = torch.empty((n, 3, 640, 640), dtype=torch.float32, device="cuda")
@@ -191,13 +207,28 @@ def main():
         run()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(a.launches):
-        run()
-    e1.record()
+    import time
+    if a.graph:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for _ in range(a.launches):
+                run()
+        graph.replay()
+        torch.cuda.synchronize()
+        e0.record()
+        graph.replay()
+        e1.record()
+        host_us = 0.0
+    else:
+        e0.record()
+        t0 = time.perf_counter()
+        for _ in range(a.launches):
+            run()
+        host_us = (time.perf_counter() - t0) / a.launches * 1e6
+        e1.record()
     torch.cuda.synchronize()
-    print(f"case {a.case} images {n} path {a.path}: {e0.elapsed_time(e1) / a.launches * 1000:.1f} us per launch, "
-          f"device error {pkg.read_device_error()}")
+    print(f"case {a.case} images {n} path {a.path}{' graph' if a.graph else ''}: {e0.elapsed_time(e1) / a.launches * 1000:.1f} us per launch, "
+          f"host {host_us:.1f} us per call, device error {pkg.read_device_error()}")
 
 
 if __name__ == "__main__":
