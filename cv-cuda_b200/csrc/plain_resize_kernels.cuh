@@ -123,6 +123,12 @@ __device__ __forceinline__ T finish_linear(double sum)
 // out once and reused down the rows -- the int<->float conversions they need run on a pipe with an eighth of the
 // float32 rate and were the bottleneck when every pixel paid for its own -- and a thread has 16 (nearest: 4)
 // independent loads in flight per row.
+#ifndef B200PP_PLAIN_GROUP
+#define B200PP_PLAIN_GROUP 2
+#endif
+#ifndef B200PP_PLAIN_CTAS
+#define B200PP_PLAIN_CTAS 4
+#endif
 constexpr int kPlainCols = 4;
 constexpr int kPlainRows = 4;
 
@@ -162,6 +168,29 @@ __device__ __forceinline__ unsigned load_packed(const uint8_t *p, bool vector)
     if (C > 3)
         w |= static_cast<unsigned>(p[3]) << 24;
     return w;
+}
+
+// The C bytes of one uint8 pixel, each zero-extended into a word of its own: one word load and a byte permute per channel
+// for four channels at aligned addresses, one-byte loads otherwise.
+template<int C>
+__device__ __forceinline__ void load_taps(const uint8_t *p, bool vector, unsigned (&b)[C])
+{
+    if (C == 4 && vector)
+    {
+        const unsigned w = *reinterpret_cast<const unsigned *>(p);
+        b[0]             = w & 0xffu;
+        if constexpr (C == 4)
+        {
+            b[1] = __byte_perm(w, 0u, 0x4441);
+            b[2] = __byte_perm(w, 0u, 0x4442);
+            b[3] = w >> 24;
+        }
+    }
+    else
+    {
+#pragma unroll
+        for (int c = 0; c < C; ++c) b[c] = p[c];
+    }
 }
 
 template<int C>
@@ -217,7 +246,7 @@ __device__ __forceinline__ void linear_tap_exact(float scale, int d, int size, i
 // the host sees odd whole-number scale factors; the shortcut still checks the weights, so a wrong guess only costs time).
 // The shortcut is kept out of the general instantiation, where its extra live ranges cost 8-17 % (spills at 80 registers).
 template<typename T, int C, int INTERP, bool SINGLE = false>
-__global__ void __launch_bounds__(256, INTERP == B200PP_INTERP_LINEAR && sizeof(T) == 1 ? 3 : 1) resize_plain_kernel(const PlainResizeKParams p)
+__global__ void __launch_bounds__(256, INTERP == B200PP_INTERP_LINEAR && sizeof(T) == 1 ? B200PP_PLAIN_CTAS : 1) resize_plain_kernel(const PlainResizeKParams p)
 {
     const int     dx0  = blockIdx.x * (32 * kPlainCols) + threadIdx.x;
     const int     dy0  = blockIdx.y * (8 * kPlainRows) + threadIdx.y;
@@ -249,7 +278,7 @@ __global__ void __launch_bounds__(256, INTERP == B200PP_INTERP_LINEAR && sizeof(
 
         // ---- columns: source byte offsets and weights, once per thread and sample
         int    off0[kPlainCols], off1[kPlainCols];
-        float  wx1f[kPlainCols];                    // uint8 fast path
+        float  wx0s[kPlainCols], wx1s[kPlainCols];  // uint8 fast path: the two weights * 2^127
         double wx1d[kPlainCols];                    // other element types
         unsigned exactCols = 0; // bit k: column k's weights are multiples of 2^-8
         unsigned zeroCols  = 0; // bit k: column k's second tap has weight exactly zero (it is then not even read)
@@ -272,7 +301,8 @@ __global__ void __launch_bounds__(256, INTERP == B200PP_INTERP_LINEAR && sizeof(
                 off1[k] = s1 * kPix;
                 if constexpr (kFast)
                 {
-                    wx1f[k] = static_cast<float>(w1);
+                    wx1s[k] = __fmul_rn(static_cast<float>(w1), 1.7014118346046923e38f);
+                    wx0s[k] = __fmul_rn(static_cast<float>(__dsub_rn(1.0, w1)), 1.7014118346046923e38f);
                     if (is_multiple_of_2_to_minus_8(w1))
                         exactCols |= 1u << k;
                     if constexpr (SINGLE)
@@ -326,7 +356,7 @@ __global__ void __launch_bounds__(256, INTERP == B200PP_INTERP_LINEAR && sizeof(
                     // weights make the float32 blend exact anyway (with a 1.5x reduction one value in sixteen is an
                     // exact tie). Adding 1.5 * 2^23 rounds half-to-even and leaves the integer in the low mantissa
                     // bits: no conversion instruction anywhere.
-                    unsigned q00[kPlainCols], q10[kPlainCols], q01[kPlainCols], q11[kPlainCols];
+                    unsigned q00[kPlainCols];
                     // All second taps of weight exactly zero (whole-number scale factors: 1080p -> 640x360): the blend of
                     // every pixel is its first tap, exactly, in float32 and in double precision alike, so the row is a
                     // gather of single pixels -- one tap of four read, one source row of two. Decided per thread (the
@@ -341,57 +371,68 @@ __global__ void __launch_bounds__(256, INTERP == B200PP_INTERP_LINEAR && sizeof(
                                 store_packed<C>(drow + static_cast<long long>(dx0 + 32 * k) * kPix, q00[k], vector);
                         continue;
                     }
-#pragma unroll
-                    for (int k = 0; k < kPlainCols; ++k)
-                    {
-                        q00[k] = load_packed<C>(r0 + off0[k], vector);
-                        q10[k] = load_packed<C>(r1 + off0[k], vector);
-                        q01[k] = load_packed<C>(r0 + off1[k], vector);
-                        q11[k] = load_packed<C>(r1 + off1[k], vector);
-                    }
-                    const float wy1f = static_cast<float>(fy);
+                    // Every tapped byte is used as the float whose bit pattern it is (the denormal b * 2^-149): with the
+                    // horizontal weights pre-multiplied by 2^127 the separable blend needs no conversion at all -- ten
+                    // float32 instructions per channel, rounding included.
+                    const float    wy1f = static_cast<float>(fy), wy0f = static_cast<float>(wy0);
                     // Weights that are multiples of 2^-8 on both axes (whole-number and simple fractional scale
-                    // factors) make the float32 blend exact (8 + 8 + 8 bits; a fused multiply-add rounds once), ties
-                    // included: nothing to redo.
+                    // factors) make the float32 blend exact (8 + 8 + 8 bits), ties included: nothing to redo.
                     const unsigned exactHere = is_multiple_of_2_to_minus_8(fy) ? exactCols : 0u;
+                    constexpr int  kGroup    = B200PP_PLAIN_GROUP; // columns whose taps are requested together
 #pragma unroll
-                    for (int k = 0; k < kPlainCols; ++k)
+                    for (int kb = 0; kb < kPlainCols; kb += kGroup)
                     {
-                        unsigned   u[4] = {0u, 0u, 0u, 0u};
-                        const bool redo = !((exactHere >> k) & 1u);
-                        auto channel = [&](auto ch) {
-                            constexpr int c   = decltype(ch)::value;
-                            const float   f00 = packed_byte_to_float<c>(q00[k]), f10 = packed_byte_to_float<c>(q10[k]);
-                            const float   top = __fmaf_rn(wx1f[k], __fsub_rn(packed_byte_to_float<c>(q01[k]), f00), f00);
-                            const float   bot = __fmaf_rn(wx1f[k], __fsub_rn(packed_byte_to_float<c>(q11[k]), f10), f10);
-                            const float   sum = __fmaf_rn(wy1f, __fsub_rn(bot, top), top);
-                            const float   biased = __fadd_rn(sum, 12582912.0f);
-                            u[c]                 = __float_as_uint(biased);
-                            if (redo && fabsf(__fsub_rn(sum, __fsub_rn(biased, 12582912.0f))) > 0.5f - 0.0009765625f)
+                        unsigned t[kGroup][4][C]; // [column][tap: upper left, upper right, lower left, lower right][channel]
+#pragma unroll
+                        for (int i = 0; i < kGroup; ++i)
+                        {
+                            load_taps<C>(r0 + off0[kb + i], vector, t[i][0]);
+                            load_taps<C>(r0 + off1[kb + i], vector, t[i][1]);
+                            load_taps<C>(r1 + off0[kb + i], vector, t[i][2]);
+                            load_taps<C>(r1 + off1[kb + i], vector, t[i][3]);
+                        }
+#pragma unroll
+                        for (int i = 0; i < kGroup; ++i)
+                        {
+                            const int k = kb + i;
+                            unsigned  u[4] = {0u, 0u, 0u, 0u};
+                            bool      nearTie = false;
+#pragma unroll
+                            for (int c = 0; c < C; ++c)
                             {
-                                // a real branch: the empty asm keeps the compiler from turning the redo into a select,
-                                // which would run the double-precision blend for every value
+                                const float top = __fmaf_rn(__uint_as_float(t[i][1][c]), wx1s[k], __fmul_rn(__uint_as_float(t[i][0][c]), wx0s[k]));
+                                const float bot = __fmaf_rn(__uint_as_float(t[i][3][c]), wx1s[k], __fmul_rn(__uint_as_float(t[i][2][c]), wx0s[k]));
+                                const float sum = __fmaf_rn(bot, wy1f, __fmul_rn(top, wy0f)); // the blend * 2^-22
+                                const float biased = __fmaf_rn(sum, 4194304.0f, 12582912.0f); // integer in the low mantissa bits
+                                u[c]               = __float_as_uint(biased);
+                                nearTie |= fabsf(__fmaf_rn(sum, 4194304.0f, __fsub_rn(12582912.0f, biased))) > 0.5f - 0.0009765625f;
+                            }
+                            if (nearTie && !((exactHere >> k) & 1u))
+                            {
+                                // a real branch: the empty asm keeps the compiler from turning the redo into selects,
+                                // which would run the double-precision blend for every pixel
                                 asm volatile("" ::: "memory");
                                 int    s0, s1;
                                 double w1;
                                 linear_tap_exact(scaleW, min(dx0 + 32 * k, D.w - 1), S.w, left, s0, s1, w1);
-                                u[c] = blend_exact<uint8_t>((q00[k] >> (8 * c)) & 0xffu, (q10[k] >> (8 * c)) & 0xffu,
-                                                            (q01[k] >> (8 * c)) & 0xffu, (q11[k] >> (8 * c)) & 0xffu, wy0, fy,
-                                                            __dsub_rn(1.0, w1), w1);
+#pragma unroll
+                                for (int c = 0; c < C; ++c)
+                                    u[c] = blend_exact<uint8_t>(static_cast<uint8_t>(t[i][0][c]), static_cast<uint8_t>(t[i][2][c]),
+                                                                static_cast<uint8_t>(t[i][1][c]), static_cast<uint8_t>(t[i][3][c]), wy0, fy,
+                                                                __dsub_rn(1.0, w1), w1);
                             }
-                        };
-                        channel(std::integral_constant<int, 0>{});
-                        if constexpr (C > 1)
-                        {
-                            channel(std::integral_constant<int, 1>{});
-                            channel(std::integral_constant<int, 2>{});
+                            if (dx0 + 32 * k < D.w)
+                            {
+                                uint8_t *d = drow + static_cast<long long>(dx0 + 32 * k) * kPix;
+                                if (C == 4 && vector) // byte 0 of each of the four words, gathered with byte permutes
+                                    *reinterpret_cast<unsigned *>(d) = __byte_perm(__byte_perm(u[0], u[1], 0x0040), __byte_perm(u[2], u[3], 0x0040), 0x5410);
+                                else
+                                {
+#pragma unroll
+                                    for (int c = 0; c < C; ++c) d[c] = static_cast<uint8_t>(u[c]);
+                                }
+                            }
                         }
-                        if constexpr (C > 3)
-                            channel(std::integral_constant<int, 3>{});
-                        // byte 0 of each of the four words, gathered with byte permutes
-                        const unsigned word = __byte_perm(__byte_perm(u[0], u[1], 0x0040), __byte_perm(u[2], u[3], 0x0040), 0x5410);
-                        if (dx0 + 32 * k < D.w)
-                            store_packed<C>(drow + static_cast<long long>(dx0 + 32 * k) * kPix, word, vector);
                     }
                 }
                 else
