@@ -1134,6 +1134,11 @@ __global__ void __launch_bounds__(288, INTERP == B200PP_INTERP_NEAREST ? 3 : 2) 
 // staged kernel is bound by instruction issue rather than by HBM (small element types, nearest neighbour).
 constexpr int kWalkRowsMax = 16;
 
+__device__ __forceinline__ void prefetch_l2(const void *p)
+{
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
+}
+
 struct alignas(16) WalkRow
 {
     long long off0, off1; // byte offsets of the two tapped rows from the first byte of the sample's (sub-)image
@@ -1202,24 +1207,45 @@ __global__ void __launch_bounds__(256, 6) resize_rowwalk_kernel(const ResizeKPar
         }
         __syncthreads();
 
-        uint8_t *dstRow = p.dst + n * p.dSample + y0 * p.dRow;
+        // L2 is asked for the NEXT row's tapped sectors before this row is blended: the next row's one-byte loads then find
+        // them at L2 latency instead of HBM latency, at no cost in registers (holding two rows' bytes in flight instead cost a
+        // CTA per SM and was slower; asking two or three rows ahead was slower too). Only where consecutive destination rows
+        // tap different source rows (vertical reduction of 1.5 or more): elsewhere the next row's sectors are mostly this
+        // row's, and the two extra requests per pixel only cost issue slots (48.2 us without this condition). Measured on a
+        // 128-image batch of random rectangles: 53.6 -> 43.6 us; not slower where the whole source already sits in L2.
+        const bool prefetch = g.scaleH >= 1.5f && cache[0].rel0 >= 0;
+        uint8_t   *dstRow   = p.dst + n * p.dSample + y0 * p.dRow;
+        WalkRow    wr       = rows[0];
         for (int r = 0; r < nRows; ++r, dstRow += p.dRow)
         {
-            const WalkRow wr = rows[r];
+            WalkRow nx = wr;
+            if (r + 1 < nRows)
+            {
+                nx = rows[r + 1];
+                if (prefetch && nx.mode != UNIT_PAD)
+                {
+                    prefetch_l2(g.base + nx.off0 + cache[0].rel0);
+                    if constexpr (INTERP == B200PP_INTERP_LINEAR)
+                        prefetch_l2(g.base + nx.off1 + cache[0].rel0);
+                }
+            }
             if (wr.mode == UNIT_PAD)
             {
                 if (valid)
                     store_pixel<DK>(pv.v, plan.co, dstRow + cache[0].dstOff);
-                continue;
             }
-            unsigned fastMask = 0;
-            if constexpr (IL && DK != DST_F16)
+            else
             {
-                // the transposing store needs word-aligned warp segments; lane 0 of every warp sits 32*m columns from 0
-                fastMask = (reinterpret_cast<unsigned long long>(dstRow) & 3ull) == 0 ? fullMask : 0u;
+                unsigned fastMask = 0;
+                if constexpr (IL && DK != DST_F16)
+                {
+                    // the transposing store needs word-aligned warp segments; lane 0 of every warp sits 32*m columns from 0
+                    fastMask = (reinterpret_cast<unsigned long long>(dstRow) & 3ull) == 0 ? fullMask : 0u;
+                }
+                consume_cached<INTERP, DK, 1, IL>(p, plan, pv, g.base + wr.off0, g.base + wr.off1, wr.wy0s, wr.wy1s, dstRow, cache,
+                                                  fastMask, lane);
             }
-            consume_cached<INTERP, DK, 1, IL>(p, plan, pv, g.base + wr.off0, g.base + wr.off1, wr.wy0s, wr.wy1s, dstRow, cache,
-                                              fastMask, lane);
+            wr = nx;
         }
         __syncthreads();
     }

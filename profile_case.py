@@ -24,7 +24,7 @@ INV_STD = tuple(float(np.float32(1.0) / np.float32(s)) for s in (58.395, 57.12, 
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--case", default="classify", choices=("classify", "classify-nhwc-u8", "classify-nhwc-f32", "classify-nhwc-u8-nearest", "4k", "4k-nearest", "letterbox", "cfnr", "cfnr-u8c1", "cfnr-f32c1", "cfnr-rgba8-f32", "cfnr-rgb8p-f32", "cfnr-rgbf32", "varshape", "varshape-narrow", "varshape-1080p", "varshape-mixed", "resize-rgba", "resize-rgba-nearest", "resize-rgb", "normalize-rgba", "normalize-rgb-f32", "reformat-u8", "reformat-f32", "convertto-u8-f32", "convertto-f32-u8", "border-rgb", "border-rgb-reflect", "border-rgba-f32", "rrc-rgb", "rrc-rgb-nearest"))
+    ap.add_argument("--case", default="classify", choices=("classify", "classify-nhwc-u8", "classify-nhwc-f32", "classify-nhwc-u8-nearest", "4k", "4k-nearest", "letterbox", "cfnr", "cfnr-u8c1", "cfnr-f32c1", "cfnr-rgba8-f32", "cfnr-rgb8p-f32", "cfnr-rgbf32", "varshape", "varshape-narrow", "varshape-small", "varshape-1080p", "varshape-mixed", "resize-rgba", "resize-rgba-nearest", "resize-rgb", "normalize-rgba", "normalize-rgb-f32", "reformat-u8", "reformat-f32", "convertto-u8-f32", "convertto-f32-u8", "border-rgb", "border-rgb-reflect", "border-rgba-f32", "rrc-rgb", "rrc-rgb-nearest"))
     ap.add_argument("--images", type=int, default=32)
     ap.add_argument("--path", type=int, default=0)
     ap.add_argument("--launches", type=int, default=5)
@@ -51,11 +51,12 @@ def main():
         out = torch.empty((n, 3, 448, 448), dtype=torch.float16, device="cuda")
         kw = dict(resize_dim=(512, 512), interp=int(a.case == "4k"), crop_pos=(32, 32), layout="NCHW", base=MEAN,
                   mul=INV_STD, srcCast=False)
-    elif a.case in ("varshape", "varshape-narrow"):
+    elif a.case in ("varshape", "varshape-narrow", "varshape-small"):
         # config 3: variable-shape RGB batch, one random rectangle per image -> 224x224 linear, horizontal flip p=0.5,
         # mean/std, float16 NCHW
         rng = np.random.default_rng(1234)
-        wmax, hmax = (3840, 2160) if a.case == "varshape" else (1300, 975)  # narrow: every row segment fits a small ring slot
+        # narrow: every row segment fits a small ring slot; small: the whole batch (40 MB) stays in L2
+        wmax, hmax = {"varshape": (3840, 2160), "varshape-narrow": (1300, 975), "varshape-small": (640, 480)}[a.case]
         sizes = [(int(rng.integers(480, wmax + 1)), int(rng.integers(360, hmax + 1))) for _ in range(n)]
         imgs = [torch.randint(0, 256, (h, (w * 3 + 31) // 32 * 32), dtype=torch.uint8, device="cuda", generator=g)
                 [:, : w * 3].unflatten(1, (w, 3)) for w, h in sizes]
