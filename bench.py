@@ -419,6 +419,14 @@ def run_harness_leg(args) -> int:
         finally:
             R.select_stage(L, -1)
         res["chain"]["stage_ms"] = stages
+    if cfg.key == "2":
+        # the stock variable-shape operator on an image list of equal-sized images (the same call in both libraries)
+        try:
+            ms = R.time_rccr_list(L, 64, cfg.h, cfg.w, cfg.resize, cfg.crop, cfg.out, cfg.interp, 1.0 / 255.0, wu, it)
+            res["image_list"] = {"ms_per_step": ms, "value": 64 / (ms / 1000.0), "images": 64,
+                                 "workload": "stock ResizeCropConvertReformat on a 64-image list, x/255, float32 NCHW"}
+        except R.HarnessError as e:
+            res["image_list"] = {"unavailable": str(e)[:300]}
     if args.harness_leg == "b200" and cfg.key in ("2", "5-linear", "5-nearest"):
         # end to end through the handle API: nvcv tensors that wrap page-locked host memory, at most 2 GiB of source per call
         try:

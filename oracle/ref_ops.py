@@ -31,7 +31,7 @@ def load(which: str) -> Optional[C.CDLL]:
         L = C.CDLL(path(which))
         L.h_last_message.restype = C.c_char_p
         L.h_which.restype = C.c_char_p
-        for name in ("h_rccr_tensor", "h_rccr_varshape", "h_cfnr", "h_time_classify", "h_time_letterbox", "h_time_varshape", "h_time_cfnr", "h_time_classify_e2e_host", "h_time_single_op"):
+        for name in ("h_rccr_tensor", "h_rccr_varshape", "h_cfnr", "h_time_classify", "h_time_letterbox", "h_time_varshape", "h_time_cfnr", "h_time_classify_e2e_host", "h_time_single_op", "h_time_rccr_list"):
             getattr(L, name).restype = C.c_int
         _loaded[which] = L
     return _loaded[which]
@@ -105,6 +105,14 @@ def time_classify(L, n, h, w, resize, crop, out_size, interp, chain: bool, max_p
     _check(L, L.h_time_classify(n, h, w, resize[0], resize[1], crop[0], crop[1], out_size[0], out_size[1], int(interp), int(chain),
                                 int(max_per_call), warmup, iters, C.byref(ms), C.byref(launches)))
     return ms.value, launches.value
+
+
+def time_rccr_list(L, n, h, w, resize, crop, out_size, interp, scale: float, warmup: int, iters: int):
+    """ms per call of the stock variable-shape ResizeCropConvertReformat on a list of n equal-sized RGB8 images -> float32 NCHW."""
+    ms = C.c_float()
+    _check(L, L.h_time_rccr_list(n, h, w, resize[0], resize[1], crop[0], crop[1], out_size[0], out_size[1], int(interp),
+                                 C.c_float(scale), warmup, iters, C.byref(ms)))
+    return ms.value
 
 
 def time_letterbox(L, n, h, w, resize, canvas, top, chain: bool, warmup: int, iters: int):

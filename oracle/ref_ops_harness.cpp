@@ -429,6 +429,32 @@ int h_time_classify(int n, int h, int w, int rw, int rh, int cx, int cy, int ow,
     });
 }
 
+// The stock variable-shape operator on a list of n equal-sized images: ResizeCropConvertReformat(batch) -> float32 NCHW, x scale.
+// Identical call in both builds (src/cvcuda/include/cvcuda/OpResizeCropConvertReformat.hpp: the ImageBatchVarShape overload).
+int h_time_rccr_list(int n, int h, int w, int rw, int rh, int cx, int cy, int ow, int oh, int interp, float scale, int warmup,
+                     int iters, float *ms)
+{
+    return guarded([&] {
+        Stream                   st;
+        std::vector<nvcv::Image> keep;
+        nvcv::ImageBatchVarShape batch(n);
+        for (int i = 0; i < n; ++i)
+        {
+            nvcv::Image img(nvcv::Size2D{w, h}, nvcv::FMT_RGB8);
+            auto        data = img.exportData<nvcv::ImageDataStridedCuda>();
+            check(cudaMemset2D(data->plane(0).basePtr, data->plane(0).rowStride, 37 + i, static_cast<size_t>(w) * 3, h), "cudaMemset2D");
+            keep.push_back(img);
+            batch.pushBack(img);
+        }
+        nvcv::Tensor                      out = make_tensor(n, oh, ow, 3, true, 6);
+        cvcuda::ResizeCropConvertReformat rccr;
+        *ms = time_passes(st.s, warmup, iters, [&] {
+            rccr(st.s, batch, out, NVCVSize2D{rw, rh}, static_cast<NVCVInterpolationType>(interp), int2{cx, cy}, NVCV_CHANNEL_NO_OP,
+                 scale, 0.f, false);
+        });
+    });
+}
+
 // Letterbox pass: n images of h x w -> resize to rw x rh -> placed at (0, top) of a cw x ch canvas padded with 114 -> x / 255
 // -> float32 NCHW. Chain: Resize -> CopyMakeBorder -> ConvertTo -> Reformat (the channel swap of the one-pass form would be a
 // fifth operator and is left out of the chain).
