@@ -634,7 +634,7 @@ extern "C" int b200ppCropFlipNormalizeReformat(const B200ppSource *src, const B2
     if (planeCase && path != 1)
     {
         const bool sf = src->dtype == B200PP_F32, df = dst->dtype == B200PP_F32;
-        const int  pix = sf ? 4 : 16, rowsPerBlock = 8 * (sf ? 4 : 2) * kSlicePlaneIters;
+        const int  pix = slice_plane_pix(sf, df), rowsPerBlock = 8 * slice_plane_rows(sf, df) * kSlicePlaneIters;
         dim3       grid((kp.dstW + 32 * pix - 1) / (32 * pix), (kp.dstH + rowsPerBlock - 1) / rowsPerBlock,
                         static_cast<unsigned>(std::min<long long>(static_cast<long long>(kp.numSamples) * channels, 32768)));
         if (sf && df)
@@ -649,7 +649,7 @@ extern "C" int b200ppCropFlipNormalizeReformat(const B200ppSource *src, const B2
     }
     if (typedCase && path != 1)
     {
-        const int rowsPerBlock = 8 * slice_typed_rows(channels);
+        const int rowsPerBlock = 8 * slice_typed_rows(channels, src->dtype == B200PP_U8);
         dim3      grid((kp.dstW + 127) / 128, (kp.dstH + rowsPerBlock - 1) / rowsPerBlock, std::min(kp.numSamples, 32768));
         launch_slice_typed(src->dtype == B200PP_F32, dst->dtype == B200PP_F32, channels, grid, block, stream, kp, src->dtype, dst->dtype);
         return check_launch("CropFlipNormalizeReformat (typed)");

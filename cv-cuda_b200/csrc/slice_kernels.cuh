@@ -360,17 +360,19 @@ __device__ __forceinline__ void slice_store4(uint8_t *d, float a, float b, float
     }
 }
 
-// Rows per thread: four for one channel, two for three or four (the loaded values of all rows live in registers).
-__host__ __device__ constexpr int slice_typed_rows(int channels)
+// Rows per thread: four for one channel and for four-byte pixels (kept as one word per pixel until they are written), two for
+// the rest (the loaded values of all rows live in registers as floats).
+__host__ __device__ constexpr int slice_typed_rows(int channels, bool srcU8)
 {
-    return channels == 1 ? 4 : 2;
+    return channels == 1 || (channels == 4 && srcU8) ? 4 : 2;
 }
 
 template<typename S, typename D, int C>
 __global__ void __launch_bounds__(256, C == 1 ? 4 : 3) slice_typed_kernel(const SliceKParams p, const int srcType, const int dstType)
 {
-    constexpr int kRows = slice_typed_rows(C);
-    const int     j0    = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    constexpr int  kRows = slice_typed_rows(C, sizeof(S) == 1);
+    constexpr bool kRaw  = sizeof(S) == 1 && C == 4; // interleaved four-byte pixels: a word per pixel, converted when written
+    const int      j0    = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
     const int     iBase = blockIdx.y * (blockDim.y * kRows) + threadIdx.y;
     if (j0 >= p.dstW || iBase >= p.dstH)
         return;
@@ -388,15 +390,35 @@ __global__ void __launch_bounds__(256, C == 1 ? 4 : 3) slice_typed_kernel(const 
         const int         xlo   = flipX ? s.cw - 1 - (j0 + 3) + s.cx : j0 + s.cx; // leftmost of the four source pixels
         const bool        colsFast = cols == 4 && j0 + 3 < s.cw && xlo >= 0 && xlo + 3 < s.w;
 
-        float v[kRows][4 * C]; // [row][source pixel q * C + channel]
-        int   mode[kRows];     // 0 no such row, 1 loaded, 3 edge / border
+        float    v[kRaw ? 1 : kRows][4 * C]; // [row][source pixel q * C + channel]
+        unsigned raw[kRaw ? kRows : 1][4];   // [row][source pixel]
+        int      mode[kRows];                // 0 no such row, 1 loaded, 3 edge / border
 #pragma unroll
         for (int r = 0; r < kRows; ++r)
         {
             const int i = iBase + r * blockDim.y;
             const int y = flipY ? s.ch - 1 - i + s.cy : i + s.cy;
             mode[r]     = i >= p.dstH ? 0 : ((colsFast && i < s.ch && y >= 0 && y < s.h) ? 1 : 3);
-            if (mode[r] == 1)
+            if constexpr (kRaw)
+            {
+                if (mode[r] == 1)
+                {
+                    const uint8_t *a = s.img + y * s.pitch + static_cast<long long>(xlo) * 4;
+                    if (p.srcPlanar || (reinterpret_cast<unsigned long long>(a) & 3ull) != 0)
+                        mode[r] = 3; // planes, or pixels off word boundaries: pixel by pixel
+                    else if ((reinterpret_cast<unsigned long long>(a) & 15ull) == 0)
+                    {
+                        const uint4 q4 = __ldg(reinterpret_cast<const uint4 *>(a));
+                        raw[r][0] = q4.x, raw[r][1] = q4.y, raw[r][2] = q4.z, raw[r][3] = q4.w;
+                    }
+                    else
+                    {
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) raw[r][q] = __ldg(reinterpret_cast<const unsigned *>(a) + q);
+                    }
+                }
+            }
+            else if (mode[r] == 1)
             {
                 if (p.srcPlanar)
                 {
@@ -454,8 +476,14 @@ __global__ void __launch_bounds__(256, C == 1 ? 4 : 3) slice_typed_kernel(const 
                 for (int q = 0; q < 4; ++q)
 #pragma unroll
                     for (int k = 0; k < C; ++k)
-                        o[FLIP ? 3 - q : q][k]
-                            = __fadd_rn(__fmul_rn(__fmul_rn(__fsub_rn(v[r][q * C + k], base[k]), mul[k]), p.gscale), p.shift);
+                    {
+                        float in;
+                        if constexpr (kRaw)
+                            in = byte_as_float(raw[r][q], 0x7540u + (k & 3));
+                        else
+                            in = v[r][q * C + k];
+                        o[FLIP ? 3 - q : q][k] = __fadd_rn(__fmul_rn(__fmul_rn(__fsub_rn(in, base[k]), mul[k]), p.gscale), p.shift);
+                    }
 
                 uint8_t *dst = p.dst + n * p.dSample + i * p.dRow + j0 * p.dPix;
                 if (dstPlanes)
@@ -523,12 +551,26 @@ __global__ void __launch_bounds__(256, C == 1 ? 4 : 3) slice_typed_kernel(const 
 // few bytes in flight to cover the memory latency (measured 125 us for 32 one-channel 1080p uint8 images).
 constexpr int kSlicePlaneIters = 4;
 
+// Rows per thread and row block, and adjacent pixels per thread: sixteen source bytes per thread and row (four float32 or
+// sixteen uint8 pixels) in four / two rows. Measured on 32 planar RGB8 1080p images -> float32: sixteen pixels x two rows
+// 212.8 us, x four rows 222.5 us, four pixels (one 16-byte store per lane and row) x four rows 216.8 us.
+__host__ __device__ constexpr int slice_plane_rows(bool srcF32, bool /*dstF32*/)
+{
+    return srcF32 ? 4 : 2;
+}
+
+__host__ __device__ constexpr int slice_plane_pix(bool srcF32, bool /*dstF32*/)
+{
+    return srcF32 ? 4 : 16;
+}
+
 template<typename S, typename D>
 __global__ void __launch_bounds__(256, 4) slice_plane_kernel(const SliceKParams p, const int srcType, const int dstType,
                                                              const int planes)
 {
-    constexpr int kPix  = 16 / static_cast<int>(sizeof(S));
-    constexpr int kRows = sizeof(S) == 1 ? 2 : 4;
+    constexpr int kPix   = slice_plane_pix(sizeof(S) == 4, sizeof(D) == 4);
+    constexpr int kWords = kPix * static_cast<int>(sizeof(S)) / 4; // source words of a thread's pixels in one row
+    constexpr int kRows = slice_plane_rows(sizeof(S) == 4, sizeof(D) == 4);
     const int     j0    = (blockIdx.x * blockDim.x + threadIdx.x) * kPix;
     const int     iFirst = blockIdx.y * (blockDim.y * kRows * kSlicePlaneIters) + threadIdx.y;
     if (j0 >= p.dstW || iFirst >= p.dstH)
@@ -584,7 +626,7 @@ __global__ void __launch_bounds__(256, 4) slice_plane_kernel(const SliceKParams 
                     asm volatile("prefetch.global.L2 [%0];" ::"l"(img + y2 * pitch + static_cast<long long>(xlo) * sizeof(S)));
             }
         }
-        unsigned w[kRows][5];
+        unsigned w[kRows][kWords + 1];
         int      mode[kRows]; // 0 no such row, 1 words loaded, 3 anything else (per pixel)
         unsigned shiftBits = 0;
 #pragma unroll
@@ -598,19 +640,25 @@ __global__ void __launch_bounds__(256, 4) slice_plane_kernel(const SliceKParams 
                 const uint8_t           *rowPtr = img + y * pitch;
                 const unsigned long long addr   = reinterpret_cast<unsigned long long>(rowPtr + static_cast<long long>(xlo) * sizeof(S));
                 const bool               extra  = (addr & 3ull) != 0; // only uint8 rows can start inside a word
-                if ((addr & ~3ull) + (extra ? 20 : 16) <= reinterpret_cast<unsigned long long>(rowPtr) + static_cast<unsigned long long>(pitch))
+                if ((addr & ~3ull) + 4 * (kWords + (extra ? 1 : 0)) <= reinterpret_cast<unsigned long long>(rowPtr) + static_cast<unsigned long long>(pitch))
                 {
                     const unsigned *wp = reinterpret_cast<const unsigned *>(addr & ~3ull);
                     shiftBits          = static_cast<unsigned>(addr & 3ull) * 8;
-                    if ((addr & 15ull) == 0)
+                    bool loaded        = false;
+                    if constexpr (kWords == 4)
                     {
-                        const uint4 q = __ldg(reinterpret_cast<const uint4 *>(wp));
-                        w[r][0] = q.x, w[r][1] = q.y, w[r][2] = q.z, w[r][3] = q.w, w[r][4] = 0;
+                        if ((addr & 15ull) == 0)
+                        {
+                            const uint4 q = __ldg(reinterpret_cast<const uint4 *>(wp));
+                            w[r][0] = q.x, w[r][1] = q.y, w[r][2] = q.z, w[r][3] = q.w, w[r][4] = 0;
+                            loaded = true;
+                        }
                     }
-                    else
+                    if (!loaded)
                     {
-                        w[r][0] = __ldg(wp), w[r][1] = __ldg(wp + 1), w[r][2] = __ldg(wp + 2), w[r][3] = __ldg(wp + 3);
-                        w[r][4] = extra ? __ldg(wp + 4) : 0u;
+#pragma unroll
+                        for (int g = 0; g < kWords; ++g) w[r][g] = __ldg(wp + g);
+                        w[r][kWords] = extra ? __ldg(wp + kWords) : 0u;
                     }
                     mode[r] = 1;
                 }
