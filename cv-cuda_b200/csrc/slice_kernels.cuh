@@ -283,27 +283,30 @@ __global__ void __launch_bounds__(256, 4) slice_u8x3_kernel(const SliceKParams p
                     o[q][c] = __fadd_rn(__fmul_rn(__fmul_rn(__fsub_rn(v, base[c]), mul[c]), p.gscale), p.shift);
                 }
 
-            // source pixel q lands in destination column q, or 3-q when mirrored
+            // source pixel q lands in destination column q, or 3-q when mirrored: the stores are compiled once per direction
+            // (as a run-time flag inside the unrolled loop both orders of every store were issued under predicates)
             uint8_t *dst = p.dst + n * p.dSample + i * p.dRow + j0 * p.dPix;
-            if (vecStore)
-            {
-#pragma unroll
-                for (int c = 0; c < 3; ++c)
+            auto     emit = [&](auto flipTag) {
+                constexpr bool FLIP = decltype(flipTag)::value;
+                if (vecStore)
                 {
-                    if (flipX)
-                        store_four<DK>(dst + c * p.dChan, o[3][c], o[2][c], o[1][c], o[0][c]);
-                    else
-                        store_four<DK>(dst + c * p.dChan, o[0][c], o[1][c], o[2][c], o[3][c]);
-                }
-            }
-            else
-            {
-#pragma unroll
-                for (int q = 0; q < 4; ++q)
 #pragma unroll
                     for (int c = 0; c < 3; ++c)
-                        store_elem<DK>(dst + (flipX ? 3 - q : q) * p.dPix + c * p.dChan, o[q][c]);
-            }
+                        store_four<DK>(dst + c * p.dChan, o[FLIP ? 3 : 0][c], o[FLIP ? 2 : 1][c], o[FLIP ? 1 : 2][c], o[FLIP ? 0 : 3][c]);
+                }
+                else
+                {
+#pragma unroll
+                    for (int q = 0; q < 4; ++q)
+#pragma unroll
+                        for (int c = 0; c < 3; ++c)
+                            store_elem<DK>(dst + (FLIP ? 3 - q : q) * p.dPix + c * p.dChan, o[q][c]);
+                }
+            };
+            if (flipX)
+                emit(std::true_type{});
+            else
+                emit(std::false_type{});
         }
     }
 }
