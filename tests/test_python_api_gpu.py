@@ -171,7 +171,7 @@ def test_values_through_the_object_surface_and_foreign_buffers(cvcuda, oracle):
     assert torch.equal(torch.as_tensor(back.cuda()), torch.as_tensor(cvcuda.convertto(nhwc, np.float32, 1 / 255.0, 0.0).cuda()))
 
 
-def test_image_batch_pushback_after_use_reuploads_descriptors(cvcuda, oracle):
+def test_image_batch_pushback_after_use_reuploads_descriptors(cvcuda, oracle, pkg):
     rng = np.random.default_rng(3)
     hosts = [rng.integers(0, 256, (h, w, 3), dtype=np.uint8) for (w, h) in ((64, 40), (33, 57), (80, 80))]
     batch = cvcuda.ImageBatchVarShape(3)
@@ -185,6 +185,11 @@ def test_image_batch_pushback_after_use_reuploads_descriptors(cvcuda, oracle):
     first = cvcuda.resize_crop_convert_reformat(batch, (32, 32), cvcuda.Interp.LINEAR, cvcuda.RectI(0, 0, 32, 32), layout="NHWC",
                                                 data_type=cvcuda.Type.U8)
     assert first.shape == (2, 32, 32, 3)
+    assert batch.max_size == (64, 57)  # kept with the batch, not recomputed per call ...
+    batch.pushback(images[2])
+    assert batch.max_size == (80, 80)  # ... and renewed by every change
+    batch.popback()
+    assert batch.max_size == (64, 57)
     batch.pushback(images[2])
     second = cvcuda.resize_crop_convert_reformat(batch, (32, 32), cvcuda.Interp.LINEAR, cvcuda.RectI(0, 0, 32, 32), layout="NHWC",
                                                  data_type=cvcuda.Type.U8)
@@ -192,3 +197,15 @@ def test_image_batch_pushback_after_use_reuploads_descriptors(cvcuda, oracle):
     assert np.array_equal(torch.as_tensor(second.cuda()).cpu().numpy(), want)
     with pytest.raises(cvcuda.Error):
         batch.pushback(cvcuda.Image((4, 4), cvcuda.Format.RGB8))  # capacity 3
+    # a wider image pushed after a call: the staged kernel sizes its ring slots from the batch's maximum width
+    wide = [rng.integers(0, 256, (40, w, 3), dtype=np.uint8) for w in (64, 200)]
+    from gpu_util import kernel_path
+    grown = pkg.ImageBatchVarShape([torch.from_numpy(wide[0]).cuda()])
+    spec = oracle.ResizeSpec(resize=(48, 32), out_size=(48, 32), interp=1, src_cast=True)
+    with kernel_path(pkg, 2):
+        pkg.resize_crop_convert_reformat(grown, (48, 32), pkg.Interp.LINEAR, (0, 0, 48, 32), layout="NHWC", data_type=torch.uint8)
+        grown.pushback(torch.from_numpy(wide[1]).cuda())
+        out = pkg.resize_crop_convert_reformat(grown, (48, 32), pkg.Interp.LINEAR, (0, 0, 48, 32), layout="NHWC", data_type=torch.uint8)
+    torch.cuda.synchronize()
+    assert np.array_equal(out.cpu().numpy(), oracle.resize_crop(wide, spec, np.uint8, False))
+    assert pkg.read_device_error() == 0
