@@ -554,6 +554,14 @@ __global__ void __launch_bounds__(256, C == 1 ? 4 : 3) slice_typed_kernel(const 
 // few bytes in flight to cover the memory latency (measured 125 us for 32 one-channel 1080p uint8 images).
 constexpr int kSlicePlaneIters = 4;
 
+// Eight float32 values as one 256-bit store (sm_100); `d` is 32-byte aligned.
+__device__ __forceinline__ void store_f32x8(uint8_t *d, float a, float b, float c, float e, float f, float g, float h, float i)
+{
+    asm volatile("st.global.v8.f32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(d), "f"(a), "f"(b), "f"(c), "f"(e), "f"(f), "f"(g),
+                 "f"(h), "f"(i)
+                 : "memory");
+}
+
 // Rows per thread and row block, and adjacent pixels per thread: sixteen source bytes per thread and row (four float32 or
 // sixteen uint8 pixels) in four / two rows. Measured on 32 planar RGB8 1080p images -> float32: sixteen pixels x two rows
 // 212.8 us, x four rows 222.5 us, four pixels (one 16-byte store per lane and row) x four rows 216.8 us.
@@ -735,7 +743,16 @@ __global__ void __launch_bounds__(256, 4) slice_plane_kernel(const SliceKParams 
                 if constexpr (sizeof(D) == 4)
                 {
                     // one decision per row: as a flag inside slice_store4 both forms of every store were issued under predicates
-                    if ((da & 15ull) == 0)
+                    if (kPix == 16 && (da & 31ull) == 0)
+                    {
+                        // sixteen float32 results per lane: two 32-byte stores, each a whole sector (as four 16-byte stores every
+                        // store instruction wrote half-sectors 64 bytes apart, twice the transactions on the way to L2)
+#pragma unroll
+                        for (int h = 0; h < kPix / 8; ++h)
+                            store_f32x8(dst + 32 * h, o[8 * h], o[8 * h + 1], o[8 * h + 2], o[8 * h + 3], o[8 * h + 4], o[8 * h + 5],
+                                        o[8 * h + 6], o[8 * h + 7]);
+                    }
+                    else if ((da & 15ull) == 0)
                     {
 #pragma unroll
                         for (int g = 0; g < kPix / 4; ++g)
