@@ -11,6 +11,7 @@
 #define CVCUDA_B200_NORMALIZE_KERNELS_CUH
 
 #include "device_math.cuh"
+#include <type_traits>
 #include "plain_resize_kernels.cuh"
 
 namespace b200pp {
@@ -255,6 +256,10 @@ __global__ void __launch_bounds__(256, 5) normalize_lut_kernel(const NormalizeKP
         const bool alignedS = ((reinterpret_cast<uintptr_t>(S.base) | static_cast<uintptr_t>(S.pitch)) & 3) == 0;
         const bool alignedD = ((reinterpret_cast<uintptr_t>(D.base) | static_cast<uintptr_t>(D.pitch)) & (4 * DE - 1)) == 0;
         // the grid's y extent may be smaller than the image: CTAs walk down in steps, so the table is built less often
+        // The pass is compiled twice, with "every row on its vector boundaries" as a constant: as run-time flags inside the
+        // unrolled loops both forms of every load and store were issued under predicates.
+        auto pass = [&](auto alignedTag) {
+        constexpr bool ALIGNED = decltype(alignedTag)::value;
         for (int yb = blockIdx.y; yb * (blockDim.y * RPT) < h; yb += gridDim.y)
         {
             const int y0 = (yb * blockDim.y + threadIdx.y) * RPT;
@@ -267,7 +272,7 @@ __global__ void __launch_bounds__(256, 5) normalize_lut_kernel(const NormalizeKP
                 for (int k = 0; k < 4; ++k)
                 {
                     const int w = min(w0 + 32 * k, rowWords - 1);
-                    if (alignedS)
+                    if (ALIGNED || alignedS)
                     {
                         // the row's last word may reach up to three bytes past its last element: still inside the
                         // aligned word that holds that element, so the load cannot leave the allocation's pages
@@ -304,7 +309,7 @@ __global__ void __launch_bounds__(256, 5) normalize_lut_kernel(const NormalizeKP
                     }
                     const int count = min(4, rowElems - 4 * w);
                     uint8_t  *out   = d + static_cast<long long>(w) * (4 * DE);
-                    if (count == 4 && alignedD)
+                    if (count == 4 && (ALIGNED || alignedD))
                     {
                         if constexpr (DE == 4)
                             *reinterpret_cast<uint4 *>(out) = make_uint4(o[0], o[1], o[2], o[3]);
@@ -315,6 +320,7 @@ __global__ void __launch_bounds__(256, 5) normalize_lut_kernel(const NormalizeKP
                     }
                     else
                     {
+                        asm volatile("" ::: "memory"); // the ragged end of a row stays a branch, not predicated stores
 #pragma unroll
                         for (int j = 0; j < 4; ++j)
                             if (j < count)
@@ -330,6 +336,11 @@ __global__ void __launch_bounds__(256, 5) normalize_lut_kernel(const NormalizeKP
                 }
             }
         }
+        };
+        if (alignedS && alignedD)
+            pass(std::true_type{});
+        else
+            pass(std::false_type{});
     }
 }
 
