@@ -164,15 +164,34 @@ __global__ void __launch_bounds__(256, 4) normalize_f32_kernel(const NormalizeKP
         cb[c] = *reinterpret_cast<const float *>(reinterpret_cast<const char *>(p.base) + c * p.baseStride[3]);
         cm[c] = normalize_mul(p, *reinterpret_cast<const float *>(reinterpret_cast<const char *>(p.scale) + c * p.scaleStride[3]));
     }
+    // element 0 of lane L's first vector is element 4 L of the span: channel (4 L) mod C = L mod C for C = 3, 0 for C = 1, 4
+    float rb[C], rm[C];
+#pragma unroll
+    for (int j = 0; j < C; ++j)
+    {
+        const int c = (static_cast<int>(threadIdx.x) * 4 + j) % C;
+        rb[j] = cb[0], rm[j] = cm[0];
+#pragma unroll
+        for (int q = 1; q < C; ++q)
+            if (c == q)
+                rb[j] = cb[q], rm[j] = cm[q];
+    }
     for (int n = blockIdx.z; n < p.numSamples; n += gridDim.z)
     {
         const PlainView S = plain_view(p.src, n), D = plain_view(p.dst, n);
         const int       w = min(S.w, D.w), h = min(S.h, D.h);
-        if (4 * g >= w)
-            continue;
-        const bool vec = 4 * g + 3 < w
-                      && ((reinterpret_cast<unsigned long long>(S.base) | reinterpret_cast<unsigned long long>(D.base)
+        // A warp's 128 pixels are 32 x C consecutive 16-byte vectors of the row: lane L takes vectors L, L + 32, ... of them, so
+        // that every load and store instruction of the warp covers 512 consecutive bytes (with C vectors side by side per lane
+        // each instruction touched 16-byte pieces 16 x C bytes apart: half-filled sectors). The channel of element i of a
+        // lane's k-th vector is (L + (32 k mod C) * 4 + i) mod C; with the constants rotated by L mod C once per thread it is
+        // known at compile time. Vectors past the row's end are skipped; a row's last one to three elements, where its length
+        // is not a multiple of four, are done by the lane whose vector they would have been.
+        const int  vb    = blockIdx.x * (32 * C); // first vector of the warp's span
+        const int  elems = w * C, fullVecs = elems >> 2;
+        const bool vec   = ((reinterpret_cast<unsigned long long>(S.base) | reinterpret_cast<unsigned long long>(D.base)
                            | static_cast<unsigned long long>(S.pitch) | static_cast<unsigned long long>(D.pitch)) & 15ull) == 0;
+        if (vec ? vb + static_cast<int>(threadIdx.x) > fullVecs : 4 * g >= w)
+            continue; // nothing of this row belongs to the thread
         float4 v[kRows][C];
         if (vec)
         {
@@ -180,9 +199,11 @@ __global__ void __launch_bounds__(256, 4) normalize_f32_kernel(const NormalizeKP
             for (int r = 0; r < kRows; ++r)
             {
                 const int y = min(y0 + r * blockDim.y, h - 1);
-                const float4 *sp = reinterpret_cast<const float4 *>(S.base + y * S.pitch) + static_cast<long long>(g) * C;
+                const float4 *sp = reinterpret_cast<const float4 *>(S.base + y * S.pitch) + vb + threadIdx.x;
 #pragma unroll
-                for (int k = 0; k < C; ++k) v[r][k] = __ldg(sp + k);
+                for (int k = 0; k < C; ++k)
+                    if (vb + static_cast<int>(threadIdx.x) + 32 * k < fullVecs)
+                        v[r][k] = __ldg(sp + 32 * k);
             }
         }
 #pragma unroll
@@ -193,7 +214,7 @@ __global__ void __launch_bounds__(256, 4) normalize_f32_kernel(const NormalizeKP
                 break;
             if (vec)
             {
-                float4 *dp = reinterpret_cast<float4 *>(D.base + y * D.pitch) + static_cast<long long>(g) * C;
+                float4 *dp = reinterpret_cast<float4 *>(D.base + y * D.pitch) + vb + threadIdx.x;
 #pragma unroll
                 for (int k = 0; k < C; ++k)
                 {
@@ -202,10 +223,23 @@ __global__ void __launch_bounds__(256, 4) normalize_f32_kernel(const NormalizeKP
                     for (int i = 0; i < 4; ++i)
                     {
                         constexpr int kDummy = 0;
-                        const int     c      = (4 * k + i) % C + kDummy; // compile-time after unrolling
-                        e[i] = __fadd_rn(__fmul_rn(__fmul_rn(__fsub_rn(e[i], cb[c]), cm[c]), p.gscale), p.shift);
+                        const int     c      = (128 * k + i) % C + kDummy; // compile-time after unrolling; rotated constants
+                        e[i] = __fadd_rn(__fmul_rn(__fmul_rn(__fsub_rn(e[i], rb[c]), rm[c]), p.gscale), p.shift);
                     }
-                    dp[k] = make_float4(e[0], e[1], e[2], e[3]);
+                    const int vi = vb + static_cast<int>(threadIdx.x) + 32 * k;
+                    if (vi < fullVecs)
+                        dp[32 * k] = make_float4(e[0], e[1], e[2], e[3]);
+                    else if (vi == fullVecs)
+                    {
+                        // the row's ragged end, from the source: these elements were not loaded as a vector
+                        const float *se = reinterpret_cast<const float *>(S.base + y * S.pitch);
+                        float       *de = reinterpret_cast<float *>(D.base + y * D.pitch);
+                        for (int x = 4 * vi; x < elems; ++x)
+                        {
+                            const int c = x % C;
+                            de[x] = __fadd_rn(__fmul_rn(__fmul_rn(__fsub_rn(se[x], cb[c]), cm[c]), p.gscale), p.shift);
+                        }
+                    }
                 }
             }
             else
