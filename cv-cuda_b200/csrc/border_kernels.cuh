@@ -11,6 +11,7 @@
 #define CVCUDA_B200_BORDER_KERNELS_CUH
 
 #include "plain_resize_kernels.cuh"
+#include <type_traits>
 #include "slice_kernels.cuh"
 
 namespace b200pp {
@@ -174,25 +175,32 @@ __global__ void __launch_bounds__(256, 6) copy_make_border_kernel(const BorderKP
             fill = make_uint4(f[0], f[1], f[2], f[3]);
         }
         uint4 v[kBorderRows];
+        // The loads are compiled twice: sixteen source bytes on a 16-byte boundary are one vector load, anything else four or
+        // five words and funnel shifts (as one loop with run-time flags every row issued all of them under predicates).
+        auto loadRows = [&](auto vecTag) {
+            constexpr bool VEC = decltype(vecTag)::value;
 #pragma unroll
-        for (int r = 0; r < kBorderRows; ++r)
-        {
-            v[r] = fill;
-            if (sy[r] < 0)
-                continue;
-            const unsigned *w = reinterpret_cast<const unsigned *>(s.S.base + sy[r] * s.S.pitch + (sb0 & ~3));
-            const unsigned  w0 = __ldg(w), w1 = __ldg(w + 1), w2 = __ldg(w + 2), w3 = __ldg(w + 3);
-            if (shift)
+            for (int r = 0; r < kBorderRows; ++r)
             {
-                const unsigned w4 = __ldg(w + 4);
-                v[r] = make_uint4(__funnelshift_r(w0, w1, shift), __funnelshift_r(w1, w2, shift),
-                                  __funnelshift_r(w2, w3, shift), __funnelshift_r(w3, w4, shift));
+                v[r] = fill;
+                if (sy[r] < 0)
+                    continue;
+                if constexpr (VEC)
+                    v[r] = __ldg(reinterpret_cast<const uint4 *>(s.S.base + sy[r] * s.S.pitch + sb0));
+                else
+                {
+                    const unsigned *w = reinterpret_cast<const unsigned *>(s.S.base + sy[r] * s.S.pitch + (sb0 & ~3));
+                    const unsigned  w0 = __ldg(w), w1 = __ldg(w + 1), w2 = __ldg(w + 2), w3 = __ldg(w + 3);
+                    const unsigned  w4 = shift ? __ldg(w + 4) : 0u;
+                    v[r] = make_uint4(__funnelshift_r(w0, w1, shift), __funnelshift_r(w1, w2, shift), __funnelshift_r(w2, w3, shift),
+                                      __funnelshift_r(w3, w4, shift));
+                }
             }
-            else
-            {
-                v[r] = make_uint4(w0, w1, w2, w3);
-            }
-        }
+        };
+        if ((sBits & 15) == 0 && (sb0 & 15) == 0)
+            loadRows(std::true_type{});
+        else
+            loadRows(std::false_type{});
 #pragma unroll
         for (int r = 0; r < kBorderRows; ++r)
             if (sy[r] != -2)
