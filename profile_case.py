@@ -1,8 +1,12 @@
 """A small, self-ending run of one kernel, sized for an `ncu` capture.
 
-    python profile_case.py [--case classify|4k|letterbox] [--images 32] [--path 0|1|2] [--launches 5]
+    python profile_case.py [--case classify|4k|letterbox|varshape|cfnr|resize-rgb|...] [--images 32] [--path 0|1|2|3]
+                           [--launches 5] [--graph]
 
-`classify` is the 1080p -> 256x256 -> 224x224 float32 NCHW case of bench.py at a reduced batch: 32 images are
+`--case` names the operator and shape (`--help` lists them: the fused passes of bench.py's configurations, image lists with and
+without rectangles, the element types of CropFlipNormalizeReformat, and the stand-alone operators). `--graph` replays the launches
+from one CUDA graph, i.e. reports device time with no host work between the kernels; without it the figure includes whatever
+the Python call costs when that is longer than the kernel (also printed, as `host ... us per call`). `classify` is the 1080p -> 256x256 -> 224x224 float32 NCHW case of bench.py at a reduced batch: 32 images are
 199 MB of source, larger than the 126 MB L2, so DRAM counters still mean something, while the whole run holds well
 under 1 GB on the device. Prints the device time per launch measured with CUDA events (never quote that figure from
 a run under a profiler).
