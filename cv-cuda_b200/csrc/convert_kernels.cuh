@@ -198,6 +198,10 @@ __global__ void __launch_bounds__(256) convert_f32_kernel(const ConvertKParams p
     const int rowGroups = (p.rowElems + 3) >> 2;
     if (g0 >= rowGroups)
         return;
+    const float alphaF = static_cast<float>(p.alpha), betaF = static_cast<float>(p.beta);
+    const float errB   = __fmul_rn(fabsf(betaF), 4.76837158203125e-07f); // |beta| * 2^-21
+    const float loF = p.dstType == B200PP_U8 || p.dstType == B200PP_U16 ? 0.0f : (DE == 1 ? -128.0f : -32768.0f);
+    const float hiF = p.dstType == B200PP_U8 ? 255.0f : (p.dstType == B200PP_S8 ? 127.0f : (p.dstType == B200PP_U16 ? 65535.0f : 32767.0f));
     for (int n = blockIdx.z; n < p.numSamples; n += gridDim.z)
     {
         float4 v[2][2];
@@ -213,6 +217,7 @@ __global__ void __launch_bounds__(256) convert_f32_kernel(const ConvertKParams p
                     v[r][k] = __ldg(reinterpret_cast<const float4 *>(s) + g);
                 else
                 {
+                    asm volatile("" ::: "memory"); // the ragged end of a row stays a branch, not predicated loads
                     const float *f = reinterpret_cast<const float *>(s) + 4 * g;
                     const int    c = p.rowElems - 4 * g;
                     v[r][k]        = make_float4(f[0], c > 1 ? f[1] : 0.f, c > 2 ? f[2] : 0.f, 0.f);
@@ -238,6 +243,26 @@ __global__ void __launch_bounds__(256) convert_f32_kernel(const ConvertKParams p
                 for (int j = 0; j < 4; ++j)
                 {
                     o[j] = 0;
+                    if constexpr (DE <= 2)
+                    {
+                        // Integer destinations of 8 or 16 bits: t = alpha * x + beta in float32 first (one fused multiply-add). It
+                        // differs from the double-precision value by less than (|alpha x| + |beta| + |t|) * 2^-24 <= err / 4 with
+                        // err = (|alpha x| + |beta|) * 2^-21. Clamped to the type's range, t is rounded half to even by adding
+                        // 1.5 * 2^23 (the integer is then the low bits of the sum, two's complement for negative results). If t is
+                        // further than err from a rounding boundary (and err <= 0.5, which keeps a clamped value clamped), the
+                        // double-precision value rounds and clamps to the same integer; everything else -- ties, huge factors,
+                        // NaN, infinities (the comparison is false for them) -- is done again in double precision.
+                        const float t   = __fmaf_rn(alphaF, in[j], betaF);
+                        const float err = __fmaf_rn(fabsf(__fmul_rn(alphaF, in[j])), 4.76837158203125e-07f, errB);
+                        const float tc  = fminf(fmaxf(t, loF), hiF);
+                        const float rb  = __fadd_rn(tc, 12582912.0f);
+                        if (__fadd_rn(fabsf(__fsub_rn(tc, __fsub_rn(rb, 12582912.0f))), err) <= 0.5f)
+                        {
+                            o[j] = __float_as_uint(rb) & (DE == 1 ? 0xffu : 0xffffu);
+                            continue;
+                        }
+                        asm volatile("" ::: "memory"); // the exact redo stays a branch
+                    }
                     store_saturated(reinterpret_cast<uint8_t *>(&o[j]), p.dstType,
                                     __dadd_rn(__dmul_rn(p.alpha, static_cast<double>(in[j])), p.beta));
                 }
@@ -254,6 +279,7 @@ __global__ void __launch_bounds__(256) convert_f32_kernel(const ConvertKParams p
                 }
                 else
                 {
+                    asm volatile("" ::: "memory"); // likewise for the stores
 #pragma unroll
                     for (int j = 0; j < 3; ++j)
                         if (j < count)
