@@ -132,3 +132,40 @@ def test_convertto_through_operator_symbols(pkg, oracle):
     assert ops.cvcudaConvertToSubmit(other, stream, NF.tensor_handle(tsrc, "NHWC"), NF.tensor_handle(tdst, "NHWC"), 1.0, 0.0) == 9
     ops.nvcvOperatorDestroy(other)
     ops.nvcvOperatorDestroy(h_op)
+
+
+@pytest.mark.parametrize("dt", [np.uint8, np.int8, np.uint16, np.int16], ids=lambda d: np.dtype(d).name)
+def test_float32_fast_path_agrees_at_rounding_boundaries(pkg, oracle, dt):
+    """float32 sources to small integers run a float32 multiply-add first and redo in double precision whatever lies near a
+    rounding boundary: exact ties, values a few float32 steps either side of one, products that cancel against beta, factors
+    float32 cannot hold, values far outside the type's range, NaN and infinities must all come out as the double-precision rule
+    gives them."""
+    info = np.iinfo(dt)
+    k = np.arange(int(info.min) - 3, int(info.max) + 4, dtype=np.float64)
+    ties = (k + 0.5).astype(np.float32)
+    near = np.concatenate([np.nextafter(ties, np.float32(np.inf)), np.nextafter(ties, np.float32(-np.inf)),
+                           np.nextafter(np.nextafter(ties, np.float32(np.inf)), np.float32(np.inf))])
+    rng = np.random.default_rng(5)
+    vals = np.concatenate([ties, near, rng.uniform(float(info.min) - 2, float(info.max) + 2, 4096).astype(np.float32),
+                           np.array([1e10, -1e10, 3e38, -3e38, np.inf, -np.inf, 0.0, -0.0], np.float32)])
+    vals = np.resize(vals, (1, (vals.size + 767) // 768, 256, 3)).astype(np.float32)  # rows of 768 elements: vector kernel
+    src = to_dev(vals)
+    cases = [(1.0, 0.0), (0.5, 0.25), (255.0, 0.0), (1.0 / 3.0, 0.5), (-1.0, 0.5), (1e6, -1e6 * 0.001), (1.0000000001, 0.0),
+             (1e-3, 100.5), (3.0, -0.5)]
+    for alpha, beta in cases:
+        want = oracle.convert_to(vals, dt, alpha, beta)
+        out = torch.zeros(vals.shape, dtype=_TORCH_DTYPE[np.dtype(dt)], device="cuda")
+        pkg.convertto_into(out, src, alpha, beta)
+        torch.cuda.synchronize()
+        _same(out.cpu().numpy(), want, f"alpha {alpha} beta {beta}")
+    # NaN: the reference's saturate cast is not defined for it; both kernels of this library must agree with each other
+    from gpu_util import kernel_path
+    nan = to_dev(np.full((1, 2, 256, 3), np.nan, np.float32))
+    got = []
+    for path in (0, 1):
+        out = torch.zeros((1, 2, 256, 3), dtype=_TORCH_DTYPE[np.dtype(dt)], device="cuda")
+        with kernel_path(pkg, path):
+            pkg.convertto_into(out, nan, 2.0, 1.0)
+        torch.cuda.synchronize()
+        got.append(out.cpu().numpy())
+    assert np.array_equal(got[0], got[1])
