@@ -363,6 +363,14 @@ __device__ __forceinline__ void slice_store4(uint8_t *d, float a, float b, float
     }
 }
 
+// Eight float32 values as one 256-bit store (sm_100); `d` is 32-byte aligned.
+__device__ __forceinline__ void store_f32x8(uint8_t *d, float a, float b, float c, float e, float f, float g, float h, float i)
+{
+    asm volatile("st.global.v8.f32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(d), "f"(a), "f"(b), "f"(c), "f"(e), "f"(f), "f"(g),
+                 "f"(h), "f"(i)
+                 : "memory");
+}
+
 // Rows per thread: four for one channel and for four-byte pixels (kept as one word per pixel until they are written), two for
 // the rest (the loaded values of all rows live in registers as floats).
 __host__ __device__ constexpr int slice_typed_rows(int channels, bool srcU8)
@@ -510,7 +518,20 @@ __global__ void __launch_bounds__(256, C == 1 ? 4 : 3) slice_typed_kernel(const 
                     for (int q = 0; q < 4; ++q)
 #pragma unroll
                         for (int k = 0; k < C; ++k) f[q * C + k] = o[q][k];
-                    if ((reinterpret_cast<unsigned long long>(dst) & (4 * sizeof(D) - 1)) == 0)
+                    const unsigned long long da = reinterpret_cast<unsigned long long>(dst);
+                    if (sizeof(D) == 4 && C == 3 && (da & 15ull) == 0)
+                    {
+                        // twelve float32 results = 48 consecutive bytes per lane, i.e. three sectors per pair of lanes. As three
+                        // 16-byte stores every instruction wrote half-sectors 48 bytes apart. Instead: one 256-bit store of the
+                        // lane's sector-aligned 32 bytes (the first eight values in lanes that start on a sector boundary, the
+                        // last eight in the others), then one 16-byte store of the rest -- the two halves of the sector a pair
+                        // of lanes shares then leave in the same instruction.
+                        const bool odd = (da & 31ull) != 0;
+                        store_f32x8(dst + (odd ? 16 : 0), odd ? f[4] : f[0], odd ? f[5] : f[1], odd ? f[6] : f[2], odd ? f[7] : f[3],
+                                    odd ? f[8] : f[4], odd ? f[9] : f[5], odd ? f[10] : f[6], odd ? f[11] : f[7]);
+                        slice_store4<D>(dst + (odd ? 0 : 32), odd ? f[0] : f[8], odd ? f[1] : f[9], odd ? f[2] : f[10], odd ? f[3] : f[11], true);
+                    }
+                    else if ((da & (4 * sizeof(D) - 1)) == 0)
                     {
 #pragma unroll
                         for (int g = 0; g < C; ++g)
@@ -553,14 +574,6 @@ __global__ void __launch_bounds__(256, C == 1 ? 4 : 3) slice_typed_kernel(const 
 // rows, all rows' loads first. With four one-byte loads per thread, as the typed kernel would issue, a thread has far too
 // few bytes in flight to cover the memory latency (measured 125 us for 32 one-channel 1080p uint8 images).
 constexpr int kSlicePlaneIters = 4;
-
-// Eight float32 values as one 256-bit store (sm_100); `d` is 32-byte aligned.
-__device__ __forceinline__ void store_f32x8(uint8_t *d, float a, float b, float c, float e, float f, float g, float h, float i)
-{
-    asm volatile("st.global.v8.f32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(d), "f"(a), "f"(b), "f"(c), "f"(e), "f"(f), "f"(g),
-                 "f"(h), "f"(i)
-                 : "memory");
-}
 
 // Rows per thread and row block, and adjacent pixels per thread: sixteen source bytes per thread and row (four float32 or
 // sixteen uint8 pixels) in four / two rows. Measured on 32 planar RGB8 1080p images -> float32: sixteen pixels x two rows
