@@ -157,6 +157,14 @@ __device__ __forceinline__ float affine(const ResizeKParams &p, int c, float v)
     return __fadd_rn(__fmul_rn(__fmul_rn(__fsub_rn(v, p.base[c]), p.mul[c]), p.gscale), p.shift);
 }
 
+// Eight float32 values as one 256-bit store (sm_100); `d` is 32-byte aligned.
+__device__ __forceinline__ void store_f32x8(uint8_t *d, float a, float b, float c, float e, float f, float g, float h, float i)
+{
+    asm volatile("st.global.v8.f32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(d), "f"(a), "f"(b), "f"(c), "f"(e), "f"(f), "f"(g),
+                 "f"(h), "f"(i)
+                 : "memory");
+}
+
 // ---- per-sample source geometry
 
 struct Geom

@@ -363,14 +363,6 @@ __device__ __forceinline__ void slice_store4(uint8_t *d, float a, float b, float
     }
 }
 
-// Eight float32 values as one 256-bit store (sm_100); `d` is 32-byte aligned.
-__device__ __forceinline__ void store_f32x8(uint8_t *d, float a, float b, float c, float e, float f, float g, float h, float i)
-{
-    asm volatile("st.global.v8.f32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(d), "f"(a), "f"(b), "f"(c), "f"(e), "f"(f), "f"(g),
-                 "f"(h), "f"(i)
-                 : "memory");
-}
-
 // Rows per thread: four for one channel and for four-byte pixels (kept as one word per pixel until they are written), two for
 // the rest (the loaded values of all rows live in registers as floats).
 __host__ __device__ constexpr int slice_typed_rows(int channels, bool srcU8)
