@@ -123,12 +123,6 @@ __device__ __forceinline__ T finish_linear(double sum)
 // out once and reused down the rows -- the int<->float conversions they need run on a pipe with an eighth of the
 // float32 rate and were the bottleneck when every pixel paid for its own -- and a thread has 16 (nearest: 4)
 // independent loads in flight per row.
-#ifndef B200PP_PLAIN_GROUP
-#define B200PP_PLAIN_GROUP 2
-#endif
-#ifndef B200PP_PLAIN_CTAS
-#define B200PP_PLAIN_CTAS 4
-#endif
 constexpr int kPlainCols = 4;
 constexpr int kPlainRows = 4;
 
@@ -245,8 +239,10 @@ __device__ __forceinline__ void linear_tap_exact(float scale, int d, int size, i
 // SINGLE: compiled with the single-tap shortcut for rows and columns whose second taps all weigh exactly zero (launched when
 // the host sees odd whole-number scale factors; the shortcut still checks the weights, so a wrong guess only costs time).
 // The shortcut is kept out of the general instantiation, where its extra live ranges cost 8-17 % (spills at 80 registers).
+// Resident CTAs per SM for the uint8 linear kernels: three for one and three channels (80 registers, no spills; four CTAs were
+// 16 % slower on 1080p -> 224 x 224), four for four channels (64 registers with a few spills, 5 % faster on 1080p -> 720p).
 template<typename T, int C, int INTERP, bool SINGLE = false>
-__global__ void __launch_bounds__(256, INTERP == B200PP_INTERP_LINEAR && sizeof(T) == 1 ? B200PP_PLAIN_CTAS : 1) resize_plain_kernel(const PlainResizeKParams p)
+__global__ void __launch_bounds__(256, INTERP == B200PP_INTERP_LINEAR && sizeof(T) == 1 ? (C == 4 ? 4 : 3) : 1) resize_plain_kernel(const PlainResizeKParams p)
 {
     const int     dx0  = blockIdx.x * (32 * kPlainCols) + threadIdx.x;
     const int     dy0  = blockIdx.y * (8 * kPlainRows) + threadIdx.y;
@@ -378,7 +374,7 @@ __global__ void __launch_bounds__(256, INTERP == B200PP_INTERP_LINEAR && sizeof(
                     // Weights that are multiples of 2^-8 on both axes (whole-number and simple fractional scale
                     // factors) make the float32 blend exact (8 + 8 + 8 bits), ties included: nothing to redo.
                     const unsigned exactHere = is_multiple_of_2_to_minus_8(fy) ? exactCols : 0u;
-                    constexpr int  kGroup    = B200PP_PLAIN_GROUP; // columns whose taps are requested together
+                    constexpr int  kGroup    = 2; // columns whose taps are requested together (four at once: slower, spills)
 #pragma unroll
                     for (int kb = 0; kb < kPlainCols; kb += kGroup)
                     {
