@@ -144,7 +144,28 @@ __device__ __forceinline__ void affine3(const ResizeKParams &p, float (&v)[3])
 // Final values of one destination pixel of the linear path. r0/r1 address byte 0 of the two tapped source rows in
 // whatever memory they live in (SmemRow or a global pointer); o0/o1 are the byte offsets of the left/right tap pixel.
 // Weights are pre-scaled: wy*s = wy * 2^127, wx*s = wx * 2^22.
-template<class Row>
+// Two float32 values in one 64-bit register and their packed product (sm_100: mul.rn.f32x2 issues at the rate of one scalar
+// multiply and rounds each half like the scalar instruction).
+__device__ __forceinline__ unsigned long long pack_f32x2(float lo, float hi)
+{
+    unsigned long long r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+
+__device__ __forceinline__ unsigned long long mul_f32x2(unsigned long long a, unsigned long long b)
+{
+    unsigned long long r;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+
+__device__ __forceinline__ void unpack_f32x2(unsigned long long v, float &lo, float &hi)
+{
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+
+template<bool PACKED = false, class Row>
 __device__ __forceinline__ void linear_values(const ResizeKParams &p, Row r0, Row r1, int o0, int o1, float wx0s,
                                               float wx1s, float wy0s, float wy1s, float (&v)[3])
 {
@@ -183,8 +204,25 @@ __device__ __forceinline__ void linear_values(const ResizeKParams &p, Row r0, Ro
         tap3(r0 + o1, b);
         tap3(r1 + o0, c2);
         tap3(r1 + o1, d);
+        if constexpr (PACKED)
+        {
+            // the eight products of a channel as four packed multiplies: (left, right) of a row by that row's weight, then by
+            // the (left, right) horizontal weights; the sum in the golden's order
+            const unsigned long long wy0p = pack_f32x2(wy0s, wy0s), wy1p = pack_f32x2(wy1s, wy1s), wxp = pack_f32x2(wx0s, wx1s);
 #pragma unroll
-        for (int c = 0; c < 3; ++c) v[c] = blend4(a[c], b[c], c2[c], d[c], wx0s, wx1s, wy0s, wy1s);
+            for (int c = 0; c < 3; ++c)
+            {
+                float t00, t01, t10, t11;
+                unpack_f32x2(mul_f32x2(mul_f32x2(pack_f32x2(a[c], b[c]), wy0p), wxp), t00, t01);
+                unpack_f32x2(mul_f32x2(mul_f32x2(pack_f32x2(c2[c], d[c]), wy1p), wxp), t10, t11);
+                v[c] = __fadd_rn(__fadd_rn(__fadd_rn(t00, t01), t10), t11);
+            }
+        }
+        else
+        {
+#pragma unroll
+            for (int c = 0; c < 3; ++c) v[c] = blend4(a[c], b[c], c2[c], d[c], wx0s, wx1s, wy0s, wy1s);
+        }
     }
     if (p.srcCast)
     {
@@ -515,7 +553,7 @@ __device__ __forceinline__ ColTap make_tap(const ResizeKParams &p, int flipX, in
 }
 
 // Final values of one destination pixel from rows r0/r1 (addressed from the unit's origin).
-template<int INTERP, class Row>
+template<int INTERP, bool PACKED = false, class Row>
 __device__ __forceinline__ void pixel_values(const ResizeKParams &p, const PadValues &pv, const ColTap &t, Row r0, Row r1,
                                              float wy0s, float wy1s, float (&v)[3])
 {
@@ -527,7 +565,7 @@ __device__ __forceinline__ void pixel_values(const ResizeKParams &p, const PadVa
     else if constexpr (INTERP == B200PP_INTERP_NEAREST)
         nearest_values(p, r0, t.rel0, v);
     else
-        linear_values(p, r0, r1, t.rel0, t.rel1, t.wx0s, t.wx1s, wy0s, wy1s, v);
+        linear_values<PACKED>(p, r0, r1, t.rel0, t.rel1, t.wx0s, t.wx1s, wy0s, wy1s, v);
 }
 
 // How a thread of the row-walk kernel writes its pixels.
@@ -550,7 +588,9 @@ __device__ __forceinline__ void consume_cached(const ResizeKParams &p, const Sto
     for (int k = 0; k < KC; ++k)
     {
         float v[3];
-        pixel_values<INTERP>(p, pv, cache[k], r0, r1, wy0s, wy1s, v);
+        // planar destinations: the blend's products as packed multiplies (3 % on an L2-resident batch, nothing lost elsewhere);
+        // the interleaved variants, already spilling at the kernel's 40 registers, keep the scalar form
+        pixel_values<INTERP, !IL>(p, pv, cache[k], r0, r1, wy0s, wy1s, v);
         uint8_t *pix = dstRow + cache[k].dstOff;
         if constexpr (IL && DK != DST_F16)
         {
